@@ -1,0 +1,68 @@
+// Shared device helpers for the sm_100a kernels of this engine.
+//
+// Every launcher in this directory is an `extern "C"` function that takes raw
+// device pointers, sizes and a stream, launches on that stream and returns the
+// CUDA error code of the launch (0 = ok) or one of the Q3_ERR_* codes below for
+// a size it refuses.  Nothing here allocates.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+// dtype tags of the C ABI
+#define Q3_F32 0
+#define Q3_BF16 1
+
+// refusals (negative so they never collide with cudaError_t)
+#define Q3_ERR_DTYPE -1      // unknown dtype tag
+#define Q3_ERR_SIZE -2       // a size this kernel does not take (see the launcher's comment)
+#define Q3_ERR_ALIGN -3      // pointer or row pitch not aligned as the kernel needs
+
+// bits of the device status word that kernels OR into `status` instead of
+// faulting when table data is bad; the host reads it after the step.
+#define Q3_STATUS_BAD_TOKEN 1   // token id outside the embedding table
+#define Q3_STATUS_BAD_PAGE 2    // page id outside the pool where a live position needs one
+#define Q3_STATUS_BAD_POSITION 4  // negative position or sequence index
+#define Q3_STATUS_BAD_LOGITS 8    // a row of logits with no comparable value (all NaN)
+
+namespace q3 {
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a whole block (blockDim.x a multiple of 32, at most 1024).  The order of
+// the additions depends only on blockDim.x, so a row's result does not depend on
+// which other rows are in the launch.  `scratch` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // scratch may still be read from an earlier call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  const int nwarps = (blockDim.x + 31) >> 5;
+  float t = (lane < nwarps) ? scratch[lane] : 0.f;
+  return warp_sum(t);
+}
+
+static inline int launch_status() { return (int)cudaGetLastError(); }
+
+}  // namespace q3

@@ -1,0 +1,109 @@
+"""Builds the device-side description of one step's batch.
+
+A batch is a list of entries (request, its next tokens, which of them want logits).  Rows
+that bring a single token are placed first (the decode kernels take that range), the
+rest after them; the wanted logits keep the order in which the caller gave the entries.
+All integer arrays go to the device in one copy from pinned memory (the reference builds a
+tensor per array, each with a copy of its own: inference/model_worker.py:177-210).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Hashable, List, Sequence, Tuple
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.storage import CacheStorage
+from ..parts.base import Runtime, StepContext
+
+
+@dataclass
+class Entry:
+    request: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()  # indices into ``tokens`` whose logits are asked for
+
+
+class BatchContext(StepContext):
+    def __init__(self, manager: CacheManager, storage: CacheStorage, rt: Runtime):
+        self.manager, self.storage, self.rt = manager, storage, rt
+        self._tables: List[torch.Tensor] = []
+
+    def kv(self, cache_id: int):
+        g = self.storage.group_of(cache_id)
+        k, v = self.storage.kv_pages(cache_id)
+        return k, v, self._tables[g]
+
+    def state(self, cache_id: int):
+        return self.storage.states[cache_id]
+
+    def build(self, entries: Sequence[Entry], vocab_size: int) -> "BatchContext":
+        """``entries``: each request at most once, every request open with pages reserved for
+        its new length.  Fills every field of StepContext."""
+        m = self.manager
+        order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
+        row_of = {orig: row for row, orig in enumerate(order)}
+        tokens: List[int] = []
+        positions: List[int] = []
+        tok_seq: List[int] = []
+        q_start = [0]
+        kv_len: List[int] = []
+        slots: List[int] = []
+        self.q_lens, self.kv_lens = [], []
+        self.requests = []
+        for row, orig in enumerate(order):
+            e = entries[orig]
+            n = len(e.tokens)
+            if n == 0:
+                raise ValueError(f"request {e.request!r} brings no tokens")
+            start = m.length(e.request)
+            for t in e.tokens:
+                if not 0 <= int(t) < vocab_size:
+                    raise ValueError(f"request {e.request!r}: token id {t} is outside the vocabulary of {vocab_size}")
+            tokens.extend(int(t) for t in e.tokens)
+            positions.extend(range(start, start + n))
+            tok_seq.extend([row] * n)
+            q_start.append(q_start[-1] + n)
+            kv_len.append(start + n)
+            slots.append(m.slot(e.request))
+            self.q_lens.append(n)
+            self.kv_lens.append(start + n)
+            self.requests.append(e.request)
+        logit_rows: List[int] = []
+        for orig, e in enumerate(entries):
+            base = q_start[row_of[orig]]
+            for w in e.want:
+                if not 0 <= int(w) < len(e.tokens):
+                    raise ValueError(f"request {e.request!r}: wanted place {w} is outside its {len(e.tokens)} tokens")
+                logit_rows.append(base + int(w))
+        T, B, R = len(tokens), len(order), len(logit_rows)
+        if T > self.rt.max_tokens:
+            raise ValueError(f"a step of {T} tokens exceeds the {self.rt.max_tokens} the engine was sized for")
+        if B > self.rt.max_seqs:
+            raise ValueError(f"a step of {B} requests exceeds the {self.rt.max_seqs} the engine was sized for")
+        n_groups = len(m.layout.groups)
+        strides = []
+        flat_tables: List[int] = []
+        for g in range(n_groups):
+            rows = [m.table(g, self.requests[row]) for row in range(B)]
+            stride = max(1, max(len(r) for r in rows))
+            strides.append(stride)
+            for r in rows:
+                flat_tables.extend(r)
+                flat_tables.extend([-1] * (stride - len(r)))
+        flat = tokens + positions + tok_seq + q_start + kv_len + slots + logit_rows + flat_tables
+        host = torch.tensor(flat, dtype=torch.int32).pin_memory()
+        dev = host.to(self.rt.device, non_blocking=True)
+        self._host_keepalive = host
+        cuts = [T, T, T, B + 1, B, B, R] + [B * s for s in strides]
+        views = torch.split(dev, cuts)
+        (self.token_ids, self.positions, self.tok_seq, self.q_start, self.kv_len, self.slot_ids,
+         self.logit_rows) = views[:7]
+        self._tables = [views[7 + g].view(B, strides[g]) for g in range(n_groups)]
+        self.num_tokens, self.num_seqs = T, B
+        self.max_q_len, self.max_kv_len = max(self.q_lens), max(self.kv_lens)
+        self.num_decode = sum(1 for n in self.q_lens if n == 1)
+        self.h2d_bytes = host.numel() * 4
+        return self

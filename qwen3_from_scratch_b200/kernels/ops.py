@@ -1,0 +1,320 @@
+"""Python face of the CUDA kernels: argument checks, then one C call per kernel.
+
+Each function takes torch tensors that live on the GPU, checks device, dtype,
+contiguity and the sizes the kernel takes, and launches on torch's current
+stream.  A size a kernel refuses raises ``KernelSizeError`` with the kernel's name
+and the offending numbers; nothing here falls back to torch or to the CPU.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Optional
+
+import torch
+
+from .build import BuildError, build_library
+
+F32, BF16 = 0, 1
+STATUS_BITS = {
+    1: "a token id outside the embedding table",
+    2: "a page id outside the pool where a live position needs one",
+    4: "a negative position or sequence index",
+    8: "a row of logits without a comparable value (all NaN)",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+class KernelSizeError(KernelError):
+    pass
+
+
+_lib = None
+_lib_path = None
+_lock = threading.Lock()
+
+_c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+_c_ll, _c_ull = ctypes.c_longlong, ctypes.c_ulonglong
+
+_SIGNATURES = {
+    "q3_embed": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "q3_add_rmsnorm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p],
+    "q3_add_rmsnorm_rows": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int,
+                            _c_float, _c_void_p],
+    "q3_rmsnorm": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p],
+    "q3_gemm_f32_nt": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "q3_qkv_post": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
+                    _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p,
+                    _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p],
+    "q3_attn_ref": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                    _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
+                    _c_void_p, _c_void_p],
+    "q3_swiglu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "q3_sample": [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ull,
+                  _c_void_p, _c_void_p, _c_void_p],
+}
+
+
+def library() -> ctypes.CDLL:
+    """The loaded kernel library; compiles it at the first call if it is not built yet."""
+    global _lib, _lib_path
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                try:
+                    path = build_library()
+                except BuildError as e:
+                    raise KernelError(str(e)) from None
+                lib = ctypes.CDLL(path)
+                for name, argtypes in _SIGNATURES.items():
+                    fn = getattr(lib, name)
+                    fn.argtypes = argtypes
+                    fn.restype = _c_int
+                _lib, _lib_path = lib, path
+    return _lib
+
+
+def library_path() -> Optional[str]:
+    library()
+    return _lib_path
+
+
+def dtype_tag(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, got {dtype}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _check(name: str, t: torch.Tensor, dtype: Optional[torch.dtype] = None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name}: tensor is on {t.device}; the kernels run on the GPU only")
+    if not t.is_contiguous():
+        raise KernelError(f"{name}: tensor must be contiguous (shape {tuple(t.shape)}, strides {t.stride()})")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
+
+
+def _done(kernel: str, code: int, detail: str = "") -> None:
+    if code == 0:
+        return
+    if code == -2:
+        raise KernelSizeError(f"{kernel}: size not taken by this kernel ({detail})")
+    if code == -1:
+        raise KernelError(f"{kernel}: dtype not taken ({detail})")
+    if code == -3:
+        raise KernelError(f"{kernel}: misaligned argument ({detail})")
+    raise KernelError(f"{kernel}: CUDA launch failed with error {code} ({detail})")
+
+
+def describe_status(word: int) -> str:
+    return "; ".join(text for bit, text in STATUS_BITS.items() if word & bit) or "ok"
+
+
+# ------------------------------------------------------------------ kernels
+def embed(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, status: torch.Tensor) -> None:
+    """resid[t] = float32(table[ids[t]])."""
+    _check("embed.table", table)
+    _check("embed.ids", ids, torch.int32)
+    _check("embed.resid", resid, torch.float32)
+    T, H = resid.shape
+    V = table.shape[0]
+    if table.shape[1] != H or ids.numel() != T:
+        raise KernelError(f"embed: table {tuple(table.shape)}, ids {tuple(ids.shape)}, resid {tuple(resid.shape)}")
+    code = library().q3_embed(table.data_ptr(), dtype_tag(table.dtype), ids.data_ptr(), resid.data_ptr(),
+                              T, H, V, status.data_ptr(), _stream())
+    _done("embed", code)
+
+
+def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+                out: torch.Tensor, eps: float) -> None:
+    """resid += delta (when given); out = rmsnorm(resid) * weight."""
+    _check("add_rmsnorm.resid", resid, torch.float32)
+    _check("add_rmsnorm.weight", weight, torch.float32)
+    _check("add_rmsnorm.out", out)
+    T, H = resid.shape
+    if delta is not None:
+        _check("add_rmsnorm.delta", delta, out.dtype)
+        if tuple(delta.shape) != (T, H):
+            raise KernelError(f"add_rmsnorm: delta {tuple(delta.shape)} vs stream {(T, H)}")
+    if tuple(out.shape) != (T, H) or weight.numel() != H:
+        raise KernelError(f"add_rmsnorm: out {tuple(out.shape)}, weight {tuple(weight.shape)}, stream {(T, H)}")
+    code = library().q3_add_rmsnorm(resid.data_ptr(), _ptr(delta), weight.data_ptr(), out.data_ptr(),
+                                    dtype_tag(out.dtype), T, H, float(eps), _stream())
+    _done("add_rmsnorm", code, f"width {H}")
+
+
+def add_rmsnorm_rows(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+                     rows: torch.Tensor, out: torch.Tensor, eps: float) -> None:
+    """out[r] = rmsnorm(resid[rows[r]] + delta[rows[r]]) * weight; resid is left as it is."""
+    _check("add_rmsnorm_rows.resid", resid, torch.float32)
+    _check("add_rmsnorm_rows.weight", weight, torch.float32)
+    _check("add_rmsnorm_rows.rows", rows, torch.int32)
+    _check("add_rmsnorm_rows.out", out)
+    T, H = resid.shape
+    R = rows.numel()
+    if delta is not None:
+        _check("add_rmsnorm_rows.delta", delta, out.dtype)
+        if tuple(delta.shape) != (T, H):
+            raise KernelError(f"add_rmsnorm_rows: delta {tuple(delta.shape)} vs stream {(T, H)}")
+    if tuple(out.shape) != (R, H) or weight.numel() != H:
+        raise KernelError(f"add_rmsnorm_rows: out {tuple(out.shape)}, rows {R}, width {H}")
+    if R == 0:
+        return
+    code = library().q3_add_rmsnorm_rows(resid.data_ptr(), _ptr(delta), weight.data_ptr(), out.data_ptr(),
+                                         dtype_tag(out.dtype), rows.data_ptr(), R, H, float(eps), _stream())
+    _done("add_rmsnorm_rows", code, f"width {H}")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float) -> None:
+    """out[r] = rmsnorm(x[r]) * weight over the last dimension."""
+    _check("rmsnorm.x", x)
+    _check("rmsnorm.out", out, x.dtype)
+    _check("rmsnorm.weight", weight, torch.float32)
+    dim = x.shape[-1]
+    rows = x.numel() // dim if dim else 0
+    if out.shape != x.shape or weight.numel() != dim:
+        raise KernelError(f"rmsnorm: x {tuple(x.shape)}, out {tuple(out.shape)}, weight {tuple(weight.shape)}")
+    code = library().q3_rmsnorm(x.data_ptr(), weight.data_ptr(), out.data_ptr(), dtype_tag(x.dtype), rows, dim,
+                                float(eps), _stream())
+    _done("rmsnorm", code)
+
+
+def gemm_f32_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = a[M, K] @ w[N, K]^T in plain float32 (no tensor cores)."""
+    _check("gemm_f32_nt.a", a, torch.float32)
+    _check("gemm_f32_nt.w", w, torch.float32)
+    _check("gemm_f32_nt.out", out, torch.float32)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm_f32_nt: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    code = library().q3_gemm_f32_nt(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, K, K, N, _stream())
+    _done("gemm_f32_nt", code, f"M {M} N {N} K {K}")
+
+
+def qkv_post(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+             q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+             inv_freq: Optional[torch.Tensor], rotary_dim: int, positions: torch.Tensor,
+             tok_seq: torch.Tensor, block_table: torch.Tensor, num_q_heads: int, num_kv_heads: int,
+             head_dim: int, write_kv: bool, status: torch.Tensor) -> None:
+    """Head norm, rotation, q to its buffer and k/v into their pages, in one pass over qkv."""
+    _check("qkv_post.qkv", qkv)
+    _check("qkv_post.q_out", q_out, qkv.dtype)
+    _check("qkv_post.k_pages", k_pages, qkv.dtype)
+    _check("qkv_post.v_pages", v_pages, qkv.dtype)
+    _check("qkv_post.positions", positions, torch.int32)
+    _check("qkv_post.tok_seq", tok_seq, torch.int32)
+    _check("qkv_post.block_table", block_table, torch.int32)
+    T = qkv.shape[0]
+    width = (num_q_heads + 2 * num_kv_heads) * head_dim
+    if qkv.shape[1] != width or q_out.numel() != T * num_q_heads * head_dim:
+        raise KernelError(f"qkv_post: qkv {tuple(qkv.shape)} expected [T, {width}]; q_out {tuple(q_out.shape)}")
+    num_pages, hkv, page_size, d = k_pages.shape
+    if hkv != num_kv_heads or d != head_dim or v_pages.shape != k_pages.shape:
+        raise KernelError(f"qkv_post: pages {tuple(k_pages.shape)} / {tuple(v_pages.shape)} "
+                          f"vs heads {num_kv_heads} x {head_dim}")
+    if positions.numel() != T or tok_seq.numel() != T or block_table.dim() != 2:
+        raise KernelError("qkv_post: positions / tok_seq must have one entry per token; block_table is 2-D")
+    for name, wt in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if wt is not None:
+            _check(f"qkv_post.{name}", wt, torch.float32)
+            if wt.numel() != head_dim:
+                raise KernelError(f"qkv_post: {name} has {wt.numel()} elements, head_dim is {head_dim}")
+    if inv_freq is not None:
+        _check("qkv_post.inv_freq", inv_freq, torch.float32)
+        if inv_freq.numel() * 2 != rotary_dim:
+            raise KernelError(f"qkv_post: inv_freq has {inv_freq.numel()} entries, rotary_dim is {rotary_dim}")
+    code = library().q3_qkv_post(
+        qkv.data_ptr(), dtype_tag(qkv.dtype), T, num_q_heads, num_kv_heads, head_dim, _ptr(q_weight),
+        _ptr(k_weight), float(eps), _ptr(inv_freq), int(rotary_dim), positions.data_ptr(), tok_seq.data_ptr(),
+        block_table.data_ptr(), block_table.shape[1], page_size, k_pages.data_ptr(), v_pages.data_ptr(),
+        num_pages, q_out.data_ptr(), 1 if write_kv else 0, status.data_ptr(), _stream())
+    _done("qkv_post", code, f"head_dim {head_dim}, rotary_dim {rotary_dim}")
+
+
+def attn_ref(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
+             q_start: torch.Tensor, kv_len: torch.Tensor, tok_seq: torch.Tensor,
+             block_table: torch.Tensor, scale: float, window: int, status: torch.Tensor) -> None:
+    """Plain paged causal attention (one warp per query and head); any head_dim up to 512."""
+    _check("attn_ref.q", q)
+    _check("attn_ref.out", out, q.dtype)
+    _check("attn_ref.k_pages", k_pages, q.dtype)
+    _check("attn_ref.v_pages", v_pages, q.dtype)
+    for name, t in (("q_start", q_start), ("kv_len", kv_len), ("tok_seq", tok_seq), ("block_table", block_table)):
+        _check(f"attn_ref.{name}", t, torch.int32)
+    T, Hq, D = q.shape
+    num_pages, Hkv, page_size, d = k_pages.shape
+    if d != D or v_pages.shape != k_pages.shape or out.numel() != q.numel():
+        raise KernelError(f"attn_ref: q {tuple(q.shape)}, pages {tuple(k_pages.shape)}, out {tuple(out.shape)}")
+    code = library().q3_attn_ref(q.data_ptr(), dtype_tag(q.dtype), k_pages.data_ptr(), v_pages.data_ptr(),
+                                 out.data_ptr(), q_start.data_ptr(), kv_len.data_ptr(), tok_seq.data_ptr(),
+                                 block_table.data_ptr(), block_table.shape[1], page_size, num_pages, T, Hq, Hkv,
+                                 D, float(scale), int(window), status.data_ptr(), _stream())
+    _done("attn_ref", code, f"heads {Hq}/{Hkv}, head_dim {D}")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out = up * silu(gate), gate = first half of the columns, up = second half."""
+    _check("swiglu.gate_up", gate_up)
+    _check("swiglu.out", out, gate_up.dtype)
+    T, two_i = gate_up.shape
+    if two_i % 2 or tuple(out.shape) != (T, two_i // 2):
+        raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)}, out {tuple(out.shape)}")
+    code = library().q3_swiglu(gate_up.data_ptr(), out.data_ptr(), dtype_tag(out.dtype), T, two_i // 2, _stream())
+    _done("swiglu", code)
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
+           temperature: Optional[torch.Tensor] = None, top_k: Optional[torch.Tensor] = None,
+           request_key: Optional[torch.Tensor] = None, position: Optional[torch.Tensor] = None,
+           seed: int = 0) -> None:
+    """One token per row of float32 logits: argmax where temperature <= 0, else a Gumbel-max draw."""
+    _check("sample.logits", logits, torch.float32)
+    _check("sample.out", out, torch.int32)
+    R, V = logits.shape
+    if out.numel() != R:
+        raise KernelError(f"sample: {R} rows of logits, {out.numel()} outputs")
+    if temperature is not None:
+        _check("sample.temperature", temperature, torch.float32)
+        if request_key is None or position is None:
+            raise KernelError("sample: a temperature needs request_key and position")
+        _check("sample.request_key", request_key, torch.int64)
+        _check("sample.position", position, torch.int32)
+    if top_k is not None:
+        _check("sample.top_k", top_k, torch.int32)
+    code = library().q3_sample(logits.data_ptr(), R, V, V, _ptr(temperature), _ptr(top_k), _ptr(request_key),
+                               _ptr(position), int(seed) & 0xFFFFFFFFFFFFFFFF, out.data_ptr(), status.data_ptr(),
+                               _stream())
+    _done("sample", code)
+
+
+def rope(x: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, positions: torch.Tensor,
+         out: torch.Tensor, status: torch.Tensor) -> None:
+    """out = rotate-half rotary encoding of x[T, heads, D] at `positions` (no norm, no cache)."""
+    _check("rope.x", x)
+    _check("rope.out", out, x.dtype)
+    _check("rope.inv_freq", inv_freq, torch.float32)
+    _check("rope.positions", positions, torch.int32)
+    T, heads, d = x.shape
+    if out.shape != x.shape or positions.numel() != T or inv_freq.numel() * 2 != rotary_dim:
+        raise KernelError(f"rope: x {tuple(x.shape)}, out {tuple(out.shape)}, positions {positions.numel()}, "
+                          f"inv_freq {inv_freq.numel()}, rotary_dim {rotary_dim}")
+    code = library().q3_qkv_post(
+        x.data_ptr(), dtype_tag(x.dtype), T, heads, 0, d, None, None, 0.0, inv_freq.data_ptr(), int(rotary_dim),
+        positions.data_ptr(), positions.data_ptr(), None, 1, 1, None, None, 0, out.data_ptr(), 0,
+        status.data_ptr(), _stream())
+    _done("rope", code, f"head_dim {d}, rotary_dim {rotary_dim}")

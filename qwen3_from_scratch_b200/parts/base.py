@@ -1,0 +1,238 @@
+"""Interfaces of the parts a model is put together from.
+
+A *part* is built from explicit sizes and constants (never from a model
+configuration object), says which tensors it needs by name (``weight_specs``),
+receives them on the device (``setup``) and then runs on activations.  The
+kinds of part and what each must offer:
+
+``Norm``
+    ``add_norm(stream, delta) -> normed``: adds ``delta`` (or nothing) into the
+    float32 residual stream and returns the normed activations in the compute
+    dtype; ``norm_rows(stream, delta, rows) -> normed`` does the same for chosen
+    rows without changing the stream; ``forward(x)`` norms a plain tensor.
+``PositionEncoding``
+    ``apply(x[T, heads, D], positions[T]) -> x'``; optionally
+    ``fused_rotary() -> (inv_freq, rotary_dim)`` when it is a rotate-half rotary
+    encoding that the attention kernels can apply themselves.
+``Mixer``
+    ``cache_spec()`` (pages of keys/values, a fixed-size state, or none) and
+    ``forward(x[T, width], ctx, cache_id, write_cache) -> y[T, width]``.
+``FeedForward``
+    ``forward(x[T, width]) -> y[T, width]``.
+``Block``
+    ``forward(stream, pending, ctx, cache_id, write_cache) -> pending'``: the
+    arrangement of norms, mixer and feed-forward around the residual stream.
+    ``pending`` is a sub-layer output not yet added to the stream (the next norm
+    adds it, which saves one pass over the activations).
+
+No part knows which model it is in: the model specification (``ModelSpec``)
+chooses parts and their parameters layer by layer and lists the order in which
+layers run.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
+
+import torch
+
+# ---------------------------------------------------------------------- weights
+
+
+@dataclass(frozen=True)
+class WeightSpec:
+    """One tensor a part needs from the model folder.
+
+    kind:
+      ``matrix``  operand of a matrix product: kept as stored (bfloat16 stays
+                  bfloat16, a tensor stored in float32 stays float32 and its
+                  product runs in float32); in a float32 run everything is
+                  widened to float32.
+      ``vector``  small parameter read by float32 arithmetic (norm weights):
+                  held in float32 on the device whatever it was stored as.
+      ``index``   integer table: held as int32.
+    init: how the random-weights writer fills it (``normal``: N(0, 0.02);
+      ``one_plus_normal``: 1 + N(0, 0.1); ``zeros``).
+    """
+
+    name: str
+    shape: Tuple[int, ...]
+    kind: str = "matrix"
+    init: str = "normal"
+
+
+# ---------------------------------------------------------------------- cache needs
+
+
+@dataclass(frozen=True)
+class KVCacheSpec:
+    """Pages of keys and values, one slot per token.  ``window`` = how many of the latest
+    keys a query still reads (None: all of them); pages a window has passed are given back."""
+
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """State of fixed size per request (a recurrent mixer's), kept in a slot while the request lives.
+    ``dtype``: ``"float32"`` or ``"compute"``."""
+
+    shape: Tuple[int, ...]
+    dtype: str = "float32"
+
+
+CacheSpec = Union[KVCacheSpec, StateSpec, None]
+
+# ---------------------------------------------------------------------- runtime
+
+
+@dataclass
+class Runtime:
+    """What a part may rely on at run time: device, compute dtype, the largest step, the status word."""
+
+    device: torch.device
+    dtype: torch.dtype
+    max_tokens: int
+    max_seqs: int
+    status: torch.Tensor = None  # int32[1] on the device; kernels OR error bits into it
+
+    def __post_init__(self):
+        if self.status is None:
+            self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def empty(self, *shape: int, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        return torch.empty(*shape, dtype=dtype or self.dtype, device=self.device)
+
+
+class StepContext:
+    """Everything the parts need to know about the batch of one step.
+
+    Device tensors (int32): ``token_ids[T]``, ``positions[T]`` (absolute position of each
+    token in its request), ``tok_seq[T]`` (row of the batch each token belongs to),
+    ``q_start[B + 1]`` (token offsets of the rows), ``kv_len[B]`` (tokens of each request
+    after this step), ``slot_ids[B]`` (state slot of each request), ``logit_rows[R]``.
+    Host mirrors: ``q_lens``, ``kv_lens``, ``max_q_len``, ``max_kv_len``, ``num_decode``
+    (rows that bring exactly one token come first in the batch).
+    ``kv(cache_id)`` gives ``(k_pages, v_pages, block_table)`` of a cache of pages and
+    ``state(cache_id)`` the ``[slots, *shape]`` tensor of a cache of fixed-size state.
+    """
+
+    num_tokens: int
+    num_seqs: int
+    token_ids: torch.Tensor
+    positions: torch.Tensor
+    tok_seq: torch.Tensor
+    q_start: torch.Tensor
+    kv_len: torch.Tensor
+    slot_ids: torch.Tensor
+    logit_rows: torch.Tensor
+    q_lens: List[int]
+    kv_lens: List[int]
+    max_q_len: int
+    max_kv_len: int
+    num_decode: int
+
+    def kv(self, cache_id: int):  # pragma: no cover - interface
+        raise NotImplementedError
+
+    def state(self, cache_id: int):  # pragma: no cover - interface
+        raise NotImplementedError
+
+
+# ---------------------------------------------------------------------- parts
+
+
+class Part:
+    """Base of all parts.  ``name`` is the prefix of its tensors in the model folder."""
+
+    def __init__(self, name: str = ""):
+        self.name = name
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return []
+
+    def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        """Takes its tensors (already on the device) and allocates what it reuses every step."""
+        self.rt = rt
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def add_norm(self, stream: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+        raise NotImplementedError
+
+    def norm_rows(self, stream: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def apply(self, x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def fused_rotary(self) -> Optional[Tuple[torch.Tensor, int]]:
+        return None
+
+
+class Mixer(Part):
+    def cache_spec(self) -> CacheSpec:
+        return None
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    mixer: Mixer
+
+    def forward(self, stream: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
+                cache_id: Optional[int], write_cache: bool) -> Optional[torch.Tensor]:
+        raise NotImplementedError
+
+
+# ---------------------------------------------------------------------- model specification
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    """Which registered part, with which parameters (sizes, constants, nested PartSpecs)."""
+
+    kind: str
+    params: Dict[str, Any] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class LayerCall:
+    """One entry of the run order: run layer ``layer`` on cache ``cache``.
+
+    A layer may appear in several calls (shared weights), each with a cache of its own,
+    or with ``write_cache=False`` on a cache that an earlier call filled (shared keys/values).
+    """
+
+    layer: int
+    cache: Optional[int]
+    write_cache: bool = True
+
+
+@dataclass
+class ModelSpec:
+    """A whole model as data: parts by layer, and the order in which layers run."""
+
+    embedding: Tuple[str, PartSpec]  # every part comes as (tensor-name prefix, spec)
+    layers: List[Tuple[str, PartSpec]]
+    order: List[LayerCall]
+    final_norm: Tuple[str, PartSpec]
+    head: Tuple[str, PartSpec]
+    vocab_size: int
+    max_positions: int
+    ignorable_weights: Tuple[str, ...] = ()
+    eos_token_id: Optional[int] = None

@@ -1,0 +1,44 @@
+"""Pre-norm residual block: h = x + mixer(norm1(x)); y = h + feed_forward(norm2(h)).
+
+Reference: models/transformer_block.py:38-46.  The residual stream is float32 and the sums are
+fused into the norms: a block receives the previous sub-layer's output as ``pending`` and hands
+its own feed-forward output on in the same way.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..registry import create_part, register_part
+from .base import Block, PartSpec, Runtime, StepContext, WeightSpec
+
+
+@register_part("block", "pre_norm")
+class PreNormBlock(Block):
+    def __init__(self, name: str, norm1: PartSpec, mixer: PartSpec, norm2: PartSpec, feed_forward: PartSpec,
+                 names: Optional[Dict[str, str]] = None):
+        super().__init__(name)
+        n = {"norm1": "norm1", "mixer": "mixer", "norm2": "norm2", "feed_forward": "feed_forward"}
+        n.update(names or {})
+        self.norm1 = create_part("norm", norm1, name=f"{name}.{n['norm1']}")
+        self.mixer = create_part("mixer", mixer, name=f"{name}.{n['mixer']}")
+        self.norm2 = create_part("norm", norm2, name=f"{name}.{n['norm2']}")
+        self.feed_forward = create_part("feed_forward", feed_forward, name=f"{name}.{n['feed_forward']}")
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return (self.norm1.weight_specs() + self.mixer.weight_specs() + self.norm2.weight_specs()
+                + self.feed_forward.weight_specs())
+
+    def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        super().setup(rt, weights)
+        for part in (self.norm1, self.mixer, self.norm2, self.feed_forward):
+            part.setup(rt, weights)
+
+    def forward(self, stream: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
+                cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
+        x = self.norm1.add_norm(stream, pending)
+        a = self.mixer.forward(x, ctx, cache_id, write_cache)
+        x = self.norm2.add_norm(stream, a)
+        return self.feed_forward.forward(x)
