@@ -133,6 +133,7 @@ class CacheManager:
         self._free_slots: List[int] = list(range(self.max_seqs - 1, -1, -1))
         self._requests: Dict[Hashable, _Request] = {}
         self.freed_log: Optional[List[Tuple[int, int]]] = None  # (group, page) of pages given back, if tracked
+        self.on_open = None  # called with the slot when a request is opened (the storage clears its state)
 
     # ------------------------------------------------------------------ queries
     def __contains__(self, req: Hashable) -> bool:
@@ -192,6 +193,8 @@ class CacheManager:
         slot = self._free_slots.pop()
         n = len(self._pools)
         self._requests[req] = _Request(slot=slot, tables=[[] for _ in range(n)], first_live=[0] * n)
+        if self.on_open is not None:
+            self.on_open(slot)
         return slot
 
     def reserve(self, req: Hashable, new_length: int) -> None:

@@ -37,6 +37,7 @@ class Session:
         self.storage = CacheStorage(layout, page_size, max_seqs, self.rt.device, self.rt.dtype)
         self.vocab_size = self.model.spec.vocab_size
         self.max_positions = self.model.spec.max_positions
+        self.manager.on_open = self.storage.clear_slot
         self.poison_freed_pages = poison_freed_pages
         if poison_freed_pages:
             self.manager.freed_log = []
@@ -44,8 +45,7 @@ class Session:
 
     # ------------------------------------------------------------------ requests
     def open(self, request: Hashable) -> None:
-        slot = self.manager.open(request)
-        self.storage.clear_slot(slot)
+        self.manager.open(request)
 
     def length(self, request: Hashable) -> int:
         return self.manager.length(request)
@@ -90,6 +90,20 @@ class Session:
             self.manager.advance(e.request, self.manager.length(e.request) + len(e.tokens))
         self._poison()
         return logits
+
+    def step_reserved(self, entries: Sequence[Entry]) -> torch.Tensor:
+        """The step for a caller (the scheduler) that has opened the requests and reserved their
+        pages itself and will record the progress itself: builds the batch and runs it."""
+        ctx = BatchContext(self.manager, self.storage, self.rt).build(entries, self.vocab_size)
+        self.last_context = ctx
+        return self.model.step(ctx)
+
+    def after_step(self) -> None:
+        self._poison()
+
+    def check_status_word_async(self) -> None:
+        """Checks the status word when the caller has just synchronised anyway (a token read)."""
+        self.check_status()
 
     def check_status(self) -> None:
         """Reads the device status word (synchronises) and raises if a kernel flagged bad table data."""

@@ -1,0 +1,179 @@
+"""Generation through the Python entry point and the command line, and trace replay as a program."""
+
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from conftest import ROOT, TINY, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+def greedy_by_plain(folder, prompt, n):
+    cfg, w = plain.read_model_folder(folder)
+    ids = list(prompt)
+    margins = []
+    for _ in range(n):
+        logits = plain.forward_logits(cfg, w, ids)[-1]
+        top = torch.topk(logits, 2).values
+        margins.append(float(top[0] - top[1]))
+        ids.append(plain.greedy_token(logits))
+    return ids[len(prompt):], margins
+
+
+@pytest.mark.parametrize("key,page", [("a", 4), ("b", 8)])
+def test_greedy_generation_equals_the_plain_implementation(tiny_folders, key, page):
+    """float32 end to end: the BASELINE tiny workloads (prompts of 5/17/31 and 1/9/33/64/100 tokens,
+    16 greedy tokens each) through batch_generate with chunked prompts and continuous batching."""
+    from qwen3_from_scratch_b200.engine.engine import SyncEngine
+    folder = tiny_folders[key]
+    vocab = TINY[key][0]["vocab_size"]
+    lengths = [5, 17, 31] if key == "a" else [1, 9, 33, 64, 100]
+    prompts = [random_tokens(vocab, n, 1 + i) for i, n in enumerate(lengths)]
+    engine = SyncEngine(folder, dtype="float32", block_size=page, num_pages=128, max_num_seqs=4,
+                        max_num_tokens=48, chunked_prefill_size=16)
+    results, batch = engine.batch_generate(prompts, max_new_tokens=16, ignore_eos=True)
+    assert batch.num_requests == len(prompts) and batch.total_tokens == 16 * len(prompts)
+    for prompt, r in zip(prompts, results):
+        want, margins = greedy_by_plain(folder, prompt, 16)
+        assert r.finish_reason == "length"
+        assert min(margins) > 1e-4, "the plain top-2 are too close for an exact comparison"
+        assert r.token_ids == want
+    engine.session.manager.check()
+    assert engine.session.manager.free_slots() == 4
+
+
+def test_bfloat16_generation_follows_plain_within_near_ties(tiny_folders):
+    from qwen3_from_scratch_b200.engine.engine import SyncEngine
+    folder = tiny_folders["a"]
+    cfg, w = plain.read_model_folder(folder)
+    prompt = random_tokens(256, 17, 2)
+    engine = SyncEngine(folder, dtype="bfloat16", block_size=4, num_pages=64, max_num_seqs=2, max_num_tokens=32)
+    got = engine.generate(prompt, max_new_tokens=12, ignore_eos=True)
+    ids = list(prompt)
+    for token in got:
+        logits = plain.forward_logits(cfg, w, ids)[-1]
+        gap = float(logits.max() - logits[token])
+        assert gap <= 2e-2 * float(logits.abs().max()), "bfloat16 picked a token the plain logits rule out"
+        ids.append(token)
+
+
+def test_temperature_and_top_k_match_plain_with_the_same_generator(tiny_folders):
+    from qwen3_from_scratch_b200.engine.engine import SyncEngine
+    from qwen3_from_scratch_b200.engine.request import SamplingParams
+    folder = tiny_folders["b"]
+    cfg, w = plain.read_model_folder(folder)
+    prompts = [random_tokens(384, n, 3 + i) for i, n in enumerate([9, 33])]
+    params = [SamplingParams(temperature=0.7, max_new_tokens=10, seed=42, ignore_eos=True),
+              SamplingParams(temperature=1.1, top_k=20, max_new_tokens=10, seed=42, ignore_eos=True)]
+    engine = SyncEngine(folder, dtype="float32", block_size=8, num_pages=64, max_num_seqs=4, max_num_tokens=32,
+                        chunked_prefill_size=16)
+    reqs = [engine.add_request(p, params=q) for p, q in zip(prompts, params)]
+    while any(r.finish_reason is None for r in reqs):
+        engine.step()
+    for req, prompt, p in zip(reqs, prompts, params):
+        ids = list(prompt)
+        for token in req.output:
+            logits = plain.forward_logits(cfg, w, ids)[-1]
+            want = plain.sample_token(logits, p.temperature, p.top_k, p.seed, req.key, len(ids))
+            assert token == want
+            ids.append(token)
+        assert len(set(req.output)) > 1  # it is sampling, not a constant
+
+
+def test_eos_stops_a_request(tiny_folders):
+    from qwen3_from_scratch_b200.engine.engine import SyncEngine
+    folder = tiny_folders["a"]
+    prompt = random_tokens(256, 9, 5)
+    want, _ = greedy_by_plain(folder, prompt, 6)
+    engine = SyncEngine(folder, dtype="float32", block_size=4, num_pages=32, max_num_seqs=2, max_num_tokens=32,
+                        eos_token_id=want[3])
+    chunks = list(engine.generate_stream(prompt, max_new_tokens=20))
+    stop = want.index(want[3])
+    assert [c.token_id for c in chunks] == want[:stop + 1]
+    assert chunks[-1].metrics.token_count == stop + 1 and chunks[-1].metrics.ttft > 0
+    assert not engine.session.manager.live_requests()
+
+
+def test_preemption_keeps_the_result(tiny_folders):
+    """A pool too small for all requests at once: some are preempted and recomputed, and every
+    request still produces what it produces alone."""
+    from qwen3_from_scratch_b200.engine.engine import SyncEngine
+    folder = tiny_folders["a"]
+    prompts = [random_tokens(256, n, 20 + i) for i, n in enumerate([30, 28, 26, 31])]
+    alone = SyncEngine(folder, dtype="float32", block_size=4, num_pages=64, max_num_seqs=4, max_num_tokens=64)
+    want = [alone.generate(p, max_new_tokens=24, ignore_eos=True) for p in prompts]
+    tight = SyncEngine(folder, dtype="float32", block_size=4, num_pages=36, max_num_seqs=4, max_num_tokens=64)
+    results, _ = tight.batch_generate(prompts, max_new_tokens=24, ignore_eos=True)
+    assert tight.scheduler.num_preemptions > 0
+    assert [r.token_ids for r in results] == want
+    tight.session.manager.check()
+
+
+def test_request_that_cannot_fit_is_refused(tiny_folders):
+    from qwen3_from_scratch_b200.engine.engine import SyncEngine
+    engine = SyncEngine(tiny_folders["a"], dtype="float32", block_size=4, num_pages=8, max_num_seqs=2,
+                        max_num_tokens=32)
+    with pytest.raises(ValueError, match="can never fit"):
+        engine.add_request([1] * 30, max_new_tokens=10)
+    with pytest.raises(ValueError, match="tokenizer"):
+        engine.add_request("text without a tokenizer")
+
+
+def run_trace(folder, dtype, steps, out, max_tokens, extra=()):
+    env = dict(os.environ)
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
+           "--out", out, "--max-tokens", str(max_tokens), *extra]
+    text = "".join(json.dumps(s) + "\n" for s in steps)
+    proc = subprocess.run(cmd, input=text, capture_output=True, text=True, env=env, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(tiny_folders, tmp_path, dtype):
+    """The program itself: portions, a request left out of a step, ends, wanted places, files."""
+    folder = tiny_folders["c"]
+    vocab = TINY["c"][0]["vocab_size"]
+    a, b = random_tokens(vocab, 70, 31), random_tokens(vocab, 50, 32)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:40], "want": [0, 39]}], "end": []},
+        {"step": 1, "entries": [{"id": "b", "tokens": b[:2], "want": []}], "end": []},
+        {"step": 2, "entries": [{"id": "a", "tokens": a[40:41], "want": [0]},
+                                {"id": "b", "tokens": b[2:50], "want": [47, 0]}], "end": ["b"]},
+        {"step": 3, "entries": [{"id": "a", "tokens": a[41:70], "want": list(range(29))}], "end": ["a"]},
+    ]
+    out = str(tmp_path / "out")
+    run_trace(folder, dtype, steps, out, max_tokens=128 + 64, extra=["--poison-freed-pages"])
+    assert sorted(os.listdir(out)) == ["0.f32", "2.f32", "3.f32"]
+    cfg, w = plain.read_model_folder(folder)
+    la, lb = plain.forward_logits(cfg, w, a), plain.forward_logits(cfg, w, b)
+    tol = {"float32": 1e-5, "bfloat16": 2e-2}[dtype]
+
+    def check(step, rows):
+        got = torch.from_numpy(np.fromfile(os.path.join(out, f"{step}.f32"), dtype="<f4")).view(len(rows), vocab)
+        want = torch.stack(rows)
+        assert float((got - want).abs().max()) <= tol * float(want.abs().max())
+
+    check(0, [la[0], la[39]])
+    check(2, [la[40], lb[49], lb[2]])
+    check(3, [la[41 + i] for i in range(29)])
+
+
+def test_command_line_generates(tiny_folders):
+    folder = tiny_folders["a"]
+    prompt = random_tokens(256, 5, 1)
+    want, _ = greedy_by_plain(folder, prompt, 6)
+    cmd = [sys.executable, "-m", "qwen3_from_scratch_b200", "generate", "--model", folder, "--dtype", "float32",
+           "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "6", "--ignore-eos",
+           "--block-size", "4", "--num-pages", "32", "--max-num-seqs", "2", "--max-num-tokens", "32"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    record = json.loads(proc.stdout.splitlines()[0])
+    assert record["token_ids"] == want and record["finish_reason"] == "length"

@@ -1,0 +1,339 @@
+"""Each kernel alone against a plain float32/float64 torch restatement of the same formula, at
+sizes other than the engine's tiny models use (odd widths, head sizes in steps of 16, scattered
+pages, ragged lengths)."""
+
+import math
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+# relative to the largest |expected| value: float32 kernels differ from float64 by summation
+# order only; bfloat16 outputs are rounded once to 8 significant bits (2^-9 = 0.002) and, where
+# inputs are bfloat16 too, the expectation is computed from the same rounded inputs.
+TOL = {"float32": 2e-6, "bfloat16": 4e-3}
+
+
+def ops():
+    from qwen3_from_scratch_b200.kernels import ops as o
+    return o
+
+
+def dev(t, dtype=None):
+    return t.to("cuda", dtype) if dtype else t.to("cuda")
+
+
+def close(got, want, dtype, scale=None):
+    got, want = got.double().cpu(), want.double().cpu()
+    scale = scale or max(float(want.abs().max()), 1e-9)
+    err = float((got - want).abs().max()) / scale
+    assert math.isfinite(err) and err <= TOL[dtype], f"relative error {err:.3g} > {TOL[dtype]:g}"
+
+
+def status():
+    return torch.zeros(1, dtype=torch.int32, device="cuda")
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_embed(dtype):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(1000, 96, generator=g).to(DT[dtype])
+    ids = torch.randint(0, 1000, (37,), generator=g, dtype=torch.int32)
+    out = torch.empty(37, 96, device="cuda")
+    st = status()
+    ops().embed(dev(table), dev(ids), out, st)
+    assert torch.equal(out.cpu(), table.float()[ids.long()])
+    assert int(st.item()) == 0
+    bad = ids.clone()
+    bad[5] = 1000
+    ops().embed(dev(table), dev(bad), out, st)
+    assert int(st.item()) == 1 and float(out[5].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("width", [100, 2560, 6])
+def test_add_rmsnorm(dtype, width):
+    g = torch.Generator().manual_seed(1)
+    T, eps = 37, 1e-5
+    stream = torch.randn(T, width, generator=g) * 3
+    delta = (torch.randn(T, width, generator=g)).to(DT[dtype])
+    w = 1 + 0.1 * torch.randn(width, generator=g)
+    s = dev(stream.clone())
+    out = torch.empty(T, width, device="cuda", dtype=DT[dtype])
+    ops().add_rmsnorm(s, dev(delta), dev(w), out, eps)
+    total = stream.double() + delta.double()
+    close(s, total, "float32")
+    close(out, plain.rms_norm(total, w.double(), eps), dtype)
+    # without a delta the stream is left alone
+    s2 = dev(stream.clone())
+    ops().add_rmsnorm(s2, None, dev(w), out, eps)
+    assert torch.equal(s2.cpu(), stream)
+    close(out, plain.rms_norm(stream.double(), w.double(), eps), dtype)
+    # chosen rows, stream unchanged
+    rows = torch.tensor([36, 0, 17, 17], dtype=torch.int32)
+    s3 = dev(stream.clone())
+    out_rows = torch.empty(4, width, device="cuda", dtype=DT[dtype])
+    ops().add_rmsnorm_rows(s3, dev(delta), dev(w), dev(rows), out_rows, eps)
+    assert torch.equal(s3.cpu(), stream)
+    close(out_rows, plain.rms_norm(total[rows.long()], w.double(), eps), dtype)
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_rmsnorm_on_head_vectors(dtype):
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(11, 5, 48, generator=g).to(DT[dtype])
+    w = 1 + 0.1 * torch.randn(48, generator=g)
+    out = torch.empty_like(dev(x))
+    ops().rmsnorm(dev(x), dev(w), out, 1e-6)
+    close(out, plain.rms_norm(x.double(), w.double(), 1e-6), dtype)
+
+
+@pytest.mark.parametrize("shape", [(37, 70, 53), (1, 331, 96), (130, 64, 200), (64, 64, 16)])
+def test_gemm_f32_is_true_float32(shape):
+    M, N, K = shape
+    g = torch.Generator().manual_seed(3)
+    a, w = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g)
+    out = torch.empty(M, N, device="cuda")
+    ops().gemm_f32_nt(dev(a), dev(w), out)
+    want = a.double() @ w.double().t()
+    # float32 FMA chain over K terms: error ~ K * 2^-24 of the row's magnitude, far below TF32's 2^-11
+    assert float((out.cpu().double() - want).abs().max()) <= 1e-6 * K ** 0.5 * float(want.abs().max())
+    # rows do not depend on the other rows of the batch
+    one = torch.empty(1, N, device="cuda")
+    ops().gemm_f32_nt(dev(a[M // 2:M // 2 + 1].contiguous()), dev(w), one)
+    assert torch.equal(one[0], out[M // 2])
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_swiglu(dtype):
+    g = torch.Generator().manual_seed(4)
+    gu = (torch.randn(19, 400, generator=g) * 3).to(DT[dtype])
+    out = torch.empty(19, 200, device="cuda", dtype=DT[dtype])
+    ops().swiglu(dev(gu), out)
+    gate, up = gu[:, :200].double(), gu[:, 200:].double()
+    close(out, up * gate * torch.sigmoid(gate), dtype)
+
+
+def paged(kv, page_size, tables, num_pages, dtype):
+    """Scatters per-request [len, Hkv, D] keys (or values) into pages [P, Hkv, page, D] (NaN elsewhere)."""
+    hkv, d = kv[0].shape[1:]
+    pages = torch.full((num_pages, hkv, page_size, d), float("nan"))
+    for seq, table in zip(kv, tables):
+        for pos in range(seq.shape[0]):
+            pages[table[pos // page_size], :, pos % page_size] = seq[pos]
+    return pages.to(dtype)
+
+
+def make_tables(lengths, page_size, seed, extra=3):
+    """Block tables that are scattered and partly reversed, to prove the indirection."""
+    need = [-(-n // page_size) for n in lengths]
+    num_pages = sum(need) + extra
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    tables, at = [], 0
+    for n in need:
+        tables.append(perm[at:at + n][::-1])
+        at += n
+    return tables, num_pages
+
+
+def table_tensor(tables):
+    stride = max(len(t) for t in tables)
+    return torch.tensor([t + [-1] * (stride - len(t)) for t in tables], dtype=torch.int32)
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("hq,hkv,d,rot", [(6, 3, 48, 48), (4, 1, 80, 32), (8, 2, 128, 128), (2, 2, 16, 16)])
+def test_qkv_post(dtype, hq, hkv, d, rot):
+    """Head norm + rotation + scatter, with a partial rotary width and pages out of order."""
+    g = torch.Generator().manual_seed(5)
+    page_size, eps, theta = 8, 1e-6, 10000.0
+    starts, news = [0, 13, 40], [21, 1, 7]  # tokens already cached, tokens of this step
+    lengths = [s + n for s, n in zip(starts, news)]
+    tables, num_pages = make_tables(lengths, page_size, 6)
+    T = sum(news)
+    qkv = torch.randn(T, (hq + 2 * hkv) * d, generator=g).to(DT[dtype])
+    qw, kw = 1 + 0.1 * torch.randn(d, generator=g), 1 + 0.1 * torch.randn(d, generator=g)
+    positions = torch.tensor([s + i for s, n in zip(starts, news) for i in range(n)], dtype=torch.int32)
+    tok_seq = torch.tensor([b for b, n in enumerate(news) for _ in range(n)], dtype=torch.int32)
+    inv_freq = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+    k_pages = torch.zeros(num_pages, hkv, page_size, d, device="cuda", dtype=DT[dtype])
+    v_pages = torch.zeros_like(k_pages)
+    q_out = torch.empty(T, hq, d, device="cuda", dtype=DT[dtype])
+    st = status()
+    ops().qkv_post(dev(qkv), q_out, k_pages, v_pages, dev(qw), dev(kw), eps, dev(inv_freq), rot, dev(positions),
+                   dev(tok_seq), dev(table_tensor(tables)), hq, hkv, d, True, st)
+    assert int(st.item()) == 0
+    x = qkv.double().view(T, hq + 2 * hkv, d)
+    q, k, v = x[:, :hq], x[:, hq:hq + hkv], x[:, hq + hkv:]
+    q, k = plain.rms_norm(q, qw.double(), eps), plain.rms_norm(k, kw.double(), eps)
+    ang = positions.double()[:, None] * inv_freq.double()[None, :]
+    cos, sin = ang.cos(), ang.sin()
+
+    def rotate(t):
+        out = t.clone()
+        out[..., :rot] = plain.apply_rope(t[..., :rot], cos, sin)
+        return out
+
+    q, k = rotate(q), rotate(k)
+    close(q_out, q, dtype)
+    kp, vp = k_pages.cpu().double(), v_pages.cpu().double()
+    for t in range(T):
+        page = tables[int(tok_seq[t])][int(positions[t]) // page_size]
+        slot = int(positions[t]) % page_size
+        close(kp[page, :, slot], k[t], dtype, scale=float(k.abs().max()))
+        close(vp[page, :, slot], v[t], dtype, scale=float(v.abs().max()))
+    # nothing else was written
+    written = torch.zeros(num_pages, page_size, dtype=torch.bool)
+    for t in range(T):
+        written[tables[int(tok_seq[t])][int(positions[t]) // page_size], int(positions[t]) % page_size] = True
+    assert float(kp.abs().sum(dim=(1, 3))[~written].sum()) == 0.0
+    # a page id outside the pool is reported, not written
+    bad = table_tensor(tables)
+    bad[0, 0] = num_pages
+    ops().qkv_post(dev(qkv), q_out, k_pages, v_pages, dev(qw), dev(kw), eps, dev(inv_freq), rot, dev(positions),
+                   dev(tok_seq), dev(bad), hq, hkv, d, True, st)
+    assert int(st.item()) & 2
+
+
+def reference_attention(q, k_list, v_list, q_lens, window):
+    """Per request: the plain whole-sequence attention, of which the last q_len rows are the step's."""
+    outs = []
+    at = 0
+    for k, v, n in zip(k_list, v_list, q_lens):
+        total = k.shape[0]
+        full_q = torch.zeros(total, q.shape[1], q.shape[2], dtype=q.dtype)
+        full_q[total - n:] = q[at:at + n]
+        outs.append(plain.causal_attention(full_q, k, v, window)[total - n:])
+        at += n
+    return torch.cat(outs)
+
+
+def attention_case(dtype, hq, hkv, d, page_size, kv_lens, q_lens, window, seed=7, kernel="attn_ref"):
+    g = torch.Generator().manual_seed(seed)
+    tables, num_pages = make_tables(kv_lens, page_size, seed + 1)
+    k_list = [torch.randn(n, hkv, d, generator=g).to(DT[dtype]) for n in kv_lens]
+    v_list = [torch.randn(n, hkv, d, generator=g).to(DT[dtype]) for n in kv_lens]
+    T = sum(q_lens)
+    q = torch.randn(T, hq, d, generator=g).to(DT[dtype])
+    return q, k_list, v_list, tables, num_pages
+
+
+def run_attention(kernel, q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, window, dtype):
+    k_pages = dev(paged(k_list, page_size, tables, num_pages, DT[dtype]))
+    v_pages = dev(paged(v_list, page_size, tables, num_pages, DT[dtype]))
+    q_start = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    tok_seq = torch.tensor([b for b, n in enumerate(q_lens) for _ in range(n)], dtype=torch.int32)
+    out = torch.empty_like(dev(q))
+    st = status()
+    scale = q.shape[-1] ** -0.5
+    getattr(ops(), kernel)(dev(q), k_pages, v_pages, out, dev(q_start), dev(torch.tensor(kv_lens, dtype=torch.int32)),
+                           dev(tok_seq), dev(table_tensor(tables)), scale, window or 0, st)
+    assert int(st.item()) == 0
+    return out
+
+
+ATTN_SHAPES = [
+    # hq, hkv, d, page, kv_lens, q_lens, window
+    (6, 3, 48, 8, [21, 14, 47], [21, 1, 7], None),      # whole prompt, one decoded token, a portion
+    (4, 1, 80, 16, [100, 3, 33], [2, 3, 1], None),      # ragged, two-token portion, head size 80
+    (8, 2, 128, 16, [300, 129], [1, 1], None),          # decode over hundreds of keys
+    (4, 2, 16, 4, [50, 9], [50, 2], 12),                # window shorter than the sequence
+    (5, 5, 32, 8, [64, 41], [5, 41], 8),                # window = page, no grouping
+    (16, 8, 64, 16, [17], [17], 1000),                  # window longer than the sequence
+]
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("case", ATTN_SHAPES)
+def test_attn_ref(dtype, case):
+    hq, hkv, d, page_size, kv_lens, q_lens, window = case
+    q, k_list, v_list, tables, num_pages = attention_case(dtype, hq, hkv, d, page_size, kv_lens, q_lens, window)
+    out = run_attention("attn_ref", q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, window, dtype)
+    want = reference_attention(q.double(), [k.double() for k in k_list], [v.double() for v in v_list], q_lens, window)
+    close(out, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("far", [0, 3, 250, 511])
+def test_attn_ref_finds_one_far_key(dtype, far):
+    """Among 512 random keys one is made to match the query strongly: the output must be that
+    key's value, whichever page it lies in (random weights alone would average everything)."""
+    hq, hkv, d, page_size = 4, 2, 64, 16
+    kv_lens, q_lens = [512], [1]
+    q, k_list, v_list, tables, num_pages = attention_case(dtype, hq, hkv, d, page_size, kv_lens, q_lens, None, seed=11)
+    q = (q.float() * 0 + 1.0).to(DT[dtype])
+    k_list[0] = (k_list[0].float() * 0.05).to(DT[dtype])
+    k_list[0][far] = 4.0  # score 4 * 64 / 8 = 32 against ~0 for the rest
+    out = run_attention("attn_ref", q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, None, dtype)
+    want = v_list[0][far].double()  # [hkv, d]
+    got = out.cpu().double().view(hq, d)
+    for h in range(hq):
+        assert float((got[h] - want[h // 2]).abs().max()) < 1e-2
+
+
+def test_attn_ref_window_edge_is_exact():
+    """The key just outside the window carries a huge value: any off-by-one shows at once."""
+    hq, hkv, d, page_size, window = 2, 1, 32, 8, 10
+    kv_lens, q_lens = [40], [40]
+    q, k_list, v_list, tables, num_pages = attention_case("float32", hq, hkv, d, page_size, kv_lens, q_lens, window, seed=13)
+    out0 = run_attention("attn_ref", q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, window, "float32")
+    want = reference_attention(q.double(), [k_list[0].double()], [v_list[0].double()], q_lens, window)
+    close(out0, want, "float32")
+    # poisoning a value outside every query's window from position 25 on changes nothing there
+    v_list[0][10] = 1e6
+    out1 = run_attention("attn_ref", q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, window, "float32")
+    assert torch.equal(out0[20:], out1[20:])      # queries 20.. see keys 11.. only
+    assert not torch.equal(out0[19], out1[19])    # query 19 still sees key 10
+
+
+def test_sample_greedy_ties_and_all_nan():
+    logits = torch.zeros(3, 1000)
+    logits[0, [400, 17, 900]] = 5.0
+    logits[1] = torch.linspace(-1, 1, 1000)
+    logits[2] = float("nan")
+    out = torch.empty(3, dtype=torch.int32, device="cuda")
+    st = status()
+    ops().sample(dev(logits), out, st)
+    assert out.tolist()[:2] == [17, 999]
+    assert int(st.item()) == 8
+
+
+@pytest.mark.parametrize("vocab", [331, 151936])
+def test_sample_matches_the_plain_generator(vocab):
+    g = torch.Generator().manual_seed(17)
+    R = 6
+    logits = torch.randn(R, vocab, generator=g) * 2
+    temps = [0.7, 0.0, 1.3, 0.7, 1.0, 0.2]
+    top_k = [0, 0, 40, 5, 1, 0]
+    keys = [3, 4, 5, 3, 99, 2 ** 40 + 7]
+    pos = [10, 11, 12, 11, 0, 40000]
+    seed = 1234
+    out = torch.empty(R, dtype=torch.int32, device="cuda")
+    st = status()
+    ops().sample(dev(logits), out, st, temperature=dev(torch.tensor(temps)), top_k=dev(torch.tensor(top_k, dtype=torch.int32)),
+                 request_key=dev(torch.tensor(keys, dtype=torch.int64)), position=dev(torch.tensor(pos, dtype=torch.int32)),
+                 seed=seed)
+    got = out.tolist()
+    want = [plain.sample_token(logits[r], temps[r], top_k[r], seed, keys[r], pos[r]) for r in range(R)]
+    assert got == want
+    assert got[1] == int(logits[1].argmax()) and got[4] == int(logits[4].argmax())  # greedy row, top-1 row
+    assert int(st.item()) == 0
+
+
+def test_sampling_follows_the_softmax_distribution():
+    """Many draws (different positions) from a small distribution: frequencies match softmax(l / T)."""
+    logits = torch.tensor([2.0, 1.0, 0.0, -1.0, 0.5])
+    T, n = 0.8, 20000
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    st = status()
+    ops().sample(dev(logits.repeat(n, 1)), out, st, temperature=dev(torch.full((n,), T)),
+                 request_key=dev(torch.zeros(n, dtype=torch.int64)),
+                 position=dev(torch.arange(n, dtype=torch.int32)), seed=5)
+    freq = torch.bincount(out.cpu().long(), minlength=5).double() / n
+    want = torch.softmax(logits.double() / T, 0)
+    assert float((freq - want).abs().max()) < 0.015  # ~4 standard errors at n = 20000

@@ -1,0 +1,337 @@
+"""Each part alone against its plain function, built with sizes of its own (no model around it),
+and a toy mixer with state of its own registered from here and run through the engine."""
+
+import json
+import os
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from harness import Replayer
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 1e-5, "bfloat16": 2e-2}
+
+
+def runtime(dtype, max_tokens=256, max_seqs=4):
+    from qwen3_from_scratch_b200.parts.base import Runtime
+    return Runtime(torch.device("cuda:0"), DT[dtype], max_tokens, max_seqs)
+
+
+def random_weights(part, dtype, seed=0):
+    """Random tensors for a part's specs: (device dict as the loader would give it, float64 CPU copies)."""
+    g = torch.Generator().manual_seed(seed)
+    dev, ref = {}, {}
+    for s in part.weight_specs():
+        if s.init == "one_plus_normal":
+            t = 1 + 0.1 * torch.randn(s.shape, generator=g)
+        else:
+            t = 0.05 * torch.randn(s.shape, generator=g)
+        stored = t.to(torch.float32 if s.kind == "vector" else DT[dtype])
+        dev[s.name] = stored.cuda()
+        ref[s.name] = stored.double()
+    return dev, ref
+
+
+def close(got, want, dtype):
+    got, want = got.double().cpu(), want.double()
+    err = float((got - want).abs().max()) / max(float(want.abs().max()), 1e-9)
+    assert err <= TOL[dtype], f"relative error {err:.3g} > {TOL[dtype]:g}"
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_norm_part(dtype):
+    from qwen3_from_scratch_b200.parts.base import PartSpec
+    from qwen3_from_scratch_b200.registry import create_part
+    part = create_part("norm", PartSpec("rms_norm", {"dim": 72, "eps": 1e-5}), name="n")
+    dev, ref = random_weights(part, dtype)
+    part.setup(runtime(dtype), dev)
+    g = torch.Generator().manual_seed(1)
+    stream = torch.randn(9, 72, generator=g)
+    delta = torch.randn(9, 72, generator=g).to(DT[dtype])
+    s = stream.cuda()
+    out = part.add_norm(s, delta.cuda())
+    close(s, stream.double() + delta.double(), "float32")
+    close(out, plain.rms_norm(stream.double() + delta.double(), ref["n.weight"], 1e-5), dtype)
+    x = torch.randn(5, 3, 72, generator=g).to(DT[dtype])
+    close(part.forward(x.cuda()), plain.rms_norm(x.double(), ref["n.weight"], 1e-5), dtype)
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("head_dim,rotary_dim", [(48, None), (64, 32)])
+def test_position_part(dtype, head_dim, rotary_dim):
+    from qwen3_from_scratch_b200.parts.base import PartSpec
+    from qwen3_from_scratch_b200.registry import create_part
+    part = create_part("position", PartSpec("rotary_neox", {"head_dim": head_dim, "theta": 12345.0,
+                                                            "max_positions": 5000, "rotary_dim": rotary_dim}))
+    part.setup(runtime(dtype), {})
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(20, 3, head_dim, generator=g).to(DT[dtype])
+    positions = torch.tensor([0, 1, 2, 3, 4, 100, 101, 999, 4000, 4999, 7, 7, 7, 50, 51, 52, 53, 54, 55, 56],
+                             dtype=torch.int32)
+    out = part.apply(x.cuda(), positions.cuda())
+    rot = rotary_dim or head_dim
+    cos, sin = plain.rope_cos_sin(positions, rot, 12345.0, dtype=torch.float64)
+    want = x.double().clone()
+    want[..., :rot] = plain.apply_rope(x.double()[..., :rot], cos, sin)
+    # the angle is a float32 product of position and frequency on both sides; sin/cos of an angle
+    # of thousands of radians carry its rounding (2^-24 * 5000 ~ 3e-4) into the result
+    tol = dict(TOL)
+    tol["float32"] = 5e-4
+    err = float((out.double().cpu() - want).abs().max()) / float(want.abs().max())
+    assert err <= tol[dtype], err
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_feed_forward_part(dtype):
+    from qwen3_from_scratch_b200.parts.base import PartSpec
+    from qwen3_from_scratch_b200.registry import create_part
+    part = create_part("feed_forward", PartSpec("swiglu", {"hidden_size": 56, "intermediate_size": 136}), name="f")
+    dev, ref = random_weights(part, dtype)
+    part.setup(runtime(dtype), dev)
+    x = (torch.randn(13, 56, generator=torch.Generator().manual_seed(3)) * 2).to(DT[dtype])
+    close(part.forward(x.cuda()), plain.swiglu_mlp(x.double(), ref, "f"), dtype)
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_embedding_and_head_parts(dtype):
+    from qwen3_from_scratch_b200.parts.base import PartSpec
+    from qwen3_from_scratch_b200.registry import create_part
+    emb = create_part("embedding", PartSpec("token_embedding", {"vocab_size": 211, "hidden_size": 40}), name="e")
+    head = create_part("head", PartSpec("lm_head", {"vocab_size": 211, "hidden_size": 40, "tied_to": "e.weight"}),
+                       name="h")
+    assert head.weight_specs() == []
+    dev, ref = random_weights(emb, dtype)
+    rt = runtime(dtype)
+    emb.setup(rt, dev)
+    head.setup(rt, dev)
+    ids = torch.tensor([0, 210, 5, 5, 17], dtype=torch.int32)
+    stream = emb.forward(ids.cuda())
+    assert stream.dtype == torch.float32
+    close(stream, ref["e.weight"][ids.long()], "float32")
+    x = torch.randn(4, 40, generator=torch.Generator().manual_seed(4)).to(DT[dtype])
+    logits = head.forward(x.cuda())
+    assert logits.dtype == torch.float32
+    close(logits, x.double() @ ref["e.weight"].t(), dtype)
+
+
+def mixer_context(part, rt, page_size, entries):
+    """A cache manager, storage and batch for one mixer alone (cache id 0)."""
+    from qwen3_from_scratch_b200.cache import CacheManager, layout_of
+    from qwen3_from_scratch_b200.cache.storage import CacheStorage
+    from qwen3_from_scratch_b200.engine.batch import BatchContext
+    layout = layout_of({0: part.cache_spec()})
+    manager = CacheManager(layout, page_size, 64, rt.max_seqs)
+    storage = CacheStorage(layout, page_size, rt.max_seqs, rt.device, rt.dtype)
+    return manager, storage, lambda: BatchContext(manager, storage, rt)
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("window", [None, 9])
+def test_attention_part_whole_then_in_portions(dtype, window):
+    from qwen3_from_scratch_b200.engine.batch import Entry
+    from qwen3_from_scratch_b200.parts.base import PartSpec
+    from qwen3_from_scratch_b200.registry import create_part
+    H, hq, hkv, d, eps, theta = 72, 6, 2, 48, 1e-5, 50000.0
+    spec = PartSpec("gqa_attention", {
+        "hidden_size": H, "num_heads": hq, "num_kv_heads": hkv, "head_dim": d, "qk_norm_eps": eps,
+        "window": window,
+        "position": PartSpec("rotary_neox", {"head_dim": d, "theta": theta, "max_positions": 4096})})
+    part = create_part("mixer", spec, name="a")
+    dev, ref = random_weights(part, dtype)
+    rt = runtime(dtype)
+    part.setup(rt, dev)
+    n = 45
+    x = torch.randn(n, H, generator=torch.Generator().manual_seed(5)).to(DT[dtype])
+    cfg = {"head_dim": d, "rms_norm_eps": eps, "rope_theta": theta}
+    want = plain.self_attention(x.double(), ref, "a", cfg, torch.arange(n), window)
+    manager, storage, new_ctx = mixer_context(part, rt, 8, None)
+    for cuts in ([n], [16, 1, 1, 7, 2, 18]):
+        manager.open("r")
+        got, at = [], 0
+        for c in cuts:
+            manager.reserve("r", at + c)
+            ctx = new_ctx().build([Entry("r", [0] * c)], vocab_size=1)
+            got.append(part.forward(x[at:at + c].cuda().contiguous(), ctx, 0, True).clone())
+            at += c
+            manager.advance("r", at)
+        manager.close("r")
+        close(torch.cat(got), want, dtype)
+    assert int(rt.status.item()) == 0
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_block_part(dtype):
+    from qwen3_from_scratch_b200.engine.batch import Entry
+    from qwen3_from_scratch_b200.parts.base import PartSpec
+    from qwen3_from_scratch_b200.registry import create_part
+    H, hq, hkv, d, inter, eps, theta = 48, 3, 1, 32, 100, 1e-6, 10000.0
+    norm = PartSpec("rms_norm", {"dim": H, "eps": eps})
+    block = create_part("block", PartSpec("pre_norm", {
+        "norm1": norm, "norm2": norm,
+        "mixer": PartSpec("gqa_attention", {
+            "hidden_size": H, "num_heads": hq, "num_kv_heads": hkv, "head_dim": d, "qk_norm_eps": eps,
+            "position": PartSpec("rotary_neox", {"head_dim": d, "theta": theta, "max_positions": 512})}),
+        "feed_forward": PartSpec("swiglu", {"hidden_size": H, "intermediate_size": inter}),
+        "names": {"norm1": "input_layernorm", "mixer": "self_attn", "norm2": "post_attention_layernorm",
+                  "feed_forward": "mlp"}}), name="model.layers.0")
+    dev, ref = random_weights(block, dtype)
+    rt = runtime(dtype)
+    block.setup(rt, dev)
+    n = 23
+    x = torch.randn(n, H, generator=torch.Generator().manual_seed(6))
+    cfg = {"head_dim": d, "rms_norm_eps": eps, "rope_theta": theta}
+    want = plain.decoder_layer(x.double(), ref, 0, cfg, torch.arange(n), None)
+    manager, storage, new_ctx = mixer_context(block.mixer, rt, 4, None)
+    manager.open("r")
+    manager.reserve("r", n)
+    ctx = new_ctx().build([Entry("r", [0] * n)], vocab_size=1)
+    stream = x.cuda()
+    pending = block.forward(stream, None, ctx, 0, True)
+    close(stream + pending.float(), want, dtype)
+
+
+# ---------------------------------------------------------------------- a toy mixer with state
+def register_toy():
+    """Registers, from the test, a mixer that keeps a decayed running sum per request in a state
+    slot, and an architecture that uses it in every second layer.  Nothing in the package changes."""
+    from qwen3_from_scratch_b200.config.model_config import ModelConfig
+    from qwen3_from_scratch_b200.parts.base import LayerCall, Mixer, ModelSpec, PartSpec, StateSpec, WeightSpec
+    from qwen3_from_scratch_b200.parts.linear import Linear
+    from qwen3_from_scratch_b200.registry import register_architecture, register_part, registered_architectures
+
+    if "ToyStateLM" in registered_architectures():
+        return
+
+    @register_part("mixer", "toy_running_sum")
+    class RunningSum(Mixer):
+        def __init__(self, name, hidden_size, decay):
+            super().__init__(name)
+            self.hidden_size, self.decay = hidden_size, decay
+
+        def weight_specs(self):
+            return [WeightSpec(f"{self.name}.proj.weight", (self.hidden_size, self.hidden_size))]
+
+        def cache_spec(self):
+            return StateSpec((self.hidden_size,), "float32")
+
+        def setup(self, rt, weights):
+            super().setup(rt, weights)
+            self.proj = Linear(weights[f"{self.name}.proj.weight"], rt.dtype, rt.max_tokens)
+
+        def forward(self, x, ctx, cache_id, write_cache):
+            state = ctx.state(cache_id)  # [slots, hidden] float32
+            slots = ctx.slot_ids.tolist()
+            sums = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+            at = 0
+            for row, n in enumerate(ctx.q_lens):
+                s = state[slots[row]]
+                for t in range(at, at + n):
+                    s = s * self.decay + x[t].float()
+                    sums[t] = s
+                state[slots[row]] = s
+                at += n
+            return self.proj(sums.to(x.dtype))
+
+    @dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        vocab_size: int = 0
+        width: int = 0
+        depth: int = 0
+        decay: float = 0.0
+
+        @classmethod
+        def from_dict(cls, data):
+            return cls(data["architectures"][0], data["vocab_size"], data["width"], data["depth"], data["decay"])
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], "vocab_size": self.vocab_size, "width": self.width,
+                    "depth": self.depth, "decay": self.decay}
+
+    @register_architecture("ToyStateLM", ToyConfig)
+    def toy_spec(cfg):
+        norm = PartSpec("rms_norm", {"dim": cfg.width, "eps": 1e-5})
+        ff = PartSpec("swiglu", {"hidden_size": cfg.width, "intermediate_size": 2 * cfg.width})
+        attn = PartSpec("gqa_attention", {"hidden_size": cfg.width, "num_heads": 2, "num_kv_heads": 1,
+                                          "head_dim": 16, "qk_norm_eps": None, "position": None})
+        toy = PartSpec("toy_running_sum", {"hidden_size": cfg.width, "decay": cfg.decay})
+        layers = [(f"layers.{i}", PartSpec("pre_norm", {"norm1": norm, "norm2": norm, "feed_forward": ff,
+                                                        "mixer": toy if i % 2 == 0 else attn}))
+                  for i in range(cfg.depth)]
+        # the run order names layer 0 twice (shared weights, a state of its own each time)
+        order = [LayerCall(i, i) for i in range(cfg.depth)] + [LayerCall(0, cfg.depth)]
+        return ModelSpec(embedding=("embed", PartSpec("token_embedding", {"vocab_size": cfg.vocab_size,
+                                                                          "hidden_size": cfg.width})),
+                         layers=layers, order=order, final_norm=("final_norm", norm),
+                         head=("head", PartSpec("lm_head", {"vocab_size": cfg.vocab_size, "hidden_size": cfg.width})),
+                         vocab_size=cfg.vocab_size, max_positions=4096)
+
+
+def toy_plain_logits(folder, ids):
+    """The toy model restated with plain torch in float64 (whole sequence, no cache, no slots)."""
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    from safetensors.torch import load_file
+    w = {k: v.double() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    x = w["embed.weight"][torch.tensor(ids)]
+    n = len(ids)
+
+    def layer(x, i):
+        p = f"layers.{i}"
+        h = plain.rms_norm(x, w[f"{p}.norm1.weight"], 1e-5)
+        if i % 2 == 0:
+            s, sums = torch.zeros(cfg["width"], dtype=torch.float64), []
+            for t in range(n):
+                s = s * cfg["decay"] + h[t]
+                sums.append(s)
+            a = torch.stack(sums) @ w[f"{p}.mixer.proj.weight"].t()
+        else:
+            q = (h @ w[f"{p}.mixer.q_proj.weight"].t()).view(n, 2, 16)
+            k = (h @ w[f"{p}.mixer.k_proj.weight"].t()).view(n, 1, 16)
+            v = (h @ w[f"{p}.mixer.v_proj.weight"].t()).view(n, 1, 16)
+            a = plain.causal_attention(q, k, v).reshape(n, -1) @ w[f"{p}.mixer.o_proj.weight"].t()
+        x = x + a
+        return x + plain.swiglu_mlp(plain.rms_norm(x, w[f"{p}.norm2.weight"], 1e-5), w, f"{p}.feed_forward")
+
+    for i in range(cfg["depth"]):
+        x = layer(x, i)
+    x = layer(x, 0)
+    return plain.rms_norm(x, w["final_norm.weight"], 1e-5) @ w["head.weight"].t()
+
+
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    register_toy()
+    from qwen3_from_scratch_b200.engine.session import Session
+    from qwen3_from_scratch_b200.registry import config_from_dict
+    from qwen3_from_scratch_b200.weights import write_random_model
+    cfg = config_from_dict({"architectures": ["ToyStateLM"], "vocab_size": 97, "width": 32, "depth": 3, "decay": 0.9})
+    folder = str(tmp_path / "toy")
+    write_random_model(folder, cfg, seed=3)
+    g = torch.Generator().manual_seed(9)
+    seqs = {"x": torch.randint(0, 97, (40,), generator=g).tolist(),
+            "y": torch.randint(0, 97, (23,), generator=g).tolist()}
+    want = {r: toy_plain_logits(folder, ids).float() for r, ids in seqs.items()}
+    session = Session(folder, dtype="float32", page_size=8, cache_tokens=256, max_seqs=4, max_step_tokens=128)
+    layout = session.model.cache_layout()
+    assert sorted(layout.states) == [0, 2, 3] and [g.cache_ids for g in layout.groups] == [[1]]
+    # whole
+    rep = Replayer(session, seqs)
+    rep.step([("x", 40), ("y", 23)])
+    whole = rep.result()
+    # in portions, the two requests interleaved: the state has to be carried from step to step
+    rep2 = Replayer(session, seqs)
+    for nx, ny in [(7, 1), (1, 9), (20, 2), (12, 11)]:
+        rep2.step([("x", nx), ("y", ny)])
+    cut = rep2.result()
+    for r in seqs:
+        scale = float(want[r].abs().max())
+        assert float((whole[r] - want[r]).abs().max()) <= 1e-5 * scale
+        assert float((cut[r] - want[r]).abs().max()) <= 1e-5 * scale
+    # a slot handed to a new request starts from zero state
+    rep3 = Replayer(session, {"z": seqs["y"]})
+    rep3.step([("z", 23)])
+    assert float((rep3.result()["z"] - want["y"]).abs().max()) <= 1e-5 * float(want["y"].abs().max())
