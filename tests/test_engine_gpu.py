@@ -35,15 +35,22 @@ def test_greedy_generation_equals_the_plain_implementation(tiny_folders, key, pa
     folder = tiny_folders[key]
     vocab = TINY[key][0]["vocab_size"]
     lengths = [5, 17, 31] if key == "a" else [1, 9, 33, 64, 100]
-    prompts = [random_tokens(vocab, n, 1 + i) for i, n in enumerate(lengths)]
+    # prompts whose plain top-2 logits stay apart at every step, so that equality of ids is a fair demand
+    prompts, expected = [], []
+    for i, n in enumerate(lengths):
+        for seed in range(1 + 100 * i, 100 + 100 * i):
+            prompt = random_tokens(vocab, n, seed)
+            want, margins = greedy_by_plain(folder, prompt, 16)
+            if min(margins) > 1e-3:
+                break
+        prompts.append(prompt)
+        expected.append(want)
     engine = SyncEngine(folder, dtype="float32", block_size=page, num_pages=128, max_num_seqs=4,
                         max_num_tokens=48, chunked_prefill_size=16)
     results, batch = engine.batch_generate(prompts, max_new_tokens=16, ignore_eos=True)
     assert batch.num_requests == len(prompts) and batch.total_tokens == 16 * len(prompts)
-    for prompt, r in zip(prompts, results):
-        want, margins = greedy_by_plain(folder, prompt, 16)
+    for want, r in zip(expected, results):
         assert r.finish_reason == "length"
-        assert min(margins) > 1e-4, "the plain top-2 are too close for an exact comparison"
         assert r.token_ids == want
     engine.session.manager.check()
     assert engine.session.manager.free_slots() == 4
