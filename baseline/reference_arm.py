@@ -1,0 +1,117 @@
+"""The reference arm of bench.py: the unmodified reference (installed under ``baseline/_ref`` with
+``pip install --no-deps --target baseline/_ref``) run through its own public classes, the same
+ones its ``SyncEngine`` wires together (inference/sync_engine.py:38-75): ``load_batch_config`` ->
+``ModelWorker`` (model + paged cache + sampler) -> ``Scheduler`` + ``SchedulerDriver`` ->
+``driver.step``.  Its ``SyncEngine`` itself cannot be constructed offline because it loads a
+HuggingFace tokenizer from the model folder; everything below the tokenizer is the stock path,
+with ``self_attn: paged_attn`` as in its example configuration.  None of this repository's
+models, kernels or engine is on this path: only the random-weights folder writer (the
+checkpoint format is the same) and the timing harness.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "baseline", "_ref")
+
+
+def unavailable(why: str) -> int:
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def run_reference(args, config: dict, page: int) -> int:
+    if not os.path.isdir(os.path.join(REF, "qwen3_from_scratch")):
+        return unavailable("baseline/_ref is not installed (pip install --no-index --no-deps --target baseline/_ref)")
+    try:
+        import torch
+    except ImportError as e:  # pragma: no cover
+        return unavailable(f"torch is not importable: {e}")
+    if not torch.cuda.is_available():
+        return unavailable("no CUDA GPU visible")
+    sys.path.insert(0, REF)
+    try:
+        from qwen3_from_scratch.factory import load_batch_config
+        from qwen3_from_scratch.inference.model_worker import ModelWorker
+        from qwen3_from_scratch.inference.scheduler import Scheduler, SchedulerConfig
+        from qwen3_from_scratch.inference.scheduler_driver import SchedulerDriver
+        from qwen3_from_scratch.inference.sequence import Sequence
+    except Exception as e:  # noqa: BLE001 - whatever stops the import is the reason
+        return unavailable(f"the reference does not import here: {type(e).__name__}: {e}")
+
+    from qwen3_from_scratch_b200.registry import config_from_dict
+    from qwen3_from_scratch_b200.weights import write_random_model
+
+    layers = args.layers or config["num_hidden_layers"]
+    cfg = dict(config, num_hidden_layers=layers)
+    batch, context, steps, warmup = args.batch, args.context, args.steps, args.warmup
+    try:
+        with tempfile.TemporaryDirectory(prefix="q3b200-ref-") as folder:
+            write_random_model(folder, config_from_dict(cfg), seed=0)
+            yaml_path = os.path.join(folder, "batch.yaml")
+            with open(yaml_path, "w") as f:
+                f.write(
+                    "generation:\n  temperature: 0.0\n  top_k: 0\n  max_new_tokens: 100\n"
+                    f"scheduler:\n  max_num_seqs: {max(batch, 1)}\n  max_num_tokens: 4096\n  block_size: {page}\n"
+                    "  gpu_utilization: 0.5\n  enable_prefix_cache: false\n  chunked_prefill_size: 2048\n"
+                    "kv_cache_dtype: bfloat16\n"
+                    f"models:\n  - name: bench\n    path: {folder}\n    device: cuda\n    dtype: bfloat16\n"
+                    f"    max_len: {context}\n    components:\n      self_attn: paged_attn\n")
+            bc = load_batch_config(yaml_path)
+            worker = ModelWorker(bc, "bench")
+            worker.init_context()
+        driver = SchedulerDriver(
+            Scheduler(SchedulerConfig(bc.scheduler.max_num_seqs, bc.scheduler.max_num_tokens, bc.scheduler.block_size,
+                                      worker.kv_cache.num_pages, enable_prefix_cache=False,
+                                      chunked_prefill_size=bc.scheduler.chunked_prefill_size),
+                      check_seq_finish_func=lambda seq: seq.generated_lens >= seq.max_new_tokens),
+            worker.forward)
+        g = torch.Generator().manual_seed(1234 + batch)
+        total_new = steps + warmup
+        seqs = []
+        for _ in range(batch):
+            prompt = torch.randint(0, cfg["vocab_size"], (context - total_new,), generator=g).tolist()
+            seq = Sequence(prompt, max_new_tokens=total_new + 8, ignore_eos=True)
+            if not driver.add_request(seq):
+                return unavailable("the reference's scheduler refused the request (cache pool too small)")
+            seqs.append(seq)
+        guard = 0
+        while any(s.is_prefill or s.last_token_id == -1 for s in seqs):
+            driver.step([])
+            guard += 1
+            if guard > 10000:
+                return unavailable("the reference did not finish its prompts in 10000 steps")
+        for _ in range(warmup):
+            driver.step([])
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        start.record()
+        for _ in range(steps):
+            planned = driver.step([])
+            assert len(planned) == batch
+        end.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        device = start.elapsed_time(end) / 1e3
+    except Exception as e:  # noqa: BLE001
+        return unavailable(f"the reference failed on this workload: {type(e).__name__}: {str(e)[:300]}")
+    value = batch * steps / device
+    print(json.dumps({
+        "metric": "decode tok/s at batch 8 (Qwen3-0.6B sizes, context 4096, bf16, random weights)",
+        "impl": "reference", "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": device / steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"model": "Qwen3-0.6B sizes, random weights", "global_batch": batch, "seq_len": context,
+                   "parallelism": "single GPU", "layers": layers, "page_size": page,
+                   "path": "load_batch_config -> ModelWorker -> Scheduler/SchedulerDriver.step (paged_attn)"},
+        "e2e": {"value": batch * steps / wall, "unit": "tokens/s", "h2d_bytes_per_step": None,
+                "d2h_bytes_per_step": batch * 8},
+    }))
+    return 0

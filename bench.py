@@ -1,0 +1,302 @@
+"""Decode and prefill throughput of the engine on one B200, with roofline fractions.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one decode step of the whole batch.  The default run uses the layer sizes of
+Qwen3-0.6B (28 layers, hidden 1024, 16/8 heads of 128, intermediate 3072, vocabulary 151936,
+tied head) with seeded random weights, a batch of 8 and a context of 4096 tokens per sequence,
+pages of 16 tokens.  It prints one JSON line:
+
+  value      decoded tokens per second, timed on the device (CUDA events) over exactly K steps
+  e2e        the same through the Python entry point (``SyncEngine.step``): every step copies its
+             token ids and block tables from pinned host memory and reads the sampled ids back
+  prefill    one step over a 2,048-token prompt: tokens/s and flops / time / bf16 peak
+  roofline   bytes a decode step has to read (every weight once + the keys and values of the live
+             requests) / its time, against the measured copy bandwidth
+  points     decode tokens/s at batch 1 and 64
+
+Peaks come from MEASURED_PEAKS.json beside this file when it exists, else from the fallback
+figures (6.65 TB/s, 1.59 PFLOP/s).  ``--impl reference`` runs the unmodified reference from
+``baseline/_ref`` through its own scheduler and worker for the same metric.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: Qwen3-0.6B layer sizes
+CONFIG = dict(
+    architectures=["Qwen3ForCausalLM"], vocab_size=151936, hidden_size=1024, hidden_act="silu",
+    num_hidden_layers=28, max_position_embeddings=40960, num_key_value_heads=8, num_attention_heads=16,
+    head_dim=128, intermediate_size=3072, rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=True)
+FULL_LAYERS = 28
+CONTEXT = 4096
+PAGE = 16
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                data = json.load(f)
+            out = {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data["bf16_tflops"]), "source": "measured"}
+            if "bf16_tflops_sustained" in data:
+                out["bf16_tflops_sustained"] = float(data["bf16_tflops_sustained"])
+            return out
+        except (OSError, ValueError, KeyError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, maxes, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                clocks.append(float(s[0]))
+                maxes.append(float(s[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, s[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None,
+                "sm_max_mhz": max(maxes) if maxes else None, "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def model_numbers(cfg, layers):
+    """Bytes of weights a decode step reads, bytes of cache per token, flops of a prefill."""
+    H, D = cfg["hidden_size"], cfg["head_dim"]
+    hq, hkv, inter, V = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["intermediate_size"], cfg["vocab_size"]
+    per_layer = (hq + 2 * hkv) * D * H + H * hq * D + 3 * H * inter
+    head = V * H  # read once as the output head (tied or not); embedding rows are negligible
+    weight_bytes = 2 * (layers * per_layer + head) + 4 * (layers * (2 * H + 2 * D) + H)
+    kv_bytes_per_token = 2 * layers * hkv * D * 2
+
+    def prefill_flops(T):
+        linear = 2 * T * layers * per_layer + 2 * V * H  # logits at one position
+        attention = layers * 4 * hq * D * T * (T + 1) // 2
+        return linear + attention
+
+    return weight_bytes, kv_bytes_per_token, prefill_flops
+
+
+def time_device_steps(fn, steps, warmup):
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / 1e3
+
+
+def decode_bench(engine, batch, context, steps, warmup, vocab):
+    """Puts ``batch`` requests of ``context - steps - warmup`` tokens in the cache through the entry
+    point, then measures (a) K engine steps end to end and (b) K replays of the last step's batch
+    on the device alone.  Returns (device seconds, e2e seconds, launches per step, h2d, d2h bytes)."""
+    import torch
+
+    from qwen3_from_scratch_b200.engine.request import RequestStatus, SamplingParams
+    from qwen3_from_scratch_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(1234 + batch)
+    total_new = steps + warmup  # the last timed step brings every request to exactly `context` tokens
+    prompt_len = context - total_new
+    reqs = []
+    for _ in range(batch):
+        prompt = torch.randint(0, vocab, (prompt_len,), generator=g).tolist()
+        reqs.append(engine.add_request(prompt, params=SamplingParams(max_new_tokens=total_new + 8, ignore_eos=True)))
+    while any(not r.is_decoding for r in reqs):
+        engine.step()
+    # (a) end to end through SyncEngine.step: host ids in (pinned copy), sampled ids out, every step
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    h2d = 0
+    for _ in range(steps):
+        plan = engine.step()
+        assert len(plan) == batch and all(s.num_tokens == 1 for s in plan)
+        h2d += engine.session.last_context.h2d_bytes
+    torch.cuda.synchronize()
+    e2e_seconds = time.perf_counter() - t0
+    d2h = batch * 4 + 4  # sampled ids and the status word
+    # (b) the same step on the device alone: replay the last batch (same lengths, same pages)
+    ctx = engine.session.last_context
+    model, sampler = engine.session.model, engine.sampler
+    zeros = [0.0] * batch
+
+    def one_step():
+        logits = model.step(ctx)
+        sampler.sample(logits, zeros, [0] * batch, [0] * batch, [0] * batch, [0] * batch)
+
+    before = ops.launch_count()
+    one_step()
+    launches = ops.launch_count() - before
+    device_seconds = time_device_steps(one_step, steps, warmup)
+    for r in reqs:
+        engine.abort(r)
+    return device_seconds, e2e_seconds, launches, h2d // steps, d2h
+
+
+def prefill_bench(engine, tokens, steps, warmup, vocab):
+    import torch
+
+    from qwen3_from_scratch_b200.engine.batch import BatchContext, Entry
+    g = torch.Generator().manual_seed(99)
+    prompt = torch.randint(0, vocab, (tokens,), generator=g).tolist()
+    session = engine.session
+    session.open("prefill-bench")
+    session.manager.reserve("prefill-bench", tokens)
+    ctx = BatchContext(session.manager, session.storage, session.rt).build(
+        [Entry("prefill-bench", prompt, (tokens - 1,))], session.vocab_size)
+    seconds = time_device_steps(lambda: session.model.step(ctx), steps, warmup)
+    session.end("prefill-bench")
+    return seconds / steps
+
+
+def ours(args):
+    import torch
+
+    from qwen3_from_scratch_b200.engine.engine import SyncEngine
+    from qwen3_from_scratch_b200.registry import config_from_dict
+    from qwen3_from_scratch_b200.weights import write_random_model
+
+    peaks = load_peaks()
+    cfg = dict(CONFIG)
+    layers = args.layers or FULL_LAYERS
+    cfg["num_hidden_layers"] = layers
+    weight_bytes, kv_per_token, prefill_flops = model_numbers(cfg, layers)
+    batches = sorted({args.batch, 1, 64})
+    with tempfile.TemporaryDirectory(prefix="q3b200-bench-") as folder:
+        t0 = time.time()
+        write_random_model(folder, config_from_dict(cfg), seed=0)
+        print(f"[bench] wrote random {layers}-layer model in {time.time() - t0:.1f}s", file=sys.stderr, flush=True)
+        pool_tokens = max(batches) * args.context + PREFILL_TOKENS + 64 * PAGE
+        engine = SyncEngine(folder, dtype="bfloat16", block_size=PAGE, num_pages=pool_tokens // PAGE,
+                            max_num_seqs=max(batches), max_num_tokens=4096, chunked_prefill_size=2048)
+    vocab = cfg["vocab_size"]
+    results = {}
+    clocks = None
+    for b in batches:
+        sampler = ClockSampler() if b == args.batch else None
+        if sampler:
+            sampler.start()
+        dev_s, e2e_s, launches, h2d, d2h = decode_bench(engine, b, args.context, args.steps, args.warmup, vocab)
+        if sampler:
+            clocks = sampler.stop()
+        results[b] = dict(device=dev_s, e2e=e2e_s, launches=launches, h2d=h2d, d2h=d2h)
+        print(f"[bench] batch {b}: {b * args.steps / dev_s:.0f} tok/s on the device, "
+              f"{b * args.steps / e2e_s:.0f} tok/s end to end", file=sys.stderr, flush=True)
+    prefill_s = prefill_bench(engine, PREFILL_TOKENS, max(3, min(args.steps, 10)), args.warmup, vocab)
+    main = results[args.batch]
+    step_s = main["device"] / args.steps
+    step_bytes = weight_bytes + args.batch * args.context * kv_per_token
+    achieved = step_bytes / step_s / 1e9
+    flops = prefill_flops(PREFILL_TOKENS)
+    line = {
+        "metric": "decode tok/s at batch 8 (Qwen3-0.6B sizes, context 4096, bf16, random weights)",
+        "value": args.batch * args.steps / main["device"], "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {
+            "model": "Qwen3-0.6B sizes, random weights", "global_batch": args.batch, "seq_len": args.context,
+            "parallelism": "single GPU", "layers": layers, "layers_full": FULL_LAYERS,
+            "hidden_size": cfg["hidden_size"], "num_attention_heads": cfg["num_attention_heads"],
+            "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+            "intermediate_size": cfg["intermediate_size"], "vocab_size": vocab, "tie_word_embeddings": True,
+            "page_size": PAGE, "prefill_tokens": PREFILL_TOKENS, "l2": "inputs larger than L2 (weights + cache)",
+            "peaks": peaks["source"],
+        },
+        "e2e": {"value": args.batch * args.steps / main["e2e"], "unit": "tokens/s",
+                "h2d_bytes_per_step": main["h2d"], "d2h_bytes_per_step": main["d2h"]},
+        "gpu_launches": main["launches"] * args.steps,
+        "prefill": {"value": PREFILL_TOKENS / prefill_s, "tokens": PREFILL_TOKENS, "ms": prefill_s * 1e3,
+                    "frac": flops / prefill_s / (peaks["bf16_tflops"] * 1e12)},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / peaks["hbm_gbs"]},
+        "points": {f"decode_b{b}": b * args.steps / results[b]["device"] for b in batches if b != args.batch},
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def main() -> int:
+    p = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=64)
+    p.add_argument("--warmup", type=int, default=8)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--context", type=int, default=CONTEXT)
+    p.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in the output)")
+    args = p.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run with --gpus 1")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        from baseline.reference_arm import run_reference
+        return run_reference(args, CONFIG, PAGE)
+    return ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

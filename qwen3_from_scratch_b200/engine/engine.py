@@ -213,6 +213,10 @@ class SyncEngine:
                 f"{self.session.max_positions} positions")
         return req
 
+    def abort(self, req: Request) -> None:
+        self.scheduler.abort(req)
+        self.session.after_step()
+
     def step(self) -> List[ScheduledRequest]:
         """One scheduling round and one model step.  Returns what ran (with tokens appended)."""
         plan = self.scheduler.schedule()

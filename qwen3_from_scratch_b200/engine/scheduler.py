@@ -157,6 +157,16 @@ class Scheduler:
         self.num_preemptions += 1
         self.waiting.appendleft(req)
 
+    def abort(self, req: Request) -> None:
+        """Takes a request out wherever it is and gives back what it holds."""
+        if req in self.running:
+            self.running.remove(req)
+            self.cache.close(req)
+        elif req in self.waiting:
+            self.waiting.remove(req)
+        req.status = RequestStatus.FINISHED
+        req.finish_reason = req.finish_reason or "abort"
+
     # ------------------------------------------------------------------ after the step
     def post_process(self, plan: List[ScheduledRequest], sampled: List[Optional[int]]) -> List[Request]:
         """``sampled[i]``: the token drawn for plan[i] (ignored unless it wanted logits).

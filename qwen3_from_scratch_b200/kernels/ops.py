@@ -53,6 +53,12 @@ _SIGNATURES = {
     "q3_attn_ref": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                     _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
                     _c_void_p, _c_void_p],
+    "q3_attn_decode": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                       _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
+                       _c_void_p, _c_void_p],
+    "q3_attn_prefill": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p,
+                        _c_void_p],
     "q3_swiglu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     "q3_sample": [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ull,
                   _c_void_p, _c_void_p, _c_void_p],
@@ -74,8 +80,31 @@ def library() -> ctypes.CDLL:
                     fn = getattr(lib, name)
                     fn.argtypes = argtypes
                     fn.restype = _c_int
-                _lib, _lib_path = lib, path
+                _lib, _lib_path = _Counting(lib), path
     return _lib
+
+
+class _Counting:
+    """The library with every launcher call counted (the benchmark reports launches per step)."""
+
+    def __init__(self, lib):
+        self._lib = lib
+        self.calls = 0
+
+    def __getattr__(self, name):
+        fn = getattr(self._lib, name)
+
+        def counted(*args):
+            self.calls += 1
+            return fn(*args)
+
+        setattr(self, name, counted)
+        return counted
+
+
+def launch_count() -> int:
+    """Kernel launches made through this module so far."""
+    return library().calls
 
 
 def library_path() -> Optional[str]:
@@ -318,3 +347,102 @@ def rope(x: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, positions: to
         positions.data_ptr(), positions.data_ptr(), None, 1, 1, None, None, 0, out.data_ptr(), 0,
         status.data_ptr(), _stream())
     _done("rope", code, f"head_dim {d}, rotary_dim {rotary_dim}")
+
+
+# ------------------------------------------------------------------ fast bfloat16 attention
+MAX_DECODE_SPLITS = 32
+_DECODE_TARGET_BLOCKS = 592  # about two resident blocks per SM on 148 SMs, twice over
+
+
+def fast_attention_takes(dtype: torch.dtype, num_q_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    """Whether the tensor-core kernels take this shape (else the plain kernel runs)."""
+    return (dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
+            and num_q_heads % num_kv_heads == 0 and num_q_heads // num_kv_heads <= 16)
+
+
+def decode_splits(num_seqs: int, num_kv_heads: int, max_kv_len: int, window: int) -> int:
+    """How many ranges a sequence's keys are cut into: enough blocks to fill the GPU, at least
+    256 keys per range."""
+    span = min(max_kv_len, window) if window and window > 0 else max_kv_len
+    by_work = max(1, span // 256)
+    want = -(-_DECODE_TARGET_BLOCKS // max(1, num_seqs * num_kv_heads))
+    return max(1, min(want, by_work, MAX_DECODE_SPLITS))
+
+
+def decode_partial_numel(num_seqs: int, num_q_heads: int, head_dim: int) -> int:
+    return num_seqs * num_q_heads * MAX_DECODE_SPLITS * (head_dim + 2)
+
+
+def _attn_common(name, q, k_pages, v_pages, out, q_start, kv_len, block_table):
+    _check(f"{name}.q", q, torch.bfloat16)
+    _check(f"{name}.out", out, torch.bfloat16)
+    _check(f"{name}.k_pages", k_pages, torch.bfloat16)
+    _check(f"{name}.v_pages", v_pages, torch.bfloat16)
+    for nm, t in (("q_start", q_start), ("kv_len", kv_len), ("block_table", block_table)):
+        _check(f"{name}.{nm}", t, torch.int32)
+    T, Hq, D = q.shape
+    num_pages, Hkv, page_size, d = k_pages.shape
+    if d != D or v_pages.shape != k_pages.shape or out.numel() != q.numel() or block_table.dim() != 2:
+        raise KernelError(f"{name}: q {tuple(q.shape)}, pages {tuple(k_pages.shape)}, out {tuple(out.shape)}")
+    return T, Hq, D, num_pages, Hkv, page_size
+
+
+def attn_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
+                partial: Optional[torch.Tensor], q_start: torch.Tensor, kv_len: torch.Tensor,
+                block_table: torch.Tensor, num_seqs: int, scale: float, window: int, num_splits: int,
+                status: torch.Tensor) -> None:
+    """Split-KV tensor-core attention for the first ``num_seqs`` rows, one query token each."""
+    T, Hq, D, num_pages, Hkv, page_size = _attn_common("attn_decode", q, k_pages, v_pages, out, q_start, kv_len,
+                                                        block_table)
+    if num_seqs > kv_len.numel() or num_seqs > block_table.shape[0]:
+        raise KernelError(f"attn_decode: {num_seqs} sequences, {kv_len.numel()} lengths")
+    if num_splits > 1:
+        if partial is None:
+            raise KernelError("attn_decode: more than one split needs scratch memory")
+        _check("attn_decode.partial", partial, torch.float32)
+        if partial.numel() < num_seqs * Hq * num_splits * (D + 2):
+            raise KernelError(f"attn_decode: scratch of {partial.numel()} floats is too small for {num_seqs} "
+                              f"sequences x {Hq} heads x {num_splits} splits")
+    code = library().q3_attn_decode(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(),
+                                    _ptr(partial), q_start.data_ptr(), kv_len.data_ptr(), block_table.data_ptr(),
+                                    block_table.shape[1], page_size, num_pages, num_seqs, Hq, Hkv, D, float(scale),
+                                    int(window), int(num_splits), status.data_ptr(), _stream())
+    _done("attn_decode", code, f"heads {Hq}/{Hkv}, head_dim {D}")
+
+
+def attn_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
+                 q_start: torch.Tensor, kv_len: torch.Tensor, block_table: torch.Tensor, num_seqs: int,
+                 max_q_len: int, scale: float, window: int, status: torch.Tensor) -> None:
+    """Tensor-core attention for ``num_seqs`` rows of any query length (q_start has num_seqs + 1 entries)."""
+    T, Hq, D, num_pages, Hkv, page_size = _attn_common("attn_prefill", q, k_pages, v_pages, out, q_start, kv_len,
+                                                        block_table)
+    if q_start.numel() < num_seqs + 1 or kv_len.numel() < num_seqs or block_table.shape[0] < num_seqs:
+        raise KernelError(f"attn_prefill: {num_seqs} sequences, q_start {q_start.numel()}, kv_len {kv_len.numel()}")
+    code = library().q3_attn_prefill(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(),
+                                     q_start.data_ptr(), kv_len.data_ptr(), block_table.data_ptr(),
+                                     block_table.shape[1], page_size, num_pages, num_seqs, int(max_q_len), Hq, Hkv, D,
+                                     float(scale), int(window), status.data_ptr(), _stream())
+    _done("attn_prefill", code, f"heads {Hq}/{Hkv}, head_dim {D}")
+
+
+def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
+                    q_start: torch.Tensor, kv_len: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
+                    num_seqs: int, num_decode: int, max_q_len: int, max_kv_len: int, scale: float, window: int,
+                    status: torch.Tensor, partial: Optional[torch.Tensor] = None) -> None:
+    """Causal attention of a mixed batch over the pages: rows [0, num_decode) bring one token each and
+    go to the split-KV decode kernel, the rest to the portion kernel; shapes the tensor-core kernels
+    do not take (and float32) go to the plain kernel."""
+    T, Hq, D = q.shape
+    Hkv = k_pages.shape[1]
+    if not fast_attention_takes(q.dtype, Hq, Hkv, D):
+        attn_ref(q, k_pages, v_pages, out, q_start, kv_len, tok_seq, block_table, scale, window, status)
+        return
+    if num_decode > 0:
+        splits = decode_splits(num_decode, Hkv, max_kv_len, window)
+        if partial is None or partial.numel() < num_decode * Hq * splits * (D + 2):
+            splits = 1 if partial is None else max(1, partial.numel() // (num_decode * Hq * (D + 2)))
+        attn_decode(q, k_pages, v_pages, out, partial, q_start, kv_len, block_table, num_decode, scale, window,
+                    splits, status)
+    if num_seqs > num_decode:
+        attn_prefill(q, k_pages, v_pages, out, q_start[num_decode:], kv_len[num_decode:], block_table[num_decode:],
+                     num_seqs - num_decode, max_q_len, scale, window, status)

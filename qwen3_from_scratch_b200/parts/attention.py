@@ -61,16 +61,20 @@ class GQAAttention(Mixer):
         dtype = torch.float32 if torch.float32 in (q.dtype, k.dtype, v.dtype) else q.dtype
         merged = torch.cat([q.to(dtype), k.to(dtype), v.to(dtype)], dim=0)  # rows ordered q, k, v
         del q, k, v
-        self.qkv = Linear(merged, rt.dtype, rt.max_tokens)
-        self.o_proj = Linear(weights.pop(f"{self.name}.o_proj.weight"), rt.dtype, rt.max_tokens)
+        self.qkv = Linear(merged, rt, tag="attn.qkv")
+        self.o_proj = Linear(weights.pop(f"{self.name}.o_proj.weight"), rt, tag="attn.o_proj")
         self.q_norm_weight = self.k_norm_weight = None
         if self.qk_norm_eps is not None:
             self.q_norm_weight = weights[f"{self.name}.q_norm.weight"]
             self.k_norm_weight = weights[f"{self.name}.k_norm.weight"]
         if self.position is not None:
             self.position.setup(rt, weights)
-        self._q = rt.empty(rt.max_tokens, self.num_heads, self.head_dim)
-        self._o = rt.empty(rt.max_tokens, self.num_heads, self.head_dim)
+        self._q = rt.shared("attn.q", rt.max_tokens, self.num_heads, self.head_dim)
+        self._o = rt.shared("attn.o", rt.max_tokens, self.num_heads, self.head_dim)
+        self._partial = None
+        if ops.fast_attention_takes(rt.dtype, self.num_heads, self.num_kv_heads, self.head_dim):
+            self._partial = rt.shared("attn.partial", ops.decode_partial_numel(rt.max_seqs, self.num_heads,
+                                                                               self.head_dim), dtype=torch.float32)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
         T = x.shape[0]
@@ -105,5 +109,6 @@ class GQAAttention(Mixer):
     def attend(self, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, table: torch.Tensor,
                ctx: StepContext, out: torch.Tensor) -> None:
         """Causal attention of this step's queries over the pages (keys of this step included)."""
-        ops.attn_ref(q, k_pages, v_pages, out, ctx.q_start, ctx.kv_len, ctx.tok_seq, table, self.scale,
-                     self.window or 0, self.rt.status)
+        ops.paged_attention(q, k_pages, v_pages, out, ctx.q_start, ctx.kv_len, ctx.tok_seq, table, ctx.num_seqs,
+                            ctx.num_decode, ctx.max_q_len, ctx.max_kv_len, self.scale, self.window or 0,
+                            self.rt.status, self._partial)

@@ -106,6 +106,18 @@ class Runtime:
     def empty(self, *shape: int, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         return torch.empty(*shape, dtype=dtype or self.dtype, device=self.device)
 
+    def shared(self, tag: str, *shape: int, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """A scratch buffer that every part asking with the same tag, shape and dtype gets.
+        Layers run one after the other, so the buffers of one role (the normed activations,
+        the merged QKV product, ...) can be the same memory in every layer.  A tag's buffer
+        must be consumed before the same role writes it again."""
+        if not hasattr(self, "_shared"):
+            self._shared = {}
+        key = (tag, tuple(shape), dtype or self.dtype)
+        if key not in self._shared:
+            self._shared[key] = self.empty(*shape, dtype=dtype)
+        return self._shared[key]
+
 
 class StepContext:
     """Everything the parts need to know about the batch of one step.

@@ -29,7 +29,7 @@ class TokenEmbedding(Part):
     def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
         super().setup(rt, weights)
         self.weight = weights[f"{self.name}.weight"]
-        self._stream = torch.empty(rt.max_tokens, self.hidden_size, dtype=torch.float32, device=rt.device)
+        self._stream = rt.shared("stream", rt.max_tokens, self.hidden_size, dtype=torch.float32)
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         stream = self._stream[: token_ids.numel()]
@@ -54,7 +54,7 @@ class LMHead(Part):
     def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
         super().setup(rt, weights)
         weight = weights[self.tied_to] if self.tied_to else weights[f"{self.name}.weight"]
-        self.proj = Linear(weight, rt.dtype, None, out_dtype=torch.float32)
+        self.proj = Linear(weight, rt, out_dtype=torch.float32, reuse_output=False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.proj(x)

@@ -14,29 +14,32 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
+from .base import Runtime
 
 
 class Linear:
     """Not a registered part of its own: mixers and feed-forwards own their projections."""
 
-    def __init__(self, weight: torch.Tensor, compute_dtype: torch.dtype, max_rows: Optional[int],
-                 out_dtype: Optional[torch.dtype] = None):
-        """``max_rows``: rows of the reused output buffer; None allocates the output at every call
-        (for the head, whose row count is what the caller wants and whose rows are a vocabulary wide)."""
+    def __init__(self, weight: torch.Tensor, rt: Runtime, tag: Optional[str] = None,
+                 out_dtype: Optional[torch.dtype] = None, reuse_output: bool = True):
+        """``tag``: role of the output buffer, shared between layers (see ``Runtime.shared``);
+        None gives this projection a buffer of its own.  ``reuse_output=False`` allocates the
+        output at every call (the head, whose rows are a vocabulary wide and as many as asked for)."""
         if weight.dim() != 2:
             raise ValueError(f"a projection weight is 2-D, got {tuple(weight.shape)}")
         self.weight = weight.contiguous()
         self.out_features, self.in_features = weight.shape
-        self.compute_dtype = compute_dtype
-        self.out_dtype = out_dtype or compute_dtype
+        self.out_dtype = out_dtype or rt.dtype
         self.full_precision = weight.dtype == torch.float32
-        self.max_rows = max_rows
+        self.max_rows = rt.max_tokens if reuse_output else None
         self._out = self._out32 = None
-        if max_rows is not None:
-            self._out = torch.empty(max_rows, self.out_features, dtype=self.out_dtype, device=weight.device)
+        if reuse_output:
+            shape = (rt.max_tokens, self.out_features)
+            make = (lambda t, dt: rt.shared(f"{tag}.{t}", *shape, dtype=dt)) if tag else (
+                lambda t, dt: rt.empty(*shape, dtype=dt))
+            self._out = make("out", self.out_dtype)
             if self.full_precision:
-                self._out32 = self._out if self.out_dtype == torch.float32 else torch.empty(
-                    max_rows, self.out_features, dtype=torch.float32, device=weight.device)
+                self._out32 = self._out if self.out_dtype == torch.float32 else make("out32", torch.float32)
         self._weight_t = self.weight.t()
 
     def _buffer(self, which: str, rows: int, dtype: torch.dtype) -> torch.Tensor:

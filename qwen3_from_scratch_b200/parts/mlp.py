@@ -35,9 +35,9 @@ class SwiGLU(FeedForward):
         dtype = torch.float32 if torch.float32 in (gate.dtype, up.dtype) else gate.dtype
         merged = torch.cat([gate.to(dtype), up.to(dtype)], dim=0)
         del gate, up
-        self.gate_up = Linear(merged, rt.dtype, rt.max_tokens)
-        self.down = Linear(weights.pop(f"{self.name}.down_proj.weight"), rt.dtype, rt.max_tokens)
-        self._act = rt.empty(rt.max_tokens, self.intermediate_size)
+        self.gate_up = Linear(merged, rt, tag="ffn.gate_up")
+        self.down = Linear(weights.pop(f"{self.name}.down_proj.weight"), rt, tag="ffn.down")
+        self._act = rt.shared("ffn.act", rt.max_tokens, self.intermediate_size)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         gu = self.gate_up(x)

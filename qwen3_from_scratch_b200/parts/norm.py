@@ -27,7 +27,7 @@ class RMSNorm(Norm):
     def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
         super().setup(rt, weights)
         self.weight = weights[f"{self.name}.weight"]
-        self._out = rt.empty(rt.max_tokens, self.dim)
+        self._out = rt.shared("normed", rt.max_tokens, self.dim)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         out = torch.empty_like(x)

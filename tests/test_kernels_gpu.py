@@ -291,6 +291,127 @@ def test_attn_ref_window_edge_is_exact():
     assert not torch.equal(out0[19], out1[19])    # query 19 still sees key 10
 
 
+def run_fast(q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, window, splits=None):
+    """The tensor-core kernels through the dispatcher (or the decode kernel with a forced split count).
+    Unused slots of the pages hold NaN: anything read past a sequence's keys poisons the result."""
+    o = ops()
+    k_pages = dev(paged(k_list, page_size, tables, num_pages, torch.bfloat16))
+    v_pages = dev(paged(v_list, page_size, tables, num_pages, torch.bfloat16))
+    order = sorted(range(len(q_lens)), key=lambda i: (q_lens[i] != 1, i))  # single-token rows first
+    starts = [0]
+    for n in q_lens:
+        starts.append(starts[-1] + n)
+    q_sorted = torch.cat([q[starts[i]:starts[i + 1]] for i in order])
+    ql = [q_lens[i] for i in order]
+    kl = [kv_lens[i] for i in order]
+    tb = [tables[i] for i in order]
+    q_start = torch.tensor([0] + list(torch.tensor(ql).cumsum(0)), dtype=torch.int32)
+    tok_seq = torch.tensor([b for b, n in enumerate(ql) for _ in range(n)], dtype=torch.int32)
+    num_decode = sum(1 for n in ql if n == 1)
+    hq, d = q.shape[1], q.shape[2]
+    partial = torch.empty(o.decode_partial_numel(len(ql), hq, d), device="cuda")
+    out = torch.full_like(dev(q_sorted), float("nan"))
+    st = status()
+    scale = d ** -0.5
+    args = (dev(q_sorted), k_pages, v_pages, out)
+    if splits is None:
+        o.paged_attention(*args, dev(q_start), dev(torch.tensor(kl, dtype=torch.int32)), dev(tok_seq),
+                          dev(table_tensor(tb)), len(ql), num_decode, max(ql), max(kl), scale, window or 0, st, partial)
+    else:
+        assert num_decode == len(ql)
+        o.attn_decode(*args, partial, dev(q_start), dev(torch.tensor(kl, dtype=torch.int32)), dev(table_tensor(tb)),
+                      len(ql), scale, window or 0, splits, st)
+    assert int(st.item()) == 0
+    # back to the caller's order
+    pieces, at = {}, 0
+    for i, n in zip(order, ql):
+        pieces[i] = out[at:at + n]
+        at += n
+    return torch.cat([pieces[i] for i in range(len(q_lens))])
+
+
+FAST_SHAPES = ATTN_SHAPES + [
+    (16, 8, 128, 16, [700, 65, 1, 333], [1, 1, 1, 1], None),     # decode, the engine's big head size
+    (16, 8, 128, 16, [700, 65, 130], [700, 64, 3], None),        # whole prompts and portions at head size 128
+    (8, 1, 64, 16, [200, 90], [40, 90], None),                   # eight heads to one kv head
+    (32, 2, 16, 4, [37], [5], None),                             # sixteen heads to one kv head, page of 4
+    (6, 2, 96, 8, [129, 64], [129, 1], 33),                      # head size 96, window across tiles
+    (4, 2, 256, 16, [150, 20], [22, 1], None),                   # largest head size
+    (3, 1, 112, 16, [77, 300], [77, 1], 100),                    # three heads to one kv head
+]
+
+
+@pytest.mark.parametrize("case", FAST_SHAPES)
+def test_fast_attention_against_plain(case):
+    hq, hkv, d, page_size, kv_lens, q_lens, window = case
+    q, k_list, v_list, tables, num_pages = attention_case("bfloat16", hq, hkv, d, page_size, kv_lens, q_lens, window)
+    out = run_fast(q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, window)
+    want = reference_attention(q.double(), [k.double() for k in k_list], [v.double() for v in v_list], q_lens, window)
+    # probabilities are rounded to bfloat16 before P.V (as the reference does) and so is the output:
+    # two roundings of 2^-9 each
+    close(out, want, "bfloat16", scale=None)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 7, 32])
+@pytest.mark.parametrize("window", [None, 150])
+def test_decode_splits_agree(splits, window):
+    hq, hkv, d, page_size = 8, 2, 64, 16
+    kv_lens, q_lens = [1000, 17, 160, 1, 16], [1, 1, 1, 1, 1]
+    q, k_list, v_list, tables, num_pages = attention_case("bfloat16", hq, hkv, d, page_size, kv_lens, q_lens, window, seed=21)
+    out = run_fast(q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, window, splits=splits)
+    want = reference_attention(q.double(), [k.double() for k in k_list], [v.double() for v in v_list], q_lens, window)
+    close(out, want, "bfloat16")
+
+
+@pytest.mark.parametrize("far", [0, 3, 250, 511])
+@pytest.mark.parametrize("q_len", [1, 6])
+def test_fast_attention_finds_one_far_key(far, q_len):
+    hq, hkv, d, page_size = 4, 2, 64, 16
+    kv_lens, q_lens = [512 + q_len - 1], [q_len]
+    q, k_list, v_list, tables, num_pages = attention_case("bfloat16", hq, hkv, d, page_size, kv_lens, q_lens, None, seed=11)
+    q = (q.float() * 0 + 1.0).to(torch.bfloat16)
+    k_list[0] = (k_list[0].float() * 0.05).to(torch.bfloat16)
+    k_list[0][far] = 4.0
+    out = run_fast(q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, None)
+    want = v_list[0][far].double()
+    got = out.cpu().double()
+    for h in range(hq):
+        assert float((got[:, h] - want[h // 2]).abs().max()) < 2e-2
+
+
+def test_fast_attention_window_edge():
+    hq, hkv, d, page_size, window = 2, 1, 32, 8, 10
+    kv_lens, q_lens = [140], [140]
+    q, k_list, v_list, tables, num_pages = attention_case("bfloat16", hq, hkv, d, page_size, kv_lens, q_lens, window, seed=13)
+    out0 = run_fast(q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, window)
+    v_list[0][70] = 3e4  # visible to queries 70..79 only
+    out1 = run_fast(q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, window)
+    changed = [(out0[i] != out1[i]).any().item() for i in range(140)]
+    assert changed == [70 <= i <= 79 for i in range(140)]
+    # and one decoded token at the edge
+    for length, sees in ((80, True), (81, False)):
+        kv, ql = [length], [1]
+        q1, kl, vl, tb, npg = attention_case("bfloat16", hq, hkv, d, page_size, kv, ql, window, seed=14)
+        a = run_fast(q1, kl, vl, tb, npg, page_size, kv, ql, window)
+        vl[0][70] = 3e4
+        b2 = run_fast(q1, kl, vl, tb, npg, page_size, kv, ql, window)
+        assert bool((a != b2).any()) == sees
+
+
+def test_fast_attention_refuses_what_it_does_not_take():
+    o = ops()
+    assert not o.fast_attention_takes(torch.bfloat16, 4, 2, 24)
+    assert not o.fast_attention_takes(torch.bfloat16, 34, 2, 64)
+    assert not o.fast_attention_takes(torch.float32, 4, 2, 64)
+    q = torch.zeros(1, 4, 24, device="cuda", dtype=torch.bfloat16)
+    pages = torch.zeros(2, 2, 8, 24, device="cuda", dtype=torch.bfloat16)
+    ints = torch.zeros(2, dtype=torch.int32, device="cuda")
+    with pytest.raises(o.KernelSizeError):
+        o.attn_prefill(q, pages, pages, q.clone(), ints, ints, ints.view(1, 2), 1, 1, 1.0, 0, status())
+    with pytest.raises(o.KernelSizeError):
+        o.attn_decode(q, pages, pages, q.clone(), None, ints, ints, ints.view(1, 2), 1, 1.0, 0, 1, status())
+
+
 def test_sample_greedy_ties_and_all_nan():
     logits = torch.zeros(3, 1000)
     logits[0, [400, 17, 900]] = 5.0

@@ -221,7 +221,7 @@ def register_toy():
 
         def setup(self, rt, weights):
             super().setup(rt, weights)
-            self.proj = Linear(weights[f"{self.name}.proj.weight"], rt.dtype, rt.max_tokens)
+            self.proj = Linear(weights[f"{self.name}.proj.weight"], rt, tag="toy.proj")
 
         def forward(self, x, ctx, cache_id, write_cache):
             state = ctx.state(cache_id)  # [slots, hidden] float32
