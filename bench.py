@@ -145,6 +145,35 @@ def time_device_steps(fn, steps, warmup):
     return start.elapsed_time(end) / 1e3
 
 
+def schedule_lead(engine, batch, prompt_len):
+    """Tokens each of ``batch`` equal requests has decoded when the last one finishes its prompt."""
+    from qwen3_from_scratch_b200.cache import CacheManager
+    from qwen3_from_scratch_b200.engine.request import Request, SamplingParams
+    from qwen3_from_scratch_b200.engine.scheduler import Scheduler
+    real = engine.session.manager
+    lead = [0] * batch
+    for _ in range(3):  # shortening a prompt by its lead can shift the schedule; it settles at once
+        cache = CacheManager(real.layout, real.page_size, real._pools[0].num_pages if real._pools else 1, real.max_seqs)
+        sched = Scheduler(engine.scheduler.config, cache)
+        reqs = [Request([0] * (prompt_len - lead[i]), SamplingParams(max_new_tokens=8 * batch + 64))
+                for i in range(batch)]
+        for r in reqs:
+            if not sched.add_request(r):
+                raise RuntimeError("the benchmark's requests do not fit the cache pool")
+        guard = 0
+        while any(not r.is_decoding for r in reqs):
+            plan = sched.schedule()
+            sched.post_process(plan, [0 if s.wants_logits else None for s in plan])
+            guard += 1
+            if not plan or guard > 100 * batch:
+                raise RuntimeError("the dry run of the schedule does not settle")
+        new = [len(r.output) - 1 for r in reqs]
+        if new == lead:
+            break
+        lead = new
+    return lead
+
+
 def decode_bench(engine, batch, context, steps, warmup, vocab):
     """Puts ``batch`` requests of ``context - steps - warmup`` tokens in the cache through the entry
     point, then measures (a) K engine steps end to end and (b) K replays of the last step's batch
@@ -155,12 +184,17 @@ def decode_bench(engine, batch, context, steps, warmup, vocab):
     from qwen3_from_scratch_b200.kernels import ops
 
     g = torch.Generator().manual_seed(1234 + batch)
-    total_new = steps + warmup  # the last timed step brings every request to exactly `context` tokens
-    prompt_len = context - total_new
+    # Requests whose prompt is done decode while later prompts are still being cut into portions, so
+    # request i is `ahead[i]` tokens ahead when the last one starts decoding.  The scheduler is
+    # deterministic: a dry run of the same schedule on a cache manager alone tells `ahead`, and the
+    # prompts are shortened by it, so that the last timed step brings every request to `context`.
+    total_new = steps + warmup
+    ahead = schedule_lead(engine, batch, context - total_new)
     reqs = []
-    for _ in range(batch):
-        prompt = torch.randint(0, vocab, (prompt_len,), generator=g).tolist()
-        reqs.append(engine.add_request(prompt, params=SamplingParams(max_new_tokens=total_new + 8, ignore_eos=True)))
+    for i in range(batch):
+        prompt = torch.randint(0, vocab, (context - total_new - ahead[i],), generator=g).tolist()
+        reqs.append(engine.add_request(prompt, params=SamplingParams(max_new_tokens=total_new + ahead[i] + 8,
+                                                                      ignore_eos=True)))
     while any(not r.is_decoding for r in reqs):
         engine.step()
     # (a) end to end through SyncEngine.step: host ids in (pinned copy), sampled ids out, every step
@@ -178,6 +212,7 @@ def decode_bench(engine, batch, context, steps, warmup, vocab):
     d2h = batch * 4 + 4  # sampled ids and the status word
     # (b) the same step on the device alone: replay the last batch (same lengths, same pages)
     ctx = engine.session.last_context
+    assert all(n == context for n in ctx.kv_lens), f"contexts {sorted(set(ctx.kv_lens))} instead of {context}"
     model, sampler = engine.session.model, engine.sampler
     zeros = [0.0] * batch
 
