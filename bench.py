@@ -213,16 +213,14 @@ def decode_bench(engine, batch, context, steps, warmup, vocab):
     # (b) the same step on the device alone: replay the last batch (same lengths, same pages)
     ctx = engine.session.last_context
     assert all(n == context for n in ctx.kv_lens), f"contexts {sorted(set(ctx.kv_lens))} instead of {context}"
-    model, sampler = engine.session.model, engine.sampler
+    session, sampler = engine.session, engine.sampler
     zeros = [0.0] * batch
 
     def one_step():
-        logits = model.step(ctx)
+        logits = session.rerun_last()
         sampler.sample(logits, zeros, [0] * batch, [0] * batch, [0] * batch, [0] * batch)
 
-    before = ops.launch_count()
-    one_step()
-    launches = ops.launch_count() - before
+    launches = session.launches_per_decode_step(ctx) + 1  # + the sampling kernel
     device_seconds = time_device_steps(one_step, steps, warmup)
     for r in reqs:
         engine.abort(r)
@@ -312,6 +310,60 @@ def ours(args):
     return 0
 
 
+def profile(args):
+    """A short run for a profiler: builds the model (``--layers`` keeps it small), brings ``--batch``
+    requests to ``--context`` tokens, then brackets two steps with cudaProfilerStart/Stop.
+    ``--profile decode``: two decode steps launched kernel by kernel; ``--profile prefill``: two
+    steps over a 2,048-token prompt."""
+    import torch
+
+    from qwen3_from_scratch_b200.engine.engine import SyncEngine
+    from qwen3_from_scratch_b200.engine.request import SamplingParams
+    from qwen3_from_scratch_b200.registry import config_from_dict
+    from qwen3_from_scratch_b200.weights import write_random_model
+
+    cfg = dict(CONFIG)
+    cfg["num_hidden_layers"] = args.layers or FULL_LAYERS
+    with tempfile.TemporaryDirectory(prefix="q3b200-prof-") as folder:
+        write_random_model(folder, config_from_dict(cfg), seed=0)
+        pool_tokens = args.batch * args.context + PREFILL_TOKENS + 64 * PAGE
+        engine = SyncEngine(folder, dtype="bfloat16", block_size=PAGE, num_pages=pool_tokens // PAGE,
+                            max_num_seqs=max(args.batch, 1), max_num_tokens=4096, chunked_prefill_size=2048,
+                            cuda_graphs=False)
+    vocab = cfg["vocab_size"]
+    if args.profile == "prefill":
+        from qwen3_from_scratch_b200.engine.batch import BatchContext, Entry
+        session = engine.session
+        g = torch.Generator().manual_seed(99)
+        prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=g).tolist()
+        session.open("p")
+        session.manager.reserve("p", PREFILL_TOKENS)
+        ctx = BatchContext(session.manager, session.storage, session.rt).build(
+            [Entry("p", prompt, (PREFILL_TOKENS - 1,))], session.vocab_size)
+        run = lambda: session.model.step(ctx)  # noqa: E731
+    else:
+        g = torch.Generator().manual_seed(1234)
+        lead = schedule_lead(engine, args.batch, args.context - 8)
+        reqs = [engine.add_request(torch.randint(0, vocab, (args.context - 8 - lead[i],), generator=g).tolist(),
+                                   params=SamplingParams(max_new_tokens=lead[i] + 64, ignore_eos=True))
+                for i in range(args.batch)]
+        while any(not r.is_decoding for r in reqs):
+            engine.step()
+        for _ in range(7):
+            engine.step()
+        run = engine.session.rerun_last
+    for _ in range(2):
+        run()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    for _ in range(2):
+        run()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print(f"profiled 2 {args.profile} steps, batch {args.batch}, context {args.context}, layers {cfg['num_hidden_layers']}")
+    return 0
+
+
 def main() -> int:
     p = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     p.add_argument("--gpus", type=int, default=1)
@@ -321,12 +373,16 @@ def main() -> int:
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=CONTEXT)
     p.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in the output)")
+    p.add_argument("--profile", choices=["decode", "prefill"], default=None,
+                   help="short run for a profiler instead of the benchmark (see profile())")
     args = p.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run with --gpus 1")
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.profile:
+        return profile(args)
     if args.impl == "reference":
         from baseline.reference_arm import run_reference
         return run_reference(args, CONFIG, PAGE)

@@ -1,38 +1,44 @@
 // SwiGLU gate on the merged gate/up projection:
 //   out[t, i] = up[t, i] * gate[t, i] * sigmoid(gate[t, i])
 // with gate = columns [0, I) and up = columns [I, 2I) of the [T, 2I] input.
-// The gate is evaluated in float32 and the product rounded once.
+// (or, with `interleave8`, gate and up alternating in blocks of eight columns, the layout the
+// fused skinny product wants of its weight).  The gate is evaluated in float32 and the product rounded once.
 // Reference: models/feedback.py:28-34 (up * silu(gate)), kernels/triton/feedback.py:145-158.
 #include "common.cuh"
 
 namespace q3 {
 
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I, size_t total,
+                              int interleave8) {
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t t = idx / I;
   const int i = (int)(idx - t * I);
   const T* row = gate_up + t * 2 * (size_t)I;
-  const float g = to_float(row[i]);
-  const float u = to_float(row[I + i]);
+  const int gate_col = interleave8 ? ((i >> 3) << 4) + (i & 7) : i;
+  const int up_col = interleave8 ? gate_col + 8 : I + i;
+  const float g = to_float(row[gate_col]);
+  const float u = to_float(row[up_col]);
   out[idx] = from_float<T>(u * (g / (1.0f + expf(-g))));
 }
 
 }  // namespace q3
 
-// gate_up: [T, 2I]; out: [T, I]; both in `dtype`.
-extern "C" int q3_swiglu(const void* gate_up, void* out, int dtype, int T, int I, cudaStream_t stream) {
+// gate_up: [T, 2I]; out: [T, I]; both in `dtype`.  interleave8: columns 16j..16j+7 gate, 16j+8..16j+15 up.
+extern "C" int q3_swiglu(const void* gate_up, void* out, int dtype, int T, int I, int interleave8,
+                         cudaStream_t stream) {
   if (T <= 0 || I <= 0) return 0;
+  if (interleave8 && I % 8) return Q3_ERR_SIZE;
   const size_t total = (size_t)T * I;
   const int threads = 256;
   const size_t blocks = (total + threads - 1) / threads;
   if (blocks > 0x7fffffffull) return Q3_ERR_SIZE;
   if (dtype == Q3_F32)
-    q3::swiglu_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, total);
+    q3::swiglu_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, total, interleave8);
   else if (dtype == Q3_BF16)
     q3::swiglu_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>(
-        (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I, total);
+        (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I, total, interleave8);
   else
     return Q3_ERR_DTYPE;
   return q3::launch_status();

@@ -39,8 +39,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out,
                    float* __restrict__ partial, const int* __restrict__ q_start,
                    const int* __restrict__ kv_len, const int* __restrict__ block_table, int table_stride,
-                   int page_size, int num_pages, int Hq, int Hkv, float scale_log2, int window,
-                   int num_splits, int* status) {
+                   int page_size, int page_shift, int num_pages, int Hq, int Hkv, float scale_log2,
+                   int window, int num_splits, int* status) {
   using S = DecodeShape<KT>;
   constexpr int D = S::D, PITCH = S::PITCH, TILE = S::TILE, STAGES = S::STAGES, CPR = D / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -89,22 +89,30 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   const int my_count = my_first < t_hi ? (t_hi - my_first + AD_WARPS - 1) / AD_WARPS : 0;
   __nv_bfloat16* my_pipe = pipe + (size_t)warp * STAGES * 2 * TILE;
 
-  auto issue = [&](int ordinal, int stage) {
-    const int tile = my_first + ordinal * AD_WARPS;
-    const int row = lane >> 1, half = lane & 1;
-    const int n = tile * AD_KEYS + row;
+  // Page ids are looked up one tile ahead of the copy that needs them, so that the copy's
+  // address never waits for the table load.
+  const int row = lane >> 1, half = lane & 1;
+  auto key_of = [&](int ordinal) { return (my_first + ordinal * AD_WARPS) * AD_KEYS + row; };
+  auto page_of = [&](int ordinal) -> int {
+    const int n = key_of(ordinal);
+    if (ordinal >= my_count || n < lo || n > pos) return -1;
+    const int page = table[page_shift >= 0 ? (n >> page_shift) : (n / page_size)];
+    if (page < 0 || page >= num_pages) {
+      atomicOr(status, Q3_STATUS_BAD_PAGE);
+      return -1;
+    }
+    return page;
+  };
+  auto issue = [&](int ordinal, int stage, int page) {
+    const int n = key_of(ordinal);
     const __nv_bfloat16 *ks = k_pages, *vs = v_pages;
     int bytes = 0;
-    if (ordinal < my_count && n >= lo && n <= pos) {
-      const int page = table[n / page_size];
-      if (page >= 0 && page < num_pages) {
-        const size_t off = (((size_t)page * Hkv + hk) * page_size + (n % page_size)) * D;
-        ks = k_pages + off;
-        vs = v_pages + off;
-        bytes = 16;
-      } else {
-        atomicOr(status, Q3_STATUS_BAD_PAGE);
-      }
+    if (page >= 0) {
+      const int slot = page_shift >= 0 ? (n & (page_size - 1)) : (n % page_size);
+      const size_t off = (((size_t)page * Hkv + hk) * page_size + slot) * D;
+      ks = k_pages + off;
+      vs = v_pages + off;
+      bytes = 16;
     }
     __nv_bfloat16* kd = my_pipe + (size_t)(stage * 2) * TILE + row * PITCH;
     __nv_bfloat16* vd = kd + TILE;
@@ -118,15 +126,17 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
-    issue(s, s);
+    issue(s, s, page_of(s));
     cp_async_commit();
   }
+  int next_page = page_of(STAGES - 1);
 
   for (int i = 0; i < my_count; ++i) {
     cp_async_wait<STAGES - 2>();
     __syncwarp();
-    issue(i + STAGES - 1, (i + STAGES - 1) % STAGES);
+    issue(i + STAGES - 1, (i + STAGES - 1) % STAGES, next_page);
     cp_async_commit();
+    next_page = page_of(i + STAGES);
 
     const int stage = i % STAGES;
     const __nv_bfloat16* kt_s = my_pipe + (size_t)(stage * 2) * TILE;
@@ -282,7 +292,7 @@ static int attn_decode_launch(const void* q, const void* k_pages, const void* v_
   dim3 grid(num_splits, Hkv, B);
   attn_decode_kernel<KT><<<grid, AD_WARPS * 32, S::SMEM_BYTES, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out,
-      partial, q_start, kv_len, block_table, table_stride, page_size, num_pages, Hq, Hkv,
+      partial, q_start, kv_len, block_table, table_stride, page_size, page_shift_of(page_size), num_pages, Hq, Hkv,
       scale * 1.4426950408889634f, window, num_splits, status);
   int code = launch_status();
   if (code != 0 || num_splits == 1) return code;

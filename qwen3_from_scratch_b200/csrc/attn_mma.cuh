@@ -66,4 +66,12 @@ __device__ __forceinline__ const T* paged_row(const T* pages, const int* table, 
   return pages + (((size_t)page * Hkv + hk) * page_size + (n % page_size)) * D;
 }
 
+// log2 of a page size that is a power of two, else -1 (the kernels then divide).
+static inline int page_shift_of(int page_size) {
+  if (page_size <= 0 || (page_size & (page_size - 1))) return -1;
+  int s = 0;
+  while ((1 << s) < page_size) ++s;
+  return s;
+}
+
 }  // namespace q3

@@ -1,0 +1,175 @@
+// Skinny matrix product for decoding: out[T, N] = X[T, K] * W[N, K]^T with T <= 16 tokens, bfloat16
+// in, float32 accumulate.  The step is bound by reading W once, so the kernel is built around that
+// stream: W is the 16-row operand of the tensor-core tile ("swap-AB": 16 output features x 8 tokens
+// per m16n8k16), every lane fetches 16 contiguous bytes of two W rows per 32 values of k straight
+// from global memory into the registers the multiply uses, and K is split over the warps of a block
+// so that enough blocks exist to keep every SM's memory pipeline full.
+//
+// Inside a group of 32 values of k the lanes use a fixed permutation (lane t of a row takes
+// k = 8t .. 8t + 7): a dot product does not care about the order of its terms as long as both
+// operands use the same one, and this order makes every load a 16-byte one.
+//
+// Epilogues: plain store (bfloat16 or float32), or SwiGLU for a weight whose rows alternate in
+// blocks of eight between gate and up (rows 16j .. 16j+7 = gate[8j ..], rows 16j+8 .. 16j+15 =
+// up[8j ..]): out[t, 8j + i] = up * gate * sigmoid(gate), so the gate/up product never goes to memory.
+//
+// Reference for the role: the projections of the reference are nn.Linear (models/self_attn.py:358-386,
+// models/feedback.py:28-34); its fused variant merges up and gate the same way (models/feedback.py:52-62).
+#include "common.cuh"
+
+namespace q3 {
+
+constexpr int GS_WARPS = 8;
+constexpr int GS_UNROLL = 4;  // groups of 32 k-values fetched before they are multiplied
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+  // weights are read once: do not keep them in L1
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// NT: token tiles of 8 (1 or 2).  WK: warps that share a group of 16 features and split K.
+// EPI: 0 store, 1 SwiGLU on alternating blocks of eight rows.
+template <int NT, int WK, int EPI, typename OutT>
+__global__ void __launch_bounds__(GS_WARPS * 32)
+gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
+                   OutT* __restrict__ out, int T, int N, int K, int ldo) {
+  constexpr int GROUPS = GS_WARPS / WK;  // feature groups per block
+  __shared__ float red[GS_WARPS][16][8 * NT + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gid = lane >> 2, tid4 = lane & 3;
+  const int group_in_block = warp / WK, ksplit = warp % WK;
+  const int row0 = (blockIdx.x * GROUPS + group_in_block) * 16;
+  const bool active = row0 < N;
+
+  float acc[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+  if (active) {
+    // this warp's share of K, in groups of 32
+    const int groups32 = (K + 31) / 32;  // K is a multiple of 8: a lane's 8 values are all inside K or all outside
+    const int per = (groups32 + WK - 1) / WK;
+    const int g_lo = ksplit * per, g_hi = min(groups32, g_lo + per);
+    const int r_lo = min(row0 + gid, N - 1), r_hi = min(row0 + gid + 8, N - 1);  // rows past N are clamped, not stored
+    const __nv_bfloat16* w_lo = W + (size_t)r_lo * K + 8 * tid4;
+    const __nv_bfloat16* w_hi = W + (size_t)r_hi * K + 8 * tid4;
+    const __nv_bfloat16* x_row[NT];
+    bool x_ok[NT];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+      const int tok = i * 8 + gid;
+      x_ok[i] = tok < T;
+      x_row[i] = X + (size_t)(x_ok[i] ? tok : 0) * K + 8 * tid4;
+    }
+    for (int g0 = g_lo; g0 < g_hi; g0 += GS_UNROLL) {
+      uint4 wl[GS_UNROLL], wh[GS_UNROLL], xv[GS_UNROLL][NT];
+#pragma unroll
+      for (int u = 0; u < GS_UNROLL; ++u) {
+        const size_t k = (size_t)(g0 + u) * 32;
+        const bool in = g0 + u < g_hi && k + 8 * tid4 < (size_t)K;
+        wl[u] = in ? ldg_stream(w_lo + k) : make_uint4(0, 0, 0, 0);
+        wh[u] = in ? ldg_stream(w_hi + k) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+          xv[u][i] = (in && x_ok[i]) ? __ldg(reinterpret_cast<const uint4*>(x_row[i] + k)) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < GS_UNROLL; ++u)
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+          mma_16816(acc[i], wl[u].x, wh[u].x, wl[u].y, wh[u].y, xv[u][i].x, xv[u][i].y);
+          mma_16816(acc[i], wl[u].z, wh[u].z, wl[u].w, wh[u].w, xv[u][i].z, xv[u][i].w);
+        }
+    }
+  }
+  // acc[i][0..1]: feature row0 + gid, tokens 8i + 2 tid4, +1;  acc[i][2..3]: feature row0 + gid + 8
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+    red[warp][gid][i * 8 + 2 * tid4] = acc[i][0];
+    red[warp][gid][i * 8 + 2 * tid4 + 1] = acc[i][1];
+    red[warp][gid + 8][i * 8 + 2 * tid4] = acc[i][2];
+    red[warp][gid + 8][i * 8 + 2 * tid4 + 1] = acc[i][3];
+  }
+  __syncthreads();
+  if (ksplit != 0 || !active) return;
+  if (EPI == 0) {
+    // 16 features x T tokens; consecutive lanes take consecutive features of one token
+    for (int e = lane; e < 16 * 8 * NT; e += 32) {
+      const int f = e & 15, tok = e >> 4;
+      if (tok >= T || row0 + f >= N) continue;
+      float v = 0.f;
+#pragma unroll
+      for (int s = 0; s < WK; ++s) v += red[warp + s][f][tok];
+      out[(size_t)tok * ldo + row0 + f] = from_float<OutT>(v);
+    }
+  } else {
+    // features 0..7 of the group are gate values, 8..15 the matching up values
+    for (int e = lane; e < 8 * 8 * NT; e += 32) {
+      const int f = e & 7, tok = e >> 3;
+      if (tok >= T) continue;
+      float gate = 0.f, up = 0.f;
+#pragma unroll
+      for (int s = 0; s < WK; ++s) {
+        gate += red[warp + s][f][tok];
+        up += red[warp + s][f + 8][tok];
+      }
+      out[(size_t)tok * ldo + (row0 >> 1) + f] = from_float<OutT>(up * (gate / (1.0f + expf(-gate))));
+    }
+  }
+}
+
+template <int NT, int EPI, typename OutT>
+static int gemm_skinny_launch(const void* X, const void* W, void* out, int T, int N, int K, int ldo,
+                              cudaStream_t stream) {
+  const int groups = (N + 15) / 16;
+  // split K over more warps while that still leaves every warp at least 128 values of k and the
+  // grid is short of about four blocks per SM
+  int wk = 1;
+  while (wk < GS_WARPS && (groups * wk * 2) / GS_WARPS < 148 * 4 && K / (wk * 2) >= 128) wk *= 2;
+  const int per_block = GS_WARPS / wk;
+  const unsigned grid = (groups + per_block - 1) / per_block;
+#define Q3_GS_GO(WK)                                                                               \
+  gemm_skinny_kernel<NT, WK, EPI, OutT><<<grid, GS_WARPS * 32, 0, stream>>>(                       \
+      (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (OutT*)out, T, N, K, ldo)
+  if (wk == 1) Q3_GS_GO(1);
+  else if (wk == 2) Q3_GS_GO(2);
+  else if (wk == 4) Q3_GS_GO(4);
+  else Q3_GS_GO(8);
+#undef Q3_GS_GO
+  return launch_status();
+}
+
+}  // namespace q3
+
+// out[T, N] (row pitch ldo) = X[T, K] * W[N, K]^T for T <= 16; X, W bfloat16, K a multiple of 8.
+// out_f32 != 0: float32 output, else bfloat16.  swiglu != 0: W's rows alternate gate/up in blocks of
+// eight, N is a multiple of 16 and out is [T, N / 2].
+extern "C" int q3_gemm_skinny(const void* X, const void* W, void* out, int T, int N, int K, int ldo, int out_f32,
+                              int swiglu, cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return 0;
+  if (T > 16 || K <= 0 || K % 8 || (swiglu && (N % 16 || out_f32))) return Q3_ERR_SIZE;
+  if ((uintptr_t)X % 16 || (uintptr_t)W % 16) return Q3_ERR_ALIGN;
+  using bf16 = __nv_bfloat16;
+  if (swiglu) {
+    if (T <= 8) return q3::gemm_skinny_launch<1, 1, bf16>(X, W, out, T, N, K, ldo, stream);
+    return q3::gemm_skinny_launch<2, 1, bf16>(X, W, out, T, N, K, ldo, stream);
+  }
+  if (out_f32) {
+    if (T <= 8) return q3::gemm_skinny_launch<1, 0, float>(X, W, out, T, N, K, ldo, stream);
+    return q3::gemm_skinny_launch<2, 0, float>(X, W, out, T, N, K, ldo, stream);
+  }
+  if (T <= 8) return q3::gemm_skinny_launch<1, 0, bf16>(X, W, out, T, N, K, ldo, stream);
+  return q3::gemm_skinny_launch<2, 0, bf16>(X, W, out, T, N, K, ldo, stream);
+}

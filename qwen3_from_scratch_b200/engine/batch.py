@@ -10,7 +10,7 @@ tensor per array, each with a copy of its own: inference/model_worker.py:177-210
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Hashable, List, Sequence, Tuple
+from typing import Hashable, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -39,9 +39,15 @@ class BatchContext(StepContext):
     def state(self, cache_id: int):
         return self.storage.states[cache_id]
 
-    def build(self, entries: Sequence[Entry], vocab_size: int) -> "BatchContext":
+    def build(self, entries: Sequence[Entry], vocab_size: int, table_stride: Optional[int] = None,
+              keep_buffer: bool = False) -> "BatchContext":
         """``entries``: each request at most once, every request open with pages reserved for
-        its new length.  Fills every field of StepContext."""
+        its new length.  Fills every field of StepContext.
+
+        ``table_stride`` fixes the row pitch of the block tables (else the longest table of the
+        batch decides).  With ``keep_buffer`` the device arrays are written into the buffer of the
+        previous build, which must have had the same layout (same counts of tokens, rows, wanted
+        logits and the same stride): this is what lets a captured CUDA graph be replayed on new data."""
         m = self.manager
         order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
         row_of = {orig: row for row, orig in enumerate(order)}
@@ -89,15 +95,31 @@ class BatchContext(StepContext):
         for g in range(n_groups):
             rows = [m.table(g, self.requests[row]) for row in range(B)]
             stride = max(1, max(len(r) for r in rows))
+            if table_stride is not None:
+                if stride > table_stride:
+                    raise ValueError(f"a block table of {stride} pages does not fit the fixed stride {table_stride}")
+                stride = table_stride
             strides.append(stride)
             for r in rows:
                 flat_tables.extend(r)
                 flat_tables.extend([-1] * (stride - len(r)))
         flat = tokens + positions + tok_seq + q_start + kv_len + slots + logit_rows + flat_tables
+        cuts = [T, T, T, B + 1, B, B, R] + [B * s for s in strides]
+        if keep_buffer and getattr(self, "_cuts", None) == cuts:
+            self._copied.synchronize()  # the previous copy out of the pinned buffer has finished
+            self._host.copy_(torch.tensor(flat, dtype=torch.int32))
+            self._dev.copy_(self._host, non_blocking=True)
+            self._copied.record()
+            self.max_q_len, self.max_kv_len = max(self.q_lens), max(self.kv_lens)
+            self.h2d_bytes = self._host.numel() * 4
+            return self
+        if keep_buffer and getattr(self, "_cuts", None) is not None:
+            raise ValueError("this batch does not have the layout of the buffer it was asked to reuse")
         host = torch.tensor(flat, dtype=torch.int32).pin_memory()
         dev = host.to(self.rt.device, non_blocking=True)
-        self._host_keepalive = host
-        cuts = [T, T, T, B + 1, B, B, R] + [B * s for s in strides]
+        self._host, self._dev, self._cuts = host, dev, cuts
+        self._copied = torch.cuda.Event()
+        self._copied.record()
         views = torch.split(dev, cuts)
         (self.token_ids, self.positions, self.tok_seq, self.q_start, self.kv_len, self.slot_ids,
          self.logit_rows) = views[:7]

@@ -71,7 +71,7 @@ class SyncEngine:
                  gpu_utilization: float = 0.5, num_pages: Optional[int] = None,
                  chunked_prefill_size: int = 512, enable_prefix_cache: bool = False,
                  temperature: float = 0.0, top_k: int = 0, max_new_tokens: int = 100, seed: int = 0,
-                 eos_token_id: Optional[int] = None, log_interval: int = 0):
+                 eos_token_id: Optional[int] = None, log_interval: int = 0, cuda_graphs: bool = True):
         """``num_pages`` fixes the size of the cache pool; otherwise ``gpu_utilization`` of the
         memory that is free after the weights are loaded is given to it."""
         if enable_prefix_cache:
@@ -85,7 +85,8 @@ class SyncEngine:
             cache_pages = self._pages_from_memory(model_path, dtype, device, block_size, gpu_utilization,
                                                   max_num_tokens)
         self.session = Session(model_path, dtype=dtype, device=device, page_size=block_size,
-                               num_pages=cache_pages, max_seqs=max_num_seqs, max_step_tokens=max_num_tokens)
+                               num_pages=cache_pages, max_seqs=max_num_seqs, max_step_tokens=max_num_tokens,
+                               cuda_graphs=cuda_graphs)
         self.config = self.session.config
         spec = self.session.model.spec
         self.eos_token_id = eos_token_id if eos_token_id is not None else spec.eos_token_id

@@ -49,6 +49,10 @@ class Model:
                 raise ValueError(f"run order entry {i} names layer {call.layer}, the model has {len(self.layers)}")
         self.rt: Optional[Runtime] = None
 
+    @property
+    def graph_capturable(self) -> bool:
+        return all(p.graph_capturable for p in [self.embedding, self.final_norm, self.head] + self.layers)
+
     def weight_specs(self):
         specs = list(self.embedding.weight_specs())
         for layer in self.layers:

@@ -22,11 +22,61 @@ class DeviceStatusError(RuntimeError):
     pass
 
 
+class DecodeGraphs:
+    """CUDA graphs of the decode step: batches in which every request brings one token and wants
+    its logits.  One graph per (number of requests, context bucket of 1024 tokens); its batch
+    arrays live in a fixed buffer that each step's data is copied into before the replay, and the
+    number of key ranges the attention uses is the one chosen for the bucket's upper end.
+    The graphs share one memory pool: only one of them runs at a time."""
+
+    BUCKET = 1024
+
+    def __init__(self, session: "Session"):
+        self.session = session
+        self.graphs = {}
+        self.pool = None
+        self.replays = 0
+
+    def applicable(self, entries: Sequence[Entry]) -> bool:
+        return all(len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries)
+
+    def run(self, entries: Sequence[Entry]) -> torch.Tensor:
+        s = self.session
+        longest = max(s.manager.length(e.request) for e in entries) + 1
+        bucket = -(-longest // self.BUCKET) * self.BUCKET
+        key = (len(entries), bucket)
+        stride = -(-bucket // s.manager.page_size)
+        slot = self.graphs.get(key)
+        if slot is None:
+            # The first step of a new shape runs kernel by kernel (it is this step's result, and
+            # first-use set-up must not happen inside a capture); then the same launches are
+            # recorded, which runs nothing, for the steps to come.
+            ctx = BatchContext(s.manager, s.storage, s.rt).build(entries, s.vocab_size, table_stride=stride)
+            ctx.max_kv_len = bucket  # the split count recorded in the graph is the bucket's
+            eager = s.model.step(ctx)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            if self.pool is None:
+                self.pool = torch.cuda.graph_pool_handle()
+            with torch.cuda.graph(graph, pool=self.pool):
+                logits = s.model.step(ctx)
+            self.graphs[key] = (ctx, graph, logits)
+            s.last_context, s.last_graph = ctx, (graph, logits)
+            return eager
+        ctx, graph, logits = slot
+        ctx.build(entries, s.vocab_size, table_stride=stride, keep_buffer=True)
+        graph.replay()
+        self.replays += 1
+        s.last_context, s.last_graph = ctx, (graph, logits)
+        return logits
+
+
 class Session:
     def __init__(self, model_dir: str, dtype="bfloat16", device="cuda:0", page_size: int = 16,
                  num_pages: Optional[int] = None, cache_tokens: Optional[int] = None, max_seqs: int = 32,
-                 max_step_tokens: int = 3000, poison_freed_pages: bool = False):
-        """``num_pages`` pages per group, or ``cache_tokens`` (rounded up to whole pages)."""
+                 max_step_tokens: int = 3000, poison_freed_pages: bool = False, cuda_graphs: bool = True):
+        """``num_pages`` pages per group, or ``cache_tokens`` (rounded up to whole pages).
+        ``cuda_graphs``: replay decode steps from captured graphs instead of launching kernel by kernel."""
         if num_pages is None:
             if cache_tokens is None:
                 raise ValueError("give num_pages or cache_tokens")
@@ -42,6 +92,8 @@ class Session:
         if poison_freed_pages:
             self.manager.freed_log = []
         self.last_context: Optional[BatchContext] = None
+        self.decode_graphs = DecodeGraphs(self) if cuda_graphs and self.model.graph_capturable else None
+        self.last_graph = None
 
     # ------------------------------------------------------------------ requests
     def open(self, request: Hashable) -> None:
@@ -83,9 +135,7 @@ class Session:
         if not entries:
             return torch.empty(0, self.vocab_size, dtype=torch.float32, device=self.rt.device)
         self.prepare(entries)
-        ctx = BatchContext(self.manager, self.storage, self.rt).build(entries, self.vocab_size)
-        self.last_context = ctx
-        logits = self.model.step(ctx)
+        logits = self._run(entries)
         for e in entries:
             self.manager.advance(e.request, self.manager.length(e.request) + len(e.tokens))
         self._poison()
@@ -94,9 +144,30 @@ class Session:
     def step_reserved(self, entries: Sequence[Entry]) -> torch.Tensor:
         """The step for a caller (the scheduler) that has opened the requests and reserved their
         pages itself and will record the progress itself: builds the batch and runs it."""
+        return self._run(entries)
+
+    def _run(self, entries: Sequence[Entry]) -> torch.Tensor:
+        if self.decode_graphs is not None and self.decode_graphs.applicable(entries):
+            return self.decode_graphs.run(entries)
         ctx = BatchContext(self.manager, self.storage, self.rt).build(entries, self.vocab_size)
-        self.last_context = ctx
+        self.last_context, self.last_graph = ctx, None
         return self.model.step(ctx)
+
+    def rerun_last(self) -> torch.Tensor:
+        """Runs the last step's batch again as it ran (graph replay or plain launches); the
+        cache is left as it was, since the same keys and values are written again.  For timing."""
+        if self.last_graph is not None:
+            graph, logits = self.last_graph
+            graph.replay()
+            return logits
+        return self.model.step(self.last_context)
+
+    def launches_per_decode_step(self, ctx: BatchContext) -> int:
+        """Launches of this engine's own kernels in one step of ``ctx`` (counted by running it once
+        kernel by kernel; library matrix products are not counted)."""
+        before = ops.launch_count()
+        self.model.step(ctx)
+        return ops.launch_count() - before
 
     def after_step(self) -> None:
         self._poison()

@@ -59,7 +59,8 @@ _SIGNATURES = {
     "q3_attn_prefill": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
                         _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p,
                         _c_void_p],
-    "q3_swiglu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "q3_swiglu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "q3_gemm_skinny": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "q3_sample": [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ull,
                   _c_void_p, _c_void_p, _c_void_p],
 }
@@ -296,15 +297,40 @@ def attn_ref(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out:
     _done("attn_ref", code, f"heads {Hq}/{Hkv}, head_dim {D}")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out = up * silu(gate), gate = first half of the columns, up = second half."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleave8: bool = False) -> None:
+    """out = up * silu(gate); gate = first half of the columns and up = second half, or with
+    ``interleave8`` alternating blocks of eight columns (gate, up, gate, up, ...)."""
     _check("swiglu.gate_up", gate_up)
     _check("swiglu.out", out, gate_up.dtype)
     T, two_i = gate_up.shape
     if two_i % 2 or tuple(out.shape) != (T, two_i // 2):
         raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)}, out {tuple(out.shape)}")
-    code = library().q3_swiglu(gate_up.data_ptr(), out.data_ptr(), dtype_tag(out.dtype), T, two_i // 2, _stream())
-    _done("swiglu", code)
+    code = library().q3_swiglu(gate_up.data_ptr(), out.data_ptr(), dtype_tag(out.dtype), T, two_i // 2,
+                               1 if interleave8 else 0, _stream())
+    _done("swiglu", code, f"width {two_i // 2}")
+
+
+SKINNY_MAX_ROWS = 16
+
+
+def gemm_skinny_takes(rows: int, weight: torch.Tensor) -> bool:
+    return rows <= SKINNY_MAX_ROWS and weight.dtype == torch.bfloat16 and weight.shape[1] % 8 == 0
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu_blocks: bool = False) -> None:
+    """out[T, N] = x[T, K] @ w[N, K]^T for T <= 16, bfloat16 in, out bfloat16 or float32.
+    ``swiglu_blocks``: w's rows alternate gate/up in blocks of eight and out is [T, N / 2]."""
+    _check("gemm_skinny.x", x, torch.bfloat16)
+    _check("gemm_skinny.w", w, torch.bfloat16)
+    _check("gemm_skinny.out", out)
+    T, K = x.shape
+    N = w.shape[0]
+    want_cols = N // 2 if swiglu_blocks else N
+    if w.shape[1] != K or tuple(out.shape) != (T, want_cols) or out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"gemm_skinny: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
+    code = library().q3_gemm_skinny(x.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, want_cols,
+                                    1 if out.dtype == torch.float32 else 0, 1 if swiglu_blocks else 0, _stream())
+    _done("gemm_skinny", code, f"T {T} N {N} K {K}")
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
@@ -351,7 +377,7 @@ def rope(x: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, positions: to
 
 # ------------------------------------------------------------------ fast bfloat16 attention
 MAX_DECODE_SPLITS = 32
-_DECODE_TARGET_BLOCKS = 592  # about two resident blocks per SM on 148 SMs, twice over
+_DECODE_TARGET_BLOCKS = 296  # two resident blocks per SM on 148 SMs: one full wave
 
 
 def fast_attention_takes(dtype: torch.dtype, num_q_heads: int, num_kv_heads: int, head_dim: int) -> bool:
@@ -365,7 +391,7 @@ def decode_splits(num_seqs: int, num_kv_heads: int, max_kv_len: int, window: int
     256 keys per range."""
     span = min(max_kv_len, window) if window and window > 0 else max_kv_len
     by_work = max(1, span // 256)
-    want = -(-_DECODE_TARGET_BLOCKS // max(1, num_seqs * num_kv_heads))
+    want = max(1, _DECODE_TARGET_BLOCKS // max(1, num_seqs * num_kv_heads))
     return max(1, min(want, by_work, MAX_DECODE_SPLITS))
 
 

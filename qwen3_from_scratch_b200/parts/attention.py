@@ -22,6 +22,8 @@ from .linear import Linear
 
 @register_part("mixer", "gqa_attention")
 class GQAAttention(Mixer):
+    graph_capturable = True
+
     def __init__(self, name: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qk_norm_eps: Optional[float] = None, position: Optional[PartSpec] = None,
                  window: Optional[int] = None):

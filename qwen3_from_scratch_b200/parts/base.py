@@ -158,7 +158,13 @@ class StepContext:
 
 
 class Part:
-    """Base of all parts.  ``name`` is the prefix of its tensors in the model folder."""
+    """Base of all parts.  ``name`` is the prefix of its tensors in the model folder.
+
+    ``graph_capturable``: the part's work is only kernel launches on the current stream, with
+    no read of device data on the host and no state kept on the host, so a step can be captured
+    in a CUDA graph and replayed.  Parts that do not say so keep the model on plain launches."""
+
+    graph_capturable = False
 
     def __init__(self, name: str = ""):
         self.name = name

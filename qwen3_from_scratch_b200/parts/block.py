@@ -27,6 +27,10 @@ class PreNormBlock(Block):
         self.norm2 = create_part("norm", norm2, name=f"{name}.{n['norm2']}")
         self.feed_forward = create_part("feed_forward", feed_forward, name=f"{name}.{n['feed_forward']}")
 
+    @property
+    def graph_capturable(self) -> bool:
+        return all(p.graph_capturable for p in (self.norm1, self.mixer, self.norm2, self.feed_forward))
+
     def weight_specs(self) -> List[WeightSpec]:
         return (self.norm1.weight_specs() + self.mixer.weight_specs() + self.norm2.weight_specs()
                 + self.feed_forward.weight_specs())

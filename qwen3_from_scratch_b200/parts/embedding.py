@@ -19,6 +19,8 @@ from .linear import Linear
 
 @register_part("embedding", "token_embedding")
 class TokenEmbedding(Part):
+    graph_capturable = True
+
     def __init__(self, name: str, vocab_size: int, hidden_size: int):
         super().__init__(name)
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
@@ -39,6 +41,8 @@ class TokenEmbedding(Part):
 
 @register_part("head", "lm_head")
 class LMHead(Part):
+    graph_capturable = True
+
     """logits = x W^T in float32.  ``tied_to``: name of the embedding tensor it shares, or None."""
 
     def __init__(self, name: str, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None):

@@ -1,8 +1,9 @@
 """Matrix product y = x W^T with a weight in the checkpoint's [out, in] layout.
 
-bfloat16: the product is a library call (cuBLAS through ``torch.mm``), as in the
-reference's engine, whose projections are ``nn.Linear`` (models/self_attn.py:358-386,
-models/feedback.py:28-34).  float32: the engine's own FFMA kernel, never a
+bfloat16: with more than 16 rows the product is a library call (cuBLAS through ``torch.mm``),
+as in the reference's engine, whose projections are ``nn.Linear`` (models/self_attn.py:358-386,
+models/feedback.py:28-34); with up to 16 rows (decoding) it is the engine's own weight-streaming
+tensor-core kernel.  float32: the engine's own FFMA kernel, never a
 reduced-precision mode.  A weight that was stored in float32 keeps its float32
 product even in a bfloat16 run.
 """
@@ -60,6 +61,11 @@ class Linear:
                 return out32
             out = self._buffer("_out", rows, self.out_dtype)
             out.copy_(out32)
+            return out
+        if ops.gemm_skinny_takes(rows, self.weight) and x.dtype == torch.bfloat16:
+            # a handful of rows: the product is a stream over the weight, done by the engine's own kernel
+            out = self._buffer("_out", rows, self.out_dtype)
+            ops.gemm_skinny(x, self.weight, out)
             return out
         if self.out_dtype == x.dtype:
             out = self._buffer("_out", rows, self.out_dtype)

@@ -18,6 +18,8 @@ from .linear import Linear
 
 @register_part("feed_forward", "swiglu")
 class SwiGLU(FeedForward):
+    graph_capturable = True
+
     def __init__(self, name: str, hidden_size: int, intermediate_size: int):
         super().__init__(name)
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
@@ -33,14 +35,23 @@ class SwiGLU(FeedForward):
         gate = weights.pop(f"{self.name}.gate_proj.weight")
         up = weights.pop(f"{self.name}.up_proj.weight")
         dtype = torch.float32 if torch.float32 in (gate.dtype, up.dtype) else gate.dtype
-        merged = torch.cat([gate.to(dtype), up.to(dtype)], dim=0)
+        h, i = self.hidden_size, self.intermediate_size
+        # bfloat16: gate and up rows alternate in blocks of eight, so that the decode kernel has a
+        # gate value and its up value in one thread and applies the activation before storing
+        self.blocks_of_eight = dtype == torch.bfloat16 and i % 8 == 0
+        if self.blocks_of_eight:
+            merged = torch.cat([gate.view(i // 8, 8, h), up.view(i // 8, 8, h)], dim=1).reshape(2 * i, h).contiguous()
+        else:
+            merged = torch.cat([gate.to(dtype), up.to(dtype)], dim=0)
         del gate, up
         self.gate_up = Linear(merged, rt, tag="ffn.gate_up")
         self.down = Linear(weights.pop(f"{self.name}.down_proj.weight"), rt, tag="ffn.down")
         self._act = rt.shared("ffn.act", rt.max_tokens, self.intermediate_size)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        gu = self.gate_up(x)
         act = self._act[: x.shape[0]]
-        ops.swiglu(gu, act)
+        if self.blocks_of_eight and ops.gemm_skinny_takes(x.shape[0], self.gate_up.weight):
+            ops.gemm_skinny(x, self.gate_up.weight, act, swiglu_blocks=True)
+        else:
+            ops.swiglu(self.gate_up(x), act, interleave8=self.blocks_of_eight)
         return self.down(act)

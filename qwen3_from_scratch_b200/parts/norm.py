@@ -17,6 +17,8 @@ from .base import Norm, Runtime, WeightSpec
 
 @register_part("norm", "rms_norm")
 class RMSNorm(Norm):
+    graph_capturable = True
+
     def __init__(self, name: str, dim: int, eps: float):
         super().__init__(name)
         self.dim, self.eps = int(dim), float(eps)

@@ -19,6 +19,8 @@ from .base import PositionEncoding, Runtime
 
 @register_part("position", "rotary_neox")
 class RotaryNeox(PositionEncoding):
+    graph_capturable = True
+
     def __init__(self, name: str, head_dim: int, theta: float, max_positions: int, rotary_dim: Optional[int] = None):
         super().__init__(name)
         self.head_dim = int(head_dim)

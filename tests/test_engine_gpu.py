@@ -94,6 +94,25 @@ def test_temperature_and_top_k_match_plain_with_the_same_generator(tiny_folders)
         assert len(set(req.output)) > 1  # it is sampling, not a constant
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graph_replay_gives_what_plain_launches_give(tiny_folders, dtype):
+    """Decode steps replayed from CUDA graphs against the same steps launched kernel by kernel."""
+    from qwen3_from_scratch_b200.engine.engine import SyncEngine
+    folder = tiny_folders["b"]
+    prompts = [random_tokens(384, n, 40 + i) for i, n in enumerate([3, 21, 40])]
+    outs = []
+    for graphs in (True, False):
+        engine = SyncEngine(folder, dtype=dtype, block_size=8, num_pages=64, max_num_seqs=4, max_num_tokens=64,
+                            cuda_graphs=graphs)
+        results, _ = engine.batch_generate(prompts, max_new_tokens=40, ignore_eos=True)
+        outs.append([r.token_ids for r in results])
+        if graphs:
+            assert engine.session.decode_graphs.replays > 30
+        else:
+            assert engine.session.decode_graphs is None
+    assert outs[0] == outs[1]
+
+
 def test_eos_stops_a_request(tiny_folders):
     from qwen3_from_scratch_b200.engine.engine import SyncEngine
     folder = tiny_folders["a"]
