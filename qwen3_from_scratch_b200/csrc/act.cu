@@ -23,6 +23,29 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
   out[idx] = from_float<T>(u * (g / (1.0f + expf(-g))));
 }
 
+// Eight outputs per thread with 16-byte accesses (bfloat16, I a multiple of 8).
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
+                                     int I, size_t total8, int interleave8) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total8) return;
+  const int per_row = I >> 3;
+  const size_t t = idx / per_row;
+  const int j = (int)(idx - t * per_row);  // block of eight outputs
+  const __nv_bfloat16* row = gate_up + t * 2 * (size_t)I;
+  const uint4 gv = *reinterpret_cast<const uint4*>(row + (interleave8 ? 16 * j : 8 * j));
+  const uint4 uv = *reinterpret_cast<const uint4*>(row + (interleave8 ? 16 * j + 8 : I + 8 * j));
+  const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+  uint32_t ow[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float g0 = __uint_as_float(gw[k] << 16), g1 = __uint_as_float(gw[k] & 0xffff0000u);
+    const float u0 = __uint_as_float(uw[k] << 16), u1 = __uint_as_float(uw[k] & 0xffff0000u);
+    __nv_bfloat162 o = __floats2bfloat162_rn(u0 * (g0 / (1.0f + expf(-g0))), u1 * (g1 / (1.0f + expf(-g1))));
+    ow[k] = *reinterpret_cast<uint32_t*>(&o);
+  }
+  *reinterpret_cast<uint4*>(out + t * (size_t)I + 8 * j) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+}
+
 }  // namespace q3
 
 // gate_up: [T, 2I]; out: [T, I]; both in `dtype`.  interleave8: columns 16j..16j+7 gate, 16j+8..16j+15 up.
@@ -34,6 +57,12 @@ extern "C" int q3_swiglu(const void* gate_up, void* out, int dtype, int T, int I
   const int threads = 256;
   const size_t blocks = (total + threads - 1) / threads;
   if (blocks > 0x7fffffffull) return Q3_ERR_SIZE;
+  if (dtype == Q3_BF16 && I % 8 == 0 && (uintptr_t)gate_up % 16 == 0 && (uintptr_t)out % 16 == 0) {
+    const size_t total8 = total / 8;
+    q3::swiglu_bf16x8_kernel<<<(unsigned)((total8 + threads - 1) / threads), threads, 0, stream>>>(
+        (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I, total8, interleave8);
+    return q3::launch_status();
+  }
   if (dtype == Q3_F32)
     q3::swiglu_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, total, interleave8);
   else if (dtype == Q3_BF16)

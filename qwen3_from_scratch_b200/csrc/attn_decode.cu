@@ -26,7 +26,7 @@ struct DecodeShape {
   static constexpr int D = 16 * KT;
   static constexpr int PITCH = D + 8;
   static constexpr int TILE = AD_KEYS * PITCH;  // elements of one 16-row tile
-  static constexpr int STAGES = KT <= 8 ? 3 : 2;
+  static constexpr int STAGES = 2;  // with two stages three blocks (twelve warps) fit an SM at D = 128
   static constexpr size_t PIPE_BYTES = sizeof(__nv_bfloat16) * (size_t)AD_WARPS * STAGES * 2 * TILE;
   static constexpr size_t MERGE_BYTES = sizeof(float) * (size_t)AD_WARPS * 16 * (D + 2);
   static constexpr size_t SMEM_BYTES =

@@ -1,7 +1,7 @@
 // Paged causal attention for prompt portions (any number of query tokens per sequence), bfloat16.
 //
 // Grid (query tile, kv head, sequence).  The rows of a query tile are (token, head-in-group)
-// pairs of one kv head, 64 to a block: row R -> token R / g, head hk * g + R % g, so the g
+// pairs of one kv head, 128 (or 64 for large heads) to a block: row R -> token R / g, head hk * g + R % g, so the g
 // query heads that share a kv head also share every key/value tile that is fetched.  Keys
 // and values come from the pages in tiles of 64 keys (cp.async, two stages); S = Q K^T and
 // O += P V run on the tensor cores (m16n8k16, bfloat16 in, float32 accumulate), the running
@@ -15,20 +15,24 @@
 
 namespace q3 {
 
-constexpr int AP_WARPS = 4;
-constexpr int AP_BM = 64;  // query rows per block
 constexpr int AP_BN = 64;  // keys per tile
 
+// Up to D = 128 a block has eight warps (128 query rows) and is held to 128 registers a thread,
+// so that two blocks, sixteen warps, share an SM: with fewer warps the long dependent chains of
+// the softmax leave the tensor cores idle.  Larger heads use four warps (64 rows).
 template <int KT>
 struct PrefillShape {
   static constexpr int D = 16 * KT;
   static constexpr int PITCH = D + 8;
   static constexpr int TILE = AP_BN * PITCH;
-  static constexpr size_t SMEM_BYTES = sizeof(__nv_bfloat16) * (size_t)(AP_BM * PITCH + 4 * TILE);
+  static constexpr int WARPS = KT <= 8 ? 8 : 4;
+  static constexpr int BM = 16 * WARPS;  // query rows per block
+  static constexpr int MIN_BLOCKS = KT <= 8 ? 2 : 1;
+  static constexpr size_t SMEM_BYTES = sizeof(__nv_bfloat16) * (size_t)(BM * PITCH + 4 * TILE);
 };
 
 template <int KT>
-__global__ void __launch_bounds__(AP_WARPS * 32)
+__global__ void __launch_bounds__(PrefillShape<KT>::WARPS * 32, PrefillShape<KT>::MIN_BLOCKS)
 attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
                     const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out,
                     const int* __restrict__ q_start, const int* __restrict__ kv_len,
@@ -36,7 +40,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     int Hq, int Hkv, float scale_log2, int window, int* status) {
   using S = PrefillShape<KT>;
   constexpr int D = S::D, PITCH = S::PITCH, TILE = S::TILE, CPR = D / 8;
-  constexpr bool Q_IN_REGS = KT <= 8;
+  constexpr int AP_WARPS = S::WARPS, AP_BM = S::BM;
+  constexpr bool Q_IN_REGS = false;  // the query fragments are re-read from shared memory: registers go to the output
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* kv_s = q_s + AP_BM * PITCH;  // [stage][K | V][64][PITCH]
@@ -72,8 +77,9 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     *reinterpret_cast<uint4*>(q_s + rr * PITCH + c * 8) = v;
   }
 
+  constexpr int LANES_PER_ROW = AP_WARPS * 32 / AP_BN;  // threads that share a key row: 2 or 4
   auto load_tile = [&](int tile, int stage) {
-    const int row = threadIdx.x >> 1, half = threadIdx.x & 1;
+    const int row = threadIdx.x / LANES_PER_ROW, half = threadIdx.x % LANES_PER_ROW;
     const int n = tile * AP_BN + row;
     const __nv_bfloat16 *ks = k_pages, *vs = v_pages;
     int bytes = 0;
@@ -91,7 +97,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     __nv_bfloat16* kd = kv_s + (size_t)(stage * 2) * TILE + row * PITCH;
     __nv_bfloat16* vd = kd + TILE;
 #pragma unroll
-    for (int c = half; c < CPR; c += 2) {
+    for (int c = half; c < CPR; c += LANES_PER_ROW) {
       const int src = bytes ? c * 8 : 0;
       cp_async_16(kd + c * 8, ks + src, bytes);
       cp_async_16(vd + c * 8, vs + src, bytes);
@@ -236,10 +242,10 @@ static int attn_prefill_launch(const void* q, const void* k_pages, const void* v
     configured = true;
   }
   const int g = Hq / Hkv;
-  const long long tiles = ((long long)max_q_len * g + AP_BM - 1) / AP_BM;
+  const long long tiles = ((long long)max_q_len * g + S::BM - 1) / S::BM;
   if (tiles > 0x7fffffffLL) return Q3_ERR_SIZE;
   dim3 grid((unsigned)tiles, Hkv, B);
-  attn_prefill_kernel<KT><<<grid, AP_WARPS * 32, S::SMEM_BYTES, stream>>>(
+  attn_prefill_kernel<KT><<<grid, S::WARPS * 32, S::SMEM_BYTES, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out,
       q_start, kv_len, block_table, table_stride, page_size, num_pages, Hq, Hkv, scale * 1.4426950408889634f, window,
       status);

@@ -89,6 +89,119 @@ qkv_post_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict_
   }
 }
 
+// The same for bfloat16 when D is a multiple of 32 and the whole head is rotated: lane l owns
+// the D / 32 consecutive values from l * D / 32, so lanes 0..15 hold the first half of the head
+// and lane l + 16 holds the rotation partners of lane l; no shared memory, 2 * VPL-byte accesses.
+constexpr int QPV_WARPS = 8;
+
+template <int VPL>
+__global__ void __launch_bounds__(QPV_WARPS * 32)
+qkv_post_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+                    __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
+                    const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                    const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                    const int* __restrict__ tok_seq, const int* __restrict__ block_table, int table_stride,
+                    int page_size, int num_pages, int Hq, int Hkv, float eps, int write_kv, int* status) {
+  constexpr int D = 32 * VPL;
+  // One block per token: the sines and cosines of the token's D / 2 angles are computed once and
+  // shared by all its heads; then each warp takes every eighth head.
+  __shared__ float cs[D];  // cos of pair j at [j], sin at [D / 2 + j]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int n_heads = Hq + 2 * Hkv;
+  const int pos = positions[t];
+  if (inv_freq != nullptr) {
+    for (int j = threadIdx.x; j < D / 2; j += QPV_WARPS * 32) {
+      float sn, c;
+      sincosf((float)pos * inv_freq[j], &sn, &c);
+      cs[j] = c;
+      cs[D / 2 + j] = sn;
+    }
+  }
+  __syncthreads();
+  for (int head = warp; head < n_heads; head += QPV_WARPS) {
+  const bool is_q = head < Hq;
+  const bool is_k = !is_q && head < Hq + Hkv;
+  if (!is_q && !write_kv) continue;
+  const __nv_bfloat16* src = qkv + ((size_t)t * n_heads + head) * D + lane * VPL;
+  float x[VPL];
+  if (VPL == 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(src);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      x[(2 * k) % VPL] = __uint_as_float(w[k] << 16);
+      x[(2 * k + 1) % VPL] = __uint_as_float(w[k] & 0xffff0000u);
+    }
+  } else if (VPL == 4) {
+    const uint2 v = *reinterpret_cast<const uint2*>(src);
+    x[0] = __uint_as_float(v.x << 16); x[1 % VPL] = __uint_as_float(v.x & 0xffff0000u);
+    x[2 % VPL] = __uint_as_float(v.y << 16); x[3 % VPL] = __uint_as_float(v.y & 0xffff0000u);
+  } else if (VPL == 2) {
+    const uint32_t v = *reinterpret_cast<const uint32_t*>(src);
+    x[0] = __uint_as_float(v << 16); x[1 % VPL] = __uint_as_float(v & 0xffff0000u);
+  } else {
+    x[0] = __bfloat162float(src[0]);
+  }
+  const float* w = is_q ? q_weight : (is_k ? k_weight : nullptr);
+  if (w) {
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) ss += x[k] * x[k];
+    ss = warp_sum(ss);
+    const float rs = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) x[k] = x[k] * rs * w[lane * VPL + k];
+  }
+  if ((is_q || is_k) && inv_freq != nullptr) {
+    const bool first_half = lane < 16;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+      const float partner = __shfl_xor_sync(0xffffffffu, x[k], 16);
+      const int j = (lane & 15) * VPL + k;  // index of the pair
+      const float c = cs[j], sn = cs[D / 2 + j];
+      x[k] = first_half ? x[k] * c - partner * sn : x[k] * c + partner * sn;
+    }
+  }
+  __nv_bfloat16* dst;
+  if (is_q) {
+    dst = q_out + ((size_t)t * Hq + head) * D;
+  } else {
+    const int seq = tok_seq[t];
+    if (pos < 0 || seq < 0) {
+      if (lane == 0) atomicOr(status, Q3_STATUS_BAD_POSITION);
+      continue;
+    }
+    const int page = block_table[(size_t)seq * table_stride + pos / page_size];
+    if (page < 0 || page >= num_pages) {
+      if (lane == 0) atomicOr(status, Q3_STATUS_BAD_PAGE);
+      continue;
+    }
+    const int hk = is_k ? head - Hq : head - Hq - Hkv;
+    dst = (is_k ? k_pages : v_pages) + (((size_t)page * Hkv + hk) * page_size + (pos % page_size)) * D;
+  }
+  dst += lane * VPL;
+  if (VPL == 8) {
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o[k] = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      __nv_bfloat162 p = __floats2bfloat162_rn(x[(2 * k) % VPL], x[(2 * k + 1) % VPL]);
+      o[k] = *reinterpret_cast<uint32_t*>(&p);
+    }
+    *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+  } else if (VPL == 4) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(x[0], x[1 % VPL]), b = __floats2bfloat162_rn(x[2 % VPL], x[3 % VPL]);
+    *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+  } else if (VPL == 2) {
+    *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(x[0], x[1 % VPL]);
+  } else {
+    dst[0] = __float2bfloat16_rn(x[0]);
+  }
+  }
+}
+
 }  // namespace q3
 
 // qkv: [T, (Hq + 2 Hkv) * D] in `dtype`, rows ordered q heads, k heads, v heads.
@@ -109,6 +222,22 @@ extern "C" int q3_qkv_post(const void* qkv, int dtype, int T, int Hq, int Hkv, i
   const int n_heads = Hq + 2 * Hkv;
   dim3 grid(T, (n_heads + q3::QP_WARPS - 1) / q3::QP_WARPS);
   if (grid.y > 65535) return Q3_ERR_SIZE;
+  const bool whole_rotation = inv_freq == nullptr || rotary_dim == D;
+  if (dtype == Q3_BF16 && whole_rotation && (D == 32 || D == 64 || D == 128 || D == 256) &&
+      (uintptr_t)qkv % 16 == 0 && (uintptr_t)q_out % 16 == 0 && (uintptr_t)k_pages % 16 == 0 &&
+      (uintptr_t)v_pages % 16 == 0) {
+#define Q3_QP_VEC(VPL)                                                                                            \
+  q3::qkv_post_vec_kernel<VPL><<<T, q3::QPV_WARPS * 32, 0, stream>>>(                                           \
+      (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, q_weight, \
+      k_weight, inv_freq, positions, tok_seq, block_table, table_stride, page_size, num_pages, Hq, Hkv, eps,       \
+      write_kv, status)
+    if (D == 32) Q3_QP_VEC(1);
+    else if (D == 64) Q3_QP_VEC(2);
+    else if (D == 128) Q3_QP_VEC(4);
+    else Q3_QP_VEC(8);
+#undef Q3_QP_VEC
+    return q3::launch_status();
+  }
   if (dtype == Q3_F32)
     q3::qkv_post_kernel<float><<<grid, q3::QP_WARPS * 32, 0, stream>>>(
         (const float*)qkv, (float*)q_out, (float*)k_pages, (float*)v_pages, q_weight, k_weight, inv_freq,

@@ -377,7 +377,6 @@ def rope(x: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, positions: to
 
 # ------------------------------------------------------------------ fast bfloat16 attention
 MAX_DECODE_SPLITS = 32
-_DECODE_TARGET_BLOCKS = 296  # two resident blocks per SM on 148 SMs: one full wave
 
 
 def fast_attention_takes(dtype: torch.dtype, num_q_heads: int, num_kv_heads: int, head_dim: int) -> bool:
@@ -386,13 +385,38 @@ def fast_attention_takes(dtype: torch.dtype, num_q_heads: int, num_kv_heads: int
             and num_q_heads % num_kv_heads == 0 and num_q_heads // num_kv_heads <= 16)
 
 
-def decode_splits(num_seqs: int, num_kv_heads: int, max_kv_len: int, window: int) -> int:
-    """How many ranges a sequence's keys are cut into: enough blocks to fill the GPU, at least
-    256 keys per range."""
+# registers per thread of attn_decode_kernel<D / 16> as compiled (ptxas -v), for the occupancy estimate
+_DECODE_REGS = {1: 56, 2: 64, 3: 72, 4: 96, 5: 128, 6: 128, 7: 128, 8: 168, 9: 168, 10: 168, 11: 216, 12: 232,
+                13: 244, 14: 252, 15: 255, 16: 255}
+_SM_COUNT = 148
+
+
+def decode_blocks_per_sm(head_dim: int) -> int:
+    """Blocks of the decode kernel that fit one SM (shared memory and registers)."""
+    tile = 16 * (head_dim + 8) * 2
+    smem = tile * (1 + 4 * 2 * 2)
+    by_smem = (227 * 1024) // smem
+    by_regs = 65536 // (_DECODE_REGS.get(head_dim // 16, 255) * 128)
+    return max(1, min(by_smem, by_regs, 16))
+
+
+def decode_splits(num_seqs: int, num_kv_heads: int, max_kv_len: int, window: int, head_dim: int = 128) -> int:
+    """How many ranges a sequence's keys are cut into.  Blocks run in waves of (SMs x blocks per
+    SM); a block costs its share of the 16-key tiles plus a fixed set-up and merge (about six
+    tiles' worth).  The count that minimises waves x cost per block wins."""
     span = min(max_kv_len, window) if window and window > 0 else max_kv_len
-    by_work = max(1, span // 256)
-    want = max(1, _DECODE_TARGET_BLOCKS // max(1, num_seqs * num_kv_heads))
-    return max(1, min(want, by_work, MAX_DECODE_SPLITS))
+    tiles = max(1, -(-span // 16))
+    slots = _SM_COUNT * decode_blocks_per_sm(head_dim)
+    pairs = max(1, num_seqs * num_kv_heads)
+    best, best_cost = 1, None
+    for s in range(1, MAX_DECODE_SPLITS + 1):
+        if s > 1 and tiles // s < 4:
+            break
+        waves = -(-pairs * s // slots)
+        cost = waves * (-(-tiles // s) + 6)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
 
 
 def decode_partial_numel(num_seqs: int, num_q_heads: int, head_dim: int) -> int:
@@ -464,7 +488,7 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         attn_ref(q, k_pages, v_pages, out, q_start, kv_len, tok_seq, block_table, scale, window, status)
         return
     if num_decode > 0:
-        splits = decode_splits(num_decode, Hkv, max_kv_len, window)
+        splits = decode_splits(num_decode, Hkv, max_kv_len, window, D)
         if partial is None or partial.numel() < num_decode * Hq * splits * (D + 2):
             splits = 1 if partial is None else max(1, partial.numel() // (num_decode * Hq * (D + 2)))
         attn_decode(q, k_pages, v_pages, out, partial, q_start, kv_len, block_table, num_decode, scale, window,
