@@ -11,6 +11,8 @@ namespace q3 {
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I, size_t total,
                               int interleave8) {
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t t = idx / I;
@@ -26,6 +28,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 // Eight outputs per thread with 16-byte accesses (bfloat16, I a multiple of 8).
 __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
                                      int I, size_t total8, int interleave8) {
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total8) return;
   const int per_row = I >> 3;
@@ -59,14 +63,14 @@ extern "C" int q3_swiglu(const void* gate_up, void* out, int dtype, int T, int I
   if (blocks > 0x7fffffffull) return Q3_ERR_SIZE;
   if (dtype == Q3_BF16 && I % 8 == 0 && (uintptr_t)gate_up % 16 == 0 && (uintptr_t)out % 16 == 0) {
     const size_t total8 = total / 8;
-    q3::swiglu_bf16x8_kernel<<<(unsigned)((total8 + threads - 1) / threads), threads, 0, stream>>>(
+    q3::launch(q3::swiglu_bf16x8_kernel, dim3((unsigned)((total8 + threads - 1) / threads)), dim3(threads), 0, stream, 
         (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I, total8, interleave8);
     return q3::launch_status();
   }
   if (dtype == Q3_F32)
-    q3::swiglu_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, total, interleave8);
+    q3::launch(q3::swiglu_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, I, total, interleave8);
   else if (dtype == Q3_BF16)
-    q3::swiglu_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>(
+    q3::launch(q3::swiglu_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, stream, 
         (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I, total, interleave8);
   else
     return Q3_ERR_DTYPE;

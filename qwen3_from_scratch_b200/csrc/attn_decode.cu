@@ -41,6 +41,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const int* __restrict__ kv_len, const int* __restrict__ block_table, int table_stride,
                    int page_size, int page_shift, int num_pages, int Hq, int Hkv, float scale_log2,
                    int window, int num_splits, int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
   using S = DecodeShape<KT>;
   constexpr int D = S::D, PITCH = S::PITCH, TILE = S::TILE, STAGES = S::STAGES, CPR = D / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -257,6 +259,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 // Merges the splits of one (sequence, head): out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
 __global__ void attn_combine_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
                                     const int* __restrict__ q_start, int Hq, int D, int num_splits) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int head = blockIdx.x, b = blockIdx.y;
   const float* base = partial + ((size_t)b * Hq + head) * num_splits * (D + 2);
   float big = -INFINITY;
@@ -290,14 +294,14 @@ static int attn_decode_launch(const void* q, const void* k_pages, const void* v_
     configured = true;
   }
   dim3 grid(num_splits, Hkv, B);
-  attn_decode_kernel<KT><<<grid, AD_WARPS * 32, S::SMEM_BYTES, stream>>>(
+  q3::launch(attn_decode_kernel<KT>, dim3(grid), dim3(AD_WARPS * 32), S::SMEM_BYTES, stream, 
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out,
       partial, q_start, kv_len, block_table, table_stride, page_size, page_shift_of(page_size), num_pages, Hq, Hkv,
       scale * 1.4426950408889634f, window, num_splits, status);
   int code = launch_status();
   if (code != 0 || num_splits == 1) return code;
   dim3 cgrid(Hq, B);
-  attn_combine_kernel<<<cgrid, 128, 0, stream>>>(partial, (__nv_bfloat16*)out, q_start, Hq, S::D, num_splits);
+  q3::launch(attn_combine_kernel, dim3(cgrid), dim3(128), 0, stream, partial, (__nv_bfloat16*)out, q_start, Hq, S::D, num_splits);
   return launch_status();
 }
 

@@ -38,6 +38,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     const int* __restrict__ q_start, const int* __restrict__ kv_len,
                     const int* __restrict__ block_table, int table_stride, int page_size, int num_pages,
                     int Hq, int Hkv, float scale_log2, int window, int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
   using S = PrefillShape<KT>;
   constexpr int D = S::D, PITCH = S::PITCH, TILE = S::TILE, CPR = D / 8;
   constexpr int AP_WARPS = S::WARPS, AP_BM = S::BM;
@@ -245,7 +247,7 @@ static int attn_prefill_launch(const void* q, const void* k_pages, const void* v
   const long long tiles = ((long long)max_q_len * g + S::BM - 1) / S::BM;
   if (tiles > 0x7fffffffLL) return Q3_ERR_SIZE;
   dim3 grid((unsigned)tiles, Hkv, B);
-  attn_prefill_kernel<KT><<<grid, S::WARPS * 32, S::SMEM_BYTES, stream>>>(
+  q3::launch(attn_prefill_kernel<KT>, dim3(grid), dim3(S::WARPS * 32), S::SMEM_BYTES, stream, 
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out,
       q_start, kv_len, block_table, table_stride, page_size, num_pages, Hq, Hkv, scale * 1.4426950408889634f, window,
       status);

@@ -23,6 +23,8 @@ attn_ref_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T*
                 const int* __restrict__ tok_seq, const int* __restrict__ block_table, int table_stride,
                 int page_size, int num_pages, int Hq, int Hkv, int D, float scale, int window,
                 int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const int head = blockIdx.y * AR_WARPS + warp;
@@ -93,7 +95,7 @@ static int attn_ref_launch(const void* q, const void* k_pages, const void* v_pag
   dim3 grid(T_total, (Hq + AR_WARPS - 1) / AR_WARPS);
   if (grid.y > 65535) return Q3_ERR_SIZE;
 #define Q3_AR_CASE(NJ)                                                                               \
-  attn_ref_kernel<T, NJ><<<grid, AR_WARPS * 32, 0, stream>>>(                                        \
+  q3::launch(attn_ref_kernel<T, NJ>, dim3(grid), dim3(AR_WARPS * 32), 0, stream,                                         \
       (const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, q_start, kv_len, tok_seq,          \
       block_table, table_stride, page_size, num_pages, Hq, Hkv, D, scale, window, status)
   if (D <= 32) Q3_AR_CASE(1);

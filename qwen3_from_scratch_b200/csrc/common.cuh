@@ -9,6 +9,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 // dtype tags of the C ABI
 #define Q3_F32 0
@@ -64,5 +65,44 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// Every kernel of this library starts with pdl_wait() and then pdl_launch_dependents().  Launched
+// with the programmatic-serialization attribute (launch() below), a kernel's blocks may become
+// resident while the kernel before it in the stream is still running; they stop at pdl_wait()
+// until that kernel has completed and its memory is visible.  Only data that no kernel writes
+// (weights, the step's integer arrays) may be touched before the wait.  Because every kernel
+// waits for its predecessor before it can finish, completion stays ordered along the whole chain;
+// because it releases its own dependents only after its wait, at most one kernel ahead of the
+// running one holds resources on the SMs.
+// Launched the ordinary way both calls do nothing.  Q3B200_PDL=0 in the environment turns the
+// attribute off.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+static inline bool pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* e = getenv("Q3B200_PDL");
+    enabled = (e && e[0] == '0') ? 0 : 1;
+  }
+  return enabled == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                         Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 }  // namespace q3

@@ -16,6 +16,8 @@ namespace q3 {
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ resid, int H, int V, int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* dst = resid + (size_t)t * H;
@@ -37,6 +39,8 @@ template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
                                    const float* __restrict__ w, T* __restrict__ out,
                                    const int* __restrict__ rows, int H, float eps) {
+  pdl_wait();
+  pdl_launch_dependents();
   extern __shared__ float row_buf[];
   __shared__ float scratch[32];
   const int src_row = rows ? rows[blockIdx.x] : blockIdx.x;
@@ -87,6 +91,8 @@ template <typename T>
 __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ resid, const T* __restrict__ delta,
                                         const float* __restrict__ w, T* __restrict__ out,
                                         const int* __restrict__ rows, int H, float eps) {
+  pdl_wait();
+  pdl_launch_dependents();
   extern __shared__ float row_buf[];
   __shared__ float scratch[32];
   const int src_row = rows ? rows[blockIdx.x] : blockIdx.x;
@@ -124,6 +130,8 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ resid, const T* __re
 template <typename T>
 __global__ void rmsnorm_rows_kernel(const T* __restrict__ x, const float* __restrict__ w,
                                     T* __restrict__ y, int rows, int dim, float eps) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -153,7 +161,7 @@ static int add_rmsnorm_launch(float* resid, const void* delta, const float* w, v
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  kern<<<n_rows, threads, smem, stream>>>(resid, (const T*)delta, w, (T*)out, rows, H, eps);
+  q3::launch(kern, dim3(n_rows), dim3(threads), smem, stream, resid, (const T*)delta, w, (T*)out, rows, H, eps);
   return launch_status();
 }
 
@@ -166,9 +174,9 @@ extern "C" int q3_embed(const void* table, int dtype, const int* ids, float* res
   int threads = ((H + 31) / 32) * 32;
   if (threads > 256) threads = 256;
   if (dtype == Q3_F32)
-    q3::embed_kernel<float><<<T, threads, 0, stream>>>((const float*)table, ids, resid, H, V, status);
+    q3::launch(q3::embed_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, ids, resid, H, V, status);
   else if (dtype == Q3_BF16)
-    q3::embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, resid, H, V, status);
+    q3::launch(q3::embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)table, ids, resid, H, V, status);
   else
     return Q3_ERR_DTYPE;
   return q3::launch_status();
@@ -199,9 +207,9 @@ extern "C" int q3_rmsnorm(const void* x, const float* w, void* y, int dtype, int
   const int warps = 4;
   const int grid = (rows + warps - 1) / warps;
   if (dtype == Q3_F32)
-    q3::rmsnorm_rows_kernel<float><<<grid, warps * 32, 0, stream>>>((const float*)x, w, (float*)y, rows, dim, eps);
+    q3::launch(q3::rmsnorm_rows_kernel<float>, dim3(grid), dim3(warps * 32), 0, stream, (const float*)x, w, (float*)y, rows, dim, eps);
   else if (dtype == Q3_BF16)
-    q3::rmsnorm_rows_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>((const __nv_bfloat16*)x, w, (__nv_bfloat16*)y, rows, dim, eps);
+    q3::launch(q3::rmsnorm_rows_kernel<__nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, stream, (const __nv_bfloat16*)x, w, (__nv_bfloat16*)y, rows, dim, eps);
   else
     return Q3_ERR_DTYPE;
   return q3::launch_status();

@@ -13,6 +13,8 @@ constexpr int GF_BM = 64, GF_BN = 64, GF_BK = 16, GF_THREADS = 256;
 __global__ void __launch_bounds__(GF_THREADS)
 gemm_f32_nt_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C,
                    int M, int N, int K, int lda, int ldw, int ldc) {
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ float As[GF_BK][GF_BM + 4];
   __shared__ float Ws[GF_BK][GF_BN + 4];
   const int m0 = blockIdx.y * GF_BM, n0 = blockIdx.x * GF_BN;
@@ -70,6 +72,6 @@ extern "C" int q3_gemm_f32_nt(const float* A, const float* W, float* C, int M, i
   if (K <= 0) return Q3_ERR_SIZE;
   dim3 grid((N + q3::GF_BN - 1) / q3::GF_BN, (M + q3::GF_BM - 1) / q3::GF_BM);
   if (grid.y > 65535) return Q3_ERR_SIZE;
-  q3::gemm_f32_nt_kernel<<<grid, q3::GF_THREADS, 0, stream>>>(A, W, C, M, N, K, lda, ldw, ldc);
+  q3::launch(q3::gemm_f32_nt_kernel, dim3(grid), dim3(q3::GF_THREADS), 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
   return q3::launch_status();
 }

@@ -57,42 +57,54 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
 #pragma unroll
   for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
-  if (active) {
-    // this warp's share of K, in groups of 32
-    const int groups32 = (K + 31) / 32;  // K is a multiple of 8: a lane's 8 values are all inside K or all outside
-    const int per = (groups32 + WK - 1) / WK;
-    const int g_lo = ksplit * per, g_hi = min(groups32, g_lo + per);
-    const int r_lo = min(row0 + gid, N - 1), r_hi = min(row0 + gid + 8, N - 1);  // rows past N are clamped, not stored
-    const __nv_bfloat16* w_lo = W + (size_t)r_lo * K + 8 * tid4;
-    const __nv_bfloat16* w_hi = W + (size_t)r_hi * K + 8 * tid4;
-    const __nv_bfloat16* x_row[NT];
-    bool x_ok[NT];
+  // this warp's share of K, in groups of 32
+  const int groups32 = (K + 31) / 32;  // K is a multiple of 8: a lane's 8 values are all inside K or all outside
+  const int per = (groups32 + WK - 1) / WK;
+  const int g_lo = ksplit * per, g_hi = active ? min(groups32, g_lo + per) : g_lo;
+  const int r_lo = min(row0 + gid, N - 1), r_hi = min(row0 + gid + 8, N - 1);  // rows past N are clamped, not stored
+  const __nv_bfloat16* w_lo = W + (size_t)r_lo * K + 8 * tid4;
+  const __nv_bfloat16* w_hi = W + (size_t)r_hi * K + 8 * tid4;
+  uint4 wl[GS_UNROLL], wh[GS_UNROLL];
+  auto load_w = [&](int g0, uint4 (&lo)[GS_UNROLL], uint4 (&hi)[GS_UNROLL]) {
 #pragma unroll
-    for (int i = 0; i < NT; ++i) {
-      const int tok = i * 8 + gid;
-      x_ok[i] = tok < T;
-      x_row[i] = X + (size_t)(x_ok[i] ? tok : 0) * K + 8 * tid4;
+    for (int u = 0; u < GS_UNROLL; ++u) {
+      const size_t k = (size_t)(g0 + u) * 32;
+      const bool in = g0 + u < g_hi && k + 8 * tid4 < (size_t)K;
+      lo[u] = in ? ldg_stream(w_lo + k) : make_uint4(0, 0, 0, 0);
+      hi[u] = in ? ldg_stream(w_hi + k) : make_uint4(0, 0, 0, 0);
     }
-    for (int g0 = g_lo; g0 < g_hi; g0 += GS_UNROLL) {
-      uint4 wl[GS_UNROLL], wh[GS_UNROLL], xv[GS_UNROLL][NT];
+  };
+  // The weights do not depend on the kernel before this one: their first batch is already on its
+  // way while that kernel finishes.  The activations are read only after the wait.
+  load_w(g_lo, wl, wh);
+  pdl_wait();
+  pdl_launch_dependents();
+  const __nv_bfloat16* x_row[NT];
+  bool x_ok[NT];
 #pragma unroll
-      for (int u = 0; u < GS_UNROLL; ++u) {
-        const size_t k = (size_t)(g0 + u) * 32;
-        const bool in = g0 + u < g_hi && k + 8 * tid4 < (size_t)K;
-        wl[u] = in ? ldg_stream(w_lo + k) : make_uint4(0, 0, 0, 0);
-        wh[u] = in ? ldg_stream(w_hi + k) : make_uint4(0, 0, 0, 0);
+  for (int i = 0; i < NT; ++i) {
+    const int tok = i * 8 + gid;
+    x_ok[i] = tok < T;
+    x_row[i] = X + (size_t)(x_ok[i] ? tok : 0) * K + 8 * tid4;
+  }
+  for (int g0 = g_lo; g0 < g_hi; g0 += GS_UNROLL) {
+    uint4 xv[GS_UNROLL][NT];
+    if (g0 != g_lo) load_w(g0, wl, wh);
 #pragma unroll
-        for (int i = 0; i < NT; ++i)
-          xv[u][i] = (in && x_ok[i]) ? __ldg(reinterpret_cast<const uint4*>(x_row[i] + k)) : make_uint4(0, 0, 0, 0);
+    for (int u = 0; u < GS_UNROLL; ++u) {
+      const size_t k = (size_t)(g0 + u) * 32;
+      const bool in = g0 + u < g_hi && k + 8 * tid4 < (size_t)K;
+#pragma unroll
+      for (int i = 0; i < NT; ++i)
+        xv[u][i] = (in && x_ok[i]) ? __ldg(reinterpret_cast<const uint4*>(x_row[i] + k)) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < GS_UNROLL; ++u)
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        mma_16816(acc[i], wl[u].x, wh[u].x, wl[u].y, wh[u].y, xv[u][i].x, xv[u][i].y);
+        mma_16816(acc[i], wl[u].z, wh[u].z, wl[u].w, wh[u].w, xv[u][i].z, xv[u][i].w);
       }
-#pragma unroll
-      for (int u = 0; u < GS_UNROLL; ++u)
-#pragma unroll
-        for (int i = 0; i < NT; ++i) {
-          mma_16816(acc[i], wl[u].x, wh[u].x, wl[u].y, wh[u].y, xv[u][i].x, xv[u][i].y);
-          mma_16816(acc[i], wl[u].z, wh[u].z, wl[u].w, wh[u].w, xv[u][i].z, xv[u][i].w);
-        }
-    }
   }
   // acc[i][0..1]: feature row0 + gid, tokens 8i + 2 tid4, +1;  acc[i][2..3]: feature row0 + gid + 8
 #pragma unroll
@@ -141,7 +153,7 @@ static int gemm_skinny_launch(const void* X, const void* W, void* out, int T, in
   const int per_block = GS_WARPS / wk;
   const unsigned grid = (groups + per_block - 1) / per_block;
 #define Q3_GS_GO(WK)                                                                               \
-  gemm_skinny_kernel<NT, WK, EPI, OutT><<<grid, GS_WARPS * 32, 0, stream>>>(                       \
+  q3::launch(gemm_skinny_kernel<NT, WK, EPI, OutT>, dim3(grid), dim3(GS_WARPS * 32), 0, stream,                        \
       (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (OutT*)out, T, N, K, ldo)
   if (wk == 1) Q3_GS_GO(1);
   else if (wk == 2) Q3_GS_GO(2);

@@ -27,6 +27,8 @@ qkv_post_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict_
                 const int* __restrict__ positions, const int* __restrict__ tok_seq,
                 const int* __restrict__ block_table, int table_stride, int page_size, int num_pages,
                 int Hq, int Hkv, int D, int rotary_dim, float eps, int write_kv, int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ float vec[QP_WARPS][QP_MAX_D];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -101,10 +103,14 @@ qkv_post_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __rest
                     const float* __restrict__ q_weight, const float* __restrict__ k_weight,
                     const float* __restrict__ inv_freq, const int* __restrict__ positions,
                     const int* __restrict__ tok_seq, const int* __restrict__ block_table, int table_stride,
-                    int page_size, int num_pages, int Hq, int Hkv, float eps, int write_kv, int* status) {
+                    int page_size, int num_pages, int Hq, int Hkv, float eps, int write_kv, int heads_per_block,
+                    int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
   constexpr int D = 32 * VPL;
-  // One block per token: the sines and cosines of the token's D / 2 angles are computed once and
-  // shared by all its heads; then each warp takes every eighth head.
+  // A block serves one token and the heads [blockIdx.y * heads_per_block, + heads_per_block): the
+  // sines and cosines of the token's D / 2 angles are computed once per block and shared by its
+  // heads (all heads of the token when there are many tokens, eight when there are few).
   __shared__ float cs[D];  // cos of pair j at [j], sin at [D / 2 + j]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -119,7 +125,8 @@ qkv_post_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __rest
     }
   }
   __syncthreads();
-  for (int head = warp; head < n_heads; head += QPV_WARPS) {
+  const int head_end = min(n_heads, (int)(blockIdx.y + 1) * heads_per_block);
+  for (int head = blockIdx.y * heads_per_block + warp; head < head_end; head += QPV_WARPS) {
   const bool is_q = head < Hq;
   const bool is_k = !is_q && head < Hq + Hkv;
   if (!is_q && !write_kv) continue;
@@ -223,14 +230,16 @@ extern "C" int q3_qkv_post(const void* qkv, int dtype, int T, int Hq, int Hkv, i
   dim3 grid(T, (n_heads + q3::QP_WARPS - 1) / q3::QP_WARPS);
   if (grid.y > 65535) return Q3_ERR_SIZE;
   const bool whole_rotation = inv_freq == nullptr || rotary_dim == D;
+  const int heads_per_block = T >= 256 ? n_heads : q3::QPV_WARPS;
   if (dtype == Q3_BF16 && whole_rotation && (D == 32 || D == 64 || D == 128 || D == 256) &&
       (uintptr_t)qkv % 16 == 0 && (uintptr_t)q_out % 16 == 0 && (uintptr_t)k_pages % 16 == 0 &&
       (uintptr_t)v_pages % 16 == 0) {
 #define Q3_QP_VEC(VPL)                                                                                            \
-  q3::qkv_post_vec_kernel<VPL><<<T, q3::QPV_WARPS * 32, 0, stream>>>(                                           \
+  q3::launch(q3::qkv_post_vec_kernel<VPL>, dim3(T, (n_heads + heads_per_block - 1) / heads_per_block),           \
+             dim3(q3::QPV_WARPS * 32), 0, stream,                                            \
       (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, q_weight, \
       k_weight, inv_freq, positions, tok_seq, block_table, table_stride, page_size, num_pages, Hq, Hkv, eps,       \
-      write_kv, status)
+      write_kv, heads_per_block, status)
     if (D == 32) Q3_QP_VEC(1);
     else if (D == 64) Q3_QP_VEC(2);
     else if (D == 128) Q3_QP_VEC(4);
@@ -239,12 +248,12 @@ extern "C" int q3_qkv_post(const void* qkv, int dtype, int T, int Hq, int Hkv, i
     return q3::launch_status();
   }
   if (dtype == Q3_F32)
-    q3::qkv_post_kernel<float><<<grid, q3::QP_WARPS * 32, 0, stream>>>(
+    q3::launch(q3::qkv_post_kernel<float>, dim3(grid), dim3(q3::QP_WARPS * 32), 0, stream, 
         (const float*)qkv, (float*)q_out, (float*)k_pages, (float*)v_pages, q_weight, k_weight, inv_freq,
         positions, tok_seq, block_table, table_stride, page_size, num_pages, Hq, Hkv, D, rotary_dim, eps,
         write_kv, status);
   else if (dtype == Q3_BF16)
-    q3::qkv_post_kernel<__nv_bfloat16><<<grid, q3::QP_WARPS * 32, 0, stream>>>(
+    q3::launch(q3::qkv_post_kernel<__nv_bfloat16>, dim3(grid), dim3(q3::QP_WARPS * 32), 0, stream, 
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages,
         q_weight, k_weight, inv_freq, positions, tok_seq, block_table, table_stride, page_size, num_pages,
         Hq, Hkv, D, rotary_dim, eps, write_kv, status);

@@ -87,6 +87,8 @@ sample_kernel(const float* __restrict__ logits, int V, size_t row_pitch,
               const float* __restrict__ temperature, const int* __restrict__ top_k,
               const long long* __restrict__ request_key, const int* __restrict__ position,
               unsigned long long seed, int* __restrict__ out, int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ Best best_scratch[32];
   __shared__ int count_scratch[32];
   const int r = blockIdx.x;
@@ -151,7 +153,7 @@ extern "C" int q3_sample(const float* logits, int R, int V, long long row_pitch,
   if (R <= 0) return 0;
   if (V <= 0) return Q3_ERR_SIZE;
   if (temperature && (!request_key || !position)) return Q3_ERR_SIZE;
-  q3::sample_kernel<<<R, 1024, 0, stream>>>(logits, V, (size_t)row_pitch, temperature, top_k, request_key,
+  q3::launch(q3::sample_kernel, dim3(R), dim3(1024), 0, stream, logits, V, (size_t)row_pitch, temperature, top_k, request_key,
                                             position, seed, out, status);
   return q3::launch_status();
 }
