@@ -333,3 +333,54 @@ extern "C" int q3_attn_decode(const void* q, const void* k_pages, const void* v_
 #undef Q3_AD_CASE
   return Q3_ERR_SIZE;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Decode attention for callers that cannot allocate (declared in attn_decode_noalloc.h).
+// The split-KV partials go to a fixed array that is part of the library image instead of a
+// buffer the caller provides.
+namespace q3 {
+
+constexpr size_t NOALLOC_SCRATCH_FLOATS = (size_t)4 << 20;  // 4 Mi floats = 16 MiB, per GPU that loads the library
+constexpr int NOALLOC_MAX_DEVICES = 64;
+
+static __device__ __align__(256) float g_decode_scratch[NOALLOC_SCRATCH_FLOATS];
+
+// In host code `g_decode_scratch` is only a handle for the symbol, not an address a kernel can use:
+// the device address is asked from the runtime once per device and kept.
+static float* g_decode_scratch_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
+
+static int noalloc_scratch(float** ptr) {
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return (int)e;
+  if (device < 0 || device >= NOALLOC_MAX_DEVICES) return Q3_ERR_SIZE;
+  if (g_decode_scratch_ptr[device] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_decode_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_decode_scratch_ptr[device] = p;
+  }
+  *ptr = g_decode_scratch_ptr[device];
+  return 0;
+}
+
+}  // namespace q3
+
+extern "C" long long q3_attn_decode_noalloc_capacity(void) { return (long long)q3::NOALLOC_SCRATCH_FLOATS; }
+
+extern "C" int q3_attn_decode_noalloc(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                      const int* q_start, const int* kv_len, const int* block_table,
+                                      int table_stride, int page_size, int num_pages, int B, int Hq, int Hkv, int D,
+                                      float scale, int window, int num_splits, int* status, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (num_splits < 1 || Hq <= 0 || D <= 0) return Q3_ERR_SIZE;
+  float* scratch = nullptr;
+  if (num_splits > 1) {
+    const unsigned long long need = (unsigned long long)B * Hq * num_splits * (unsigned long long)(D + 2);
+    if (need > q3::NOALLOC_SCRATCH_FLOATS) return Q3_ERR_SCRATCH;
+    const int code = q3::noalloc_scratch(&scratch);
+    if (code != 0) return code;
+  }
+  return q3_attn_decode(q, k_pages, v_pages, out, scratch, q_start, kv_len, block_table, table_stride, page_size,
+                        num_pages, B, Hq, Hkv, D, scale, window, num_splits, status, stream);
+}

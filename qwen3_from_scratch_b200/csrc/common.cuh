@@ -19,6 +19,7 @@
 #define Q3_ERR_DTYPE -1      // unknown dtype tag
 #define Q3_ERR_SIZE -2       // a size this kernel does not take (see the launcher's comment)
 #define Q3_ERR_ALIGN -3      // pointer or row pitch not aligned as the kernel needs
+#define Q3_ERR_SCRATCH -4    // the call needs more scratch memory than the fixed array holds
 
 // bits of the device status word that kernels OR into `status` instead of
 // faulting when table data is bad; the host reads it after the step.
