@@ -152,41 +152,53 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       mma_bf16(s[1], qa[kt], kb[2], kb[3]);
     }
     const int base_n = (my_first + i * AD_WARPS) * AD_KEYS;
-    const bool edge = base_n < lo || base_n + AD_KEYS - 1 > pos;
+    if (base_n < lo || base_n + AD_KEYS - 1 > pos) {  // only the first and the last tile of a sequence
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
+      for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int n = base_n + nt * 8 + 2 * tid4 + (j & 1);
-        float v = s[nt][j] * scale_log2;
-        if (edge && (n < lo || n > pos)) v = -INFINITY;
-        s[nt][j] = v;
-      }
+        for (int j = 0; j < 4; ++j) {
+          const int n = base_n + nt * 8 + 2 * tid4 + (j & 1);
+          if (n < lo || n > pos) s[nt][j] = -INFINITY;
+        }
+    }
+    // The scale is positive, so the maximum can be taken on the raw scores and the scale folded
+    // into the exponent: p = 2^(s * scale - m).
     float mx[2];
     mx[0] = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
     mx[1] = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+    float alpha[2], m_use[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-      const float m_new = fmaxf(m[r], mx[r]);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = exp2f(m[r] - m_use);
+      const float m_new = fmaxf(m[r], mx[r] * scale_log2);
+      m_use[r] = m_new == -INFINITY ? 0.f : m_new;
+      alpha[r] = exp2f(m[r] - m_use[r]);
       m[r] = m_new;
-      l[r] *= alpha;
+    }
+    // Once the running maximum has settled the correction factor is exactly one for every row of
+    // the warp, and the pass over the output registers is skipped.
+    if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {
 #pragma unroll
-      for (int i2 = 0; i2 < 2 * KT; ++i2) {
-        o[i2][2 * r] *= alpha;
-        o[i2][2 * r + 1] *= alpha;
+      for (int r = 0; r < 2; ++r) {
+        l[r] *= alpha[r];
+#pragma unroll
+        for (int i2 = 0; i2 < 2 * KT; ++i2) {
+          o[i2][2 * r] *= alpha[r];
+          o[i2][2 * r + 1] *= alpha[r];
+        }
       }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
-        const float p0 = exp2f(s[nt][2 * r] - m_use), p1 = exp2f(s[nt][2 * r + 1] - m_use);
+        const float p0 = exp2f(fmaf(s[nt][2 * r], scale_log2, -m_use[r]));
+        const float p1 = exp2f(fmaf(s[nt][2 * r + 1], scale_log2, -m_use[r]));
         s[nt][2 * r] = p0;
         s[nt][2 * r + 1] = p1;
         l[r] += p0 + p1;
       }
-    }
     uint32_t pa[4];
     pa[0] = pack_bf16(s[0][0], s[0][1]);
     pa[1] = pack_bf16(s[0][2], s[0][3]);
