@@ -1,0 +1,365 @@
+// Paged causal attention for prompt portions on the fifth-generation tensor cores (tcgen05),
+// bfloat16, head size 64 or 128, pages of 8 to 64 tokens, no window.
+//
+// A block owns 128 query rows of one kv head (rows are (token, head-in-group) pairs as in
+// attn_prefill.cu) and walks the keys in tiles of 64:
+//   loader thread   TMA brings the tile's pages of K and of V into shared memory (128-byte swizzle),
+//                   one box per page and per 64 values of the head; the page ids come from the
+//                   block table, the tensor maps cover a layer's whole K (or V) pool.
+//   issue thread    S = Q K^T   (tcgen05.mma, both operands K-major, accumulator: 64 TMEM columns)
+//                   O += P V    (P K-major from shared memory, V MN-major; accumulator: D columns)
+//   128 softmax threads, one per query row: read S from TMEM (a thread owns a whole row, so the
+//                   row maximum and sum need no shuffles), mask the diagonal tile, keep a running
+//                   reference maximum and denominator in float32, write P as bfloat16 into shared
+//                   memory in the swizzled layout the tensor cores read, and rescale O in TMEM
+//                   when the reference maximum has to move (it moves only when the row maximum
+//                   exceeds it by more than 2^8, so the rescale is rare after the first tiles).
+// Two blocks fit an SM (80 KB of shared memory, 256 TMEM columns each), so one block's softmax
+// overlaps the other's matrix products.  All mbarrier waits are bounded (see tc_common.cuh).
+//
+// Reference for the math: kernels/triton/paged_attn.py:89-181 (online softmax with exp2, P rounded
+// to the value dtype before P V), models/attn.py:388-400 (scale, causal on absolute positions).
+#include "tc_common.cuh"
+
+namespace q3 {
+
+constexpr int AT_BM = 128;  // query rows per block
+constexpr int AT_BN = 64;   // keys per tile
+constexpr int AT_THREADS = 192;
+
+template <int D>
+struct AttnTcShape {
+  static constexpr int ATOMS = D / 64;                 // 64-wide swizzle atoms along the head
+  static constexpr int Q_BYTES = AT_BM * D * 2;
+  static constexpr int K_BYTES = AT_BN * D * 2;
+  static constexpr int V_BYTES = AT_BN * D * 2;
+  static constexpr int P_BYTES = AT_BM * AT_BN * 2;
+  static constexpr int BAR_BYTES = 128;
+  static constexpr size_t SMEM_BYTES = (size_t)Q_BYTES + K_BYTES + V_BYTES + P_BYTES + BAR_BYTES + 1024;
+  static constexpr int TMEM_COLS = 256;                // S: 64 columns at 0, O: D columns at 64
+};
+
+// byte offset of value (row, col) in a [rows x 64] bfloat16 tile with the 128-byte swizzle
+__device__ __forceinline__ uint32_t sw128_offset(int row, int col) {
+  return (uint32_t)row * 128u + ((((uint32_t)col >> 3) ^ ((uint32_t)row & 7u)) << 4) + (((uint32_t)col & 7u) << 1);
+}
+
+template <int D>
+__global__ void __launch_bounds__(AT_THREADS, 2)
+attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+               const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+               const int* __restrict__ q_start, const int* __restrict__ kv_len,
+               const int* __restrict__ block_table, int table_stride, int page_size, int num_pages, int Hq,
+               int Hkv, float scale_log2, int* status) {
+  using S = AttnTcShape<D>;
+  constexpr int ATOMS = S::ATOMS;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* q_s = base;
+  unsigned char* k_s = q_s + S::Q_BYTES;
+  unsigned char* v_s = k_s + S::K_BYTES;
+  unsigned char* p_s = v_s + S::V_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + S::P_BYTES);
+  uint64_t* k_full = bars + 0;
+  uint64_t* k_empty = bars + 1;
+  uint64_t* v_full = bars + 2;
+  uint64_t* v_empty = bars + 3;
+  uint64_t* s_ready = bars + 4;
+  uint64_t* p_ready = bars + 5;
+  uint64_t* pv_done = bars + 6;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 8);
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hk = blockIdx.y, b = blockIdx.z;
+  const int g = Hq / Hkv;
+  const int qs = q_start[b];
+  const int q_len = q_start[b + 1] - qs;
+  const int len = kv_len[b];
+  const int total_rows = q_len * g;
+  // heavy tiles (late queries, many keys) are scheduled first
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int row0 = qt * AT_BM;
+  if (row0 >= total_rows) return;  // before any barrier or allocation: the whole block leaves
+  const int past = len - q_len;
+  const int last_row = min(total_rows, row0 + AT_BM) - 1;
+  const int pos_first = past + row0 / g, pos_last = past + last_row / g;
+  const int n_tiles = pos_last / AT_BN + 1;
+  const int* table = block_table + (size_t)b * table_stride;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(k_full, 1);
+    mbar_init(k_empty, 1);
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
+    mbar_init(s_ready, 1);
+    mbar_init(p_ready, AT_BM);
+    mbar_init(pv_done, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  pdl_wait();  // q and the pages come from the kernels before this one
+  pdl_launch_dependents();
+  // Tensor memory is taken only after the wait: a block that holds TMEM while it waits for the
+  // kernel before it could keep that kernel's own blocks from ever getting theirs.
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_holder)),
+                 "r"((uint32_t)S::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+
+  // the query tile, written in the swizzled K-major layout by the softmax threads (row = thread)
+  if (warp < 4) {
+    const int rr = warp * 32 + lane;
+    const int R = row0 + rr;
+    const __nv_bfloat16* src = R < total_rows ? q + ((size_t)(qs + R / g) * Hq + hk * g + R % g) * D : nullptr;
+#pragma unroll
+    for (int c = 0; c < D / 8; ++c) {
+      const uint4 v = src ? *reinterpret_cast<const uint4*>(src + c * 8) : make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(q_s + (c / 8) * (AT_BM * 128) + sw128_offset(rr, (c % 8) * 8)) = v;
+    }
+    fence_async_proxy();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_s = *tmem_holder;
+  const uint32_t tmem_o = tmem_s + AT_BN;
+
+  if (warp == 5) {
+    // ------------------------------------------------------------------ loader
+    if (lane == 0) {
+      const int pages_per_tile = AT_BN / page_size;
+      for (int j = 0; j < n_tiles; ++j) {
+        // pages of this tile that the sequence really has (the last tile may reach past kv_len)
+        int have = 0;
+        for (int p = 0; p < pages_per_tile; ++p)
+          if (j * AT_BN + p * page_size < len) have = p + 1;
+        const uint32_t bytes = (uint32_t)have * page_size * D * 2;
+        if (j > 0 && !mbar_wait(k_empty, (j - 1) & 1, &abort_flag)) { abort_flag = 1; atomicOr(status, Q3_STATUS_TIMEOUT); break; }
+        mbar_expect_tx(k_full, bytes);
+        for (int p = 0; p < have; ++p) {
+          const int page = table[(j * AT_BN) / page_size + p];
+          const bool ok = page >= 0 && page < num_pages;
+          if (!ok) atomicOr(status, Q3_STATUS_BAD_PAGE);
+          const int y = ((ok ? page : 0) * Hkv + hk) * page_size;
+#pragma unroll
+          for (int a = 0; a < ATOMS; ++a)
+            tma_load_2d(k_s + a * (AT_BN * 128) + p * page_size * 128, &map_k, k_full, a * 64, y);
+        }
+        if (j > 0 && !mbar_wait(v_empty, (j - 1) & 1, &abort_flag)) { abort_flag = 1; atomicOr(status, Q3_STATUS_TIMEOUT); break; }
+        mbar_expect_tx(v_full, bytes);
+        for (int p = 0; p < have; ++p) {
+          const int page = table[(j * AT_BN) / page_size + p];
+          const bool ok = page >= 0 && page < num_pages;
+          const int y = ((ok ? page : 0) * Hkv + hk) * page_size;
+#pragma unroll
+          for (int a = 0; a < ATOMS; ++a)
+            tma_load_2d(v_s + a * (AT_BN * 128) + p * page_size * 128, &map_v, v_full, a * 64, y);
+        }
+      }
+    }
+  } else if (warp == 4) {
+    // ------------------------------------------------------------------ tensor-core issue
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc(AT_BN, 0);  // 128 x 64, K and Q both K-major
+      constexpr uint32_t idesc_o = umma_idesc(D, 1);      // 128 x D, V MN-major
+      for (int j = 0; j < n_tiles; ++j) {
+        if (!mbar_wait(k_full, j & 1, &abort_flag)) { abort_flag = 1; atomicOr(status, Q3_STATUS_TIMEOUT); break; }
+        tcgen05_fence_after();
+#pragma unroll
+        for (int t = 0; t < D / 16; ++t) {
+          const uint64_t a_desc = umma_desc_sw128(q_s + (t / 4) * (AT_BM * 128)) + 2 * (t % 4);
+          const uint64_t b_desc = umma_desc_sw128(k_s + (t / 4) * (AT_BN * 128)) + 2 * (t % 4);
+          umma_f16(tmem_s, a_desc, b_desc, idesc_s, t != 0);
+        }
+        umma_commit(s_ready);
+        umma_commit(k_empty);
+        if (!mbar_wait(p_ready, j & 1, &abort_flag)) { abort_flag = 1; atomicOr(status, Q3_STATUS_TIMEOUT); break; }
+        if (!mbar_wait(v_full, j & 1, &abort_flag)) { abort_flag = 1; atomicOr(status, Q3_STATUS_TIMEOUT); break; }
+        tcgen05_fence_after();
+#pragma unroll
+        for (int t = 0; t < AT_BN / 16; ++t) {
+          const uint64_t a_desc = umma_desc_sw128(p_s) + 2 * t;
+          const uint64_t b_desc = umma_desc_sw128_mn(v_s + t * 2048, AT_BN * 128);
+          umma_f16(tmem_o, a_desc, b_desc, idesc_o, (j | t) != 0);
+        }
+        umma_commit(pv_done);
+        umma_commit(v_empty);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax, one row per thread
+    const int rr = warp * 32 + lane;
+    const int R = row0 + rr;
+    const bool valid_row = R < total_rows;
+    const int my_pos = valid_row ? past + R / g : pos_last;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (!mbar_wait(s_ready, j & 1, &abort_flag)) { ok = false; break; }
+      tcgen05_fence_after();
+      uint32_t sv[2][32];
+      tmem_ld_32(tmem_s + lane_base, sv[0]);
+      tmem_ld_32(tmem_s + lane_base + 32, sv[1]);
+      tmem_wait_ld();
+      const int base_n = j * AT_BN;
+      float mx = -INFINITY;
+      if (base_n + AT_BN - 1 > pos_first) {  // the diagonal: keys beyond this row's position are hidden
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const float v = (base_n + h * 32 + c <= my_pos) ? __uint_as_float(sv[h][c]) : -INFINITY;
+            sv[h][c] = __float_as_uint(v);
+            mx = fmaxf(mx, v);
+          }
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(sv[h][c]));
+      }
+      mx *= scale_log2;
+      // the reference maximum moves only when it must: probabilities up to 2^8 are harmless
+      float alpha = 1.f;
+      if (mx > m_ref + 8.f) {
+        alpha = m_ref == -INFINITY ? 0.f : exp2f(m_ref - mx);
+        m_ref = mx;
+      }
+      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+      // P and O belong to the tensor cores until the previous tile's P V has finished
+      if (j > 0 && !mbar_wait(pv_done, (j - 1) & 1, &abort_flag)) { ok = false; break; }
+      tcgen05_fence_after();
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t ov[32];
+          tmem_ld_32(tmem_o + lane_base + c0, ov);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * alpha);
+          tmem_st_32(tmem_o + lane_base + c0, ov);
+        }
+        tmem_wait_st();
+      }
+      l *= alpha;
+      float sum = 0.f;
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) {
+          uint32_t pk[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float p0 = exp2f(fmaf(__uint_as_float(sv[h][c8 * 8 + 2 * e]), scale_log2, -m_use));
+            const float p1 = exp2f(fmaf(__uint_as_float(sv[h][c8 * 8 + 2 * e + 1]), scale_log2, -m_use));
+            sum += p0 + p1;
+            pk[e] = pack2(__float_as_uint(p0), __float_as_uint(p1));
+          }
+          *reinterpret_cast<uint4*>(p_s + sw128_offset(rr, h * 32 + c8 * 8)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+      l += sum;
+      // keys past the end of the sequence in the last tile: their V rows were not loaded; zero them
+      if (base_n + AT_BN > len) {
+        if (!mbar_wait(v_full, j & 1, &abort_flag)) { ok = false; break; }
+        const int first_bad = len - base_n;
+        for (int e = threadIdx.x; e < (AT_BN - first_bad) * (D / 8); e += AT_BM) {
+          const int key = first_bad + e / (D / 8), c = e % (D / 8);
+          *reinterpret_cast<uint4*>(v_s + (c / 8) * (AT_BN * 128) + sw128_offset(key, (c % 8) * 8)) =
+              make_uint4(0, 0, 0, 0);
+        }
+      }
+      fence_async_proxy();
+      tcgen05_fence_before();
+      mbar_arrive(p_ready);
+    }
+    if (!ok && lane == 0) {
+      abort_flag = 1;
+      atomicOr(status, Q3_STATUS_TIMEOUT);
+    }
+    // the last P V, then O / l
+    if (ok && mbar_wait(pv_done, (n_tiles - 1) & 1, &abort_flag)) {
+      tcgen05_fence_after();
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      __nv_bfloat16* dst = valid_row ? out + ((size_t)(qs + R / g) * Hq + hk * g + R % g) * D : nullptr;
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t ov[32];
+        tmem_ld_32(tmem_o + lane_base + c0, ov);
+        tmem_wait_ld();
+        if (dst) {
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            uint4 pk;
+            pk.x = pack2(__float_as_uint(__uint_as_float(ov[8 * v4 + 0]) * inv), __float_as_uint(__uint_as_float(ov[8 * v4 + 1]) * inv));
+            pk.y = pack2(__float_as_uint(__uint_as_float(ov[8 * v4 + 2]) * inv), __float_as_uint(__uint_as_float(ov[8 * v4 + 3]) * inv));
+            pk.z = pack2(__float_as_uint(__uint_as_float(ov[8 * v4 + 4]) * inv), __float_as_uint(__uint_as_float(ov[8 * v4 + 5]) * inv));
+            pk.w = pack2(__float_as_uint(__uint_as_float(ov[8 * v4 + 6]) * inv), __float_as_uint(__uint_as_float(ov[8 * v4 + 7]) * inv));
+            reinterpret_cast<uint4*>(dst + c0)[v4] = pk;
+          }
+        }
+      }
+    } else if (lane == 0) {
+      abort_flag = 1;
+      atomicOr(status, Q3_STATUS_TIMEOUT);
+    }
+  }
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"((uint32_t)S::TMEM_COLS)
+                 : "memory");
+  }
+}
+
+template <int D>
+static int attn_tc_launch(const void* q, const void* k_pages, const void* v_pages, void* out, const int* q_start,
+                          const int* kv_len, const int* block_table, int table_stride, int page_size, int num_pages,
+                          int B, int max_q_len, int Hq, int Hkv, float scale, int* status, cudaStream_t stream) {
+  using S = AttnTcShape<D>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  CUtensorMap map_k, map_v;
+  const uint64_t rows = (uint64_t)num_pages * Hkv * page_size;
+  int code = cached_map(&map_k, k_pages, rows, D, (uint32_t)page_size);
+  if (code) return code;
+  code = cached_map(&map_v, v_pages, rows, D, (uint32_t)page_size);
+  if (code) return code;
+  const int g = Hq / Hkv;
+  const long long tiles = ((long long)max_q_len * g + AT_BM - 1) / AT_BM;
+  if (tiles > 0x7fffffffLL) return Q3_ERR_SIZE;
+  dim3 grid((unsigned)tiles, Hkv, B);
+  q3::launch(attn_tc_kernel<D>, grid, dim3(AT_THREADS), S::SMEM_BYTES, stream, map_k, map_v, (const __nv_bfloat16*)q,
+             (__nv_bfloat16*)out, q_start, kv_len, block_table, table_stride, page_size, num_pages, Hq, Hkv,
+             scale * 1.4426950408889634f, status);
+  return launch_status();
+}
+
+}  // namespace q3
+
+// Same arguments as q3_attn_prefill, without a window.  Takes D = 64 or 128 and page sizes 8, 16, 32, 64;
+// refuses the rest (the caller then uses q3_attn_prefill).
+extern "C" int q3_attn_tc(const void* q, const void* k_pages, const void* v_pages, void* out, const int* q_start,
+                          const int* kv_len, const int* block_table, int table_stride, int page_size, int num_pages,
+                          int B, int max_q_len, int Hq, int Hkv, int D, float scale, int* status,
+                          cudaStream_t stream) {
+  if (B <= 0 || max_q_len <= 0) return 0;
+  if (Hkv <= 0 || Hq % Hkv || (D != 64 && D != 128) || table_stride <= 0 || B > 65535 || Hkv > 65535 ||
+      (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64))
+    return Q3_ERR_SIZE;
+  if ((uintptr_t)q % 16 || (uintptr_t)k_pages % 16 || (uintptr_t)v_pages % 16 || (uintptr_t)out % 16)
+    return Q3_ERR_ALIGN;
+  if (D == 64)
+    return q3::attn_tc_launch<64>(q, k_pages, v_pages, out, q_start, kv_len, block_table, table_stride, page_size,
+                                  num_pages, B, max_q_len, Hq, Hkv, scale, status, stream);
+  return q3::attn_tc_launch<128>(q, k_pages, v_pages, out, q_start, kv_len, block_table, table_stride, page_size,
+                                 num_pages, B, max_q_len, Hq, Hkv, scale, status, stream);
+}

@@ -20,6 +20,7 @@
 #define Q3_ERR_SIZE -2       // a size this kernel does not take (see the launcher's comment)
 #define Q3_ERR_ALIGN -3      // pointer or row pitch not aligned as the kernel needs
 #define Q3_ERR_SCRATCH -4    // the call needs more scratch memory than the fixed array holds
+#define Q3_ERR_DRIVER -5     // the CUDA driver refused a tensor-map request (or lacks the entry point)
 
 // bits of the device status word that kernels OR into `status` instead of
 // faulting when table data is bad; the host reads it after the step.
@@ -27,6 +28,7 @@
 #define Q3_STATUS_BAD_PAGE 2    // page id outside the pool where a live position needs one
 #define Q3_STATUS_BAD_POSITION 4  // negative position or sequence index
 #define Q3_STATUS_BAD_LOGITS 8    // a row of logits with no comparable value (all NaN)
+#define Q3_STATUS_TIMEOUT 16      // a bounded wait on an mbarrier ran out; the block gave up cleanly
 
 namespace q3 {
 

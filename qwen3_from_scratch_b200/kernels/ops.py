@@ -22,6 +22,7 @@ STATUS_BITS = {
     2: "a page id outside the pool where a live position needs one",
     4: "a negative position or sequence index",
     8: "a row of logits without a comparable value (all NaN)",
+    16: "a bounded wait inside a kernel ran out (the kernel gave up cleanly)",
 }
 
 
@@ -59,7 +60,11 @@ _SIGNATURES = {
     "q3_attn_prefill": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
                         _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p,
                         _c_void_p],
+    "q3_attn_tc": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
     "q3_swiglu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "q3_gemm_tc": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                   _c_void_p],
     "q3_gemm_skinny": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "q3_sample": [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ull,
                   _c_void_p, _c_void_p, _c_void_p],
@@ -147,6 +152,10 @@ def _done(kernel: str, code: int, detail: str = "") -> None:
         raise KernelError(f"{kernel}: dtype not taken ({detail})")
     if code == -3:
         raise KernelError(f"{kernel}: misaligned argument ({detail})")
+    if code == -4:
+        raise KernelSizeError(f"{kernel}: needs more scratch memory than is provided ({detail})")
+    if code == -5:
+        raise KernelError(f"{kernel}: the CUDA driver refused a tensor-map request ({detail})")
     raise KernelError(f"{kernel}: CUDA launch failed with error {code} ({detail})")
 
 
@@ -375,6 +384,28 @@ def rope(x: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, positions: to
     _done("rope", code, f"head_dim {d}, rotary_dim {rotary_dim}")
 
 
+def gemm_tc_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.shape[1] % 8 == 0
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
+            swiglu_blocks: bool = False) -> None:
+    """out[M, N] = x[M, K] @ w[N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in TMEM).
+    ``swiglu_blocks``: w's rows alternate gate/up in blocks of eight and out is [M, N / 2]."""
+    _check("gemm_tc.x", x, torch.bfloat16)
+    _check("gemm_tc.w", w, torch.bfloat16)
+    _check("gemm_tc.out", out)
+    M, K = x.shape
+    N = w.shape[0]
+    want_cols = N // 2 if swiglu_blocks else N
+    if w.shape[1] != K or tuple(out.shape) != (M, want_cols) or out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"gemm_tc: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
+    code = library().q3_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, want_cols,
+                                1 if out.dtype == torch.float32 else 0, 1 if swiglu_blocks else 0,
+                                status.data_ptr(), _stream())
+    _done("gemm_tc", code, f"M {M} N {N} K {K}")
+
+
 # ------------------------------------------------------------------ fast bfloat16 attention
 MAX_DECODE_SPLITS = 32
 
@@ -475,13 +506,35 @@ def attn_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, 
     _done("attn_prefill", code, f"heads {Hq}/{Hkv}, head_dim {D}")
 
 
+def attn_tc_takes(head_dim: int, page_size: int, window: int) -> bool:
+    """Whether the tcgen05 portion kernel takes this shape (else the mma.sync one runs)."""
+    return head_dim in (64, 128) and page_size in (8, 16, 32, 64) and not (window and window > 0)
+
+
+def attn_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
+            q_start: torch.Tensor, kv_len: torch.Tensor, block_table: torch.Tensor, num_seqs: int,
+            max_q_len: int, scale: float, status: torch.Tensor) -> None:
+    """Portion attention on the tcgen05 tensor cores: TMA-fed pages, S and O in tensor memory."""
+    T, Hq, D, num_pages, Hkv, page_size = _attn_common("attn_tc", q, k_pages, v_pages, out, q_start, kv_len,
+                                                        block_table)
+    if q_start.numel() < num_seqs + 1 or kv_len.numel() < num_seqs or block_table.shape[0] < num_seqs:
+        raise KernelError(f"attn_tc: {num_seqs} sequences, q_start {q_start.numel()}, kv_len {kv_len.numel()}")
+    code = library().q3_attn_tc(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(),
+                                q_start.data_ptr(), kv_len.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+                                page_size, num_pages, num_seqs, int(max_q_len), Hq, Hkv, D, float(scale),
+                                status.data_ptr(), _stream())
+    _done("attn_tc", code, f"heads {Hq}/{Hkv}, head_dim {D}, page {page_size}")
+
+
 def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                     q_start: torch.Tensor, kv_len: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
                     num_seqs: int, num_decode: int, max_q_len: int, max_kv_len: int, scale: float, window: int,
-                    status: torch.Tensor, partial: Optional[torch.Tensor] = None) -> None:
+                    status: torch.Tensor, partial: Optional[torch.Tensor] = None,
+                    portion_kernel: str = "auto") -> None:
     """Causal attention of a mixed batch over the pages: rows [0, num_decode) bring one token each and
-    go to the split-KV decode kernel, the rest to the portion kernel; shapes the tensor-core kernels
-    do not take (and float32) go to the plain kernel."""
+    go to the split-KV decode kernel, the rest to a portion kernel (tcgen05 where it takes the shape,
+    else mma.sync; ``portion_kernel="mma"`` forces the latter); shapes no tensor-core kernel takes
+    (and float32) go to the plain kernel."""
     T, Hq, D = q.shape
     Hkv = k_pages.shape[1]
     if not fast_attention_takes(q.dtype, Hq, Hkv, D):
@@ -494,5 +547,8 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         attn_decode(q, k_pages, v_pages, out, partial, q_start, kv_len, block_table, num_decode, scale, window,
                     splits, status)
     if num_seqs > num_decode:
-        attn_prefill(q, k_pages, v_pages, out, q_start[num_decode:], kv_len[num_decode:], block_table[num_decode:],
-                     num_seqs - num_decode, max_q_len, scale, window, status)
+        rest = (q_start[num_decode:], kv_len[num_decode:], block_table[num_decode:], num_seqs - num_decode, max_q_len)
+        if portion_kernel != "mma" and attn_tc_takes(D, k_pages.shape[2], window):
+            attn_tc(q, k_pages, v_pages, out, *rest, scale, status)
+        else:
+            attn_prefill(q, k_pages, v_pages, out, *rest, scale, window, status)

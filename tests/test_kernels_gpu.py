@@ -326,7 +326,8 @@ def test_attn_ref_window_edge_is_exact():
     assert not torch.equal(out0[19], out1[19])    # query 19 still sees key 10
 
 
-def run_fast(q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, window, splits=None):
+def run_fast(q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, window, splits=None,
+             portion_kernel="auto"):
     """The tensor-core kernels through the dispatcher (or the decode kernel with a forced split count).
     Unused slots of the pages hold NaN: anything read past a sequence's keys poisons the result."""
     o = ops()
@@ -351,7 +352,8 @@ def run_fast(q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, w
     args = (dev(q_sorted), k_pages, v_pages, out)
     if splits is None:
         o.paged_attention(*args, dev(q_start), dev(torch.tensor(kl, dtype=torch.int32)), dev(tok_seq),
-                          dev(table_tensor(tb)), len(ql), num_decode, max(ql), max(kl), scale, window or 0, st, partial)
+                          dev(table_tensor(tb)), len(ql), num_decode, max(ql), max(kl), scale, window or 0, st, partial,
+                          portion_kernel=portion_kernel)
     else:
         assert num_decode == len(ql)
         o.attn_decode(*args, partial, dev(q_start), dev(torch.tensor(kl, dtype=torch.int32)), dev(table_tensor(tb)),
@@ -376,11 +378,23 @@ FAST_SHAPES = ATTN_SHAPES + [
 ]
 
 
+FAST_SHAPES += [
+    (16, 8, 128, 16, [2048], [2048], None),                      # a whole long prompt: many key tiles per query tile
+    (4, 2, 64, 8, [333, 64, 191], [100, 64, 191], None),          # head size 64, pages of 8, ragged ends
+    (8, 4, 128, 32, [500, 70], [37, 70], None),                   # pages of 32
+    (2, 1, 128, 64, [129], [129], None),                          # pages of 64
+]
+
+
+@pytest.mark.parametrize("portion_kernel", ["auto", "mma"])
 @pytest.mark.parametrize("case", FAST_SHAPES)
-def test_fast_attention_against_plain(case):
+def test_fast_attention_against_plain(case, portion_kernel):
+    """``auto`` sends portions to the tcgen05 kernel where it takes the shape (head 64 / 128, pages of
+    8..64, no window) and to the mma.sync kernel otherwise; ``mma`` tests the latter on every shape."""
     hq, hkv, d, page_size, kv_lens, q_lens, window = case
     q, k_list, v_list, tables, num_pages = attention_case("bfloat16", hq, hkv, d, page_size, kv_lens, q_lens, window)
-    out = run_fast(q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, window)
+    out = run_fast(q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, window,
+                   portion_kernel=portion_kernel)
     want = reference_attention(q.double(), [k.double() for k in k_list], [v.double() for v in v_list], q_lens, window)
     # probabilities are rounded to bfloat16 before P.V (as the reference does) and so is the output:
     # two roundings of 2^-9 each
