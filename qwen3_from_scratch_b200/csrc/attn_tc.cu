@@ -14,8 +14,9 @@
 //                   memory in the swizzled layout the tensor cores read, and rescale O in TMEM
 //                   when the reference maximum has to move (it moves only when the row maximum
 //                   exceeds it by more than 2^8, so the rescale is rare after the first tiles).
-// Two blocks fit an SM (80 KB of shared memory, 256 TMEM columns each), so one block's softmax
-// overlaps the other's matrix products.  All mbarrier waits are bounded (see tc_common.cuh).
+// K and V tiles are double-buffered and so is S in TMEM, so the loads and the next tile's Q K^T run
+// while the softmax threads work.  Two blocks fit an SM (112 KB of shared memory, 256 TMEM columns
+// each), so one block's softmax also overlaps the other's matrix products.  All mbarrier waits are bounded (see tc_common.cuh).
 //
 // Reference for the math: kernels/triton/paged_attn.py:89-181 (online softmax with exp2, P rounded
 // to the value dtype before P V), models/attn.py:388-400 (scale, causal on absolute positions).
@@ -35,8 +36,10 @@ struct AttnTcShape {
   static constexpr int V_BYTES = AT_BN * D * 2;
   static constexpr int P_BYTES = AT_BM * AT_BN * 2;
   static constexpr int BAR_BYTES = 128;
-  static constexpr size_t SMEM_BYTES = (size_t)Q_BYTES + K_BYTES + V_BYTES + P_BYTES + BAR_BYTES + 1024;
-  static constexpr int TMEM_COLS = 256;                // S: 64 columns at 0, O: D columns at 64
+  // K and V tiles are double-buffered; no slack for alignment: the dynamic shared memory of a block
+  // that has no static shared memory starts on a 1024-byte boundary (checked in the kernel)
+  static constexpr size_t SMEM_BYTES = (size_t)Q_BYTES + 2 * K_BYTES + 2 * V_BYTES + P_BYTES + BAR_BYTES;
+  static constexpr int TMEM_COLS = 256;                // S: two buffers of 64 columns at 0 and 64, O: D columns at 128
 };
 
 // byte offset of value (row, col) in a [rows x 64] bfloat16 tile with the 128-byte swizzle
@@ -53,22 +56,22 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                int Hkv, float scale_log2, int* status) {
   using S = AttnTcShape<D>;
   constexpr int ATOMS = S::ATOMS;
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  unsigned char* q_s = base;
-  unsigned char* k_s = q_s + S::Q_BYTES;
-  unsigned char* v_s = k_s + S::K_BYTES;
-  unsigned char* p_s = v_s + S::V_BYTES;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* q_s = smem_raw;
+  unsigned char* k_s = q_s + S::Q_BYTES;       // two stages
+  unsigned char* v_s = k_s + 2 * S::K_BYTES;   // two stages
+  unsigned char* p_s = v_s + 2 * S::V_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + S::P_BYTES);
-  uint64_t* k_full = bars + 0;
-  uint64_t* k_empty = bars + 1;
-  uint64_t* v_full = bars + 2;
-  uint64_t* v_empty = bars + 3;
-  uint64_t* s_ready = bars + 4;
-  uint64_t* p_ready = bars + 5;
-  uint64_t* pv_done = bars + 6;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 8);
-  __shared__ int abort_flag;
+  uint64_t* k_full = bars + 0;   // [2]
+  uint64_t* k_empty = bars + 2;  // [2]
+  uint64_t* v_full = bars + 4;   // [2]
+  uint64_t* v_empty = bars + 6;  // [2]
+  uint64_t* s_ready = bars + 8;  // [2]
+  uint64_t* p_ready = bars + 10;
+  uint64_t* pv_done = bars + 11;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 12);
+  int* abort_word = reinterpret_cast<int*>(bars + 13);
+#define abort_flag (*abort_word)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hk = blockIdx.y, b = blockIdx.z;
@@ -89,11 +92,17 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    mbar_init(k_full, 1);
-    mbar_init(k_empty, 1);
-    mbar_init(v_full, 1);
-    mbar_init(v_empty, 1);
-    mbar_init(s_ready, 1);
+    if (s_addr(smem_raw) & 1023u) {  // the swizzled tiles need this; never seen, but a wrong answer must not be silent
+      abort_flag = 1;
+      atomicOr(status, Q3_STATUS_TIMEOUT);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(k_full + i, 1);
+      mbar_init(k_empty + i, 1);
+      mbar_init(v_full + i, 1);
+      mbar_init(v_empty + i, 1);
+      mbar_init(s_ready + i, 1);
+    }
     mbar_init(p_ready, AT_BM);
     mbar_init(pv_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -124,8 +133,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
-  const uint32_t tmem_s = *tmem_holder;
-  const uint32_t tmem_o = tmem_s + AT_BN;
+  const uint32_t tmem_s = *tmem_holder;           // S of tile j lives at column (j & 1) * 64
+  const uint32_t tmem_o = tmem_s + 2 * AT_BN;
 
   if (warp == 5) {
     // ------------------------------------------------------------------ loader
@@ -137,8 +146,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         for (int p = 0; p < pages_per_tile; ++p)
           if (j * AT_BN + p * page_size < len) have = p + 1;
         const uint32_t bytes = (uint32_t)have * page_size * D * 2;
-        if (j > 0 && !mbar_wait(k_empty, (j - 1) & 1, &abort_flag)) { abort_flag = 1; atomicOr(status, Q3_STATUS_TIMEOUT); break; }
-        mbar_expect_tx(k_full, bytes);
+        const int st = j & 1;
+        const uint32_t use = (uint32_t)j >> 1;
+        if (use > 0 && !mbar_wait(k_empty + st, (use - 1) & 1, &abort_flag)) { abort_flag = 1; atomicOr(status, Q3_STATUS_TIMEOUT); break; }
+        mbar_expect_tx(k_full + st, bytes);
         for (int p = 0; p < have; ++p) {
           const int page = table[(j * AT_BN) / page_size + p];
           const bool ok = page >= 0 && page < num_pages;
@@ -146,17 +157,17 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
           const int y = ((ok ? page : 0) * Hkv + hk) * page_size;
 #pragma unroll
           for (int a = 0; a < ATOMS; ++a)
-            tma_load_2d(k_s + a * (AT_BN * 128) + p * page_size * 128, &map_k, k_full, a * 64, y);
+            tma_load_2d(k_s + st * S::K_BYTES + a * (AT_BN * 128) + p * page_size * 128, &map_k, k_full + st, a * 64, y);
         }
-        if (j > 0 && !mbar_wait(v_empty, (j - 1) & 1, &abort_flag)) { abort_flag = 1; atomicOr(status, Q3_STATUS_TIMEOUT); break; }
-        mbar_expect_tx(v_full, bytes);
+        if (use > 0 && !mbar_wait(v_empty + st, (use - 1) & 1, &abort_flag)) { abort_flag = 1; atomicOr(status, Q3_STATUS_TIMEOUT); break; }
+        mbar_expect_tx(v_full + st, bytes);
         for (int p = 0; p < have; ++p) {
           const int page = table[(j * AT_BN) / page_size + p];
           const bool ok = page >= 0 && page < num_pages;
           const int y = ((ok ? page : 0) * Hkv + hk) * page_size;
 #pragma unroll
           for (int a = 0; a < ATOMS; ++a)
-            tma_load_2d(v_s + a * (AT_BN * 128) + p * page_size * 128, &map_v, v_full, a * 64, y);
+            tma_load_2d(v_s + st * S::V_BYTES + a * (AT_BN * 128) + p * page_size * 128, &map_v, v_full + st, a * 64, y);
         }
       }
     }
@@ -165,28 +176,41 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc(AT_BN, 0);  // 128 x 64, K and Q both K-major
       constexpr uint32_t idesc_o = umma_idesc(D, 1);      // 128 x D, V MN-major
-      for (int j = 0; j < n_tiles; ++j) {
-        if (!mbar_wait(k_full, j & 1, &abort_flag)) { abort_flag = 1; atomicOr(status, Q3_STATUS_TIMEOUT); break; }
+      // S of tile j + 1 is issued before the wait for tile j's probabilities, so it runs on the
+      // tensor cores while the softmax threads work on tile j.
+      auto issue_s = [&](int j) -> bool {
+        const int st = j & 1;
+        if (!mbar_wait(k_full + st, ((uint32_t)j >> 1) & 1, &abort_flag)) return false;
         tcgen05_fence_after();
 #pragma unroll
         for (int t = 0; t < D / 16; ++t) {
           const uint64_t a_desc = umma_desc_sw128(q_s + (t / 4) * (AT_BM * 128)) + 2 * (t % 4);
-          const uint64_t b_desc = umma_desc_sw128(k_s + (t / 4) * (AT_BN * 128)) + 2 * (t % 4);
-          umma_f16(tmem_s, a_desc, b_desc, idesc_s, t != 0);
+          const uint64_t b_desc = umma_desc_sw128(k_s + st * S::K_BYTES + (t / 4) * (AT_BN * 128)) + 2 * (t % 4);
+          umma_f16(tmem_s + st * AT_BN, a_desc, b_desc, idesc_s, t != 0);
         }
-        umma_commit(s_ready);
-        umma_commit(k_empty);
-        if (!mbar_wait(p_ready, j & 1, &abort_flag)) { abort_flag = 1; atomicOr(status, Q3_STATUS_TIMEOUT); break; }
-        if (!mbar_wait(v_full, j & 1, &abort_flag)) { abort_flag = 1; atomicOr(status, Q3_STATUS_TIMEOUT); break; }
+        umma_commit(s_ready + st);
+        umma_commit(k_empty + st);
+        return true;
+      };
+      bool ok = issue_s(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j & 1;
+        if (j + 1 < n_tiles && !issue_s(j + 1)) { ok = false; break; }
+        if (!mbar_wait(p_ready, j & 1, &abort_flag)) { ok = false; break; }
+        if (!mbar_wait(v_full + st, ((uint32_t)j >> 1) & 1, &abort_flag)) { ok = false; break; }
         tcgen05_fence_after();
 #pragma unroll
         for (int t = 0; t < AT_BN / 16; ++t) {
           const uint64_t a_desc = umma_desc_sw128(p_s) + 2 * t;
-          const uint64_t b_desc = umma_desc_sw128_mn(v_s + t * 2048, AT_BN * 128);
+          const uint64_t b_desc = umma_desc_sw128_mn(v_s + st * S::V_BYTES + t * 2048, AT_BN * 128);
           umma_f16(tmem_o, a_desc, b_desc, idesc_o, (j | t) != 0);
         }
         umma_commit(pv_done);
-        umma_commit(v_empty);
+        umma_commit(v_empty + st);
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicOr(status, Q3_STATUS_TIMEOUT);
       }
     }
   } else {
@@ -199,11 +223,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
-      if (!mbar_wait(s_ready, j & 1, &abort_flag)) { ok = false; break; }
+      const int st = j & 1;
+      if (!mbar_wait(s_ready + st, ((uint32_t)j >> 1) & 1, &abort_flag)) { ok = false; break; }
       tcgen05_fence_after();
       uint32_t sv[2][32];
-      tmem_ld_32(tmem_s + lane_base, sv[0]);
-      tmem_ld_32(tmem_s + lane_base + 32, sv[1]);
+      tmem_ld_32(tmem_s + st * AT_BN + lane_base, sv[0]);
+      tmem_ld_32(tmem_s + st * AT_BN + lane_base + 32, sv[1]);
       tmem_wait_ld();
       const int base_n = j * AT_BN;
       float mx = -INFINITY;
@@ -264,11 +289,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       l += sum;
       // keys past the end of the sequence in the last tile: their V rows were not loaded; zero them
       if (base_n + AT_BN > len) {
-        if (!mbar_wait(v_full, j & 1, &abort_flag)) { ok = false; break; }
+        if (!mbar_wait(v_full + st, ((uint32_t)j >> 1) & 1, &abort_flag)) { ok = false; break; }
         const int first_bad = len - base_n;
         for (int e = threadIdx.x; e < (AT_BN - first_bad) * (D / 8); e += AT_BM) {
           const int key = first_bad + e / (D / 8), c = e % (D / 8);
-          *reinterpret_cast<uint4*>(v_s + (c / 8) * (AT_BN * 128) + sw128_offset(key, (c % 8) * 8)) =
+          *reinterpret_cast<uint4*>(v_s + st * S::V_BYTES + (c / 8) * (AT_BN * 128) + sw128_offset(key, (c % 8) * 8)) =
               make_uint4(0, 0, 0, 0);
         }
       }
@@ -314,6 +339,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"((uint32_t)S::TMEM_COLS)
                  : "memory");
   }
+#undef abort_flag
 }
 
 template <int D>
