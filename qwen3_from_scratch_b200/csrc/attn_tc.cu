@@ -2,21 +2,23 @@
 // bfloat16, head size 64 or 128, pages of 8 to 64 tokens, no window.
 //
 // A block owns 128 query rows of one kv head (rows are (token, head-in-group) pairs as in
-// attn_prefill.cu) and walks the keys in tiles of 64:
+// attn_prefill.cu) and walks the keys in tiles of 128:
 //   loader thread   TMA brings the tile's pages of K and of V into shared memory (128-byte swizzle),
 //                   one box per page and per 64 values of the head; the page ids come from the
 //                   block table, the tensor maps cover a layer's whole K (or V) pool.
-//   issue thread    S = Q K^T   (tcgen05.mma, both operands K-major, accumulator: 64 TMEM columns)
+//   issue thread    S = Q K^T   (tcgen05.mma, both operands K-major, accumulator: 128 TMEM columns)
 //                   O += P V    (P K-major from shared memory, V MN-major; accumulator: D columns)
-//   128 softmax threads, one per query row: read S from TMEM (a thread owns a whole row, so the
-//                   row maximum and sum need no shuffles), mask the diagonal tile, keep a running
+//   256 softmax threads, two per query row (one for keys 0..63 of the tile, one for 64..127; they
+//                   agree on the row maximum through shared memory): read S from TMEM (a thread
+//                   owns half a row, no shuffles), mask the diagonal tile, keep a running
 //                   reference maximum and denominator in float32, write P as bfloat16 into shared
 //                   memory in the swizzled layout the tensor cores read, and rescale O in TMEM
 //                   when the reference maximum has to move (it moves only when the row maximum
 //                   exceeds it by more than 2^8, so the rescale is rare after the first tiles).
 // K and V tiles are double-buffered and so is S in TMEM, so the loads and the next tile's Q K^T run
-// while the softmax threads work.  Two blocks fit an SM (112 KB of shared memory, 256 TMEM columns
-// each), so one block's softmax also overlaps the other's matrix products.  All mbarrier waits are bounded (see tc_common.cuh).
+// while the softmax threads work.  The time of a prompt is set by its last query tile, which walks
+// every key: tiles of 128 keys shared by two threads per row halve that chain.  One block per SM
+// (192 KB of shared memory, all 512 TMEM columns).  All mbarrier waits are bounded (see tc_common.cuh).
 //
 // Reference for the math: kernels/triton/paged_attn.py:89-181 (online softmax with exp2, P rounded
 // to the value dtype before P V), models/attn.py:388-400 (scale, causal on absolute positions).
@@ -24,9 +26,11 @@
 
 namespace q3 {
 
-constexpr int AT_BM = 128;  // query rows per block
-constexpr int AT_BN = 64;   // keys per tile
-constexpr int AT_THREADS = 192;
+constexpr int AT_BM = 128;   // query rows per block
+constexpr int AT_BN = 128;   // keys per tile
+constexpr int AT_HALF = 64;  // keys per softmax thread
+constexpr int AT_SOFTMAX = 2 * AT_BM;          // softmax threads: warps 0..7
+constexpr int AT_THREADS = AT_SOFTMAX + 64;    // + issue warp (8) and loader warp (9)
 
 template <int D>
 struct AttnTcShape {
@@ -36,10 +40,11 @@ struct AttnTcShape {
   static constexpr int V_BYTES = AT_BN * D * 2;
   static constexpr int P_BYTES = AT_BM * AT_BN * 2;
   static constexpr int BAR_BYTES = 128;
+  static constexpr int XCHG_BYTES = 2 * 2 * AT_BM * 4;  // [tile parity][half][row]
   // K and V tiles are double-buffered; no slack for alignment: the dynamic shared memory of a block
   // that has no static shared memory starts on a 1024-byte boundary (checked in the kernel)
-  static constexpr size_t SMEM_BYTES = (size_t)Q_BYTES + 2 * K_BYTES + 2 * V_BYTES + P_BYTES + BAR_BYTES;
-  static constexpr int TMEM_COLS = 256;                // S: two buffers of 64 columns at 0 and 64, O: D columns at 128
+  static constexpr size_t SMEM_BYTES = (size_t)Q_BYTES + 2 * K_BYTES + 2 * V_BYTES + P_BYTES + BAR_BYTES + XCHG_BYTES;
+  static constexpr int TMEM_COLS = 512;                // S: two buffers of 128 columns at 0 and 128, O: D columns at 256
 };
 
 // byte offset of value (row, col) in a [rows x 64] bfloat16 tile with the 128-byte swizzle
@@ -48,7 +53,7 @@ __device__ __forceinline__ uint32_t sw128_offset(int row, int col) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(AT_THREADS, 2)
+__global__ void __launch_bounds__(AT_THREADS, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                const int* __restrict__ q_start, const int* __restrict__ kv_len,
@@ -71,17 +76,19 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   uint64_t* pv_done = bars + 11;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 12);
   int* abort_word = reinterpret_cast<int*>(bars + 13);
+  float* row_xchg = reinterpret_cast<float*>(p_s + S::P_BYTES + S::BAR_BYTES);  // [2][128] row maxima, then sums
 #define abort_flag (*abort_word)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int hk = blockIdx.y, b = blockIdx.z;
+  const int hk = blockIdx.x, b = blockIdx.z;
   const int g = Hq / Hkv;
   const int qs = q_start[b];
   const int q_len = q_start[b + 1] - qs;
   const int len = kv_len[b];
   const int total_rows = q_len * g;
-  // heavy tiles (late queries, many keys) are scheduled first
-  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;
+  // Blocks are handed to the SMs in the order x, then y: the kv heads are x, so that the heaviest
+  // query tiles (late queries, many keys) of all heads start first and the light ones fill the gaps.
+  const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;
   const int row0 = qt * AT_BM;
   if (row0 >= total_rows) return;  // before any barrier or allocation: the whole block leaves
   const int past = len - q_len;
@@ -103,7 +110,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       mbar_init(v_empty + i, 1);
       mbar_init(s_ready + i, 1);
     }
-    mbar_init(p_ready, AT_BM);
+    mbar_init(p_ready, AT_SOFTMAX);
     mbar_init(pv_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -111,14 +118,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   pdl_launch_dependents();
   // Tensor memory is taken only after the wait: a block that holds TMEM while it waits for the
   // kernel before it could keep that kernel's own blocks from ever getting theirs.
-  if (warp == 4) {
+  if (warp == 8) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_holder)),
                  "r"((uint32_t)S::TMEM_COLS)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
 
-  // the query tile, written in the swizzled K-major layout by the softmax threads (row = thread)
+  // the query tile, written in the swizzled K-major layout by the first 128 threads (row = thread)
   if (warp < 4) {
     const int rr = warp * 32 + lane;
     const int R = row0 + rr;
@@ -133,48 +140,58 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
-  const uint32_t tmem_s = *tmem_holder;           // S of tile j lives at column (j & 1) * 64
+  const uint32_t tmem_s = *tmem_holder;           // S of tile j lives at column (j & 1) * 128
   const uint32_t tmem_o = tmem_s + 2 * AT_BN;
 
-  if (warp == 5) {
+  if (warp == 9) {
     // ------------------------------------------------------------------ loader
-    if (lane == 0) {
-      const int pages_per_tile = AT_BN / page_size;
-      for (int j = 0; j < n_tiles; ++j) {
-        // pages of this tile that the sequence really has (the last tile may reach past kv_len)
-        int have = 0;
-        for (int p = 0; p < pages_per_tile; ++p)
-          if (j * AT_BN + p * page_size < len) have = p + 1;
-        const uint32_t bytes = (uint32_t)have * page_size * D * 2;
-        const int st = j & 1;
-        const uint32_t use = (uint32_t)j >> 1;
-        if (use > 0 && !mbar_wait(k_empty + st, (use - 1) & 1, &abort_flag)) { abort_flag = 1; atomicOr(status, Q3_STATUS_TIMEOUT); break; }
-        mbar_expect_tx(k_full + st, bytes);
-        for (int p = 0; p < have; ++p) {
-          const int page = table[(j * AT_BN) / page_size + p];
-          const bool ok = page >= 0 && page < num_pages;
-          if (!ok) atomicOr(status, Q3_STATUS_BAD_PAGE);
-          const int y = ((ok ? page : 0) * Hkv + hk) * page_size;
-#pragma unroll
-          for (int a = 0; a < ATOMS; ++a)
-            tma_load_2d(k_s + st * S::K_BYTES + a * (AT_BN * 128) + p * page_size * 128, &map_k, k_full + st, a * 64, y);
-        }
-        if (use > 0 && !mbar_wait(v_empty + st, (use - 1) & 1, &abort_flag)) { abort_flag = 1; atomicOr(status, Q3_STATUS_TIMEOUT); break; }
-        mbar_expect_tx(v_full + st, bytes);
-        for (int p = 0; p < have; ++p) {
-          const int page = table[(j * AT_BN) / page_size + p];
-          const bool ok = page >= 0 && page < num_pages;
-          const int y = ((ok ? page : 0) * Hkv + hk) * page_size;
-#pragma unroll
-          for (int a = 0; a < ATOMS; ++a)
-            tma_load_2d(v_s + st * S::V_BYTES + a * (AT_BN * 128) + p * page_size * 128, &map_v, v_full + st, a * 64, y);
-        }
+    // Lane p of the warp owns page p of a tile: it looks its page id up (for the next tile already
+    // while the current one is in flight) and issues that page's boxes, so the sixteen lookups and
+    // the copies of a tile go out together instead of one after the other.
+    const int pages_per_tile = AT_BN / page_size;
+    auto page_row = [&](int j) -> int {  // first row of lane's page of tile j in the [pages * heads * page_size, D] view
+      if (lane >= pages_per_tile || j >= n_tiles || j * AT_BN + lane * page_size >= len) return -1;
+      const int page = table[(j * AT_BN) / page_size + lane];
+      if (page < 0 || page >= num_pages) {
+        atomicOr(status, Q3_STATUS_BAD_PAGE);
+        return -1;
       }
+      return (page * Hkv + hk) * page_size;
+    };
+    int y = page_row(0);
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int st = j & 1;
+      const uint32_t use = (uint32_t)j >> 1;
+      const int y_next = page_row(j + 1);
+      const uint32_t have = __popc(__ballot_sync(0xffffffffu, y >= 0));
+      const uint32_t bytes = have * page_size * D * 2;
+      if (use > 0) ok = ok && mbar_wait(k_empty + st, (use - 1) & 1, &abort_flag);
+      if (lane == 0 && ok) mbar_expect_tx(k_full + st, bytes);
+      __syncwarp();
+      if (y >= 0 && ok) {
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a)
+          tma_load_2d(k_s + st * S::K_BYTES + a * (AT_BN * 128) + lane * page_size * 128, &map_k, k_full + st, a * 64, y);
+      }
+      if (use > 0) ok = ok && mbar_wait(v_empty + st, (use - 1) & 1, &abort_flag);
+      if (lane == 0 && ok) mbar_expect_tx(v_full + st, bytes);
+      __syncwarp();
+      if (y >= 0 && ok) {
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a)
+          tma_load_2d(v_s + st * S::V_BYTES + a * (AT_BN * 128) + lane * page_size * 128, &map_v, v_full + st, a * 64, y);
+      }
+      y = y_next;
     }
-  } else if (warp == 4) {
+    if (!ok && lane == 0) {
+      abort_flag = 1;
+      atomicOr(status, Q3_STATUS_TIMEOUT);
+    }
+  } else if (warp == 8) {
     // ------------------------------------------------------------------ tensor-core issue
     if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc(AT_BN, 0);  // 128 x 64, K and Q both K-major
+      constexpr uint32_t idesc_s = umma_idesc(AT_BN, 0);  // 128 x 128, K and Q both K-major
       constexpr uint32_t idesc_o = umma_idesc(D, 1);      // 128 x D, V MN-major
       // S of tile j + 1 is issued before the wait for tile j's probabilities, so it runs on the
       // tensor cores while the softmax threads work on tile j.
@@ -201,7 +218,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         tcgen05_fence_after();
 #pragma unroll
         for (int t = 0; t < AT_BN / 16; ++t) {
-          const uint64_t a_desc = umma_desc_sw128(p_s) + 2 * t;
+          const uint64_t a_desc = umma_desc_sw128(p_s + (t / 4) * (AT_BM * 128)) + 2 * (t % 4);
           const uint64_t b_desc = umma_desc_sw128_mn(v_s + st * S::V_BYTES + t * 2048, AT_BN * 128);
           umma_f16(tmem_o, a_desc, b_desc, idesc_o, (j | t) != 0);
         }
@@ -214,25 +231,32 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax, one row per thread
-    const int rr = warp * 32 + lane;
+    // ------------------------------------------------------------------ softmax, two threads per row
+    // warps 0..3 take keys 0..63 of every tile, warps 4..7 keys 64..127; both see TMEM lanes
+    // (warp % 4) * 32 .., i.e. row (warp % 4) * 32 + lane.
+    const int half = warp >> 2;
+    const int rr = (warp & 3) * 32 + lane;
     const int R = row0 + rr;
     const bool valid_row = R < total_rows;
     const int my_pos = valid_row ? past + R / g : pos_last;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const int soft_tid = threadIdx.x;  // 0 .. 255
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
+    // Every softmax thread runs every iteration and meets the others at the named barrier even
+    // after a wait has run out (the barrier itself cannot time out); `ok` only switches the work off.
+    for (int j = 0; j < n_tiles; ++j) {
       const int st = j & 1;
-      if (!mbar_wait(s_ready + st, ((uint32_t)j >> 1) & 1, &abort_flag)) { ok = false; break; }
+      float* xchg = row_xchg + (j & 1) * (2 * AT_BM);
+      ok = ok && mbar_wait(s_ready + st, ((uint32_t)j >> 1) & 1, &abort_flag);
       tcgen05_fence_after();
       uint32_t sv[2][32];
-      tmem_ld_32(tmem_s + st * AT_BN + lane_base, sv[0]);
-      tmem_ld_32(tmem_s + st * AT_BN + lane_base + 32, sv[1]);
+      tmem_ld_32(tmem_s + st * AT_BN + half * AT_HALF + lane_base, sv[0]);
+      tmem_ld_32(tmem_s + st * AT_BN + half * AT_HALF + lane_base + 32, sv[1]);
       tmem_wait_ld();
-      const int base_n = j * AT_BN;
+      const int base_n = j * AT_BN + half * AT_HALF;
       float mx = -INFINITY;
-      if (base_n + AT_BN - 1 > pos_first) {  // the diagonal: keys beyond this row's position are hidden
+      if (j * AT_BN + AT_BN - 1 > pos_first) {  // the diagonal: keys beyond this row's position are hidden
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -247,7 +271,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 #pragma unroll
           for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(sv[h][c]));
       }
-      mx *= scale_log2;
+      // the two threads of a row agree on its maximum
+      xchg[half * AT_BM + rr] = mx;
+      asm volatile("bar.sync 1, %0;" ::"n"(AT_SOFTMAX) : "memory");
+      mx = fmaxf(mx, xchg[(half ^ 1) * AT_BM + rr]) * scale_log2;
       // the reference maximum moves only when it must: probabilities up to 2^8 are harmless
       float alpha = 1.f;
       if (mx > m_ref + 8.f) {
@@ -256,11 +283,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       }
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
       // P and O belong to the tensor cores until the previous tile's P V has finished
-      if (j > 0 && !mbar_wait(pv_done, (j - 1) & 1, &abort_flag)) { ok = false; break; }
+      if (j > 0) ok = ok && mbar_wait(pv_done, (j - 1) & 1, &abort_flag);
       tcgen05_fence_after();
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        // each of the row's two threads rescales its half of the output columns
 #pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
+        for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
           uint32_t ov[32];
           tmem_ld_32(tmem_o + lane_base + c0, ov);
           tmem_wait_ld();
@@ -272,6 +300,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       }
       l *= alpha;
       float sum = 0.f;
+      unsigned char* p_atom = p_s + half * (AT_BM * 128);  // keys 0..63 -> first atom, 64..127 -> second
 #pragma unroll
       for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -284,14 +313,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             sum += p0 + p1;
             pk[e] = pack2(__float_as_uint(p0), __float_as_uint(p1));
           }
-          *reinterpret_cast<uint4*>(p_s + sw128_offset(rr, h * 32 + c8 * 8)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint4*>(p_atom + sw128_offset(rr, h * 32 + c8 * 8)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
       l += sum;
       // keys past the end of the sequence in the last tile: their V rows were not loaded; zero them
-      if (base_n + AT_BN > len) {
-        if (!mbar_wait(v_full + st, ((uint32_t)j >> 1) & 1, &abort_flag)) { ok = false; break; }
-        const int first_bad = len - base_n;
-        for (int e = threadIdx.x; e < (AT_BN - first_bad) * (D / 8); e += AT_BM) {
+      if (j * AT_BN + AT_BN > len) {
+        ok = ok && mbar_wait(v_full + st, ((uint32_t)j >> 1) & 1, &abort_flag);
+        const int first_bad = len - j * AT_BN;
+        for (int e = soft_tid; e < (AT_BN - first_bad) * (D / 8); e += AT_SOFTMAX) {
           const int key = first_bad + e / (D / 8), c = e % (D / 8);
           *reinterpret_cast<uint4*>(v_s + st * S::V_BYTES + (c / 8) * (AT_BN * 128) + sw128_offset(key, (c % 8) * 8)) =
               make_uint4(0, 0, 0, 0);
@@ -305,13 +334,18 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       abort_flag = 1;
       atomicOr(status, Q3_STATUS_TIMEOUT);
     }
-    // the last P V, then O / l
-    if (ok && mbar_wait(pv_done, (n_tiles - 1) & 1, &abort_flag)) {
+    // the last P V, then O / l with l summed over the row's two threads; each writes half the columns
+    const bool done = ok && mbar_wait(pv_done, (n_tiles - 1) & 1, &abort_flag);
+    float* xchg = row_xchg + (n_tiles & 1) * (2 * AT_BM);
+    xchg[half * AT_BM + rr] = l;
+    asm volatile("bar.sync 1, %0;" ::"n"(AT_SOFTMAX) : "memory");
+    if (done) {
       tcgen05_fence_after();
-      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      const float total = l + xchg[(half ^ 1) * AT_BM + rr];
+      const float inv = total > 0.f ? 1.0f / total : 0.f;
       __nv_bfloat16* dst = valid_row ? out + ((size_t)(qs + R / g) * Hq + hk * g + R % g) * D : nullptr;
 #pragma unroll 1
-      for (int c0 = 0; c0 < D; c0 += 32) {
+      for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
         uint32_t ov[32];
         tmem_ld_32(tmem_o + lane_base + c0, ov);
         tmem_wait_ld();
@@ -335,7 +369,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   __syncwarp();
   tcgen05_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"((uint32_t)S::TMEM_COLS)
                  : "memory");
   }
@@ -361,8 +395,8 @@ static int attn_tc_launch(const void* q, const void* k_pages, const void* v_page
   if (code) return code;
   const int g = Hq / Hkv;
   const long long tiles = ((long long)max_q_len * g + AT_BM - 1) / AT_BM;
-  if (tiles > 0x7fffffffLL) return Q3_ERR_SIZE;
-  dim3 grid((unsigned)tiles, Hkv, B);
+  if (tiles > 65535) return Q3_ERR_SIZE;
+  dim3 grid(Hkv, (unsigned)tiles, B);
   q3::launch(attn_tc_kernel<D>, grid, dim3(AT_THREADS), S::SMEM_BYTES, stream, map_k, map_v, (const __nv_bfloat16*)q,
              (__nv_bfloat16*)out, q_start, kv_len, block_table, table_stride, page_size, num_pages, Hq, Hkv,
              scale * 1.4426950408889634f, status);
