@@ -396,3 +396,13 @@ extern "C" int q3_attn_decode_noalloc(const void* q, const void* k_pages, const 
   return q3_attn_decode(q, k_pages, v_pages, out, scratch, q_start, kv_len, block_table, table_stride, page_size,
                         num_pages, B, Hq, Hkv, D, scale, window, num_splits, status, stream);
 }
+
+// The merge of the splits alone, for other decode kernels that write the same partial records.
+extern "C" int q3_attn_combine(const float* partial, void* out, const int* q_start, int B, int Hq, int D,
+                               int num_splits, cudaStream_t stream) {
+  if (B <= 0 || num_splits <= 1) return 0;
+  dim3 cgrid(Hq, B);
+  q3::launch(q3::attn_combine_kernel, cgrid, dim3(128), 0, stream, partial, (__nv_bfloat16*)out, q_start, Hq, D,
+             num_splits);
+  return q3::launch_status();
+}

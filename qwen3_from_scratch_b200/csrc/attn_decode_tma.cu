@@ -1,0 +1,339 @@
+// Paged decode attention with a TMA producer: the same split-KV scheme and tensor-core arithmetic
+// as attn_decode.cu, but the key/value tiles are brought in by a dedicated loader warp through
+// TMA (cp.async.bulk.tensor, 128-byte swizzle) into a ring of eight stages shared by four consumer
+// warps.  How many bytes are in flight no longer depends on how fast a consumer gets through its
+// tile: the loader runs up to eight 16-key tiles (64 KB per block at D = 128) ahead, which is what
+// a bandwidth-bound kernel wants, and the consumers issue no copy instructions at all.
+//
+// Takes D = 64 or 128 and page sizes that are multiples of 16 (a 16-key tile then lies in one
+// page); everything else goes to attn_decode.cu.  Mbarrier waits are bounded (tc_common.cuh).
+#include "attn_mma.cuh"
+#include "tc_common.cuh"
+
+extern "C" int q3_attn_combine(const float* partial, void* out, const int* q_start, int B, int Hq, int D,
+                               int num_splits, cudaStream_t stream);
+
+namespace q3 {
+
+constexpr int DT_CONSUMERS = 4;
+constexpr int DT_THREADS = (DT_CONSUMERS + 1) * 32;
+constexpr int DT_KEYS = 16;
+constexpr int DT_STAGES = 8;
+
+template <int D>
+struct DecodeTmaShape {
+  static constexpr int ATOMS = D / 64;
+  static constexpr int TILE_BYTES = DT_KEYS * D * 2;        // K (or V) of one tile: ATOMS atoms of 2048 bytes
+  static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  static constexpr int RING_BYTES = DT_STAGES * STAGE_BYTES;
+  static constexpr int Q_PITCH = D + 8;
+  static constexpr int Q_BYTES = 16 * Q_PITCH * 2;
+  static constexpr int MERGE_BYTES = DT_CONSUMERS * 16 * (D + 2) * 4;
+  static constexpr int BAR_BYTES = 2 * DT_STAGES * 8 + 16;
+  static constexpr size_t SMEM_BYTES =
+      (size_t)(RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES) + Q_BYTES + BAR_BYTES;
+};
+
+// address of 16-byte chunk `chunk` of row `row` in a tile made of [16 x 64] atoms with the 128-byte swizzle
+__device__ __forceinline__ const unsigned char* sw_chunk(const unsigned char* tile, int row, int chunk) {
+  return tile + (chunk >> 3) * 2048 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+}
+
+template <int D>
+__global__ void __launch_bounds__(DT_THREADS, 2)
+attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+                       float* __restrict__ partial, const int* __restrict__ q_start,
+                       const int* __restrict__ kv_len, const int* __restrict__ block_table, int table_stride,
+                       int page_size, int num_pages, int Hq, int Hkv, float scale_log2, int window,
+                       int num_splits, int* status) {
+  using S = DecodeTmaShape<D>;
+  constexpr int KT = D / 16, CPR = D / 8, PITCH = S::Q_PITCH;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* ring = smem_raw;
+  constexpr int RING_OR_MERGE = S::RING_BYTES > S::MERGE_BYTES ? S::RING_BYTES : S::MERGE_BYTES;
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw + RING_OR_MERGE);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw + RING_OR_MERGE + S::Q_BYTES);
+  uint64_t* empty = full + DT_STAGES;
+  int* abort_word = reinterpret_cast<int*>(empty + DT_STAGES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gid = lane >> 2, tid4 = lane & 3;
+  const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int g = Hq / Hkv;
+  const int tq = q_start[b];
+  const int pos = kv_len[b] - 1;
+  const int* table = block_table + (size_t)b * table_stride;
+
+  int t_lo = 0, t_hi = 0, lo = 0;
+  if (pos >= 0) {
+    lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int first = lo / DT_KEYS, last = pos / DT_KEYS;
+    const int per = (last - first + num_splits) / num_splits;
+    t_lo = first + split * per;
+    t_hi = min(t_lo + per, last + 1);
+  } else if (threadIdx.x == 0) {
+    atomicOr(status, Q3_STATUS_BAD_POSITION);
+  }
+  const int count = max(0, t_hi - t_lo);
+
+  if (threadIdx.x == 0) {
+    *abort_word = (s_addr(smem_raw) & 1023u) ? 1 : 0;
+    if (*abort_word) atomicOr(status, Q3_STATUS_TIMEOUT);
+    for (int s = 0; s < DT_STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int e = threadIdx.x; e < 16 * CPR; e += DT_THREADS) {
+    const int row = e / CPR, c = e % CPR;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < g) v = *reinterpret_cast<const uint4*>(q + ((size_t)tq * Hq + hk * g + row) * D + c * 8);
+    *reinterpret_cast<uint4*>(q_s + row * PITCH + c * 8) = v;
+  }
+  __syncthreads();
+
+  float o[2 * KT][4];
+#pragma unroll
+  for (int i = 0; i < 2 * KT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  if (warp == DT_CONSUMERS) {
+    // ------------------------------------------------------------------ loader
+    bool ok = true;
+    for (int chunk0 = 0; chunk0 < count; chunk0 += 32) {
+      // thirty-two page ids at once, one per lane
+      int my_y = -1;
+      if (chunk0 + lane < count) {
+        const int n0 = (t_lo + chunk0 + lane) * DT_KEYS;
+        int page = table[n0 / page_size];
+        if (page < 0 || page >= num_pages) {
+          atomicOr(status, Q3_STATUS_BAD_PAGE);
+          page = 0;
+        }
+        my_y = (page * Hkv + hk) * page_size + (n0 % page_size);
+      }
+      const int in_chunk = min(32, count - chunk0);
+      for (int u = 0; u < in_chunk; ++u) {
+        const int i = chunk0 + u;
+        const int s = i % DT_STAGES;
+        const uint32_t use = (uint32_t)i / DT_STAGES;
+        const int y = __shfl_sync(0xffffffffu, my_y, u);
+        if (use > 0) ok = ok && mbar_wait(empty + s, (use - 1) & 1, abort_word);
+        if (lane == 0 && ok) {
+          unsigned char* stage = ring + (size_t)s * S::STAGE_BYTES;
+          mbar_expect_tx(full + s, S::STAGE_BYTES);
+#pragma unroll
+          for (int a = 0; a < S::ATOMS; ++a) {
+            tma_load_2d(stage + a * 2048, &map_k, full + s, a * 64, y);
+            tma_load_2d(stage + S::TILE_BYTES + a * 2048, &map_v, full + s, a * 64, y);
+          }
+        }
+      }
+    }
+    if (!ok && lane == 0) {
+      *abort_word = 1;
+      atomicOr(status, Q3_STATUS_TIMEOUT);
+    }
+  } else {
+    // ------------------------------------------------------------------ consumers
+    uint32_t qa[KT][4];
+#pragma unroll
+    for (int kt = 0; kt < KT; ++kt)
+      ldmatrix_x4(qa[kt], q_s + ((lane & 7) + ((lane >> 3) & 1) * 8) * PITCH + kt * 16 + (lane >> 4) * 8);
+    bool ok = true;
+    for (int i = warp; i < count; i += DT_CONSUMERS) {
+      const int s = i % DT_STAGES;
+      ok = ok && mbar_wait(full + s, ((uint32_t)i / DT_STAGES) & 1, abort_word);
+      const unsigned char* k_t = ring + (size_t)s * S::STAGE_BYTES;
+      unsigned char* v_t = ring + (size_t)s * S::STAGE_BYTES + S::TILE_BYTES;
+      const int base_n = (t_lo + i) * DT_KEYS;
+      const bool edge = base_n < lo || base_n + DT_KEYS - 1 > pos;
+      if (base_n + DT_KEYS - 1 > pos) {
+        // the page's slots past the sequence hold whatever was there: zero those value rows
+        const int first_bad = pos - base_n + 1;
+        for (int e = lane; e < (DT_KEYS - first_bad) * CPR; e += 32) {
+          const int row = first_bad + e / CPR, c = e % CPR;
+          *reinterpret_cast<uint4*>(v_t + (c >> 3) * 2048 + row * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
+        }
+        fence_async_proxy();  // these stores are ordered before the loader's next copy into this stage
+        __syncwarp();
+      }
+      float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int kt = 0; kt < KT; ++kt) {
+        uint32_t kb[4];
+        ldmatrix_x4(kb, sw_chunk(k_t, (lane & 7) + ((lane >> 4) << 3), kt * 2 + ((lane >> 3) & 1)));
+        mma_bf16(sc[0], qa[kt], kb[0], kb[1]);
+        mma_bf16(sc[1], qa[kt], kb[2], kb[3]);
+      }
+      if (edge) {
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int n = base_n + nt * 8 + 2 * tid4 + (j & 1);
+            if (n < lo || n > pos) sc[nt][j] = -INFINITY;
+          }
+      }
+      float mx[2];
+      mx[0] = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
+      mx[1] = fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3]));
+      float alpha[2], m_use[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m[r], mx[r] * scale_log2);
+        m_use[r] = m_new == -INFINITY ? 0.f : m_new;
+        alpha[r] = exp2f(m[r] - m_use[r]);
+        m[r] = m_new;
+      }
+      if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          l[r] *= alpha[r];
+#pragma unroll
+          for (int i2 = 0; i2 < 2 * KT; ++i2) {
+            o[i2][2 * r] *= alpha[r];
+            o[i2][2 * r + 1] *= alpha[r];
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const float p0 = exp2f(fmaf(sc[nt][2 * r], scale_log2, -m_use[r]));
+          const float p1 = exp2f(fmaf(sc[nt][2 * r + 1], scale_log2, -m_use[r]));
+          sc[nt][2 * r] = p0;
+          sc[nt][2 * r + 1] = p1;
+          l[r] += p0 + p1;
+        }
+      uint32_t pa[4];
+      pa[0] = pack_bf16(sc[0][0], sc[0][1]);
+      pa[1] = pack_bf16(sc[0][2], sc[0][3]);
+      pa[2] = pack_bf16(sc[1][0], sc[1][1]);
+      pa[3] = pack_bf16(sc[1][2], sc[1][3]);
+#pragma unroll
+      for (int dt = 0; dt < KT; ++dt) {
+        uint32_t vb[4];
+        ldmatrix_x4_trans(vb, sw_chunk(v_t, (lane & 7) + ((lane >> 3) & 1) * 8, dt * 2 + (lane >> 4)));
+        mma_bf16(o[2 * dt], pa, vb[0], vb[1]);
+        mma_bf16(o[2 * dt + 1], pa, vb[2], vb[3]);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty + s);  // the stage goes back to the loader
+    }
+    if (!ok && lane == 0) {
+      *abort_word = 1;
+      atomicOr(status, Q3_STATUS_TIMEOUT);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+  }
+  __syncthreads();  // every tile has been consumed: the ring now holds the merge buffers
+
+  float* merge = reinterpret_cast<float*>(ring);  // [consumer][16 rows][D + 2]
+  if (warp < DT_CONSUMERS) {
+    float* mine = merge + (size_t)warp * 16 * (D + 2);
+#pragma unroll
+    for (int nt = 0; nt < 2 * KT; ++nt) {
+      const int d = nt * 8 + 2 * tid4;
+      mine[gid * (D + 2) + d] = o[nt][0];
+      mine[gid * (D + 2) + d + 1] = o[nt][1];
+      mine[(gid + 8) * (D + 2) + d] = o[nt][2];
+      mine[(gid + 8) * (D + 2) + d + 1] = o[nt][3];
+    }
+    if (tid4 == 0) {
+      mine[gid * (D + 2) + D] = m[0];
+      mine[gid * (D + 2) + D + 1] = l[0];
+      mine[(gid + 8) * (D + 2) + D] = m[1];
+      mine[(gid + 8) * (D + 2) + D + 1] = l[1];
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < g * D; e += DT_THREADS) {
+    const int r = e / D, d = e % D;
+    float big = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DT_CONSUMERS; ++w) big = fmaxf(big, merge[((size_t)w * 16 + r) * (D + 2) + D]);
+    float acc = 0.f, den = 0.f;
+    if (big != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < DT_CONSUMERS; ++w) {
+        const float* row = merge + ((size_t)w * 16 + r) * (D + 2);
+        const float wgt = row[D] == -INFINITY ? 0.f : exp2f(row[D] - big);
+        acc += row[d] * wgt;
+        den += row[D + 1] * wgt;
+      }
+    }
+    const int head = hk * g + r;
+    if (num_splits == 1) {
+      out[((size_t)tq * Hq + head) * D + d] = __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
+    } else {
+      float* p = partial + (((size_t)b * Hq + head) * num_splits + split) * (D + 2);
+      p[d] = acc;
+      if (d == 0) {
+        p[D] = big;
+        p[D + 1] = den;
+      }
+    }
+  }
+}
+
+template <int D>
+static int attn_decode_tma_launch(const void* q, const void* k_pages, const void* v_pages, void* out, float* partial,
+                                  const int* q_start, const int* kv_len, const int* block_table, int table_stride,
+                                  int page_size, int num_pages, int B, int Hq, int Hkv, float scale, int window,
+                                  int num_splits, int* status, cudaStream_t stream) {
+  using S = DecodeTmaShape<D>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)S::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  CUtensorMap map_k, map_v;
+  const uint64_t rows = (uint64_t)num_pages * Hkv * page_size;
+  int code = cached_map(&map_k, k_pages, rows, D, DT_KEYS);
+  if (code) return code;
+  code = cached_map(&map_v, v_pages, rows, D, DT_KEYS);
+  if (code) return code;
+  dim3 grid(num_splits, Hkv, B);
+  q3::launch(attn_decode_tma_kernel<D>, grid, dim3(DT_THREADS), S::SMEM_BYTES, stream, map_k, map_v,
+             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, partial, q_start, kv_len, block_table, table_stride,
+             page_size, num_pages, Hq, Hkv, scale * 1.4426950408889634f, window, num_splits, status);
+  code = launch_status();
+  if (code != 0 || num_splits == 1) return code;
+  return q3_attn_combine(partial, out, q_start, B, Hq, D, num_splits, stream);
+}
+
+}  // namespace q3
+
+// Same arguments as q3_attn_decode.  Takes D = 64 or 128, page sizes that are multiples of 16 and up to
+// 16 query heads per kv head; refuses the rest.
+extern "C" int q3_attn_decode_tma(const void* q, const void* k_pages, const void* v_pages, void* out, float* partial,
+                                  const int* q_start, const int* kv_len, const int* block_table, int table_stride,
+                                  int page_size, int num_pages, int B, int Hq, int Hkv, int D, float scale,
+                                  int window, int num_splits, int* status, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (Hkv <= 0 || Hq % Hkv || Hq / Hkv > 16 || (D != 64 && D != 128) || page_size <= 0 || page_size % 16 ||
+      num_splits < 1 || table_stride <= 0 || B > 65535 || Hkv > 65535)
+    return Q3_ERR_SIZE;
+  if ((uintptr_t)q % 16 || (uintptr_t)k_pages % 16 || (uintptr_t)v_pages % 16) return Q3_ERR_ALIGN;
+  if (D == 64)
+    return q3::attn_decode_tma_launch<64>(q, k_pages, v_pages, out, partial, q_start, kv_len, block_table,
+                                          table_stride, page_size, num_pages, B, Hq, Hkv, scale, window, num_splits,
+                                          status, stream);
+  return q3::attn_decode_tma_launch<128>(q, k_pages, v_pages, out, partial, q_start, kv_len, block_table,
+                                         table_stride, page_size, num_pages, B, Hq, Hkv, scale, window, num_splits,
+                                         status, stream);
+}

@@ -57,6 +57,9 @@ _SIGNATURES = {
     "q3_attn_decode": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
                        _c_void_p, _c_void_p],
+    "q3_attn_decode_tma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                           _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
+                           _c_void_p, _c_void_p],
     "q3_attn_prefill": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
                         _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p,
                         _c_void_p],
@@ -431,13 +434,19 @@ def decode_blocks_per_sm(head_dim: int) -> int:
     return max(1, min(by_smem, by_regs, 16))
 
 
-def decode_splits(num_seqs: int, num_kv_heads: int, max_kv_len: int, window: int, head_dim: int = 128) -> int:
+def decode_tma_takes(head_dim: int, page_size: int) -> bool:
+    """Whether the decode kernel with the TMA loader takes this shape (else the cp.async one runs)."""
+    return head_dim in (64, 128) and page_size % 16 == 0
+
+
+def decode_splits(num_seqs: int, num_kv_heads: int, max_kv_len: int, window: int, head_dim: int = 128,
+                  blocks_per_sm: Optional[int] = None) -> int:
     """How many ranges a sequence's keys are cut into.  Blocks run in waves of (SMs x blocks per
     SM); a block costs its share of the 16-key tiles plus a fixed set-up and merge (about six
     tiles' worth).  The count that minimises waves x cost per block wins."""
     span = min(max_kv_len, window) if window and window > 0 else max_kv_len
     tiles = max(1, -(-span // 16))
-    slots = _SM_COUNT * decode_blocks_per_sm(head_dim)
+    slots = _SM_COUNT * (blocks_per_sm or decode_blocks_per_sm(head_dim))
     pairs = max(1, num_seqs * num_kv_heads)
     best, best_cost = 1, None
     for s in range(1, MAX_DECODE_SPLITS + 1):
@@ -471,8 +480,10 @@ def _attn_common(name, q, k_pages, v_pages, out, q_start, kv_len, block_table):
 def attn_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                 partial: Optional[torch.Tensor], q_start: torch.Tensor, kv_len: torch.Tensor,
                 block_table: torch.Tensor, num_seqs: int, scale: float, window: int, num_splits: int,
-                status: torch.Tensor) -> None:
-    """Split-KV tensor-core attention for the first ``num_seqs`` rows, one query token each."""
+                status: torch.Tensor, loader: str = "cp_async") -> None:
+    """Split-KV tensor-core attention for the first ``num_seqs`` rows, one query token each.
+    ``loader``: ``"cp_async"`` (every warp copies its own tiles) or ``"tma"`` (a loader warp feeds a
+    ring of stages through TMA; head size 64 / 128 and pages that are multiples of 16 only)."""
     T, Hq, D, num_pages, Hkv, page_size = _attn_common("attn_decode", q, k_pages, v_pages, out, q_start, kv_len,
                                                         block_table)
     if num_seqs > kv_len.numel() or num_seqs > block_table.shape[0]:
@@ -484,11 +495,12 @@ def attn_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, o
         if partial.numel() < num_seqs * Hq * num_splits * (D + 2):
             raise KernelError(f"attn_decode: scratch of {partial.numel()} floats is too small for {num_seqs} "
                               f"sequences x {Hq} heads x {num_splits} splits")
-    code = library().q3_attn_decode(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(),
-                                    _ptr(partial), q_start.data_ptr(), kv_len.data_ptr(), block_table.data_ptr(),
-                                    block_table.shape[1], page_size, num_pages, num_seqs, Hq, Hkv, D, float(scale),
-                                    int(window), int(num_splits), status.data_ptr(), _stream())
-    _done("attn_decode", code, f"heads {Hq}/{Hkv}, head_dim {D}")
+    fn = library().q3_attn_decode_tma if loader == "tma" else library().q3_attn_decode
+    code = fn(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(),
+              _ptr(partial), q_start.data_ptr(), kv_len.data_ptr(), block_table.data_ptr(),
+              block_table.shape[1], page_size, num_pages, num_seqs, Hq, Hkv, D, float(scale),
+              int(window), int(num_splits), status.data_ptr(), _stream())
+    _done("attn_decode", code, f"heads {Hq}/{Hkv}, head_dim {D}, page {page_size}, loader {loader}")
 
 
 def attn_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
@@ -530,7 +542,7 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
                     q_start: torch.Tensor, kv_len: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
                     num_seqs: int, num_decode: int, max_q_len: int, max_kv_len: int, scale: float, window: int,
                     status: torch.Tensor, partial: Optional[torch.Tensor] = None,
-                    portion_kernel: str = "auto") -> None:
+                    portion_kernel: str = "auto", decode_kernel: str = "auto") -> None:
     """Causal attention of a mixed batch over the pages: rows [0, num_decode) bring one token each and
     go to the split-KV decode kernel, the rest to a portion kernel (tcgen05 where it takes the shape,
     else mma.sync; ``portion_kernel="mma"`` forces the latter); shapes no tensor-core kernel takes
@@ -541,11 +553,12 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         attn_ref(q, k_pages, v_pages, out, q_start, kv_len, tok_seq, block_table, scale, window, status)
         return
     if num_decode > 0:
-        splits = decode_splits(num_decode, Hkv, max_kv_len, window, D)
+        tma = decode_kernel != "cp_async" and decode_tma_takes(D, k_pages.shape[2])
+        splits = decode_splits(num_decode, Hkv, max_kv_len, window, D, blocks_per_sm=2 if tma else None)
         if partial is None or partial.numel() < num_decode * Hq * splits * (D + 2):
             splits = 1 if partial is None else max(1, partial.numel() // (num_decode * Hq * (D + 2)))
         attn_decode(q, k_pages, v_pages, out, partial, q_start, kv_len, block_table, num_decode, scale, window,
-                    splits, status)
+                    splits, status, loader="tma" if tma else "cp_async")
     if num_seqs > num_decode:
         rest = (q_start[num_decode:], kv_len[num_decode:], block_table[num_decode:], num_seqs - num_decode, max_q_len)
         if portion_kernel != "mma" and attn_tc_takes(D, k_pages.shape[2], window):

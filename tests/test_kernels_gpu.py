@@ -327,7 +327,7 @@ def test_attn_ref_window_edge_is_exact():
 
 
 def run_fast(q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, window, splits=None,
-             portion_kernel="auto"):
+             portion_kernel="auto", loader="cp_async"):
     """The tensor-core kernels through the dispatcher (or the decode kernel with a forced split count).
     Unused slots of the pages hold NaN: anything read past a sequence's keys poisons the result."""
     o = ops()
@@ -353,11 +353,12 @@ def run_fast(q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, w
     if splits is None:
         o.paged_attention(*args, dev(q_start), dev(torch.tensor(kl, dtype=torch.int32)), dev(tok_seq),
                           dev(table_tensor(tb)), len(ql), num_decode, max(ql), max(kl), scale, window or 0, st, partial,
-                          portion_kernel=portion_kernel)
+                          portion_kernel=portion_kernel,
+                          decode_kernel="cp_async" if portion_kernel == "mma" else "auto")
     else:
         assert num_decode == len(ql)
         o.attn_decode(*args, partial, dev(q_start), dev(torch.tensor(kl, dtype=torch.int32)), dev(table_tensor(tb)),
-                      len(ql), scale, window or 0, splits, st)
+                      len(ql), scale, window or 0, splits, st, loader=loader)
     assert int(st.item()) == 0
     # back to the caller's order
     pieces, at = {}, 0
@@ -401,13 +402,16 @@ def test_fast_attention_against_plain(case, portion_kernel):
     close(out, want, "bfloat16", scale=None)
 
 
+@pytest.mark.parametrize("loader,d,page_size", [("cp_async", 64, 16), ("tma", 64, 16), ("tma", 128, 32),
+                                                ("cp_async", 48, 8)])
 @pytest.mark.parametrize("splits", [1, 2, 3, 7, 32])
 @pytest.mark.parametrize("window", [None, 150])
-def test_decode_splits_agree(splits, window):
-    hq, hkv, d, page_size = 8, 2, 64, 16
+def test_decode_splits_agree(splits, window, loader, d, page_size):
+    hq, hkv = 8, 2
     kv_lens, q_lens = [1000, 17, 160, 1, 16], [1, 1, 1, 1, 1]
     q, k_list, v_list, tables, num_pages = attention_case("bfloat16", hq, hkv, d, page_size, kv_lens, q_lens, window, seed=21)
-    out = run_fast(q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, window, splits=splits)
+    out = run_fast(q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, window, splits=splits,
+                   loader=loader)
     want = reference_attention(q.double(), [k.double() for k in k_list], [v.double() for v in v_list], q_lens, window)
     close(out, want, "bfloat16")
 
