@@ -113,6 +113,7 @@ class _Request:
     length: int = 0  # tokens whose keys/values are in the cache
     tables: List[List[int]] = field(default_factory=list)  # per group: logical page -> page id or -1
     first_live: List[int] = field(default_factory=list)  # per group: first logical page not given back
+    version: int = 0  # unique over the manager's life; renewed whenever a block table of the request changes
 
 
 class CacheManager:
@@ -150,6 +151,15 @@ class CacheManager:
 
     def table(self, group: int, req: Hashable) -> List[int]:
         return self._requests[req].tables[group]
+
+    def table_version(self, req: Hashable) -> int:
+        """A number that is renewed whenever one of the request's block tables changes, and that no
+        other request, nor a later request of the same name, ever has."""
+        return self._requests[req].version
+
+    def _new_version(self) -> int:
+        self._versions = getattr(self, "_versions", 0) + 1
+        return self._versions
 
     def free_pages(self, group: int = 0) -> int:
         return len(self._pools[group].free)
@@ -192,7 +202,8 @@ class CacheManager:
             raise OutOfSlots(f"all {self.max_seqs} request slots are in use")
         slot = self._free_slots.pop()
         n = len(self._pools)
-        self._requests[req] = _Request(slot=slot, tables=[[] for _ in range(n)], first_live=[0] * n)
+        self._requests[req] = _Request(slot=slot, tables=[[] for _ in range(n)], first_live=[0] * n,
+                                       version=self._new_version())
         if self.on_open is not None:
             self.on_open(slot)
         return slot
@@ -211,6 +222,8 @@ class CacheManager:
         for g, (n, pool) in enumerate(zip(need, self._pools)):
             for _ in range(n):
                 r.tables[g].append(pool.take(req))
+            if n:
+                r.version = self._new_version()
 
     def advance(self, req: Hashable, new_length: int) -> None:
         """Records that ``req`` now holds ``new_length`` tokens and gives back what windows have passed."""
@@ -227,6 +240,7 @@ class CacheManager:
                 if page >= 0:
                     pool.give_back(page, req)
                     r.tables[g][i] = -1
+                    r.version = self._new_version()
                     if self.freed_log is not None:
                         self.freed_log.append((g, page))
             r.first_live[g] = max(r.first_live[g], keep_from)

@@ -230,13 +230,17 @@ class SyncEngine:
         sampled: List[Optional[int]] = [None] * len(plan)
         if wanting:
             reqs = [s.request for s in wanting]
-            ids = self.sampler.sample(
+            box = self.session.rt.mailbox
+            self.sampler.sample(
                 logits, [r.params.temperature for r in reqs], [r.params.top_k for r in reqs],
-                [r.key for r in reqs], [len(r) for r in reqs], [r.params.seed for r in reqs])
-            host = ids.tolist()  # the step's one device-to-host read
-            it = iter(host)
+                [r.key for r in reqs], [len(r) for r in reqs], [r.params.seed for r in reqs],
+                out=box[1:1 + len(reqs)])
+            host = box[:1 + len(reqs)].tolist()  # the step's one device-to-host read: status word, then tokens
+            self.session.raise_on_status(host[0])
+            it = iter(host[1:])
             sampled = [next(it) if s.wants_logits else None for s in plan]
-        self.session.check_status_word_async()
+        else:
+            self.session.check_status()
         now = time.perf_counter()
         for s in wanting:
             if s.request.first_token_time is None:

@@ -75,10 +75,12 @@ class Request:
         return self.remaining == 1 and self.num_computed > 0
 
     def next_tokens(self, n: int) -> List[int]:
-        start = self.num_computed
-        if start + n <= len(self.prompt):
+        start, plen = self.num_computed, len(self.prompt)
+        if start + n <= plen:
             return self.prompt[start:start + n]
-        return self.tokens[start:start + n]
+        if start >= plen:
+            return self.output[start - plen:start - plen + n]
+        return self.prompt[start:] + self.output[:start + n - plen]
 
     def __hash__(self):
         return hash(self.request_id)

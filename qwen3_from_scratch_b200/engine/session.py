@@ -172,13 +172,12 @@ class Session:
     def after_step(self) -> None:
         self._poison()
 
-    def check_status_word_async(self) -> None:
-        """Checks the status word when the caller has just synchronised anyway (a token read)."""
-        self.check_status()
-
     def check_status(self) -> None:
         """Reads the device status word (synchronises) and raises if a kernel flagged bad table data."""
-        word = int(self.rt.status.item())
+        self.raise_on_status(int(self.rt.status.item()))
+
+    def raise_on_status(self, word: int) -> None:
+        """``word``: the status word as the caller has just read it from the device."""
         if word:
             self.rt.status.zero_()
             raise DeviceStatusError(f"a kernel reported: {ops.describe_status(word)}")

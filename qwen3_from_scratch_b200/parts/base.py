@@ -98,10 +98,13 @@ class Runtime:
     max_tokens: int
     max_seqs: int
     status: torch.Tensor = None  # int32[1] on the device; kernels OR error bits into it
+    mailbox: torch.Tensor = None  # int32[1 + max_seqs]: the status word, then a step's sampled tokens
 
     def __post_init__(self):
         if self.status is None:
-            self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+            # the status word and the sampled tokens lie side by side, so that one read brings both
+            self.mailbox = torch.zeros(1 + max(1, self.max_seqs), dtype=torch.int32, device=self.device)
+            self.status = self.mailbox[:1]
 
     def empty(self, *shape: int, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         return torch.empty(*shape, dtype=dtype or self.dtype, device=self.device)

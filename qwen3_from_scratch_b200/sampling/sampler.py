@@ -21,11 +21,14 @@ class Sampler:
         self.status = status
 
     def sample(self, logits: torch.Tensor, temperature: Sequence[float], top_k: Sequence[int],
-               request_key: Sequence[int], position: Sequence[int], seed: Sequence[int]) -> torch.Tensor:
+               request_key: Sequence[int], position: Sequence[int], seed: Sequence[int],
+               out: torch.Tensor = None) -> torch.Tensor:
         """logits: float32 [R, V] on the device; the sequences have R entries each (``position``
-        = index the new token will have in its request).  Returns int32 [R] on the device."""
+        = index the new token will have in its request).  Returns int32 [R] on the device
+        (``out`` if given)."""
         R = logits.shape[0]
-        out = torch.empty(R, dtype=torch.int32, device=self.device)
+        if out is None:
+            out = torch.empty(R, dtype=torch.int32, device=self.device)
         if R == 0:
             return out
         if all(t <= 0 for t in temperature):
