@@ -95,6 +95,7 @@ qkv_post_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict_
 // the D / 32 consecutive values from l * D / 32, so lanes 0..15 hold the first half of the head
 // and lane l + 16 holds the rotation partners of lane l; no shared memory, 2 * VPL-byte accesses.
 constexpr int QPV_WARPS = 8;
+constexpr int QPV_UNROLL = 4;
 
 template <int VPL>
 __global__ void __launch_bounds__(QPV_WARPS * 32)
@@ -126,86 +127,97 @@ qkv_post_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __rest
   }
   __syncthreads();
   const int head_end = min(n_heads, (int)(blockIdx.y + 1) * heads_per_block);
-  for (int head = blockIdx.y * heads_per_block + warp; head < head_end; head += QPV_WARPS) {
-  const bool is_q = head < Hq;
-  const bool is_k = !is_q && head < Hq + Hkv;
-  if (!is_q && !write_kv) continue;
-  const __nv_bfloat16* src = qkv + ((size_t)t * n_heads + head) * D + lane * VPL;
-  float x[VPL];
-  if (VPL == 8) {
-    const uint4 v = *reinterpret_cast<const uint4*>(src);
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  // Up to QPV_UNROLL heads of a warp are loaded before the first is worked on, so that a warp has
+  // several loads in flight: with one it could not keep the memory system busy on a long prompt.
+  for (int head0 = blockIdx.y * heads_per_block + warp; head0 < head_end; head0 += QPV_WARPS * QPV_UNROLL) {
+    float x[QPV_UNROLL][VPL];
+    bool live[QPV_UNROLL];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      x[(2 * k) % VPL] = __uint_as_float(w[k] << 16);
-      x[(2 * k + 1) % VPL] = __uint_as_float(w[k] & 0xffff0000u);
+    for (int u = 0; u < QPV_UNROLL; ++u) {
+      const int head = head0 + u * QPV_WARPS;
+      live[u] = head < head_end && (head < Hq || write_kv);
+      if (!live[u]) continue;
+      const __nv_bfloat16* src = qkv + ((size_t)t * n_heads + head) * D + lane * VPL;
+      if (VPL == 8) {
+        const uint4 v = *reinterpret_cast<const uint4*>(src);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          x[u][(2 * k) % VPL] = __uint_as_float(w[k] << 16);
+          x[u][(2 * k + 1) % VPL] = __uint_as_float(w[k] & 0xffff0000u);
+        }
+      } else if (VPL == 4) {
+        const uint2 v = *reinterpret_cast<const uint2*>(src);
+        x[u][0] = __uint_as_float(v.x << 16); x[u][1 % VPL] = __uint_as_float(v.x & 0xffff0000u);
+        x[u][2 % VPL] = __uint_as_float(v.y << 16); x[u][3 % VPL] = __uint_as_float(v.y & 0xffff0000u);
+      } else if (VPL == 2) {
+        const uint32_t v = *reinterpret_cast<const uint32_t*>(src);
+        x[u][0] = __uint_as_float(v << 16); x[u][1 % VPL] = __uint_as_float(v & 0xffff0000u);
+      } else {
+        x[u][0] = __bfloat162float(src[0]);
+      }
     }
-  } else if (VPL == 4) {
-    const uint2 v = *reinterpret_cast<const uint2*>(src);
-    x[0] = __uint_as_float(v.x << 16); x[1 % VPL] = __uint_as_float(v.x & 0xffff0000u);
-    x[2 % VPL] = __uint_as_float(v.y << 16); x[3 % VPL] = __uint_as_float(v.y & 0xffff0000u);
-  } else if (VPL == 2) {
-    const uint32_t v = *reinterpret_cast<const uint32_t*>(src);
-    x[0] = __uint_as_float(v << 16); x[1 % VPL] = __uint_as_float(v & 0xffff0000u);
-  } else {
-    x[0] = __bfloat162float(src[0]);
-  }
-  const float* w = is_q ? q_weight : (is_k ? k_weight : nullptr);
-  if (w) {
-    float ss = 0.f;
 #pragma unroll
-    for (int k = 0; k < VPL; ++k) ss += x[k] * x[k];
-    ss = warp_sum(ss);
-    const float rs = 1.0f / sqrtf(ss / (float)D + eps);
+    for (int u = 0; u < QPV_UNROLL; ++u) {
+      if (!live[u]) continue;  // uniform over the warp
+      const int head = head0 + u * QPV_WARPS;
+      const bool is_q = head < Hq;
+      const bool is_k = !is_q && head < Hq + Hkv;
+      const float* w = is_q ? q_weight : (is_k ? k_weight : nullptr);
+      if (w) {
+        float ss = 0.f;
 #pragma unroll
-    for (int k = 0; k < VPL; ++k) x[k] = x[k] * rs * w[lane * VPL + k];
-  }
-  if ((is_q || is_k) && inv_freq != nullptr) {
-    const bool first_half = lane < 16;
+        for (int k = 0; k < VPL; ++k) ss += x[u][k] * x[u][k];
+        ss = warp_sum(ss);
+        const float rs = 1.0f / sqrtf(ss / (float)D + eps);
 #pragma unroll
-    for (int k = 0; k < VPL; ++k) {
-      const float partner = __shfl_xor_sync(0xffffffffu, x[k], 16);
-      const int j = (lane & 15) * VPL + k;  // index of the pair
-      const float c = cs[j], sn = cs[D / 2 + j];
-      x[k] = first_half ? x[k] * c - partner * sn : x[k] * c + partner * sn;
+        for (int k = 0; k < VPL; ++k) x[u][k] = x[u][k] * rs * w[lane * VPL + k];
+      }
+      if ((is_q || is_k) && inv_freq != nullptr) {
+        const bool first_half = lane < 16;
+#pragma unroll
+        for (int k = 0; k < VPL; ++k) {
+          const float partner = __shfl_xor_sync(0xffffffffu, x[u][k], 16);
+          const int j = (lane & 15) * VPL + k;  // index of the pair
+          const float c = cs[j], sn = cs[D / 2 + j];
+          x[u][k] = first_half ? x[u][k] * c - partner * sn : x[u][k] * c + partner * sn;
+        }
+      }
+      __nv_bfloat16* dst;
+      if (is_q) {
+        dst = q_out + ((size_t)t * Hq + head) * D;
+      } else {
+        const int seq = tok_seq[t];
+        if (pos < 0 || seq < 0) {
+          if (lane == 0) atomicOr(status, Q3_STATUS_BAD_POSITION);
+          continue;
+        }
+        const int page = block_table[(size_t)seq * table_stride + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+          if (lane == 0) atomicOr(status, Q3_STATUS_BAD_PAGE);
+          continue;
+        }
+        const int hk = is_k ? head - Hq : head - Hq - Hkv;
+        dst = (is_k ? k_pages : v_pages) + (((size_t)page * Hkv + hk) * page_size + (pos % page_size)) * D;
+      }
+      dst += lane * VPL;
+      if (VPL == 8) {
+        uint32_t o[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          __nv_bfloat162 p = __floats2bfloat162_rn(x[u][(2 * k) % VPL], x[u][(2 * k + 1) % VPL]);
+          o[k] = *reinterpret_cast<uint32_t*>(&p);
+        }
+        *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+      } else if (VPL == 4) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(x[u][0], x[u][1 % VPL]), b = __floats2bfloat162_rn(x[u][2 % VPL], x[u][3 % VPL]);
+        *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+      } else if (VPL == 2) {
+        *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(x[u][0], x[u][1 % VPL]);
+      } else {
+        dst[0] = __float2bfloat16_rn(x[u][0]);
+      }
     }
-  }
-  __nv_bfloat16* dst;
-  if (is_q) {
-    dst = q_out + ((size_t)t * Hq + head) * D;
-  } else {
-    const int seq = tok_seq[t];
-    if (pos < 0 || seq < 0) {
-      if (lane == 0) atomicOr(status, Q3_STATUS_BAD_POSITION);
-      continue;
-    }
-    const int page = block_table[(size_t)seq * table_stride + pos / page_size];
-    if (page < 0 || page >= num_pages) {
-      if (lane == 0) atomicOr(status, Q3_STATUS_BAD_PAGE);
-      continue;
-    }
-    const int hk = is_k ? head - Hq : head - Hq - Hkv;
-    dst = (is_k ? k_pages : v_pages) + (((size_t)page * Hkv + hk) * page_size + (pos % page_size)) * D;
-  }
-  dst += lane * VPL;
-  if (VPL == 8) {
-    uint32_t o[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) o[k] = 0;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      __nv_bfloat162 p = __floats2bfloat162_rn(x[(2 * k) % VPL], x[(2 * k + 1) % VPL]);
-      o[k] = *reinterpret_cast<uint32_t*>(&p);
-    }
-    *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
-  } else if (VPL == 4) {
-    __nv_bfloat162 a = __floats2bfloat162_rn(x[0], x[1 % VPL]), b = __floats2bfloat162_rn(x[2 % VPL], x[3 % VPL]);
-    *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
-  } else if (VPL == 2) {
-    *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(x[0], x[1 % VPL]);
-  } else {
-    dst[0] = __float2bfloat16_rn(x[0]);
-  }
   }
 }
 
