@@ -360,6 +360,19 @@ def profile(args):
         run()
     torch.cuda.synchronize()
     torch.cuda.profiler.stop()
+    if args.time_ops:
+        from qwen3_from_scratch_b200.kernels import ops
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ops.op_timing() as timing:
+            t0.record()
+            run()
+            t1.record()
+        totals = timing.totals()
+        whole = t0.elapsed_time(t1) * 1e3
+        for name, (calls, us) in sorted(totals.items(), key=lambda kv: -kv[1][1]):
+            print(f"  {us:9.1f} us {calls:4d}x {us / calls:8.2f} us each  {name}")
+        print(f"  {whole - sum(us for _, us in totals.values()):9.1f} us  outside this module's launchers (library products)")
+        print(f"  {whole:9.1f} us  the step")
     print(f"profiled 2 {args.profile} steps, batch {args.batch}, context {args.context}, layers {cfg['num_hidden_layers']}")
     return 0
 
@@ -373,6 +386,8 @@ def main() -> int:
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=CONTEXT)
     p.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in the output)")
+    p.add_argument("--time-ops", action="store_true",
+                   help="with --profile: one more step with CUDA events around every launcher call, summed by name")
     p.add_argument("--profile", choices=["decode", "prefill"], default=None,
                    help="short run for a profiler instead of the benchmark (see profile())")
     args = p.parse_args()

@@ -89,6 +89,7 @@ class Model:
     @torch.inference_mode()
     def step(self, ctx: StepContext) -> torch.Tensor:
         """One batch through every layer of the run order; float32 logits [len(logit_rows), vocab]."""
+        ctx.per_step = {}  # what parts share within a step is computed anew (and so is recorded by a graph capture)
         stream = self.embedding.forward(ctx.token_ids)
         pending = None
         for call in self.spec.order:

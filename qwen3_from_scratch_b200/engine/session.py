@@ -7,6 +7,7 @@ step's tokens are recorded after it; ``end`` gives everything back.
 
 from __future__ import annotations
 
+import gc
 from typing import Hashable, List, Optional, Sequence
 
 import torch
@@ -58,8 +59,17 @@ class DecodeGraphs:
             graph = torch.cuda.CUDAGraph()
             if self.pool is None:
                 self.pool = torch.cuda.graph_pool_handle()
-            with torch.cuda.graph(graph, pool=self.pool):
-                logits = s.model.step(ctx)
+            # No garbage collection while recording: the collector may destroy an older engine's graphs,
+            # and destroying a graph is a CUDA call that invalidates a capture in progress.
+            gc.collect()
+            collecting = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph, pool=self.pool):
+                    logits = s.model.step(ctx)
+            finally:
+                if collecting:
+                    gc.enable()
             self.graphs[key] = (ctx, graph, logits)
             s.last_context, s.last_graph = ctx, (graph, logits)
             return eager

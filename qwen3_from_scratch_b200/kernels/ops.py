@@ -48,8 +48,9 @@ _SIGNATURES = {
                             _c_float, _c_void_p],
     "q3_rmsnorm": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p],
     "q3_gemm_f32_nt": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "q3_rope_table": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
     "q3_qkv_post": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
-                    _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p,
+                    _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p,
                     _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p],
     "q3_attn_ref": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                     _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
@@ -99,16 +100,48 @@ class _Counting:
     def __init__(self, lib):
         self._lib = lib
         self.calls = 0
+        self.events = None  # a list while op_timing() is active: (launcher name, start event, end event)
 
     def __getattr__(self, name):
         fn = getattr(self._lib, name)
 
         def counted(*args):
             self.calls += 1
-            return fn(*args)
+            if self.events is None:
+                return fn(*args)
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            code = fn(*args)
+            end.record()
+            self.events.append((name, start, end))
+            return code
 
         setattr(self, name, counted)
         return counted
+
+
+class op_timing:
+    """``with op_timing() as t: ...`` brackets every launcher call of this module with CUDA events;
+    afterwards ``t.totals()`` gives {launcher name: (calls, microseconds)} as the device saw them in
+    place (warm caches, the stream's real order), which a profiler that replays kernels one by one
+    with flushed caches does not show.  Work that does not go through this module (library matrix
+    products) falls between the brackets and is not counted."""
+
+    def __enter__(self):
+        library().events = []
+        return self
+
+    def __exit__(self, *exc):
+        self._events, library().events = library().events, None
+        return False
+
+    def totals(self):
+        torch.cuda.synchronize()
+        out = {}
+        for name, start, end in self._events:
+            calls, us = out.get(name, (0, 0.0))
+            out[name] = (calls + 1, us + start.elapsed_time(end) * 1e3)
+        return out
 
 
 def launch_count() -> int:
@@ -252,8 +285,9 @@ def qkv_post(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor, v_pa
              q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
              inv_freq: Optional[torch.Tensor], rotary_dim: int, positions: torch.Tensor,
              tok_seq: torch.Tensor, block_table: torch.Tensor, num_q_heads: int, num_kv_heads: int,
-             head_dim: int, write_kv: bool, status: torch.Tensor) -> None:
-    """Head norm, rotation, q to its buffer and k/v into their pages, in one pass over qkv."""
+             head_dim: int, write_kv: bool, status: torch.Tensor, cos_sin: Optional[torch.Tensor] = None) -> None:
+    """Head norm, rotation, q to its buffer and k/v into their pages, in one pass over qkv.
+    ``cos_sin``: the table of ``rope_table`` for the same positions and inv_freq (optional)."""
     _check("qkv_post.qkv", qkv)
     _check("qkv_post.q_out", q_out, qkv.dtype)
     _check("qkv_post.k_pages", k_pages, qkv.dtype)
@@ -280,12 +314,28 @@ def qkv_post(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor, v_pa
         _check("qkv_post.inv_freq", inv_freq, torch.float32)
         if inv_freq.numel() * 2 != rotary_dim:
             raise KernelError(f"qkv_post: inv_freq has {inv_freq.numel()} entries, rotary_dim is {rotary_dim}")
+    if cos_sin is not None:
+        _check("qkv_post.cos_sin", cos_sin, torch.float32)
+        if inv_freq is None or tuple(cos_sin.shape) != (T, rotary_dim):
+            raise KernelError(f"qkv_post: cos_sin {tuple(cos_sin.shape)} expected [{T}, {rotary_dim}] with inv_freq")
     code = library().q3_qkv_post(
         qkv.data_ptr(), dtype_tag(qkv.dtype), T, num_q_heads, num_kv_heads, head_dim, _ptr(q_weight),
-        _ptr(k_weight), float(eps), _ptr(inv_freq), int(rotary_dim), positions.data_ptr(), tok_seq.data_ptr(),
+        _ptr(k_weight), float(eps), _ptr(inv_freq), _ptr(cos_sin), int(rotary_dim), positions.data_ptr(), tok_seq.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], page_size, k_pages.data_ptr(), v_pages.data_ptr(),
         num_pages, q_out.data_ptr(), 1 if write_kv else 0, status.data_ptr(), _stream())
     _done("qkv_post", code, f"head_dim {head_dim}, rotary_dim {rotary_dim}")
+
+
+def rope_table(inv_freq: torch.Tensor, positions: torch.Tensor, table: torch.Tensor) -> None:
+    """table[t] = cos(positions[t] * inv_freq) then sin(...): float32 [T, 2 * len(inv_freq)]."""
+    _check("rope_table.inv_freq", inv_freq, torch.float32)
+    _check("rope_table.positions", positions, torch.int32)
+    _check("rope_table.table", table, torch.float32)
+    T, half = positions.numel(), inv_freq.numel()
+    if tuple(table.shape) != (T, 2 * half):
+        raise KernelError(f"rope_table: table {tuple(table.shape)} expected [{T}, {2 * half}]")
+    code = library().q3_rope_table(inv_freq.data_ptr(), positions.data_ptr(), table.data_ptr(), T, half, _stream())
+    _done("rope_table", code)
 
 
 def attn_ref(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
@@ -381,7 +431,7 @@ def rope(x: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, positions: to
         raise KernelError(f"rope: x {tuple(x.shape)}, out {tuple(out.shape)}, positions {positions.numel()}, "
                           f"inv_freq {inv_freq.numel()}, rotary_dim {rotary_dim}")
     code = library().q3_qkv_post(
-        x.data_ptr(), dtype_tag(x.dtype), T, heads, 0, d, None, None, 0.0, inv_freq.data_ptr(), int(rotary_dim),
+        x.data_ptr(), dtype_tag(x.dtype), T, heads, 0, d, None, None, 0.0, inv_freq.data_ptr(), None, int(rotary_dim),
         positions.data_ptr(), positions.data_ptr(), None, 1, 1, None, None, 0, out.data_ptr(), 0,
         status.data_ptr(), _stream())
     _done("rope", code, f"head_dim {d}, rotary_dim {rotary_dim}")

@@ -88,8 +88,10 @@ class GQAAttention(Mixer):
         fused = self.position.fused_rotary() if self.position is not None else None
         if self.position is None or fused is not None:
             inv_freq, rotary_dim = fused if fused is not None else (None, 0)
+            cos_sin = self.position.step_table(ctx) if fused is not None else None
             ops.qkv_post(qkv, q, k_pages, v_pages, self.q_norm_weight, self.k_norm_weight, eps, inv_freq,
-                         rotary_dim, ctx.positions, ctx.tok_seq, table, hq, hkv, d, write_cache, self.rt.status)
+                         rotary_dim, ctx.positions, ctx.tok_seq, table, hq, hkv, d, write_cache, self.rt.status,
+                         cos_sin=cos_sin)
         else:
             # a position encoding the kernel does not know: norm, encode, then scatter, as separate steps
             heads = qkv.view(T, hq + 2 * hkv, d)

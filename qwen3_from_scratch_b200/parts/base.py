@@ -150,6 +150,15 @@ class StepContext:
     max_kv_len: int
     num_decode: int
 
+    def shared_in_step(self, key, make):
+        """What ``make()`` returns, computed once per step: parts of different layers that need the
+        same derived data of the batch (a table of angles for the step's positions, ...) ask with
+        the same key.  ``Model.step`` empties ``per_step`` before the first layer runs."""
+        store = self.__dict__.setdefault("per_step", {})
+        if key not in store:
+            store[key] = make()
+        return store[key]
+
     def kv(self, cache_id: int):  # pragma: no cover - interface
         raise NotImplementedError
 
@@ -196,6 +205,13 @@ class PositionEncoding(Part):
         raise NotImplementedError
 
     def fused_rotary(self) -> Optional[Tuple[torch.Tensor, int]]:
+        """(inv_freq, rotary_dim) if the encoding is a rotate-half rotation by position * inv_freq
+        that the fused kernel can apply, else None (``apply`` is then used)."""
+        return None
+
+    def step_table(self, ctx: "StepContext") -> Optional[torch.Tensor]:
+        """With ``fused_rotary``: float32 [T, rotary_dim] cosines then sines of the step's tokens,
+        shared by all layers of the step, or None (the fused kernel then computes the angles)."""
         return None
 
 

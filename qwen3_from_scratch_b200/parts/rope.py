@@ -2,8 +2,9 @@
 
 Reference: models/rotary.py:36-45 (inv_freq[j] = theta^(-2j/D), angle = position * inv_freq[j])
 and models/rotary.py:13-22 (y1 = x1 cos - x2 sin, y2 = x2 cos + x1 sin on the two halves).
-The angle, sine and cosine are float32 on the device; there is no table of positions,
-so ``max_positions`` only bounds what a request may reach.
+The angle, sine and cosine are float32 on the device.  There is no table over all positions
+(``max_positions`` only bounds what a request may reach): the sines and cosines of the positions
+of one step are computed once per step and read by every layer.
 """
 
 from __future__ import annotations
@@ -36,8 +37,18 @@ class RotaryNeox(PositionEncoding):
         exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim
         self.inv_freq = (1.0 / (self.theta ** exponent)).to(rt.device)
 
+        self._table = rt.shared(f"rotary.table.{self.theta!r}.{self.rotary_dim}", rt.max_tokens, self.rotary_dim,
+                                dtype=torch.float32)
+
     def fused_rotary(self) -> Optional[Tuple[torch.Tensor, int]]:
         return self.inv_freq, self.rotary_dim
+
+    def step_table(self, ctx) -> Optional[torch.Tensor]:
+        def make():
+            table = self._table[:ctx.positions.numel()]
+            ops.rope_table(self.inv_freq, ctx.positions, table)
+            return table
+        return ctx.shared_in_step(("rotary_neox", self.theta, self.rotary_dim), make)
 
     def apply(self, x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         out = torch.empty_like(x)

@@ -224,9 +224,12 @@ def table_tensor(tables):
 
 
 @pytest.mark.parametrize("dtype", list(DT))
-@pytest.mark.parametrize("hq,hkv,d,rot", [(6, 3, 48, 48), (4, 1, 80, 32), (8, 2, 128, 128), (2, 2, 16, 16)])
-def test_qkv_post(dtype, hq, hkv, d, rot):
-    """Head norm + rotation + scatter, with a partial rotary width and pages out of order."""
+@pytest.mark.parametrize("with_table", [False, True])
+@pytest.mark.parametrize("hq,hkv,d,rot", [(6, 3, 48, 48), (4, 1, 80, 32), (8, 2, 128, 128), (2, 2, 16, 16),
+                                          (3, 1, 64, 64), (5, 1, 32, 32), (3, 2, 256, 256), (16, 8, 128, 128)])
+def test_qkv_post(dtype, hq, hkv, d, rot, with_table):
+    """Head norm + rotation + scatter, with a partial rotary width and pages out of order; with the
+    angles computed in the kernel and with the step's table of sines and cosines."""
     g = torch.Generator().manual_seed(5)
     page_size, eps, theta = 8, 1e-6, 10000.0
     starts, news = [0, 13, 40], [21, 1, 7]  # tokens already cached, tokens of this step
@@ -242,8 +245,14 @@ def test_qkv_post(dtype, hq, hkv, d, rot):
     v_pages = torch.zeros_like(k_pages)
     q_out = torch.empty(T, hq, d, device="cuda", dtype=DT[dtype])
     st = status()
+    cos_sin = None
+    if with_table:
+        cos_sin = torch.empty(T, rot, device="cuda", dtype=torch.float32)
+        ops().rope_table(dev(inv_freq), dev(positions), cos_sin)
+        ang32 = positions.float()[:, None] * inv_freq[None, :]
+        assert torch.allclose(cos_sin.cpu(), torch.cat([ang32.cos(), ang32.sin()], dim=1), atol=2e-6)
     ops().qkv_post(dev(qkv), q_out, k_pages, v_pages, dev(qw), dev(kw), eps, dev(inv_freq), rot, dev(positions),
-                   dev(tok_seq), dev(table_tensor(tables)), hq, hkv, d, True, st)
+                   dev(tok_seq), dev(table_tensor(tables)), hq, hkv, d, True, st, cos_sin=cos_sin)
     assert int(st.item()) == 0
     x = qkv.double().view(T, hq + 2 * hkv, d)
     q, k, v = x[:, :hq], x[:, hq:hq + hkv], x[:, hq + hkv:]
@@ -273,7 +282,7 @@ def test_qkv_post(dtype, hq, hkv, d, rot):
     bad = table_tensor(tables)
     bad[0, 0] = num_pages
     ops().qkv_post(dev(qkv), q_out, k_pages, v_pages, dev(qw), dev(kw), eps, dev(inv_freq), rot, dev(positions),
-                   dev(tok_seq), dev(bad), hq, hkv, d, True, st)
+                   dev(tok_seq), dev(bad), hq, hkv, d, True, st, cos_sin=cos_sin)
     assert int(st.item()) & 2
 
 
