@@ -269,26 +269,75 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 }
 
 // Merges the splits of one (sequence, head): out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
-__global__ void attn_combine_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
-                                    const int* __restrict__ q_start, int Hq, int D, int num_splits) {
+// The splits are dealt to the warps of the block and each lane owns pairs of output values, so all
+// of a block's loads are in flight at once: the kernel is two round trips to memory long, however
+// many splits there are.  D is even and at most 256.
+constexpr int AC_WARPS = 8;
+constexpr int AC_MAX_D = 256;
+
+__global__ void __launch_bounds__(AC_WARPS * 32)
+attn_combine_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
+                    const int* __restrict__ q_start, int Hq, int D, int num_splits) {
   pdl_wait();
   pdl_launch_dependents();
+  __shared__ float acc_s[AC_WARPS][AC_MAX_D];
+  __shared__ float den_s[AC_WARPS];
+  __shared__ float max_s[AC_WARPS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.x, b = blockIdx.y;
   const float* base = partial + ((size_t)b * Hq + head) * num_splits * (D + 2);
-  float big = -INFINITY;
-  for (int s = 0; s < num_splits; ++s) big = fmaxf(big, base[(size_t)s * (D + 2) + D]);
-  const int tq = q_start[b];
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float acc = 0.f, den = 0.f;
-    if (big != -INFINITY) {
-      for (int s = 0; s < num_splits; ++s) {
-        const float* row = base + (size_t)s * (D + 2);
-        const float wgt = row[D] == -INFINITY ? 0.f : exp2f(row[D] - big);
-        acc += row[d] * wgt;
-        den += row[D + 1] * wgt;
+  float mx = -INFINITY;
+  for (int s = threadIdx.x; s < num_splits; s += AC_WARPS * 32) mx = fmaxf(mx, base[(size_t)s * (D + 2) + D]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) max_s[warp] = mx;
+  __syncthreads();
+  float big = max_s[0];
+#pragma unroll
+  for (int w = 1; w < AC_WARPS; ++w) big = fmaxf(big, max_s[w]);
+
+  // lane owns the value pairs d = 2 * lane + 64 * j; warp owns the splits warp, warp + AC_WARPS, ...
+  float2 acc[AC_MAX_D / 64];
+#pragma unroll
+  for (int j = 0; j < AC_MAX_D / 64; ++j) acc[j] = make_float2(0.f, 0.f);
+  float den = 0.f;
+  if (big != -INFINITY) {
+#pragma unroll 2
+    for (int s = warp; s < num_splits; s += AC_WARPS) {
+      const float* row = base + (size_t)s * (D + 2);
+      const float2 ml = *reinterpret_cast<const float2*>(row + D);  // (maximum, denominator) of the split
+      const float wgt = ml.x == -INFINITY ? 0.f : exp2f(ml.x - big);
+      den += ml.y * wgt;
+#pragma unroll
+      for (int j = 0; j < AC_MAX_D / 64; ++j) {
+        const int d = 2 * lane + 64 * j;
+        if (d < D) {
+          const float2 v = *reinterpret_cast<const float2*>(row + d);
+          acc[j].x += v.x * wgt;
+          acc[j].y += v.y * wgt;
+        }
       }
     }
-    out[((size_t)tq * Hq + head) * D + d] = __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
+  }
+#pragma unroll
+  for (int j = 0; j < AC_MAX_D / 64; ++j) {
+    const int d = 2 * lane + 64 * j;
+    if (d < D) {
+      acc_s[warp][d] = acc[j].x;
+      acc_s[warp][d + 1] = acc[j].y;
+    }
+  }
+  if (lane == 0) den_s[warp] = den;
+  __syncthreads();
+  const int tq = q_start[b];
+  for (int d = threadIdx.x; d < D; d += AC_WARPS * 32) {
+    float a = 0.f, dn = 0.f;
+#pragma unroll
+    for (int w = 0; w < AC_WARPS; ++w) {
+      a += acc_s[w][d];
+      dn += den_s[w];
+    }
+    out[((size_t)tq * Hq + head) * D + d] = __float2bfloat16_rn(dn > 0.f ? a / dn : 0.f);
   }
 }
 
@@ -313,7 +362,7 @@ static int attn_decode_launch(const void* q, const void* k_pages, const void* v_
   int code = launch_status();
   if (code != 0 || num_splits == 1) return code;
   dim3 cgrid(Hq, B);
-  q3::launch(attn_combine_kernel, dim3(cgrid), dim3(128), 0, stream, partial, (__nv_bfloat16*)out, q_start, Hq, S::D, num_splits);
+  q3::launch(attn_combine_kernel, dim3(cgrid), dim3(AC_WARPS * 32), 0, stream, partial, (__nv_bfloat16*)out, q_start, Hq, S::D, num_splits);
   return launch_status();
 }
 
@@ -401,8 +450,9 @@ extern "C" int q3_attn_decode_noalloc(const void* q, const void* k_pages, const 
 extern "C" int q3_attn_combine(const float* partial, void* out, const int* q_start, int B, int Hq, int D,
                                int num_splits, cudaStream_t stream) {
   if (B <= 0 || num_splits <= 1) return 0;
+  if (D <= 0 || D > q3::AC_MAX_D || (D & 1)) return Q3_ERR_SIZE;
   dim3 cgrid(Hq, B);
-  q3::launch(q3::attn_combine_kernel, cgrid, dim3(128), 0, stream, partial, (__nv_bfloat16*)out, q_start, Hq, D,
+  q3::launch(q3::attn_combine_kernel, cgrid, dim3(q3::AC_WARPS * 32), 0, stream, partial, (__nv_bfloat16*)out, q_start, Hq, D,
              num_splits);
   return q3::launch_status();
 }
