@@ -3,22 +3,25 @@
 //
 // A block owns 128 query rows of one kv head (rows are (token, head-in-group) pairs as in
 // attn_prefill.cu) and walks the keys in tiles of 128:
-//   loader thread   TMA brings the tile's pages of K and of V into shared memory (128-byte swizzle),
-//                   one box per page and per 64 values of the head; the page ids come from the
-//                   block table, the tensor maps cover a layer's whole K (or V) pool.
+//   two loader warps (one for K, one for V): TMA brings the tile's pages into shared memory (128-byte
+//                   swizzle), one box per page and per 64 values of the head, each lane issuing the
+//                   boxes of one page; the page ids come from the block table, two tiles ahead; the
+//                   tensor maps cover a layer's whole K (or V) pool.
 //   issue thread    S = Q K^T   (tcgen05.mma, both operands K-major, accumulator: 128 TMEM columns)
-//                   O += P V    (P K-major from shared memory, V MN-major; accumulator: D columns)
-//   256 softmax threads, two per query row (one for keys 0..63 of the tile, one for 64..127; they
-//                   agree on the row maximum through shared memory): read S from TMEM (a thread
-//                   owns half a row, no shuffles), mask the diagonal tile, keep a running
-//                   reference maximum and denominator in float32, write P as bfloat16 into shared
-//                   memory in the swizzled layout the tensor cores read, and rescale O in TMEM
-//                   when the reference maximum has to move (it moves only when the row maximum
-//                   exceeds it by more than 2^8, so the rescale is rare after the first tiles).
-// K and V tiles are double-buffered and so is S in TMEM, so the loads and the next tile's Q K^T run
-// while the softmax threads work.  The time of a prompt is set by its last query tile, which walks
-// every key: tiles of 128 keys shared by two threads per row halve that chain.  One block per SM
-// (192 KB of shared memory, all 512 TMEM columns).  All mbarrier waits are bounded (see tc_common.cuh).
+//                   O += P V    (P from tensor memory, where it overwrites its own S; V MN-major from
+//                                shared memory; accumulator: D columns)
+//   512 softmax threads, four per query row (each takes 32 of the tile's 128 keys; they agree on
+//                   the row maximum through shared memory): read S from TMEM (a thread owns a
+//                   quarter of a row, no shuffles), mask the diagonal tile, keep a running
+//                   reference maximum and denominator in float32, write P as bfloat16 pairs into
+//                   the first 64 columns of the tile's S, and rescale O in TMEM when the reference
+//                   maximum has to move (it moves only when the row maximum exceeds it by more
+//                   than 2^8, so the rescale is rare after the first tiles; only then do the
+//                   threads wait for the previous tile's P V).
+// K and V tiles are double-buffered and so is S (with its P) in TMEM, so the loads, the next tile's
+// Q K^T and the previous tile's P V run while the softmax threads work.  The time of a prompt is set by its last query tile, which walks
+// every key one tile after the other: the more threads share a row, the shorter that chain.  One block per SM
+// (164 KB of shared memory, all 512 TMEM columns).  All mbarrier waits are bounded (see tc_common.cuh).
 //
 // Reference for the math: kernels/triton/paged_attn.py:89-181 (online softmax with exp2, P rounded
 // to the value dtype before P V), models/attn.py:388-400 (scale, causal on absolute positions).
@@ -28,9 +31,11 @@ namespace q3 {
 
 constexpr int AT_BM = 128;   // query rows per block
 constexpr int AT_BN = 128;   // keys per tile
-constexpr int AT_HALF = 64;  // keys per softmax thread
-constexpr int AT_SOFTMAX = 2 * AT_BM;          // softmax threads: warps 0..7
-constexpr int AT_THREADS = AT_SOFTMAX + 64;    // + issue warp (8) and loader warp (9)
+constexpr int AT_PARTS = 4;                    // softmax threads per query row
+constexpr int AT_PART = AT_BN / AT_PARTS;      // keys per softmax thread: 32, one tcgen05.ld
+constexpr int AT_SOFTMAX = AT_PARTS * AT_BM;   // softmax threads: warps 0..15
+constexpr int AT_ISSUE_WARP = AT_SOFTMAX / 32, AT_LOAD_WARP = AT_ISSUE_WARP + 1;
+constexpr int AT_THREADS = AT_SOFTMAX + 96;    // + issue warp and two loader warps (K, V)
 
 template <int D>
 struct AttnTcShape {
@@ -38,12 +43,11 @@ struct AttnTcShape {
   static constexpr int Q_BYTES = AT_BM * D * 2;
   static constexpr int K_BYTES = AT_BN * D * 2;
   static constexpr int V_BYTES = AT_BN * D * 2;
-  static constexpr int P_BYTES = AT_BM * AT_BN * 2;
   static constexpr int BAR_BYTES = 128;
-  static constexpr int XCHG_BYTES = 2 * 2 * AT_BM * 4;  // [tile parity][half][row]
+  static constexpr int XCHG_BYTES = 2 * AT_PARTS * AT_BM * 4;  // [tile parity][part][row]
   // K and V tiles are double-buffered; no slack for alignment: the dynamic shared memory of a block
   // that has no static shared memory starts on a 1024-byte boundary (checked in the kernel)
-  static constexpr size_t SMEM_BYTES = (size_t)Q_BYTES + 2 * K_BYTES + 2 * V_BYTES + P_BYTES + BAR_BYTES + XCHG_BYTES;
+  static constexpr size_t SMEM_BYTES = (size_t)Q_BYTES + 2 * K_BYTES + 2 * V_BYTES + BAR_BYTES + XCHG_BYTES;
   static constexpr int TMEM_COLS = 512;                // S: two buffers of 128 columns at 0 and 128, O: D columns at 256
 };
 
@@ -65,8 +69,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   unsigned char* q_s = smem_raw;
   unsigned char* k_s = q_s + S::Q_BYTES;       // two stages
   unsigned char* v_s = k_s + 2 * S::K_BYTES;   // two stages
-  unsigned char* p_s = v_s + 2 * S::V_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + S::P_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * S::V_BYTES);
   uint64_t* k_full = bars + 0;   // [2]
   uint64_t* k_empty = bars + 2;  // [2]
   uint64_t* v_full = bars + 4;   // [2]
@@ -76,7 +79,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   uint64_t* pv_done = bars + 11;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 12);
   int* abort_word = reinterpret_cast<int*>(bars + 13);
-  float* row_xchg = reinterpret_cast<float*>(p_s + S::P_BYTES + S::BAR_BYTES);  // [2][128] row maxima, then sums
+  float* row_xchg = reinterpret_cast<float*>(v_s + 2 * S::V_BYTES + S::BAR_BYTES);  // [2][parts][128] row maxima, then sums
 #define abort_flag (*abort_word)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -110,7 +113,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       mbar_init(v_empty + i, 1);
       mbar_init(s_ready + i, 1);
     }
-    mbar_init(p_ready, AT_SOFTMAX);
+    mbar_init(p_ready, AT_SOFTMAX / 32);
     mbar_init(pv_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -118,7 +121,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   pdl_launch_dependents();
   // Tensor memory is taken only after the wait: a block that holds TMEM while it waits for the
   // kernel before it could keep that kernel's own blocks from ever getting theirs.
-  if (warp == 8) {
+  if (warp == AT_ISSUE_WARP) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_holder)),
                  "r"((uint32_t)S::TMEM_COLS)
                  : "memory");
@@ -143,52 +146,52 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   const uint32_t tmem_s = *tmem_holder;           // S of tile j lives at column (j & 1) * 128
   const uint32_t tmem_o = tmem_s + 2 * AT_BN;
 
-  if (warp == 9) {
-    // ------------------------------------------------------------------ loader
-    // Lane p of the warp owns page p of a tile: it looks its page id up (for the next tile already
-    // while the current one is in flight) and issues that page's boxes, so the sixteen lookups and
-    // the copies of a tile go out together instead of one after the other.
+  if (warp >= AT_LOAD_WARP) {
+    // ------------------------------------------------------------------ loaders: one warp for K, one for V
+    // Lane p of a loader warp owns page p of a tile: it looks its page id up two tiles ahead (so the
+    // lookup's latency never stops the loop) and issues that page's boxes, so the sixteen lookups and
+    // the copies of a tile go out together instead of one after the other.  Two warps, because one
+    // warp alone does not issue the boxes of K and V (64 per tile at 16 tokens a page) fast enough.
+    const bool is_v = warp != AT_LOAD_WARP;
+    const CUtensorMap* map = is_v ? &map_v : &map_k;
+    unsigned char* dst_base = is_v ? v_s : k_s;
+    uint64_t* full = is_v ? v_full : k_full;
+    uint64_t* empty = is_v ? v_empty : k_empty;
     const int pages_per_tile = AT_BN / page_size;
-    auto page_row = [&](int j) -> int {  // first row of lane's page of tile j in the [pages * heads * page_size, D] view
+    auto page_id = [&](int j) -> int {  // lane's page of tile j, or -1 if the tile has no such page
       if (lane >= pages_per_tile || j >= n_tiles || j * AT_BN + lane * page_size >= len) return -1;
-      const int page = table[(j * AT_BN) / page_size + lane];
-      if (page < 0 || page >= num_pages) {
-        atomicOr(status, Q3_STATUS_BAD_PAGE);
-        return -1;
-      }
-      return (page * Hkv + hk) * page_size;
+      return table[(j * AT_BN) / page_size + lane];
     };
-    int y = page_row(0);
+    int page = page_id(0), page_next = page_id(1);
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int st = j & 1;
       const uint32_t use = (uint32_t)j >> 1;
-      const int y_next = page_row(j + 1);
+      const int page_after = page_id(j + 2);
+      const bool wanted = lane < pages_per_tile && j * AT_BN + lane * page_size < len;
+      if (wanted && (page < 0 || page >= num_pages)) {
+        if (!is_v) atomicOr(status, Q3_STATUS_BAD_PAGE);
+        page = -1;
+      }
+      const int y = page < 0 ? -1 : (page * Hkv + hk) * page_size;  // first row in the [pages * heads * page_size, D] view
       const uint32_t have = __popc(__ballot_sync(0xffffffffu, y >= 0));
       const uint32_t bytes = have * page_size * D * 2;
-      if (use > 0) ok = ok && mbar_wait(k_empty + st, (use - 1) & 1, &abort_flag);
-      if (lane == 0 && ok) mbar_expect_tx(k_full + st, bytes);
+      if (use > 0) ok = ok && mbar_wait(empty + st, (use - 1) & 1, &abort_flag);
+      if (lane == 0 && ok) mbar_expect_tx(full + st, bytes);
       __syncwarp();
       if (y >= 0 && ok) {
 #pragma unroll
         for (int a = 0; a < ATOMS; ++a)
-          tma_load_2d(k_s + st * S::K_BYTES + a * (AT_BN * 128) + lane * page_size * 128, &map_k, k_full + st, a * 64, y);
+          tma_load_2d(dst_base + st * S::K_BYTES + a * (AT_BN * 128) + lane * page_size * 128, map, full + st, a * 64, y);
       }
-      if (use > 0) ok = ok && mbar_wait(v_empty + st, (use - 1) & 1, &abort_flag);
-      if (lane == 0 && ok) mbar_expect_tx(v_full + st, bytes);
-      __syncwarp();
-      if (y >= 0 && ok) {
-#pragma unroll
-        for (int a = 0; a < ATOMS; ++a)
-          tma_load_2d(v_s + st * S::V_BYTES + a * (AT_BN * 128) + lane * page_size * 128, &map_v, v_full + st, a * 64, y);
-      }
-      y = y_next;
+      page = page_next;
+      page_next = page_after;
     }
     if (!ok && lane == 0) {
       abort_flag = 1;
       atomicOr(status, Q3_STATUS_TIMEOUT);
     }
-  } else if (warp == 8) {
+  } else if (warp == AT_ISSUE_WARP) {
     // ------------------------------------------------------------------ tensor-core issue
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc(AT_BN, 0);  // 128 x 128, K and Q both K-major
@@ -217,10 +220,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         if (!mbar_wait(v_full + st, ((uint32_t)j >> 1) & 1, &abort_flag)) { ok = false; break; }
         tcgen05_fence_after();
 #pragma unroll
-        for (int t = 0; t < AT_BN / 16; ++t) {
-          const uint64_t a_desc = umma_desc_sw128(p_s + (t / 4) * (AT_BM * 128)) + 2 * (t % 4);
+        for (int t = 0; t < AT_BN / 16; ++t) {  // 16 keys: 8 packed columns of P, 16 rows of V
           const uint64_t b_desc = umma_desc_sw128_mn(v_s + st * S::V_BYTES + t * 2048, AT_BN * 128);
-          umma_f16(tmem_o, a_desc, b_desc, idesc_o, (j | t) != 0);
+          umma_f16_ts(tmem_o, tmem_s + st * AT_BN + 8 * t, b_desc, idesc_o, (j | t) != 0);
         }
         umma_commit(pv_done);
         umma_commit(v_empty + st);
@@ -231,50 +233,47 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax, two threads per row
-    // warps 0..3 take keys 0..63 of every tile, warps 4..7 keys 64..127; both see TMEM lanes
-    // (warp % 4) * 32 .., i.e. row (warp % 4) * 32 + lane.
-    const int half = warp >> 2;
+    // ------------------------------------------------------------------ softmax, four threads per row
+    // warps 4 p .. 4 p + 3 take keys 32 p .. 32 p + 31 of every tile; warp w sees TMEM lanes
+    // (w % 4) * 32 .., i.e. row (w % 4) * 32 + lane.
+    const int part = warp >> 2;
     const int rr = (warp & 3) * 32 + lane;
     const int R = row0 + rr;
     const bool valid_row = R < total_rows;
     const int my_pos = valid_row ? past + R / g : pos_last;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const int soft_tid = threadIdx.x;  // 0 .. 255
+    const int soft_tid = threadIdx.x;  // 0 .. 511
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     // Every softmax thread runs every iteration and meets the others at the named barrier even
     // after a wait has run out (the barrier itself cannot time out); `ok` only switches the work off.
     for (int j = 0; j < n_tiles; ++j) {
       const int st = j & 1;
-      float* xchg = row_xchg + (j & 1) * (2 * AT_BM);
+      float* xchg = row_xchg + (j & 1) * (AT_PARTS * AT_BM);
       ok = ok && mbar_wait(s_ready + st, ((uint32_t)j >> 1) & 1, &abort_flag);
       tcgen05_fence_after();
-      uint32_t sv[2][32];
-      tmem_ld_32(tmem_s + st * AT_BN + half * AT_HALF + lane_base, sv[0]);
-      tmem_ld_32(tmem_s + st * AT_BN + half * AT_HALF + lane_base + 32, sv[1]);
+      uint32_t sv[32];
+      tmem_ld_32(tmem_s + st * AT_BN + part * AT_PART + lane_base, sv);
       tmem_wait_ld();
-      const int base_n = j * AT_BN + half * AT_HALF;
+      const int base_n = j * AT_BN + part * AT_PART;
       float mx = -INFINITY;
       if (j * AT_BN + AT_BN - 1 > pos_first) {  // the diagonal: keys beyond this row's position are hidden
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const float v = (base_n + h * 32 + c <= my_pos) ? __uint_as_float(sv[h][c]) : -INFINITY;
-            sv[h][c] = __float_as_uint(v);
-            mx = fmaxf(mx, v);
-          }
+        for (int c = 0; c < 32; ++c) {
+          const float v = (base_n + c <= my_pos) ? __uint_as_float(sv[c]) : -INFINITY;
+          sv[c] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
       } else {
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(sv[h][c]));
+        for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
       }
-      // the two threads of a row agree on its maximum
-      xchg[half * AT_BM + rr] = mx;
+      // the threads of a row agree on its maximum
+      xchg[part * AT_BM + rr] = mx;
       asm volatile("bar.sync 1, %0;" ::"n"(AT_SOFTMAX) : "memory");
-      mx = fmaxf(mx, xchg[(half ^ 1) * AT_BM + rr]) * scale_log2;
+#pragma unroll
+      for (int o = 0; o < AT_PARTS; ++o) mx = fmaxf(mx, xchg[o * AT_BM + rr]);
+      mx *= scale_log2;
       // the reference maximum moves only when it must: probabilities up to 2^8 are harmless
       float alpha = 1.f;
       if (mx > m_ref + 8.f) {
@@ -282,39 +281,35 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         m_ref = mx;
       }
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-      // P and O belong to the tensor cores until the previous tile's P V has finished
-      if (j > 0) ok = ok && mbar_wait(pv_done, (j - 1) & 1, &abort_flag);
-      tcgen05_fence_after();
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        // each of the row's two threads rescales its half of the output columns
-#pragma unroll 1
-        for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
+        // O belongs to the tensor cores until the previous tile's P V has finished
+        ok = ok && mbar_wait(pv_done, (j - 1) & 1, &abort_flag);
+        tcgen05_fence_after();
+        // the row's threads rescale 32 output columns each (with D = 64 the first two of them)
+        if (part * 32 < D) {
           uint32_t ov[32];
-          tmem_ld_32(tmem_o + lane_base + c0, ov);
+          tmem_ld_32(tmem_o + lane_base + part * 32, ov);
           tmem_wait_ld();
 #pragma unroll
           for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * alpha);
-          tmem_st_32(tmem_o + lane_base + c0, ov);
+          tmem_st_32(tmem_o + lane_base + part * 32, ov);
+          tmem_wait_st();
         }
-        tmem_wait_st();
       }
       l *= alpha;
       float sum = 0.f;
-      unsigned char* p_atom = p_s + half * (AT_BM * 128);  // keys 0..63 -> first atom, 64..127 -> second
+      // P over the tile's own S: key k of the row goes to the half of column k / 2.  Every thread of
+      // the row has its S in registers since the barrier above, so the columns may be overwritten.
+      uint32_t pk[16];
 #pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) {
-          uint32_t pk[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float p0 = exp2f(fmaf(__uint_as_float(sv[h][c8 * 8 + 2 * e]), scale_log2, -m_use));
-            const float p1 = exp2f(fmaf(__uint_as_float(sv[h][c8 * 8 + 2 * e + 1]), scale_log2, -m_use));
-            sum += p0 + p1;
-            pk[e] = pack2(__float_as_uint(p0), __float_as_uint(p1));
-          }
-          *reinterpret_cast<uint4*>(p_atom + sw128_offset(rr, h * 32 + c8 * 8)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-        }
+      for (int e = 0; e < 16; ++e) {
+        const float p0 = ex2_approx(fmaf(__uint_as_float(sv[2 * e]), scale_log2, -m_use));
+        const float p1 = ex2_approx(fmaf(__uint_as_float(sv[2 * e + 1]), scale_log2, -m_use));
+        sum += p0 + p1;
+        pk[e] = pack2(__float_as_uint(p0), __float_as_uint(p1));
+      }
+      tmem_st_16(tmem_s + st * AT_BN + part * (AT_PART / 2) + lane_base, pk);
+      tmem_wait_st();
       l += sum;
       // keys past the end of the sequence in the last tile: their V rows were not loaded; zero them
       if (j * AT_BN + AT_BN > len) {
@@ -326,26 +321,31 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
               make_uint4(0, 0, 0, 0);
         }
       }
+      // every thread has finished its own writes (the zeroed V rows go through the async proxy); one
+      // arrival per warp then tells the issuing thread
       fence_async_proxy();
       tcgen05_fence_before();
-      mbar_arrive(p_ready);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_ready);
     }
     if (!ok && lane == 0) {
       abort_flag = 1;
       atomicOr(status, Q3_STATUS_TIMEOUT);
     }
-    // the last P V, then O / l with l summed over the row's two threads; each writes half the columns
+    // the last P V, then O / l with l summed over the row's threads; each writes 32 of the columns
     const bool done = ok && mbar_wait(pv_done, (n_tiles - 1) & 1, &abort_flag);
-    float* xchg = row_xchg + (n_tiles & 1) * (2 * AT_BM);
-    xchg[half * AT_BM + rr] = l;
+    float* xchg = row_xchg + (n_tiles & 1) * (AT_PARTS * AT_BM);
+    xchg[part * AT_BM + rr] = l;
     asm volatile("bar.sync 1, %0;" ::"n"(AT_SOFTMAX) : "memory");
     if (done) {
       tcgen05_fence_after();
-      const float total = l + xchg[(half ^ 1) * AT_BM + rr];
+      float total = 0.f;
+#pragma unroll
+      for (int o = 0; o < AT_PARTS; ++o) total += xchg[o * AT_BM + rr];
       const float inv = total > 0.f ? 1.0f / total : 0.f;
       __nv_bfloat16* dst = valid_row ? out + ((size_t)(qs + R / g) * Hq + hk * g + R % g) * D : nullptr;
-#pragma unroll 1
-      for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
+      if (part * 32 < D) {
+        const int c0 = part * 32;
         uint32_t ov[32];
         tmem_ld_32(tmem_o + lane_base + c0, ov);
         tmem_wait_ld();
@@ -369,7 +369,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   __syncwarp();
   tcgen05_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == AT_ISSUE_WARP) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"((uint32_t)S::TMEM_COLS)
                  : "memory");
   }
