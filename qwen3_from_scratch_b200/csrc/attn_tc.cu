@@ -119,6 +119,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   }
   pdl_wait();  // q and the pages come from the kernels before this one
   pdl_launch_dependents();
+  __syncthreads();  // the barriers exist; from here the loader warps go their own way until the end
   // Tensor memory is taken only after the wait: a block that holds TMEM while it waits for the
   // kernel before it could keep that kernel's own blocks from ever getting theirs.
   if (warp == AT_ISSUE_WARP) {
@@ -128,23 +129,39 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
 
-  // the query tile, written in the swizzled K-major layout by the first 128 threads (row = thread)
-  if (warp < 4) {
-    const int rr = warp * 32 + lane;
-    const int R = row0 + rr;
-    const __nv_bfloat16* src = R < total_rows ? q + ((size_t)(qs + R / g) * Hq + hk * g + R % g) * D : nullptr;
+  // the query tile, written in the swizzled K-major layout by the softmax threads; neighbouring
+  // threads take neighbouring 16-byte chunks of a row, so a warp reads whole rows at a time
+  if (warp < AT_ISSUE_WARP) {
+    constexpr int CH = D / 8;                              // 16-byte chunks per row
+    constexpr int PER_THREAD = AT_BM * CH / AT_SOFTMAX;    // 4 at D = 128, 2 at D = 64
+    uint4 v[PER_THREAD];
 #pragma unroll
-    for (int c = 0; c < D / 8; ++c) {
-      const uint4 v = src ? *reinterpret_cast<const uint4*>(src + c * 8) : make_uint4(0, 0, 0, 0);
-      *reinterpret_cast<uint4*>(q_s + (c / 8) * (AT_BM * 128) + sw128_offset(rr, (c % 8) * 8)) = v;
+    for (int i = 0; i < PER_THREAD; ++i) {
+      const int idx = threadIdx.x + i * AT_SOFTMAX;
+      const int r = idx / CH, c = idx % CH;
+      const int R = row0 + r;
+      v[i] = R < total_rows
+                 ? *reinterpret_cast<const uint4*>(q + ((size_t)(qs + R / g) * Hq + hk * g + R % g) * D + c * 8)
+                 : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < PER_THREAD; ++i) {
+      const int idx = threadIdx.x + i * AT_SOFTMAX;
+      const int r = idx / CH, c = idx % CH;
+      *reinterpret_cast<uint4*>(q_s + (c / 8) * (AT_BM * 128) + sw128_offset(r, (c % 8) * 8)) = v[i];
     }
     fence_async_proxy();
   }
-  tcgen05_fence_before();
-  __syncthreads();
-  tcgen05_fence_after();
-  const uint32_t tmem_s = *tmem_holder;           // S of tile j lives at column (j & 1) * 128
-  const uint32_t tmem_o = tmem_s + 2 * AT_BN;
+  uint32_t tmem_s = 0, tmem_o = 0;
+  if (warp < AT_LOAD_WARP) {
+    // the query tile and the tensor memory address, among the softmax and issue warps only: the
+    // loaders are already fetching the first tiles meanwhile
+    tcgen05_fence_before();
+    asm volatile("bar.sync 2, %0;" ::"n"(AT_SOFTMAX + 32) : "memory");
+    tcgen05_fence_after();
+    tmem_s = *tmem_holder;           // S of tile j lives at column (j & 1) * 128
+    tmem_o = tmem_s + 2 * AT_BN;
+  }
 
   if (warp >= AT_LOAD_WARP) {
     // ------------------------------------------------------------------ loaders: one warp for K, one for V
@@ -198,15 +215,22 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       constexpr uint32_t idesc_o = umma_idesc(D, 1);      // 128 x D, V MN-major
       // S of tile j + 1 is issued before the wait for tile j's probabilities, so it runs on the
       // tensor cores while the softmax threads work on tile j.
+      // Descriptors are built once; inside the loops only constants are added to their address
+      // field (in units of 16 bytes), so that the issuing thread is not held up by address arithmetic.
+      const uint64_t q_desc = umma_desc_sw128(q_s);
+      const uint64_t k_desc0 = umma_desc_sw128(k_s), k_desc1 = umma_desc_sw128(k_s + S::K_BYTES);
+      const uint64_t v_desc0 = umma_desc_sw128_mn(v_s, AT_BN * 128), v_desc1 = umma_desc_sw128_mn(v_s + S::V_BYTES, AT_BN * 128);
       auto issue_s = [&](int j) -> bool {
         const int st = j & 1;
         if (!mbar_wait(k_full + st, ((uint32_t)j >> 1) & 1, &abort_flag)) return false;
         tcgen05_fence_after();
+        const uint64_t kd = st ? k_desc1 : k_desc0;
+        const uint32_t acc = tmem_s + st * AT_BN;
 #pragma unroll
         for (int t = 0; t < D / 16; ++t) {
-          const uint64_t a_desc = umma_desc_sw128(q_s + (t / 4) * (AT_BM * 128)) + 2 * (t % 4);
-          const uint64_t b_desc = umma_desc_sw128(k_s + st * S::K_BYTES + (t / 4) * (AT_BN * 128)) + 2 * (t % 4);
-          umma_f16(tmem_s + st * AT_BN, a_desc, b_desc, idesc_s, t != 0);
+          constexpr int ATOM16 = (AT_BM * 128) >> 4;  // one 64-wide atom of 128 rows, in 16-byte units
+          umma_f16(acc, q_desc + (uint64_t)((t / 4) * ATOM16 + 2 * (t % 4)), kd + (uint64_t)((t / 4) * ATOM16 + 2 * (t % 4)),
+                   idesc_s, t != 0);
         }
         umma_commit(s_ready + st);
         umma_commit(k_empty + st);
@@ -219,11 +243,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         if (!mbar_wait(p_ready, j & 1, &abort_flag)) { ok = false; break; }
         if (!mbar_wait(v_full + st, ((uint32_t)j >> 1) & 1, &abort_flag)) { ok = false; break; }
         tcgen05_fence_after();
+        const uint64_t vd = st ? v_desc1 : v_desc0;
+        const uint32_t p_cols = tmem_s + st * AT_BN;
 #pragma unroll
-        for (int t = 0; t < AT_BN / 16; ++t) {  // 16 keys: 8 packed columns of P, 16 rows of V
-          const uint64_t b_desc = umma_desc_sw128_mn(v_s + st * S::V_BYTES + t * 2048, AT_BN * 128);
-          umma_f16_ts(tmem_o, tmem_s + st * AT_BN + 8 * t, b_desc, idesc_o, (j | t) != 0);
-        }
+        for (int t = 0; t < AT_BN / 16; ++t)  // 16 keys: 8 packed columns of P, 16 rows (2048 bytes) of V
+          umma_f16_ts(tmem_o, p_cols + 8 * t, vd + (uint64_t)(t * (2048 >> 4)), idesc_o, (j | t) != 0);
         umma_commit(pv_done);
         umma_commit(v_empty + st);
       }
@@ -343,27 +367,43 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 #pragma unroll
       for (int o = 0; o < AT_PARTS; ++o) total += xchg[o * AT_BM + rr];
       const float inv = total > 0.f ? 1.0f / total : 0.f;
-      __nv_bfloat16* dst = valid_row ? out + ((size_t)(qs + R / g) * Hq + hk * g + R % g) * D : nullptr;
+      // The output tile goes through shared memory (where the query tile was: every product that read
+      // it has finished), so that it leaves in whole rows instead of one 64-byte piece per thread.
+      // Chunk c of row r sits at chunk position c ^ (r % CH) of its row, which spreads a warp's rows
+      // over the banks.
+      constexpr int CH = D / 8;
       if (part * 32 < D) {
-        const int c0 = part * 32;
         uint32_t ov[32];
-        tmem_ld_32(tmem_o + lane_base + c0, ov);
+        tmem_ld_32(tmem_o + lane_base + part * 32, ov);
         tmem_wait_ld();
-        if (dst) {
 #pragma unroll
-          for (int v4 = 0; v4 < 4; ++v4) {
-            uint4 pk;
-            pk.x = pack2(__float_as_uint(__uint_as_float(ov[8 * v4 + 0]) * inv), __float_as_uint(__uint_as_float(ov[8 * v4 + 1]) * inv));
-            pk.y = pack2(__float_as_uint(__uint_as_float(ov[8 * v4 + 2]) * inv), __float_as_uint(__uint_as_float(ov[8 * v4 + 3]) * inv));
-            pk.z = pack2(__float_as_uint(__uint_as_float(ov[8 * v4 + 4]) * inv), __float_as_uint(__uint_as_float(ov[8 * v4 + 5]) * inv));
-            pk.w = pack2(__float_as_uint(__uint_as_float(ov[8 * v4 + 6]) * inv), __float_as_uint(__uint_as_float(ov[8 * v4 + 7]) * inv));
-            reinterpret_cast<uint4*>(dst + c0)[v4] = pk;
-          }
+        for (int v4 = 0; v4 < 4; ++v4) {
+          uint4 pk;
+          pk.x = pack2(__float_as_uint(__uint_as_float(ov[8 * v4 + 0]) * inv), __float_as_uint(__uint_as_float(ov[8 * v4 + 1]) * inv));
+          pk.y = pack2(__float_as_uint(__uint_as_float(ov[8 * v4 + 2]) * inv), __float_as_uint(__uint_as_float(ov[8 * v4 + 3]) * inv));
+          pk.z = pack2(__float_as_uint(__uint_as_float(ov[8 * v4 + 4]) * inv), __float_as_uint(__uint_as_float(ov[8 * v4 + 5]) * inv));
+          pk.w = pack2(__float_as_uint(__uint_as_float(ov[8 * v4 + 6]) * inv), __float_as_uint(__uint_as_float(ov[8 * v4 + 7]) * inv));
+          const int c = part * 4 + v4;
+          *reinterpret_cast<uint4*>(q_s + rr * (D * 2) + ((c ^ (rr % CH)) << 4)) = pk;
         }
       }
     } else if (lane == 0) {
       abort_flag = 1;
       atomicOr(status, Q3_STATUS_TIMEOUT);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(AT_SOFTMAX) : "memory");
+    if (done) {
+      constexpr int CH = D / 8;
+      constexpr int PER_THREAD = AT_BM * CH / AT_SOFTMAX;
+#pragma unroll
+      for (int i = 0; i < PER_THREAD; ++i) {
+        const int idx = threadIdx.x + i * AT_SOFTMAX;
+        const int r = idx / CH, c = idx % CH;
+        const int Rr = row0 + r;
+        if (Rr < total_rows)
+          *reinterpret_cast<uint4*>(out + ((size_t)(qs + Rr / g) * Hq + hk * g + Rr % g) * D + c * 8) =
+              *reinterpret_cast<const uint4*>(q_s + r * (D * 2) + ((c ^ (r % CH)) << 4));
+      }
     }
   }
   __syncwarp();
