@@ -23,62 +23,78 @@ class DeviceStatusError(RuntimeError):
     pass
 
 
-class DecodeGraphs:
-    """CUDA graphs of the decode step: batches in which every request brings one token and wants
-    its logits.  One graph per (number of requests, context bucket of 1024 tokens); its batch
-    arrays live in a fixed buffer that each step's data is copied into before the replay, and the
-    number of key ranges the attention uses is the one chosen for the bucket's upper end.
-    The graphs share one memory pool: only one of them runs at a time."""
+class StepGraphs:
+    """CUDA graphs of steps whose shape comes again.  What a graph fixes is the shape of the launches:
+    tokens, requests, how many of them bring a single token, the longest portion, the number of
+    wanted logits and the context bucket of 1024 tokens (it sets the row pitch of the block tables and
+    the number of key ranges the decode attention uses).  Everything else - token ids, positions,
+    lengths, tables, which rows are wanted - is data in a fixed buffer that each step's batch is
+    copied into before the replay.
+
+    Decode-only steps (every request brings one token and wants its logits) are recorded the first
+    time their shape appears; other shapes (full-size prompt portions, which a long prompt repeats)
+    when they appear a second time, so that one-off shapes are never recorded.  The first step of a
+    shape always runs kernel by kernel: it is this step's result, and first-use set-up must not
+    happen inside a capture.  The graphs share one memory pool: only one of them runs at a time."""
 
     BUCKET = 1024
+    MAX_GRAPHS = 96
 
     def __init__(self, session: "Session"):
         self.session = session
         self.graphs = {}
+        self.seen = {}
         self.pool = None
         self.replays = 0
 
-    def applicable(self, entries: Sequence[Entry]) -> bool:
+    @staticmethod
+    def decode_only(entries: Sequence[Entry]) -> bool:
         return all(len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries)
 
     def run(self, entries: Sequence[Entry]) -> torch.Tensor:
         s = self.session
-        longest = max(s.manager.length(e.request) for e in entries) + 1
+        longest = max(s.manager.length(e.request) + len(e.tokens) for e in entries)
         bucket = -(-longest // self.BUCKET) * self.BUCKET
-        key = (len(entries), bucket)
         stride = -(-bucket // s.manager.page_size)
+        lens = [len(e.tokens) for e in entries]
+        key = (sum(lens), len(entries), sum(1 for n in lens if n == 1), max(lens),
+               sum(len(e.want) for e in entries), bucket)
         slot = self.graphs.get(key)
-        if slot is None:
-            # The first step of a new shape runs kernel by kernel (it is this step's result, and
-            # first-use set-up must not happen inside a capture); then the same launches are
-            # recorded, which runs nothing, for the steps to come.
-            ctx = BatchContext(s.manager, s.storage, s.rt).build(entries, s.vocab_size, table_stride=stride)
-            ctx.max_kv_len = bucket  # the split count recorded in the graph is the bucket's
-            eager = s.model.step(ctx)
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            if self.pool is None:
-                self.pool = torch.cuda.graph_pool_handle()
-            # No garbage collection while recording: the collector may destroy an older engine's graphs,
-            # and destroying a graph is a CUDA call that invalidates a capture in progress.
-            gc.collect()
-            collecting = gc.isenabled()
-            gc.disable()
-            try:
-                with torch.cuda.graph(graph, pool=self.pool):
-                    logits = s.model.step(ctx)
-            finally:
-                if collecting:
-                    gc.enable()
-            self.graphs[key] = (ctx, graph, logits)
+        if slot is not None:
+            ctx, graph, logits = slot
+            ctx.build(entries, s.vocab_size, table_stride=stride, keep_buffer=True)
+            graph.replay()
+            self.replays += 1
             s.last_context, s.last_graph = ctx, (graph, logits)
+            return logits
+        ctx = BatchContext(s.manager, s.storage, s.rt).build(entries, s.vocab_size, table_stride=stride)
+        ctx.max_kv_len = bucket  # the split count recorded in a graph is the bucket's
+        eager = s.model.step(ctx)
+        s.last_context, s.last_graph = ctx, None
+        self.seen[key] = self.seen.get(key, 0) + 1
+        if len(self.seen) > 4096:
+            self.seen.clear()
+        wanted = self.decode_only(entries) or self.seen[key] >= 2
+        if not wanted or len(self.graphs) >= self.MAX_GRAPHS:
             return eager
-        ctx, graph, logits = slot
-        ctx.build(entries, s.vocab_size, table_stride=stride, keep_buffer=True)
-        graph.replay()
-        self.replays += 1
-        s.last_context, s.last_graph = ctx, (graph, logits)
-        return logits
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        if self.pool is None:
+            self.pool = torch.cuda.graph_pool_handle()
+        # No garbage collection while recording: the collector may destroy an older engine's graphs,
+        # and destroying a graph is a CUDA call that invalidates a capture in progress.
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph, pool=self.pool):
+                logits = s.model.step(ctx)
+        finally:
+            if collecting:
+                gc.enable()
+        self.graphs[key] = (ctx, graph, logits)
+        s.last_graph = (graph, logits)
+        return eager
 
 
 class Session:
@@ -86,7 +102,8 @@ class Session:
                  num_pages: Optional[int] = None, cache_tokens: Optional[int] = None, max_seqs: int = 32,
                  max_step_tokens: int = 3000, poison_freed_pages: bool = False, cuda_graphs: bool = True):
         """``num_pages`` pages per group, or ``cache_tokens`` (rounded up to whole pages).
-        ``cuda_graphs``: replay decode steps from captured graphs instead of launching kernel by kernel."""
+        ``cuda_graphs``: replay steps whose shape repeats (decode steps, full-size prompt portions) from
+        captured graphs instead of launching kernel by kernel."""
         if num_pages is None:
             if cache_tokens is None:
                 raise ValueError("give num_pages or cache_tokens")
@@ -102,7 +119,7 @@ class Session:
         if poison_freed_pages:
             self.manager.freed_log = []
         self.last_context: Optional[BatchContext] = None
-        self.decode_graphs = DecodeGraphs(self) if cuda_graphs and self.model.graph_capturable else None
+        self.step_graphs = StepGraphs(self) if cuda_graphs and self.model.graph_capturable else None
         self.last_graph = None
 
     # ------------------------------------------------------------------ requests
@@ -157,8 +174,8 @@ class Session:
         return self._run(entries)
 
     def _run(self, entries: Sequence[Entry]) -> torch.Tensor:
-        if self.decode_graphs is not None and self.decode_graphs.applicable(entries):
-            return self.decode_graphs.run(entries)
+        if self.step_graphs is not None:
+            return self.step_graphs.run(entries)
         ctx = BatchContext(self.manager, self.storage, self.rt).build(entries, self.vocab_size)
         self.last_context, self.last_graph = ctx, None
         return self.model.step(ctx)

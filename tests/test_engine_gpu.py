@@ -95,6 +95,35 @@ def test_temperature_and_top_k_match_plain_with_the_same_generator(tiny_folders)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_portion_graphs_give_what_plain_launches_give(tiny_folders, dtype):
+    """Equal prompt portions: from the third on they are replayed from a graph recorded at the second.
+    The logits of every portion against the same portions launched kernel by kernel, for two
+    requests whose portions alternate (so a graph is replayed on another request's tables)."""
+    from qwen3_from_scratch_b200.engine.session import Session
+    folder = tiny_folders["c"]
+    prompts = {"x": random_tokens(331, 6 * 24, 7), "y": random_tokens(331, 5 * 24 + 9, 8)}
+    outs = []
+    for graphs in (True, False):
+        session = Session(folder, dtype=dtype, page_size=8, num_pages=64, max_seqs=4, max_step_tokens=64,
+                          cuda_graphs=graphs)
+        got = []
+        at = {"x": 0, "y": 0}
+        while any(at[r] < len(prompts[r]) for r in prompts):
+            for r in prompts:
+                piece = prompts[r][at[r]:at[r] + 24]
+                if piece:
+                    got.append(session.step([(r, piece, (len(piece) - 1,))]).float().cpu())
+                    at[r] += len(piece)
+        outs.append(torch.cat(got))
+        if graphs:
+            assert session.step_graphs.replays >= 7
+    if dtype == "float32":
+        assert torch.equal(outs[0], outs[1])
+    else:
+        assert torch.allclose(outs[0], outs[1], atol=1e-5, rtol=0)  # the same kernels in the same order
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_graph_replay_gives_what_plain_launches_give(tiny_folders, dtype):
     """Decode steps replayed from CUDA graphs against the same steps launched kernel by kernel."""
     from qwen3_from_scratch_b200.engine.engine import SyncEngine
@@ -107,9 +136,9 @@ def test_graph_replay_gives_what_plain_launches_give(tiny_folders, dtype):
         results, _ = engine.batch_generate(prompts, max_new_tokens=40, ignore_eos=True)
         outs.append([r.token_ids for r in results])
         if graphs:
-            assert engine.session.decode_graphs.replays > 30
+            assert engine.session.step_graphs.replays > 30
         else:
-            assert engine.session.decode_graphs is None
+            assert engine.session.step_graphs is None
     assert outs[0] == outs[1]
 
 
