@@ -124,6 +124,66 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ resid, const T* __re
   }
 }
 
+// One warp per row, for many rows of a width that is a multiple of 128 (up to 2048): a lane keeps
+// its H / 32 values in registers, all of a row's loads are in flight together, and the only
+// reduction is a warp shuffle.  Used for bfloat16 prompt portions; the float32 path keeps one
+// kernel (and so one order of summation) for every number of rows.
+constexpr int NW_WARPS = 8;
+
+template <typename T, int NCH>
+__global__ void __launch_bounds__(NW_WARPS * 32)
+add_rmsnorm_warp_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ w,
+                        T* __restrict__ out, const int* __restrict__ rows, int n_rows, float eps) {
+  pdl_wait();
+  pdl_launch_dependents();
+  constexpr int H = NCH * 128;
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * NW_WARPS + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  const int src_row = rows ? rows[row] : row;
+  float* r = resid + (size_t)src_row * H;
+  const T* d = delta ? delta + (size_t)src_row * H : nullptr;
+  float v[NCH][4];
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) Vec4<float>::load(r + (i * 32 + lane) * 4, v[i]);
+  if (d) {
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      float dv[4];
+      Vec4<T>::load(d + (i * 32 + lane) * 4, dv);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) v[i][k] += dv[k];
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NCH; ++i)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) ss += v[i][k] * v[i][k];
+  ss = warp_sum(ss);
+  const float rs = 1.0f / sqrtf(ss / (float)H + eps);
+  if (!rows && d) {
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) Vec4<float>::store(r + (i * 32 + lane) * 4, v[i]);
+  }
+  T* o = out + (size_t)row * H;
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) {
+    float wv[4], y[4];
+    Vec4<float>::load(w + (i * 32 + lane) * 4, wv);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) y[k] = v[i][k] * rs * wv[k];
+    Vec4<T>::store(o + (i * 32 + lane) * 4, y);
+  }
+}
+
+template <typename T, int NCH>
+static void add_rmsnorm_warp_launch(float* resid, const T* delta, const float* w, T* out, const int* rows, int n_rows,
+                                    float eps, cudaStream_t stream) {
+  q3::launch(add_rmsnorm_warp_kernel<T, NCH>, dim3((n_rows + NW_WARPS - 1) / NW_WARPS), dim3(NW_WARPS * 32), 0, stream,
+             resid, delta, w, out, rows, n_rows, eps);
+}
+
 // ---------------------------------------------------------------- plain RMSNorm on vectors
 // y[r, :] = rmsnorm(x[r, :]) * w, x and y in the compute dtype, one warp per row.
 // For short vectors (a head) and for tests of the norm part alone.
@@ -152,6 +212,15 @@ static int add_rmsnorm_launch(float* resid, const void* delta, const float* w, v
   if (smem > 200 * 1024) return Q3_ERR_SIZE;  // width beyond 51200 is refused
   const bool vec = (H % 4 == 0) && ((uintptr_t)resid % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
                    ((uintptr_t)out % 16 == 0) && (!delta || (uintptr_t)delta % 16 == 0);
+  if (vec && sizeof(T) == 2 && n_rows >= 64 && H % 128 == 0 && H <= 2048) {
+    switch (H / 128) {
+#define Q3_NW(N) case N: add_rmsnorm_warp_launch<T, N>(resid, (const T*)delta, w, (T*)out, rows, n_rows, eps, stream); break;
+      Q3_NW(1) Q3_NW(2) Q3_NW(3) Q3_NW(4) Q3_NW(5) Q3_NW(6) Q3_NW(7) Q3_NW(8)
+      Q3_NW(9) Q3_NW(10) Q3_NW(11) Q3_NW(12) Q3_NW(13) Q3_NW(14) Q3_NW(15) Q3_NW(16)
+#undef Q3_NW
+    }
+    return launch_status();
+  }
   int threads = vec ? (H / 4) : H;
   threads = ((threads + 31) / 32) * 32;
   if (threads > 512) threads = 512;

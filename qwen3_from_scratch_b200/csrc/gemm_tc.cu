@@ -12,6 +12,12 @@
 //                        alternate gate/up in blocks of eight.
 // There are two accumulators in TMEM, so the epilogue of one tile runs under the main loop of the next.
 //
+// A third epilogue serves the merged QKV projection of an attention layer: the tile's columns are
+// whole heads, and instead of storing them the epilogue rounds them to bfloat16 (what a stored
+// projection would hold), applies the per-head RMSNorm and the rotation to q and k heads and writes q
+// to its buffer and k, v straight into their cache pages - the work of qkv_post.cu, without the
+// projection ever going to memory (reference: models/self_attn.py:319-336).
+//
 // Every wait on an mbarrier is bounded: a wait that runs out sets the TIMEOUT bit of the status
 // word and a block-wide abort flag, every role leaves its loop, TMEM is released and the block
 // returns; nothing spins forever.
@@ -24,16 +30,115 @@ namespace q3 {
 constexpr int TC_BM = 128;
 constexpr int TC_THREADS = 192;
 
-template <int BN>
+constexpr int TC_HEAD_STAGE_BYTES = TC_BM * 128 * 2;  // one head (up to 128 wide) of the tile's 128 rows, bfloat16
+
+template <int BN, int EPI = 0>
 struct TcShape {
   static constexpr int A_BYTES = TC_BM * TC_BK * 2;
   static constexpr int B_BYTES = BN * TC_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;  // 4 stages of 48 KB or 6 of 32 KB
   static constexpr int BAR_BYTES = 256;  // 2 * STAGES + 4 barriers and the TMEM address
-  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + room to align to 1024
+  static constexpr int EPI_BYTES = EPI == 2 ? TC_HEAD_STAGE_BYTES : 0;  // where the QKV epilogue turns a head around
+  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + BAR_BYTES + EPI_BYTES + 1024;  // + room to align to 1024
   static constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulators
 };
+
+// What the QKV epilogue needs beside the product (see q3_qkv_post for the meaning of each).
+struct QkvEpilogue {
+  __nv_bfloat16* q_out;
+  __nv_bfloat16* k_pages;
+  __nv_bfloat16* v_pages;
+  const float* q_weight;
+  const float* k_weight;
+  const float* cos_sin;  // [M, D] cosines then sines of each row's position, or null: no rotation
+  const int* positions;
+  const int* tok_seq;
+  const int* block_table;
+  int table_stride, page_size, num_pages, Hq, Hkv;
+  float eps;
+  int write_kv;
+};
+
+// One head of the warp's 32 rows.  The thread that owns a row (thread = row, as tcgen05.ld hands the
+// accumulator out) takes the head's D values into registers, rounds them to bfloat16 as a stored
+// projection would be, and does the head norm and the rotation on its own: no shuffles, and every
+// load it needs (its row of cosines and sines) is independent of the others, so their latencies
+// overlap.  The finished row goes to shared memory (16-byte chunk c of row r at chunk position
+// c ^ (r % CH)) and from there to q_out or the cache pages in whole rows, D / 8 lanes to a row.
+// `kv_off`: element offset of this lane's row in a page array (without the head), or -1.
+template <int D>
+__device__ __forceinline__ void qkv_head_rows(uint32_t tmem_head, unsigned char* mine, int row_base, int rows_here,
+                                              int head, const QkvEpilogue& e, int lane, long long kv_off) {
+  constexpr int CH = D / 8, LPH = D / 8, RPW = 32 / LPH;
+  const bool is_q = head < e.Hq, is_k = !is_q && head < e.Hq + e.Hkv;
+  const float* w = is_q ? e.q_weight : (is_k ? e.k_weight : nullptr);
+  const bool live = lane < rows_here;
+  const int t = row_base + lane;
+  float x[D];
+#pragma unroll
+  for (int c0 = 0; c0 < D; c0 += 32) {
+    uint32_t v[32];
+    tmem_ld_32(tmem_head + (uint32_t)c0, v);
+    tmem_wait_ld();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x[c0 + i] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i])));
+  }
+  if (is_q || is_k) {  // uniform over the warp
+    if (w) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < D; ++i) ss += x[i] * x[i];
+      const float rs = 1.0f / sqrtf(ss / (float)D + e.eps);
+#pragma unroll
+      for (int i = 0; i < D; i += 4) {
+        const float4 wv = *reinterpret_cast<const float4*>(w + i);
+        x[i] = x[i] * rs * wv.x;
+        x[i + 1] = x[i + 1] * rs * wv.y;
+        x[i + 2] = x[i + 2] * rs * wv.z;
+        x[i + 3] = x[i + 3] * rs * wv.w;
+      }
+    }
+    if (e.cos_sin != nullptr && live) {
+      const float* row = e.cos_sin + (size_t)t * D;
+#pragma unroll
+      for (int j = 0; j < D / 2; j += 4) {
+        const float4 c = *reinterpret_cast<const float4*>(row + j), sn = *reinterpret_cast<const float4*>(row + D / 2 + j);
+        const float cv[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float a = x[j + u], b2 = x[j + u + D / 2];
+          x[j + u] = a * cv[u] - b2 * sv[u];
+          x[j + u + D / 2] = b2 * cv[u] + a * sv[u];
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    uint4 pk;
+    pk.x = pack2(__float_as_uint(x[8 * c + 0]), __float_as_uint(x[8 * c + 1]));
+    pk.y = pack2(__float_as_uint(x[8 * c + 2]), __float_as_uint(x[8 * c + 3]));
+    pk.z = pack2(__float_as_uint(x[8 * c + 4]), __float_as_uint(x[8 * c + 5]));
+    pk.w = pack2(__float_as_uint(x[8 * c + 6]), __float_as_uint(x[8 * c + 7]));
+    *reinterpret_cast<uint4*>(mine + lane * (D * 2) + ((c ^ (lane % CH)) << 4)) = pk;
+  }
+  __syncwarp();
+  const int sub = lane / LPH, l = lane % LPH;
+  const int hk = is_k ? head - e.Hq : head - e.Hq - e.Hkv;
+#pragma unroll 4
+  for (int r0 = 0; r0 < 32; r0 += RPW) {
+    const int r = r0 + sub;
+    const long long off = __shfl_sync(0xffffffffu, kv_off, r);
+    if (r >= rows_here) continue;
+    const uint4 chunk = *reinterpret_cast<const uint4*>(mine + r * (D * 2) + ((l ^ (r % CH)) << 4));
+    if (is_q)
+      *reinterpret_cast<uint4*>(e.q_out + ((size_t)(row_base + r) * e.Hq + head) * D + l * 8) = chunk;
+    else if (off >= 0)
+      *reinterpret_cast<uint4*>((is_k ? e.k_pages : e.v_pages) + off + (size_t)hk * e.page_size * D + l * 8) = chunk;
+  }
+  __syncwarp();
+}
 
 // Stores 32 consecutive columns of one row.  EPI 0: as they are.  EPI 1: SwiGLU on column blocks
 // (gate 8, up 8, ...), 16 outputs at half the column index.
@@ -97,11 +202,12 @@ __device__ __forceinline__ void tc_store_chunk(const uint32_t (&v)[32], OutT* __
   }
 }
 
-template <int BN, int EPI, typename OutT>
+// EPI 0: store.  EPI 1: SwiGLU.  EPI 2: the QKV epilogue with heads of HD values (C is not written).
+template <int BN, int EPI, typename OutT, int HD = 128>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               OutT* __restrict__ C, int M, int N, int K, int ldc, int* status) {
-  using S = TcShape<BN>;
+               OutT* __restrict__ C, int M, int N, int K, int ldc, const __grid_constant__ QkvEpilogue qkv, int* status) {
+  using S = TcShape<BN, EPI>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* tiles = base;
@@ -110,6 +216,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint64_t* acc_full = empty + S::STAGES;  // [2]
   uint64_t* acc_empty = acc_full + 2;      // [2]
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  unsigned char* head_stage = base + (size_t)S::STAGES * S::STAGE_BYTES + S::BAR_BYTES;  // EPI 2 only
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -223,17 +330,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       tcgen05_fence_after();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t tmem_acc = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+      if (EPI == 2) {
+        // head by head; the cache position of the thread's own row is looked up once per tile
+        unsigned char* mine = head_stage + quarter * 32 * (HD * 2);
+        const int rows_here = min(32, M - (m0 + quarter * 32));
+        long long kv_off = -1;
+        if (qkv.write_kv && lane < rows_here && n0 + BN > qkv.Hq * HD) {
+          const int pos = qkv.positions[row], seq = qkv.tok_seq[row];
+          if (pos < 0 || seq < 0) {
+            atomicOr(status, Q3_STATUS_BAD_POSITION);
+          } else {
+            const int page = qkv.block_table[(size_t)seq * qkv.table_stride + pos / qkv.page_size];
+            if (page < 0 || page >= qkv.num_pages)
+              atomicOr(status, Q3_STATUS_BAD_PAGE);
+            else
+              kv_off = ((long long)page * qkv.Hkv * qkv.page_size + (pos % qkv.page_size)) * HD;
+          }
+        }
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        if (n0 + c0 >= N) break;  // uniform over the warp
-        uint32_t v[32];
-        tmem_ld_32(tmem_acc + (uint32_t)c0, v);
-        tmem_wait_ld();
-        if (row < M) tc_store_chunk<EPI, OutT>(v, C, row, n0 + c0, N, ldc);
+        for (int h0 = 0; h0 < BN; h0 += HD) {
+          if (n0 + h0 >= N) break;  // uniform over the warp
+          qkv_head_rows<HD>(tmem_acc + (uint32_t)h0, mine, m0 + quarter * 32, rows_here, (n0 + h0) / HD, qkv, lane, kv_off);
+        }
+        // the accumulator has been read: the next tile may use it
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (n0 + c0 >= N) break;  // uniform over the warp
+          uint32_t v[32];
+          tmem_ld_32(tmem_acc + (uint32_t)c0, v);
+          tmem_wait_ld();
+          if (row < M) tc_store_chunk<EPI == 2 ? 0 : EPI, OutT>(v, C, row, n0 + c0, N, ldc);
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
       }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
   }
   tcgen05_fence_before();
@@ -255,13 +390,13 @@ static int tc_sm_count() {
   return sms;
 }
 
-template <int BN, int EPI, typename OutT>
+template <int BN, int EPI, typename OutT, int HD = 128>
 static int gemm_tc_launch(const void* A, const void* W, void* C, int M, int N, int K, int ldc, int* status,
-                          cudaStream_t stream) {
-  using S = TcShape<BN>;
+                          cudaStream_t stream, const QkvEpilogue& qkv = QkvEpilogue{}) {
+  using S = TcShape<BN, EPI>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, OutT, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)S::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     configured = true;
@@ -274,8 +409,8 @@ static int gemm_tc_launch(const void* A, const void* W, void* C, int M, int N, i
   const long long tiles = (long long)((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM);
   if (tiles > 0x7fffffffLL) return Q3_ERR_SIZE;
   const int grid = (int)(tiles < tc_sm_count() ? tiles : tc_sm_count());
-  q3::launch(gemm_tc_kernel<BN, EPI, OutT>, dim3(grid), dim3(TC_THREADS), S::SMEM_BYTES, stream, map_a, map_b,
-             (OutT*)C, M, N, K, ldc, status);
+  q3::launch(gemm_tc_kernel<BN, EPI, OutT, HD>, dim3(grid), dim3(TC_THREADS), S::SMEM_BYTES, stream, map_a, map_b,
+             (OutT*)C, M, N, K, ldc, qkv, status);
   return launch_status();
 }
 
@@ -309,4 +444,43 @@ extern "C" int q3_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
   if (swiglu) return q3::gemm_tc_dispatch<1, bf16>(A, W, C, M, N, K, ldc, status, stream);
   if (out_f32) return q3::gemm_tc_dispatch<0, float>(A, W, C, M, N, K, ldc, status, stream);
   return q3::gemm_tc_dispatch<0, bf16>(A, W, C, M, N, K, ldc, status, stream);
+}
+
+// The merged QKV projection of an attention layer with the work of q3_qkv_post in its epilogue:
+// qkv = A[T, K] * W[(Hq + 2 Hkv) D, K]^T is rounded to bfloat16 and, head by head, normed, rotated and
+// written to q_out / the cache pages; it is never stored itself.  Arguments as q3_qkv_post, with A and W
+// as q3_gemm_tc.  Takes bfloat16, D = 64 or 128 and a whole rotation (cos_sin from q3_rope_table) or
+// none; refuses the rest.
+extern "C" int q3_gemm_tc_qkv(const void* A, const void* W, int T, int K, int Hq, int Hkv, int D, const float* q_weight,
+                              const float* k_weight, float eps, const float* cos_sin, const int* positions,
+                              const int* tok_seq, const int* block_table, int table_stride, int page_size,
+                              void* k_pages, void* v_pages, int num_pages, void* q_out, int write_kv, int* status,
+                              cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (K <= 0 || K % 8 || (D != 64 && D != 128) || Hq < 0 || Hkv < 0 || page_size <= 0 || table_stride <= 0)
+    return Q3_ERR_SIZE;
+  if ((uintptr_t)A % 16 || (uintptr_t)W % 16 || (uintptr_t)q_out % 16 || (uintptr_t)k_pages % 16 ||
+      (uintptr_t)v_pages % 16 || (uintptr_t)q_weight % 16 || (uintptr_t)k_weight % 16 || (uintptr_t)cos_sin % 16)
+    return Q3_ERR_ALIGN;
+  q3::QkvEpilogue e;
+  e.q_out = (__nv_bfloat16*)q_out;
+  e.k_pages = (__nv_bfloat16*)k_pages;
+  e.v_pages = (__nv_bfloat16*)v_pages;
+  e.q_weight = q_weight;
+  e.k_weight = k_weight;
+  e.cos_sin = cos_sin;
+  e.positions = positions;
+  e.tok_seq = tok_seq;
+  e.block_table = block_table;
+  e.table_stride = table_stride;
+  e.page_size = page_size;
+  e.num_pages = num_pages;
+  e.Hq = Hq;
+  e.Hkv = Hkv;
+  e.eps = eps;
+  e.write_kv = write_kv;
+  const int N = (Hq + 2 * Hkv) * D;
+  using bf16 = __nv_bfloat16;
+  if (D == 128) return q3::gemm_tc_launch<256, 2, bf16, 128>(A, W, nullptr, T, N, K, 0, status, stream, e);
+  return q3::gemm_tc_launch<256, 2, bf16, 64>(A, W, nullptr, T, N, K, 0, status, stream, e);
 }

@@ -115,7 +115,7 @@ constexpr int QPV_WARPS = 8;
 constexpr int QPV_UNROLL = 2;
 
 template <int LPH>
-__global__ void __launch_bounds__(QPV_WARPS * 32)
+__global__ void __launch_bounds__(QPV_WARPS * 32, 4)
 qkv_post_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
                     __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
                     const float* __restrict__ q_weight, const float* __restrict__ k_weight,
@@ -169,6 +169,12 @@ qkv_post_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __rest
     const float4 s0 = *reinterpret_cast<const float4*>(row + D / 2), s1 = *reinterpret_cast<const float4*>(row + D / 2 + 4);
     cv[0] = c0.x; cv[1] = c0.y; cv[2] = c0.z; cv[3] = c0.w; cv[4] = c1.x; cv[5] = c1.y; cv[6] = c1.z; cv[7] = c1.w;
     sv[0] = s0.x; sv[1] = s0.y; sv[2] = s0.z; sv[3] = s0.w; sv[4] = s1.x; sv[5] = s1.y; sv[6] = s1.z; sv[7] = s1.w;
+    // y = x cos - partner sin in the first half of the head, x cos + partner sin in the second: the sign goes
+    // into the sine once, so that the rotation is one multiply and one fused multiply-add per value
+    if (l < HALF) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) sv[k] = -sv[k];
+    }
   }
   for (int head0 = blockIdx.y * heads_per_block; head0 < head_end; head0 += STEP) {
     uint4 cur[QPV_UNROLL];
@@ -207,11 +213,10 @@ qkv_post_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __rest
           for (int k = 0; k < 8; ++k) x[k] = x[k] * rs * wv[k];
         }
         if (cos_sin != nullptr) {
-          const bool first_half = l < HALF;
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const float partner = __shfl_xor_sync(0xffffffffu, x[k], HALF);
-            x[k] = first_half ? x[k] * cv[k] - partner * sv[k] : x[k] * cv[k] + partner * sv[k];
+            x[k] = fmaf(partner, sv[k], x[k] * cv[k]);
           }
         }
         if (is_q || is_k) {

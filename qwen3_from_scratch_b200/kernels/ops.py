@@ -69,6 +69,9 @@ _SIGNATURES = {
     "q3_swiglu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "q3_gemm_tc": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                    _c_void_p],
+    "q3_gemm_tc_qkv": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
+                       _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
+                       _c_void_p, _c_int, _c_void_p, _c_void_p],
     "q3_gemm_skinny": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "q3_sample": [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ull,
                   _c_void_p, _c_void_p, _c_void_p],
@@ -461,6 +464,57 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.T
 
 # ------------------------------------------------------------------ fast bfloat16 attention
 MAX_DECODE_SPLITS = 32
+
+
+def gemm_tc_qkv_takes(rows: int, x: torch.Tensor, weight: torch.Tensor, head_dim: int, rotary_dim: int) -> bool:
+    """Whether the QKV projection with head norm, rotation and cache write in its epilogue takes this
+    case: a prompt portion (128 rows or more) in bfloat16, heads of 64 or 128, rotated whole or not at all."""
+    return (rows >= 128 and gemm_tc_takes(x, weight) and head_dim in (64, 128) and rotary_dim in (0, head_dim))
+
+
+def gemm_tc_qkv_pays(rows: int, weight: torch.Tensor) -> bool:
+    """Whether the fused kernel is the faster way.  Its epilogue (norm and rotation of two heads of 128
+    rows by four warps) runs under the next tile's main loop only if that loop is long enough: with an
+    input width of 1024 the fused kernel took 44 us for 2048 rows where the library product and
+    qkv_post take 17 + 16, so it is used from a width of 4096 on."""
+    return weight.shape[1] >= 4096
+
+
+def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                cos_sin: Optional[torch.Tensor], positions: torch.Tensor, tok_seq: torch.Tensor,
+                block_table: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int, write_kv: bool,
+                status: torch.Tensor) -> None:
+    """x[T, K] @ w[(Hq + 2 Hkv) D, K]^T on the tensor cores with ``qkv_post`` as the epilogue: the
+    projection is rounded to bfloat16, normed and rotated head by head and written to ``q_out`` and the
+    cache pages; it is never stored itself."""
+    for name, t in (("x", x), ("w", w), ("q_out", q_out), ("k_pages", k_pages), ("v_pages", v_pages)):
+        _check(f"gemm_tc_qkv.{name}", t, torch.bfloat16)
+    for name, t in (("positions", positions), ("tok_seq", tok_seq), ("block_table", block_table)):
+        _check(f"gemm_tc_qkv.{name}", t, torch.int32)
+    T, K = x.shape
+    width = (num_q_heads + 2 * num_kv_heads) * head_dim
+    num_pages, hkv, page_size, d = k_pages.shape
+    if (tuple(w.shape) != (width, K) or q_out.numel() != T * num_q_heads * head_dim or hkv != num_kv_heads
+            or d != head_dim or v_pages.shape != k_pages.shape or positions.numel() != T or tok_seq.numel() != T
+            or block_table.dim() != 2):
+        raise KernelError(f"gemm_tc_qkv: x {tuple(x.shape)}, w {tuple(w.shape)}, q_out {tuple(q_out.shape)}, "
+                          f"pages {tuple(k_pages.shape)}, heads {num_q_heads}/{num_kv_heads} x {head_dim}")
+    for name, wt in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if wt is not None:
+            _check(f"gemm_tc_qkv.{name}", wt, torch.float32)
+            if wt.numel() != head_dim:
+                raise KernelError(f"gemm_tc_qkv: {name} has {wt.numel()} elements, head_dim is {head_dim}")
+    if cos_sin is not None:
+        _check("gemm_tc_qkv.cos_sin", cos_sin, torch.float32)
+        if tuple(cos_sin.shape) != (T, head_dim):
+            raise KernelError(f"gemm_tc_qkv: cos_sin {tuple(cos_sin.shape)} expected [{T}, {head_dim}]")
+    code = library().q3_gemm_tc_qkv(
+        x.data_ptr(), w.data_ptr(), T, K, num_q_heads, num_kv_heads, head_dim, _ptr(q_weight), _ptr(k_weight),
+        float(eps), _ptr(cos_sin), positions.data_ptr(), tok_seq.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], page_size, k_pages.data_ptr(), v_pages.data_ptr(), num_pages, q_out.data_ptr(),
+        1 if write_kv else 0, status.data_ptr(), _stream())
+    _done("gemm_tc_qkv", code, f"T {T} K {K} heads {num_q_heads}/{num_kv_heads} x {head_dim}")
 
 
 def fast_attention_takes(dtype: torch.dtype, num_q_heads: int, num_kv_heads: int, head_dim: int) -> bool:

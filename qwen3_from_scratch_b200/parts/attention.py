@@ -82,10 +82,20 @@ class GQAAttention(Mixer):
         T = x.shape[0]
         hq, hkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         k_pages, v_pages, table = ctx.kv(cache_id)
-        qkv = self.qkv(x)
         q = self._q[:T]
         eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
         fused = self.position.fused_rotary() if self.position is not None else None
+        if ((self.position is None or fused is not None)
+                and ops.gemm_tc_qkv_takes(T, x, self.qkv.weight, d, fused[1] if fused is not None else 0)
+                and ops.gemm_tc_qkv_pays(T, self.qkv.weight)):
+            # a prompt portion: the projection on the tensor cores with norm, rotation and cache write in its epilogue
+            cos_sin = self.position.step_table(ctx) if fused is not None else None
+            ops.gemm_tc_qkv(x, self.qkv.weight, q, k_pages, v_pages, self.q_norm_weight, self.k_norm_weight, eps,
+                            cos_sin, ctx.positions, ctx.tok_seq, table, hq, hkv, d, write_cache, self.rt.status)
+            out = self._o[:T]
+            self.attend(q, k_pages, v_pages, table, ctx, out)
+            return self.o_proj(out.view(T, hq * d))
+        qkv = self.qkv(x)
         if self.position is None or fused is not None:
             inv_freq, rotary_dim = fused if fused is not None else (None, 0)
             cos_sin = self.position.step_table(ctx) if fused is not None else None

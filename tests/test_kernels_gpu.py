@@ -90,6 +90,30 @@ def test_add_rmsnorm(dtype, width):
 
 
 @pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("width", [128, 640, 1024, 2048, 2176])
+def test_add_rmsnorm_many_rows(dtype, width):
+    """Enough rows for the one-warp-per-row kernel (bfloat16, widths that are multiples of 128 up to
+    2048); the other widths and float32 take the one-block-per-row kernel."""
+    g = torch.Generator().manual_seed(11)
+    T, eps = 200, 1e-6
+    stream = torch.randn(T, width, generator=g) * 2
+    delta = torch.randn(T, width, generator=g).to(DT[dtype])
+    w = 1 + 0.1 * torch.randn(width, generator=g)
+    s = dev(stream.clone())
+    out = torch.empty(T, width, device="cuda", dtype=DT[dtype])
+    ops().add_rmsnorm(s, dev(delta), dev(w), out, eps)
+    total = stream.double() + delta.double()
+    close(s, total, "float32")
+    close(out, plain.rms_norm(total, w.double(), eps), dtype)
+    rows = torch.randperm(T, generator=g)[:100].to(torch.int32)
+    s3 = dev(stream.clone())
+    out_rows = torch.empty(100, width, device="cuda", dtype=DT[dtype])
+    ops().add_rmsnorm_rows(s3, dev(delta), dev(w), dev(rows), out_rows, eps)
+    assert torch.equal(s3.cpu(), stream)
+    close(out_rows, plain.rms_norm(total[rows.long()], w.double(), eps), dtype)
+
+
+@pytest.mark.parametrize("dtype", list(DT))
 def test_rmsnorm_on_head_vectors(dtype):
     g = torch.Generator().manual_seed(2)
     x = torch.randn(11, 5, 48, generator=g).to(DT[dtype])
@@ -284,6 +308,58 @@ def test_qkv_post(dtype, hq, hkv, d, rot, with_table):
     ops().qkv_post(dev(qkv), q_out, k_pages, v_pages, dev(qw), dev(kw), eps, dev(inv_freq), rot, dev(positions),
                    dev(tok_seq), dev(bad), hq, hkv, d, True, st, cos_sin=cos_sin)
     assert int(st.item()) & 2
+
+
+@pytest.mark.parametrize("rotate", [True, False])
+@pytest.mark.parametrize("hq,hkv,d,K,T", [(8, 2, 128, 256, 200), (5, 2, 128, 96, 130), (3, 1, 64, 136, 333),
+                                          (16, 8, 128, 1024, 256)])
+def test_gemm_tc_qkv(hq, hkv, d, K, T, rotate):
+    """The QKV projection with head norm, rotation and cache write in its epilogue against the plain
+    formulas applied to the projection rounded to bfloat16; rows and heads that do not fill a tile."""
+    g = torch.Generator().manual_seed(13)
+    page_size, eps, theta = 16, 1e-6, 10000.0
+    starts, news = [5, 0], [T - 40, 40]
+    lengths = [s + n for s, n in zip(starts, news)]
+    tables, num_pages = make_tables(lengths, page_size, 4)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn((hq + 2 * hkv) * d, K, generator=g) / K ** 0.5).to(torch.bfloat16)
+    qw, kw = 1 + 0.1 * torch.randn(d, generator=g), 1 + 0.1 * torch.randn(d, generator=g)
+    positions = torch.tensor([s + i for s, n in zip(starts, news) for i in range(n)], dtype=torch.int32)
+    tok_seq = torch.tensor([b for b, n in enumerate(news) for _ in range(n)], dtype=torch.int32)
+    inv_freq = 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    k_pages = torch.zeros(num_pages, hkv, page_size, d, device="cuda", dtype=torch.bfloat16)
+    v_pages = torch.zeros_like(k_pages)
+    q_out = torch.full((T, hq, d), float("nan"), device="cuda", dtype=torch.bfloat16)
+    st = status()
+    cos_sin = None
+    if rotate:
+        cos_sin = torch.empty(T, d, device="cuda", dtype=torch.float32)
+        ops().rope_table(dev(inv_freq), dev(positions), cos_sin)
+    assert ops().gemm_tc_qkv_takes(T, dev(x), dev(w), d, d if rotate else 0)
+    ops().gemm_tc_qkv(dev(x), dev(w), q_out, k_pages, v_pages, dev(qw), dev(kw), eps, cos_sin, dev(positions),
+                      dev(tok_seq), dev(table_tensor(tables)), hq, hkv, d, True, st)
+    assert int(st.item()) == 0
+    qkv = (x.double() @ w.double().t()).to(torch.bfloat16).double().view(T, hq + 2 * hkv, d)
+    q, k, v = qkv[:, :hq], qkv[:, hq:hq + hkv], qkv[:, hq + hkv:]
+    q, k = plain.rms_norm(q, qw.double(), eps), plain.rms_norm(k, kw.double(), eps)
+    if rotate:
+        ang = positions.double()[:, None] * inv_freq.double()[None, :]
+        q, k = plain.apply_rope(q, ang.cos(), ang.sin()), plain.apply_rope(k, ang.cos(), ang.sin())
+    # The projection is rounded to bfloat16 before the norm.  Where float32 accumulation (the kernel) and
+    # the exact product (here) fall on different sides of a rounding boundary, the norm's input differs
+    # by one bfloat16 step, 2^-8 relative; with the 2^-9 of the output's own rounding: 1.5 * 2^-8.
+    flip_tol = 1.5 * 2.0 ** -8
+    close(q_out, q, "bfloat16", tol=flip_tol)
+    kp, vp = k_pages.cpu().double(), v_pages.cpu().double()
+    for t in range(T):
+        page = tables[int(tok_seq[t])][int(positions[t]) // page_size]
+        slot = int(positions[t]) % page_size
+        close(kp[page, :, slot], k[t], "bfloat16", scale=float(k.abs().max()), tol=flip_tol)
+        close(vp[page, :, slot], v[t], "bfloat16", scale=float(v.abs().max()))
+    written = torch.zeros(num_pages, page_size, dtype=torch.bool)
+    for t in range(T):
+        written[tables[int(tok_seq[t])][int(positions[t]) // page_size], int(positions[t]) % page_size] = True
+    assert float(kp.abs().sum(dim=(1, 3))[~written].sum()) == 0.0
 
 
 def reference_attention(q, k_list, v_list, q_lens, window):
