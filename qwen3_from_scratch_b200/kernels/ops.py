@@ -472,14 +472,6 @@ def gemm_tc_qkv_takes(rows: int, x: torch.Tensor, weight: torch.Tensor, head_dim
     return (rows >= 128 and gemm_tc_takes(x, weight) and head_dim in (64, 128) and rotary_dim in (0, head_dim))
 
 
-def gemm_tc_qkv_pays(rows: int, weight: torch.Tensor) -> bool:
-    """Whether the fused kernel is the faster way.  Its epilogue (norm and rotation of two heads of 128
-    rows by four warps) runs under the next tile's main loop only if that loop is long enough: with an
-    input width of 1024 the fused kernel took 44 us for 2048 rows where the library product and
-    qkv_post take 17 + 16, so it is used from a width of 4096 on."""
-    return weight.shape[1] >= 4096
-
-
 def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                 q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                 cos_sin: Optional[torch.Tensor], positions: torch.Tensor, tok_seq: torch.Tensor,
@@ -487,7 +479,10 @@ def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages: 
                 status: torch.Tensor) -> None:
     """x[T, K] @ w[(Hq + 2 Hkv) D, K]^T on the tensor cores with ``qkv_post`` as the epilogue: the
     projection is rounded to bfloat16, normed and rotated head by head and written to ``q_out`` and the
-    cache pages; it is never stored itself."""
+    cache pages; it is never stored itself.  The attention part does not use it yet: its epilogue (two
+    heads of 128 rows by four warps) hides under the next tile's main loop only when that loop is long,
+    and at an input width of 1024 it took 44 us for 2048 rows where the library product and qkv_post
+    take 17 + 16."""
     for name, t in (("x", x), ("w", w), ("q_out", q_out), ("k_pages", k_pages), ("v_pages", v_pages)):
         _check(f"gemm_tc_qkv.{name}", t, torch.bfloat16)
     for name, t in (("positions", positions), ("tok_seq", tok_seq), ("block_table", block_table)):

@@ -85,16 +85,6 @@ class GQAAttention(Mixer):
         q = self._q[:T]
         eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
         fused = self.position.fused_rotary() if self.position is not None else None
-        if ((self.position is None or fused is not None)
-                and ops.gemm_tc_qkv_takes(T, x, self.qkv.weight, d, fused[1] if fused is not None else 0)
-                and ops.gemm_tc_qkv_pays(T, self.qkv.weight)):
-            # a prompt portion: the projection on the tensor cores with norm, rotation and cache write in its epilogue
-            cos_sin = self.position.step_table(ctx) if fused is not None else None
-            ops.gemm_tc_qkv(x, self.qkv.weight, q, k_pages, v_pages, self.q_norm_weight, self.k_norm_weight, eps,
-                            cos_sin, ctx.positions, ctx.tok_seq, table, hq, hkv, d, write_cache, self.rt.status)
-            out = self._o[:T]
-            self.attend(q, k_pages, v_pages, table, ctx, out)
-            return self.o_proj(out.view(T, hq * d))
         qkv = self.qkv(x)
         if self.position is None or fused is not None:
             inv_freq, rotary_dim = fused if fused is not None else (None, 0)
