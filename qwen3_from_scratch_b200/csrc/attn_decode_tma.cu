@@ -86,15 +86,22 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  pdl_wait();
-  pdl_launch_dependents();
-  for (int e = threadIdx.x; e < 16 * CPR; e += DT_THREADS) {
-    const int row = e / CPR, c = e % CPR;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (row < g) v = *reinterpret_cast<const uint4*>(q + ((size_t)tq * Hq + hk * g + row) * D + c * 8);
-    *reinterpret_cast<uint4*>(q_s + row * PITCH + c * 8) = v;
+  __syncthreads();  // the barriers exist
+  // Keys and values of earlier steps are in memory already, and the lengths and tables were copied
+  // before the step's first kernel: the loader starts on them at once, while the kernel before this
+  // one (which writes this step's key, value and query) may still be running.  Only the tile that
+  // holds the sequence's last position, and the query, wait for that kernel.
+  if (warp != DT_CONSUMERS) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int e = threadIdx.x; e < 16 * CPR; e += DT_CONSUMERS * 32) {
+      const int row = e / CPR, c = e % CPR;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (row < g) v = *reinterpret_cast<const uint4*>(q + ((size_t)tq * Hq + hk * g + row) * D + c * 8);
+      *reinterpret_cast<uint4*>(q_s + row * PITCH + c * 8) = v;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(DT_CONSUMERS * 32) : "memory");
   }
-  __syncthreads();
 
   float o[2 * KT][4];
 #pragma unroll
@@ -104,36 +111,49 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   if (warp == DT_CONSUMERS) {
     // ------------------------------------------------------------------ loader
     bool ok = true;
-    for (int chunk0 = 0; chunk0 < count; chunk0 += 32) {
-      // thirty-two page ids at once, one per lane
-      int my_y = -1;
-      if (chunk0 + lane < count) {
-        const int n0 = (t_lo + chunk0 + lane) * DT_KEYS;
-        int page = table[n0 / page_size];
-        if (page < 0 || page >= num_pages) {
-          atomicOr(status, Q3_STATUS_BAD_PAGE);
-          page = 0;
+    // the block counts as having let its dependents go once every thread has: the consumers do after
+    // their wait, so this does not let the next kernel in before the one before this has finished
+    pdl_launch_dependents();
+    // tiles [i_lo, i_hi) of this block's range; the wait for the kernel before lies between two such
+    // runs, not inside the loop
+    auto issue = [&](int i_lo, int i_hi) {
+      for (int chunk0 = i_lo; chunk0 < i_hi; chunk0 += 32) {
+        // thirty-two page ids at once, one per lane
+        int my_y = -1;
+        if (chunk0 + lane < i_hi) {
+          const int n0 = (t_lo + chunk0 + lane) * DT_KEYS;
+          int page = table[n0 / page_size];
+          if (page < 0 || page >= num_pages) {
+            atomicOr(status, Q3_STATUS_BAD_PAGE);
+            page = 0;
+          }
+          my_y = (page * Hkv + hk) * page_size + (n0 % page_size);
         }
-        my_y = (page * Hkv + hk) * page_size + (n0 % page_size);
-      }
-      const int in_chunk = min(32, count - chunk0);
-      for (int u = 0; u < in_chunk; ++u) {
-        const int i = chunk0 + u;
-        const int s = i % DT_STAGES;
-        const uint32_t use = (uint32_t)i / DT_STAGES;
-        const int y = __shfl_sync(0xffffffffu, my_y, u);
-        if (use > 0) ok = ok && mbar_wait(empty + s, (use - 1) & 1, abort_word);
-        if (lane == 0 && ok) {
-          unsigned char* stage = ring + (size_t)s * S::STAGE_BYTES;
-          mbar_expect_tx(full + s, S::STAGE_BYTES);
+        const int in_chunk = min(32, i_hi - chunk0);
+        for (int u = 0; u < in_chunk; ++u) {
+          const int i = chunk0 + u;
+          const int s = i % DT_STAGES;
+          const uint32_t use = (uint32_t)i / DT_STAGES;
+          const int y = __shfl_sync(0xffffffffu, my_y, u);
+          if (use > 0) ok = ok && mbar_wait(empty + s, (use - 1) & 1, abort_word);
+          if (lane == 0 && ok) {
+            unsigned char* stage = ring + (size_t)s * S::STAGE_BYTES;
+            mbar_expect_tx(full + s, S::STAGE_BYTES);
 #pragma unroll
-          for (int a = 0; a < S::ATOMS; ++a) {
-            tma_load_2d(stage + a * 2048, &map_k, full + s, a * 64, y);
-            tma_load_2d(stage + S::TILE_BYTES + a * 2048, &map_v, full + s, a * 64, y);
+            for (int a = 0; a < S::ATOMS; ++a) {
+              tma_load_2d(stage + a * 2048, &map_k, full + s, a * 64, y);
+              tma_load_2d(stage + S::TILE_BYTES + a * 2048, &map_v, full + s, a * 64, y);
+            }
           }
         }
       }
-    }
+    };
+    // this step's key and value are written into tile pos / 16 by the kernel before: everything
+    // before that tile can be fetched while that kernel still runs
+    const int early_tiles = min(count, max(0, pos / DT_KEYS - t_lo));
+    issue(0, early_tiles);
+    pdl_wait();
+    issue(early_tiles, count);
     if (!ok && lane == 0) {
       *abort_word = 1;
       atomicOr(status, Q3_STATUS_TIMEOUT);
