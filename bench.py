@@ -373,19 +373,55 @@ def profile(args):
         run()
     torch.cuda.synchronize()
     torch.cuda.profiler.stop()
-    if args.time_ops:
+    if args.leave_out:
+        # What each kind of kernel costs inside the step as it really runs: the step is recorded as a
+        # CUDA graph (warm caches, programmatic dependent launch between neighbours) once whole and once
+        # with every launch of one kind left out, and the replays are timed.  A profiler that runs
+        # kernels one by one with flushed caches cannot show this.  The results of such a step are wrong,
+        # of course; nothing reads them.
         from qwen3_from_scratch_b200.kernels import ops
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ops.op_timing() as timing:
+        step = (lambda: engine.session.model.step(engine.session.last_context)) if args.profile == "decode" else run
+
+        def replay_us():
+            for _ in range(2):
+                step()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            for _ in range(5):
+                graph.replay()
+            torch.cuda.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             t0.record()
-            run()
+            for _ in range(20):
+                graph.replay()
             t1.record()
-        totals = timing.totals()
-        whole = t0.elapsed_time(t1) * 1e3
-        for name, (calls, us) in sorted(totals.items(), key=lambda kv: -kv[1][1]):
-            print(f"  {us:9.1f} us {calls:4d}x {us / calls:8.2f} us each  {name}")
-        print(f"  {whole - sum(us for _, us in totals.values()):9.1f} us  outside this module's launchers (library products)")
-        print(f"  {whole:9.1f} us  the step")
+            torch.cuda.synchronize()
+            return t0.elapsed_time(t1) * 1e3 / 20
+
+        layers = cfg["num_hidden_layers"]
+        whole = replay_us()
+        print(f"  whole step {whole:9.1f} us, {whole / layers:7.2f} per layer")
+        kinds = ["paged_attention", "gemm_skinny", "gemm_tc", "add_rmsnorm", "qkv_post", "swiglu", "rope_table", "embed"]
+        for kind in kinds:
+            real = getattr(ops, kind)
+            setattr(ops, kind, lambda *a, **k: None)
+            try:
+                without = replay_us()
+            finally:
+                setattr(ops, kind, real)
+            print(f"  without {kind:16s} {without:9.1f} us: it costs {whole - without:8.1f} us, "
+                  f"{(whole - without) / layers:6.2f} per layer")
+        real_mm = torch.mm
+        torch.mm = lambda a, b, out=None, **k: out if out is not None else torch.empty(
+            a.shape[0], b.shape[1], dtype=k.get("out_dtype", a.dtype), device=a.device)
+        try:
+            without = replay_us()
+        finally:
+            torch.mm = real_mm
+        print(f"  without {'library products':16s} {without:9.1f} us: they cost {whole - without:8.1f} us, "
+              f"{(whole - without) / layers:6.2f} per layer")
     print(f"profiled 2 {args.profile} steps, batch {args.batch}, context {args.context}, layers {cfg['num_hidden_layers']}")
     return 0
 
@@ -399,8 +435,8 @@ def main() -> int:
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=CONTEXT)
     p.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in the output)")
-    p.add_argument("--time-ops", action="store_true",
-                   help="with --profile: one more step with CUDA events around every launcher call, summed by name")
+    p.add_argument("--leave-out", action="store_true",
+                   help="with --profile: time the step as a CUDA graph, whole and with each kind of kernel left out")
     p.add_argument("--profile", choices=["decode", "prefill"], default=None,
                    help="short run for a profiler instead of the benchmark (see profile())")
     args = p.parse_args()

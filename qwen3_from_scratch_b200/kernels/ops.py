@@ -103,48 +103,16 @@ class _Counting:
     def __init__(self, lib):
         self._lib = lib
         self.calls = 0
-        self.events = None  # a list while op_timing() is active: (launcher name, start event, end event)
 
     def __getattr__(self, name):
         fn = getattr(self._lib, name)
 
         def counted(*args):
             self.calls += 1
-            if self.events is None:
-                return fn(*args)
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
-            code = fn(*args)
-            end.record()
-            self.events.append((name, start, end))
-            return code
+            return fn(*args)
 
         setattr(self, name, counted)
         return counted
-
-
-class op_timing:
-    """``with op_timing() as t: ...`` brackets every launcher call of this module with CUDA events;
-    afterwards ``t.totals()`` gives {launcher name: (calls, microseconds)} as the device saw them in
-    place (warm caches, the stream's real order), which a profiler that replays kernels one by one
-    with flushed caches does not show.  Work that does not go through this module (library matrix
-    products) falls between the brackets and is not counted."""
-
-    def __enter__(self):
-        library().events = []
-        return self
-
-    def __exit__(self, *exc):
-        self._events, library().events = library().events, None
-        return False
-
-    def totals(self):
-        torch.cuda.synchronize()
-        out = {}
-        for name, start, end in self._events:
-            calls, us = out.get(name, (0, 0.0))
-            out[name] = (calls + 1, us + start.elapsed_time(end) * 1e3)
-        return out
 
 
 def launch_count() -> int:
