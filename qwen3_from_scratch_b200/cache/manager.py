@@ -152,6 +152,11 @@ class CacheManager:
     def table(self, group: int, req: Hashable) -> List[int]:
         return self._requests[req].tables[group]
 
+    def row_state(self, req: Hashable):
+        """(tokens computed, state slot, table version) of a request in one lookup."""
+        r = self._requests[req]
+        return r.length, r.slot, r.version
+
     def table_version(self, req: Hashable) -> int:
         """A number that is renewed whenever one of the request's block tables changes, and that no
         other request, nor a later request of the same name, ever has."""

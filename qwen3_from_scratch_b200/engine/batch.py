@@ -30,6 +30,49 @@ class BatchContext(StepContext):
     def __init__(self, manager: CacheManager, storage: CacheStorage, rt: Runtime):
         self.manager, self.storage, self.rt = manager, storage, rt
         self._tables: List[torch.Tensor] = []
+        self._head_views = None
+        self._cuts = None
+        self.requests: List[Hashable] = []
+
+    def _decode_only_rebuild(self, entries: Sequence[Entry], vocab_size: int, table_stride: Optional[int]) -> bool:
+        """The common step of a running engine in as little Python as possible: the same requests as the
+        last build in the same order, one token each, each wanting its logits, no block table changed.
+        Writes tokens, positions and lengths into the pinned buffer and copies them; False if the step is
+        not of that kind (nothing has been touched then)."""
+        m, B = self.manager, len(entries)
+        if self._cuts[:7] != [B, B, B, B + 1, B, B, B] or (table_stride is not None and self._fixed_stride != table_stride):
+            return False
+        tokens, starts, versions = [], [], []
+        for e, request in zip(entries, self.requests):
+            if e.request != request or len(e.tokens) != 1 or tuple(e.want) != (0,):
+                return False
+            t = int(e.tokens[0])
+            if not 0 <= t < vocab_size:
+                raise ValueError(f"request {e.request!r}: token id {t} is outside the vocabulary of {vocab_size}")
+            length, _, version = m.row_state(request)
+            tokens.append(t)
+            starts.append(length)
+            versions.append(version)
+        if versions != self._versions:
+            return False
+        lens = [n + 1 for n in starts]
+        # order of the buffer: tokens, positions, tok_seq, q_start, kv_len, slots, logit_rows; the rows'
+        # numbers (tok_seq, q_start, slots, logit_rows) are those of the last build
+        if self._head_views is None or self._head_views[0] != 7 * B + 1:
+            n = 7 * B + 1
+            self._head_views = (n, self._host.numpy()[:n], self._host[:n], self._dev[:n])
+        _, host_np, host_head, dev_head = self._head_views
+        self._copied.synchronize()
+        host_np[:B] = tokens
+        host_np[B:2 * B] = starts
+        host_np[4 * B + 1:5 * B + 1] = lens
+        dev_head.copy_(host_head, non_blocking=True)
+        self._copied.record()
+        self.q_lens, self.kv_lens = [1] * B, lens
+        self.num_tokens = self.num_seqs = self.num_decode = B
+        self.max_q_len, self.max_kv_len = 1, max(lens)
+        self.h2d_bytes = (7 * B + 1) * 4
+        return True
 
     def kv(self, cache_id: int):
         g = self.storage.group_of(cache_id)
@@ -49,6 +92,9 @@ class BatchContext(StepContext):
         previous build, which must have had the same layout (same counts of tokens, rows, wanted
         logits and the same stride): this is what lets a captured CUDA graph be replayed on new data."""
         m = self.manager
+        if (keep_buffer and self._cuts is not None and len(entries) == len(self.requests)
+                and self._decode_only_rebuild(entries, vocab_size, table_stride)):
+            return self
         order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
         row_of = {orig: row for row, orig in enumerate(order)}
         tokens: List[int] = []
@@ -99,9 +145,12 @@ class BatchContext(StepContext):
                 and self._versions == versions and (table_stride is None or self._fixed_stride == table_stride)):
             # same requests, no block table changed since the last build: only the short arrays travel
             n_head = len(head)
+            if self._head_views is None or self._head_views[0] != n_head:
+                self._head_views = (n_head, self._host.numpy()[:n_head], self._host[:n_head], self._dev[:n_head])
+            _, host_np, host_head, dev_head = self._head_views
             self._copied.synchronize()
-            self._host[:n_head].copy_(torch.tensor(head, dtype=torch.int32))
-            self._dev[:n_head].copy_(self._host[:n_head], non_blocking=True)
+            host_np[:] = head  # straight into the pinned buffer
+            dev_head.copy_(host_head, non_blocking=True)
             self._copied.record()
             self.h2d_bytes = n_head * 4
             return self
@@ -133,6 +182,7 @@ class BatchContext(StepContext):
         host = torch.tensor(flat, dtype=torch.int32).pin_memory()
         dev = host.to(self.rt.device, non_blocking=True)
         self._host, self._dev, self._cuts = host, dev, cuts
+        self._head_views = None
         self._copied = torch.cuda.Event()
         self._copied.record()
         views = torch.split(dev, cuts)
