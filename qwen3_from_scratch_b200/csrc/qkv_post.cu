@@ -14,6 +14,10 @@
 // keys of one head are contiguous.
 #include "common.cuh"
 
+#ifndef Q3_QPV_MANY
+#define Q3_QPV_MANY 2  // warps per block of the bfloat16 fast path when there are many tokens
+#endif
+
 namespace q3 {
 
 constexpr int QP_WARPS = 4;
@@ -111,11 +115,12 @@ __global__ void rope_table_kernel(const float* __restrict__ inv_freq, const int*
 // neighbouring lanes, each owning eight consecutive values (one 16-byte load and store), so a warp
 // works on 32 / LPH heads at once; the rotation partner of a lane is LPH / 2 lanes away.  No shared
 // memory and no block-wide barrier.
-constexpr int QPV_WARPS = 8;
 constexpr int QPV_UNROLL = 2;
 
-template <int LPH>
-__global__ void __launch_bounds__(QPV_WARPS * 32, 4)
+// QPV_WARPS: warps per block: few for many tokens (small blocks come and go quickly and keep more loads
+// in flight per SM), eight for a few tokens (all heads of a token at once).
+template <int LPH, int QPV_WARPS>
+__global__ void __launch_bounds__(QPV_WARPS * 32, 1024 / (QPV_WARPS * 32))
 qkv_post_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
                     __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
                     const float* __restrict__ q_weight, const float* __restrict__ k_weight,
@@ -265,24 +270,31 @@ extern "C" int q3_qkv_post(const void* qkv, int dtype, int T, int Hq, int Hkv, i
   if (grid.y > 65535) return Q3_ERR_SIZE;
   const bool whole_rotation = inv_freq == nullptr || rotary_dim == D;
   // few tokens: one pass of a block's warps (eight warps x 256 / D heads), so that more blocks share the work
-  const int heads_per_block = T >= 256 ? n_heads : q3::QPV_WARPS * (D <= 256 ? 256 / D : 1);
+  const int warps = T >= 256 ? Q3_QPV_MANY : 8;
+  const int heads_per_block = T >= 256 ? n_heads : warps * (D <= 256 ? 256 / D : 1);
   if (dtype == Q3_BF16 && whole_rotation && (inv_freq == nullptr || cos_sin != nullptr) && (uintptr_t)cos_sin % 16 == 0 &&
       (D == 16 || D == 32 || D == 64 || D == 128 || D == 256) &&
       (q_weight == nullptr || (uintptr_t)q_weight % 16 == 0) && (k_weight == nullptr || (uintptr_t)k_weight % 16 == 0) &&
       (uintptr_t)qkv % 16 == 0 && (uintptr_t)q_out % 16 == 0 && (uintptr_t)k_pages % 16 == 0 &&
       (uintptr_t)v_pages % 16 == 0) {
-#define Q3_QP_VEC(LPH)                                                                                            \
-  q3::launch(q3::qkv_post_vec_kernel<LPH>, dim3(T, (n_heads + heads_per_block - 1) / heads_per_block),           \
-             dim3(q3::QPV_WARPS * 32), 0, stream,                                            \
+#define Q3_QP_VEC_W(LPH, W)                                                                                       \
+  q3::launch(q3::qkv_post_vec_kernel<LPH, W>, dim3(T, (n_heads + heads_per_block - 1) / heads_per_block),        \
+             dim3(W * 32), 0, stream,                                                                             \
       (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, q_weight, \
       k_weight, inv_freq ? cos_sin : nullptr, positions, tok_seq, block_table, table_stride, page_size, num_pages, \
       Hq, Hkv, eps, write_kv, heads_per_block, status)
+#define Q3_QP_VEC(LPH)                   \
+  do {                                   \
+    if (warps == 8) Q3_QP_VEC_W(LPH, 8); \
+    else Q3_QP_VEC_W(LPH, Q3_QPV_MANY);  \
+  } while (0)
     if (D == 16) Q3_QP_VEC(2);
     else if (D == 32) Q3_QP_VEC(4);
     else if (D == 64) Q3_QP_VEC(8);
     else if (D == 128) Q3_QP_VEC(16);
     else Q3_QP_VEC(32);
 #undef Q3_QP_VEC
+#undef Q3_QP_VEC_W
     return q3::launch_status();
   }
   if (dtype == Q3_F32)
