@@ -1,5 +1,7 @@
 """Each part alone against its plain function, built with sizes of its own (no model around it),
-and a toy mixer with state of its own registered from here and run through the engine."""
+and toy parts registered from here and run through the engine without a change to its files: a
+mixer with state of its own, a feed-forward that routes tokens to experts, a position encoding the
+fused kernel does not know; each in a toy architecture with its own configuration class."""
 
 import json
 import os
@@ -335,3 +337,162 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     rep3 = Replayer(session, {"z": seqs["y"]})
     rep3.step([("z", 23)])
     assert float((rep3.result()["z"] - want["y"]).abs().max()) <= 1e-5 * float(want["y"].abs().max())
+
+
+def register_toy_routed():
+    """A second toy architecture, again defined here alone: attention with a position encoding the
+    fused kernel does not know (a gain that depends on the position), and a feed-forward that routes
+    every token to one of a few small experts (router logits and softmax in float32)."""
+    from qwen3_from_scratch_b200.config import ModelConfig
+    from qwen3_from_scratch_b200.parts.base import (FeedForward, LayerCall, ModelSpec, PartSpec, PositionEncoding,
+                                                   WeightSpec)
+    from qwen3_from_scratch_b200.registry import register_architecture, register_part, registered_architectures
+    if "ToyRoutedLM" in registered_architectures():
+        return
+
+    @register_part("position", "toy_position_gain")
+    class PositionGain(PositionEncoding):
+        """y[t, h, j] = x[t, h, j] * (1 + depth * cos(position_t * rate^j))."""
+
+        def __init__(self, name, head_dim, depth, rate):
+            super().__init__(name)
+            self.head_dim, self.depth, self.rate = head_dim, depth, rate
+
+        def setup(self, rt, weights):
+            super().setup(rt, weights)
+            self.freq = (self.rate ** torch.arange(self.head_dim, dtype=torch.float32)).to(rt.device)
+
+        def apply(self, x, positions):
+            gain = 1 + self.depth * torch.cos(positions.float()[:, None] * self.freq[None, :])
+            return (x.float() * gain[:, None, :]).to(x.dtype)
+
+    @register_part("feed_forward", "toy_routed")
+    class Routed(FeedForward):
+        def __init__(self, name, hidden_size, inner, experts):
+            super().__init__(name)
+            self.hidden_size, self.inner, self.experts = hidden_size, inner, experts
+
+        def weight_specs(self):
+            specs = [WeightSpec(f"{self.name}.router.weight", (self.experts, self.hidden_size))]
+            for e in range(self.experts):
+                specs += [WeightSpec(f"{self.name}.experts.{e}.w_in.weight", (self.inner, self.hidden_size)),
+                          WeightSpec(f"{self.name}.experts.{e}.w_out.weight", (self.hidden_size, self.inner))]
+            return specs
+
+        def setup(self, rt, weights):
+            super().setup(rt, weights)
+            self.router = weights[f"{self.name}.router.weight"]
+            self.w_in = [weights[f"{self.name}.experts.{e}.w_in.weight"] for e in range(self.experts)]
+            self.w_out = [weights[f"{self.name}.experts.{e}.w_out.weight"] for e in range(self.experts)]
+
+        def forward(self, x):
+            probs = torch.softmax(x.float() @ self.router.float().t(), dim=-1)
+            weight, choice = probs.max(dim=-1)
+            out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+            for e in range(self.experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    h = torch.relu(x[rows].float() @ self.w_in[e].float().t())
+                    out[rows] = (h @ self.w_out[e].float().t()) * weight[rows, None]
+            return out.to(x.dtype)
+
+    @dataclass(frozen=True)
+    class RoutedConfig(ModelConfig):
+        vocab_size: int = 0
+        width: int = 0
+        depth: int = 0
+        experts: int = 0
+
+        @classmethod
+        def from_dict(cls, data):
+            return cls(data["architectures"][0], data["vocab_size"], data["width"], data["depth"], data["experts"])
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], "vocab_size": self.vocab_size, "width": self.width,
+                    "depth": self.depth, "experts": self.experts}
+
+    @register_architecture("ToyRoutedLM", RoutedConfig)
+    def routed_spec(cfg):
+        norm = PartSpec("rms_norm", {"dim": cfg.width, "eps": 1e-6})
+        position = PartSpec("toy_position_gain", {"head_dim": 16, "depth": 0.5, "rate": 0.8})
+        attn = PartSpec("gqa_attention", {"hidden_size": cfg.width, "num_heads": 4, "num_kv_heads": 2, "head_dim": 16,
+                                          "qk_norm_eps": 1e-6, "position": position})
+        routed = PartSpec("toy_routed", {"hidden_size": cfg.width, "inner": 24, "experts": cfg.experts})
+        dense = PartSpec("swiglu", {"hidden_size": cfg.width, "intermediate_size": 40})
+        layers = [(f"layers.{i}", PartSpec("pre_norm", {"norm1": norm, "norm2": norm, "mixer": attn,
+                                                        "feed_forward": routed if i % 2 == 0 else dense}))
+                  for i in range(cfg.depth)]
+        return ModelSpec(embedding=("embed", PartSpec("token_embedding", {"vocab_size": cfg.vocab_size,
+                                                                          "hidden_size": cfg.width})),
+                         layers=layers, order=[LayerCall(i, i) for i in range(cfg.depth)],
+                         final_norm=("final_norm", norm),
+                         head=("head", PartSpec("lm_head", {"vocab_size": cfg.vocab_size, "hidden_size": cfg.width})),
+                         vocab_size=cfg.vocab_size, max_positions=4096)
+
+
+def routed_plain_logits(folder, ids):
+    """The routed toy model in float64, whole sequence, no cache.  Returns the logits and the smallest
+    margin between the two largest router probabilities (a near-tie could route differently in float32)."""
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    from safetensors.torch import load_file
+    w = {k: v.double() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    x = w["embed.weight"][torch.tensor(ids)]
+    n = len(ids)
+    gain = 1 + 0.5 * torch.cos(torch.arange(n, dtype=torch.float64)[:, None] * (0.8 ** torch.arange(16, dtype=torch.float64))[None, :])
+    margin = 1.0
+    for i in range(cfg["depth"]):
+        p = f"layers.{i}"
+        h = plain.rms_norm(x, w[f"{p}.norm1.weight"], 1e-6)
+        q = (h @ w[f"{p}.mixer.q_proj.weight"].t()).view(n, 4, 16)
+        k = (h @ w[f"{p}.mixer.k_proj.weight"].t()).view(n, 2, 16)
+        v = (h @ w[f"{p}.mixer.v_proj.weight"].t()).view(n, 2, 16)
+        q = plain.rms_norm(q, w[f"{p}.mixer.q_norm.weight"], 1e-6) * gain[:, None, :]
+        k = plain.rms_norm(k, w[f"{p}.mixer.k_norm.weight"], 1e-6) * gain[:, None, :]
+        x = x + plain.causal_attention(q, k, v).reshape(n, -1) @ w[f"{p}.mixer.o_proj.weight"].t()
+        h = plain.rms_norm(x, w[f"{p}.norm2.weight"], 1e-6)
+        if i % 2 == 0:
+            probs = torch.softmax(h @ w[f"{p}.feed_forward.router.weight"].t(), dim=-1)
+            top2 = probs.topk(2, dim=-1).values
+            margin = min(margin, float((top2[:, 0] - top2[:, 1]).min()))
+            weight, choice = probs.max(dim=-1)
+            f = torch.zeros_like(h)
+            for t in range(n):
+                e = int(choice[t])
+                inner = torch.relu(h[t] @ w[f"{p}.feed_forward.experts.{e}.w_in.weight"].t())
+                f[t] = inner @ w[f"{p}.feed_forward.experts.{e}.w_out.weight"].t() * weight[t]
+        else:
+            f = plain.swiglu_mlp(h, w, f"{p}.feed_forward")
+        x = x + f
+    return plain.rms_norm(x, w["final_norm.weight"], 1e-6) @ w["head.weight"].t(), margin
+
+
+def test_toy_routed_feed_forward_and_position_encoding(tmp_path):
+    """A feed-forward with routing and a position encoding of its own, registered from this file, built
+    from a configuration, loaded from a folder and stepped whole and in portions."""
+    register_toy_routed()
+    from qwen3_from_scratch_b200.engine.session import Session
+    from qwen3_from_scratch_b200.registry import config_from_dict
+    from qwen3_from_scratch_b200.weights import write_random_model
+    cfg = config_from_dict({"architectures": ["ToyRoutedLM"], "vocab_size": 83, "width": 48, "depth": 3, "experts": 3})
+    folder = str(tmp_path / "routed")
+    write_random_model(folder, cfg, seed=4, dtype="float32")
+    g = torch.Generator().manual_seed(10)
+    seqs = {"x": torch.randint(0, 83, (37,), generator=g).tolist(), "y": torch.randint(0, 83, (18,), generator=g).tolist()}
+    want = {}
+    for r, ids in seqs.items():
+        logits, margin = routed_plain_logits(folder, ids)
+        assert margin > 1e-4  # no token sits on the fence between two experts
+        want[r] = logits.float()
+    session = Session(folder, dtype="float32", page_size=8, cache_tokens=256, max_seqs=4, max_step_tokens=128)
+    rep = Replayer(session, seqs)
+    rep.step([("x", 37), ("y", 18)])
+    whole = rep.result()
+    rep2 = Replayer(session, seqs)
+    for nx, ny in [(5, 2), (1, 1), (19, 9), (12, 6)]:
+        rep2.step([("x", nx), ("y", ny)])
+    cut = rep2.result()
+    for r in seqs:
+        scale = float(want[r].abs().max())
+        assert float((whole[r] - want[r]).abs().max()) <= 1e-5 * scale
+        assert float((cut[r] - want[r]).abs().max()) <= 1e-5 * scale
