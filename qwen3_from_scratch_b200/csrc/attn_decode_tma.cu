@@ -77,6 +77,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   }
   const int count = max(0, t_hi - t_lo);
 
+  if (warp == DT_CONSUMERS && lane == 0) {
+    tma_prefetch_map(&map_k);
+    tma_prefetch_map(&map_v);
+  }
   if (threadIdx.x == 0) {
     *abort_word = (s_addr(smem_raw) & 1023u) ? 1 : 0;
     if (*abort_word) atomicOr(status, Q3_STATUS_TIMEOUT);

@@ -100,6 +100,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   const int n_tiles = pos_last / AT_BN + 1;
   const int* table = block_table + (size_t)b * table_stride;
 
+  if (warp == AT_LOAD_WARP && lane == 0) tma_prefetch_map(&map_k);
+  if (warp == AT_LOAD_WARP + 1 && lane == 0) tma_prefetch_map(&map_v);
   if (threadIdx.x == 0) {
     abort_flag = 0;
     if (s_addr(smem_raw) & 1023u) {  // the swizzled tiles need this; never seen, but a wrong answer must not be silent

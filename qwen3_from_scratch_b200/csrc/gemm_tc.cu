@@ -224,6 +224,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
   const int num_tiles = m_tiles * n_tiles;
 
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_map(&map_a);
+    tma_prefetch_map(&map_b);
+  }
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < S::STAGES; ++s) {
