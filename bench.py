@@ -64,16 +64,48 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: through NVML from a thread of
+    this process (a query takes tens of microseconds), or with nvidia-smi if NVML cannot be loaded.
+    Reading only; no setting of the GPU is touched."""
 
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self):
-        self.samples = []
+        self.samples = []  # (sm MHz, max sm MHz, [active reasons])
         self.proc = None
+        self.stopping = threading.Event()
+        self.thread = None
+        self.source = None
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByIndex(0)
+            bits = {"hw_slowdown": pynvml.nvmlClocksThrottleReasonHwSlowdown,
+                    "hw_thermal_slowdown": pynvml.nvmlClocksThrottleReasonHwThermalSlowdown,
+                    "sw_thermal_slowdown": pynvml.nvmlClocksThrottleReasonSwThermalSlowdown,
+                    "sw_power_cap": pynvml.nvmlClocksThrottleReasonSwPowerCap}
+            top = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+
+            def poll():
+                while not self.stopping.is_set():
+                    try:
+                        mhz = float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+                        mask = int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle))
+                        self.samples.append((mhz, top, [n for n, bit in bits.items() if mask & bit]))
+                    except pynvml.NVMLError:
+                        pass
+                    self.stopping.wait(0.02)
+
+            self.source = "nvml"
+            self.thread = threading.Thread(target=poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:  # no NVML binding or no library: fall back to the command line tool
+            self.source = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
@@ -81,6 +113,7 @@ class ClockSampler:
         except OSError:
             self.proc = None
             return
+        self.source = "nvidia-smi"
         self.thread = threading.Thread(target=self._read, daemon=True)
         self.thread.start()
 
@@ -88,30 +121,30 @@ class ClockSampler:
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) >= 6:
-                self.samples.append(parts)
+                try:
+                    self.samples.append((float(parts[0]), float(parts[1]),
+                                         [n for n, flag in zip(self.NAMES, parts[2:6]) if flag.lower().startswith("active")]))
+                except ValueError:
+                    continue
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        clocks, maxes, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
+        if self.source is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no NVML and no nvidia-smi"]}
+        if self.source == "nvml":
+            self.stopping.set()
+            self.thread.join(timeout=2)
+        else:
+            time.sleep(0.15)
+            self.proc.terminate()
             try:
-                clocks.append(float(s[0]))
-                maxes.append(float(s[1]))
-            except ValueError:
-                continue
-            for name, flag in zip(names, s[2:6]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        clocks = [s[0] for s in self.samples]
+        reasons = sorted({r for s in self.samples for r in s[2]})
         return {"sm_mhz": statistics.median(clocks) if clocks else None,
-                "sm_max_mhz": max(maxes) if maxes else None, "reasons": sorted(reasons), "samples": len(clocks)}
+                "sm_max_mhz": max(s[1] for s in self.samples) if self.samples else None, "reasons": reasons,
+                "samples": len(clocks), "source": self.source}
 
 
 def model_numbers(cfg, layers):
@@ -203,12 +236,15 @@ def decode_bench(engine, batch, context, steps, warmup, vocab):
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     h2d = 0
-    for _ in range(steps):
+    for i in range(steps):
+        if i == steps - 1:
+            engine.lookahead = False  # the last call launches nothing beyond the K-th step
         plan = engine.step()
         assert len(plan) == batch and all(s.num_tokens == 1 for s in plan)
         h2d += engine.session.last_context.h2d_bytes
     torch.cuda.synchronize()
     e2e_seconds = time.perf_counter() - t0
+    engine.lookahead = True
     d2h = batch * 4 + 4  # sampled ids and the status word
     # (b) the same step on the device alone: replay the last batch (same lengths, same pages)
     ctx = engine.session.last_context

@@ -34,7 +34,8 @@ class BatchContext(StepContext):
         self._cuts = None
         self.requests: List[Hashable] = []
 
-    def _decode_only_rebuild(self, entries: Sequence[Entry], vocab_size: int, table_stride: Optional[int]) -> bool:
+    def _decode_only_rebuild(self, entries: Sequence[Entry], vocab_size: int, table_stride: Optional[int],
+                             ahead: int = 0) -> bool:
         """The common step of a running engine in as little Python as possible: the same requests as the
         last build in the same order, one token each, each wanting its logits, no block table changed.
         Writes tokens, positions and lengths into the pinned buffer and copies them; False if the step is
@@ -51,7 +52,7 @@ class BatchContext(StepContext):
                 raise ValueError(f"request {e.request!r}: token id {t} is outside the vocabulary of {vocab_size}")
             length, _, version = m.row_state(request)
             tokens.append(t)
-            starts.append(length)
+            starts.append(length + ahead)
             versions.append(version)
         if versions != self._versions:
             return False
@@ -83,17 +84,19 @@ class BatchContext(StepContext):
         return self.storage.states[cache_id]
 
     def build(self, entries: Sequence[Entry], vocab_size: int, table_stride: Optional[int] = None,
-              keep_buffer: bool = False) -> "BatchContext":
+              keep_buffer: bool = False, ahead: int = 0) -> "BatchContext":
         """``entries``: each request at most once, every request open with pages reserved for
         its new length.  Fills every field of StepContext.
 
         ``table_stride`` fixes the row pitch of the block tables (else the longest table of the
         batch decides).  With ``keep_buffer`` the device arrays are written into the buffer of the
         previous build, which must have had the same layout (same counts of tokens, rows, wanted
-        logits and the same stride): this is what lets a captured CUDA graph be replayed on new data."""
+        logits and the same stride): this is what lets a captured CUDA graph be replayed on new data.
+        ``ahead``: tokens of every request that an earlier step, still running, will have added by the
+        time this one runs: positions and lengths count them in."""
         m = self.manager
         if (keep_buffer and self._cuts is not None and len(entries) == len(self.requests)
-                and self._decode_only_rebuild(entries, vocab_size, table_stride)):
+                and self._decode_only_rebuild(entries, vocab_size, table_stride, ahead)):
             return self
         order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
         row_of = {orig: row for row, orig in enumerate(order)}
@@ -110,7 +113,7 @@ class BatchContext(StepContext):
             n = len(e.tokens)
             if n == 0:
                 raise ValueError(f"request {e.request!r} brings no tokens")
-            start = m.length(e.request)
+            start = m.length(e.request) + ahead
             for t in e.tokens:
                 if not 0 <= int(t) < vocab_size:
                     raise ValueError(f"request {e.request!r}: token id {t} is outside the vocabulary of {vocab_size}")

@@ -65,15 +65,29 @@ class GenerationResult:
     metrics: PerfMetrics
 
 
+@dataclass
+class _InFlight:
+    """A step that has been put on the device and whose results have not been read yet."""
+    plan: List[ScheduledRequest]
+    wanting: List[ScheduledRequest]
+    box: torch.Tensor          # device: [0] unused here, then the sampled tokens
+    host_box: torch.Tensor     # pinned copy of it
+    host_status: torch.Tensor  # pinned copy of the status word
+    done: torch.cuda.Event
+    ahead: bool                # launched before the step before it had been read
+
+
 class SyncEngine:
     def __init__(self, model_path: str, *, dtype: str = "bfloat16", device: str = "cuda:0",
                  max_num_seqs: int = 32, max_num_tokens: int = 3000, block_size: int = 16,
                  gpu_utilization: float = 0.5, num_pages: Optional[int] = None,
                  chunked_prefill_size: int = 512, enable_prefix_cache: bool = False,
                  temperature: float = 0.0, top_k: int = 0, max_new_tokens: int = 100, seed: int = 0,
-                 eos_token_id: Optional[int] = None, log_interval: int = 0, cuda_graphs: bool = True):
+                 eos_token_id: Optional[int] = None, log_interval: int = 0, cuda_graphs: bool = True,
+                 lookahead: bool = True):
         """``num_pages`` fixes the size of the cache pool; otherwise ``gpu_utilization`` of the
-        memory that is free after the weights are loaded is given to it."""
+        memory that is free after the weights are loaded is given to it.  ``lookahead``: while a plain
+        decode step runs, the step after it is already put on the device (see ``step``)."""
         if enable_prefix_cache:
             raise NotImplementedError("prefix sharing between requests is not built; pass enable_prefix_cache=False")
         self.model_path = model_path
@@ -97,6 +111,16 @@ class SyncEngine:
         self.sampler = Sampler(self.session.rt.device, self.session.rt.status)
         self.tokenizer = self._load_tokenizer(model_path)
         self.num_steps = 0
+        # Two places for a step's sampled tokens (a step and the one launched ahead of its results use one
+        # each), and pinned host copies of them with the status word.
+        rt = self.session.rt
+        self.lookahead = bool(lookahead)
+        self._boxes = [rt.mailbox, torch.zeros_like(rt.mailbox)]
+        self._host_boxes = [torch.zeros(rt.mailbox.numel(), dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._host_status = [torch.zeros(1, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._launches = 0
+        self.num_ahead = 0  # steps launched before the step before them had been read
+        self._inflight: Optional[_InFlight] = None
 
     # ------------------------------------------------------------------ construction helpers
     @classmethod
@@ -215,41 +239,115 @@ class SyncEngine:
         return req
 
     def abort(self, req: Request) -> None:
+        self.drain()
         self.scheduler.abort(req)
         self.session.after_step()
 
     def step(self) -> List[ScheduledRequest]:
-        """One scheduling round and one model step.  Returns what ran (with tokens appended)."""
-        plan = self.scheduler.schedule()
-        if not plan:
-            return []
-        entries = [Entry(s.request, s.request.next_tokens(s.num_tokens),
-                         (s.num_tokens - 1,) if s.wants_logits else ()) for s in plan]
-        logits = self.session.step_reserved(entries)
+        """One scheduling round and one model step.  Returns what ran (with tokens appended).
+
+        With ``lookahead``, a step in which every running request decodes one token is followed on the
+        device by the next such step before its own tokens have been read: the next step's token ids
+        are copied from the sampler's output on the device, and positions, lengths and pages do not
+        depend on which tokens were drawn.  The host then reads a step's tokens while the next one
+        runs, so the device does not wait for the host between steps.  A request that turns out to have
+        finished (an end-of-sequence token) has then been run one token too far; that token is dropped.
+        Anything else (prompts to compute, requests waiting, a request at its last token, pages running
+        short) is planned by the scheduler with all results in hand, as without lookahead."""
+        flight = self._inflight
+        self._inflight = None
+        if flight is None:
+            plan = self.scheduler.schedule()
+            if not plan:
+                return []
+            flight = self._launch(plan, None)
+        if self.lookahead:
+            self._inflight = self._launch_ahead(flight)
+        self._collect(flight)
+        return flight.plan
+
+    def drain(self) -> None:
+        """Waits for a step launched ahead, if there is one, and records its results."""
+        if self._inflight is not None:
+            flight, self._inflight = self._inflight, None
+            self._collect(flight)
+
+    def _launch(self, plan: List[ScheduledRequest], after: Optional["_InFlight"]) -> "_InFlight":
+        """Puts the plan's step on the device: batch, model, sampling, and the copy of the sampled tokens
+        and the status word to pinned memory.  ``after``: the step (still running) whose sampled tokens
+        are this step's input."""
+        ahead = 0 if after is None else 1
+        if after is None:
+            entries = [Entry(s.request, s.request.next_tokens(s.num_tokens),
+                             (s.num_tokens - 1,) if s.wants_logits else ()) for s in plan]
+            logits = self.session.step_reserved(entries)
+        else:
+            entries = [Entry(s.request, (0,), (0,)) for s in plan]  # the ids come from the device
+            logits = self.session.step_reserved(entries, ahead=1, token_source=after.box[1:1 + len(plan)])
         wanting = [s for s in plan if s.wants_logits]
-        sampled: List[Optional[int]] = [None] * len(plan)
+        which = self._launches % 2
+        self._launches += 1
+        box = self._boxes[which]
+        flight = _InFlight(plan, wanting, box, self._host_boxes[which], self._host_status[which], torch.cuda.Event(),
+                           ahead == 1)
         if wanting:
             reqs = [s.request for s in wanting]
-            box = self.session.rt.mailbox
             self.sampler.sample(
                 logits, [r.params.temperature for r in reqs], [r.params.top_k for r in reqs],
-                [r.key for r in reqs], [len(r) for r in reqs], [r.params.seed for r in reqs],
+                [r.key for r in reqs], [len(r) + ahead for r in reqs], [r.params.seed for r in reqs],
                 out=box[1:1 + len(reqs)])
-            host = box[:1 + len(reqs)].tolist()  # the step's one device-to-host read: status word, then tokens
-            self.session.raise_on_status(host[0])
-            it = iter(host[1:])
+            flight.host_box[:1 + len(reqs)].copy_(box[:1 + len(reqs)], non_blocking=True)
+        flight.host_status.copy_(self.session.rt.status, non_blocking=True)
+        flight.done.record()
+        return flight
+
+    def _launch_ahead(self, flight: "_InFlight") -> Optional["_InFlight"]:
+        """The step after ``flight``, if it needs no decision that depends on flight's tokens."""
+        sched = self.scheduler
+        plan = flight.plan
+        if sched.waiting or len(plan) != len(sched.running) or not all(s.num_tokens == 1 and s.wants_logits for s in plan):
+            return None
+        reqs = [s.request for s in plan]
+        limit = self.session.max_positions
+        for r in reqs:
+            # (its last token, by count or by position, is decided when the scheduler sees it finished)
+            if (r.status != RequestStatus.RUNNING or len(r.output) + 2 > r.params.max_new_tokens
+                    or len(r) + 1 > limit or not sched.cache.can_reserve(r, len(r) + 1)):
+                return None
+        need = None
+        for r in reqs:
+            more = sched.cache.pages_needed(r, len(r) + 1)
+            need = more if need is None else [a + b for a, b in zip(need, more)]
+        if any(n > sched.cache.free_pages(g) for g, n in enumerate(need)):
+            return None
+        for r in reqs:
+            sched.cache.reserve(r, len(r) + 1)
+        self.num_ahead += 1
+        return self._launch([ScheduledRequest(r, 1, True) for r in reqs], flight)
+
+    def _collect(self, flight: "_InFlight") -> None:
+        """Waits for the step, reads its tokens and lets the scheduler record them."""
+        flight.done.synchronize()
+        self.session.raise_on_status(int(flight.host_status[0]))
+        plan = flight.plan
+        sampled: List[Optional[int]] = [None] * len(plan)
+        if flight.wanting:
+            it = iter(flight.host_box[1:1 + len(flight.wanting)].tolist())
             sampled = [next(it) if s.wants_logits else None for s in plan]
+        if flight.ahead:
+            # a request that finished or was taken out while this step ran has been run one token too far
+            live = [i for i, s in enumerate(plan) if s.request.status == RequestStatus.RUNNING]
+            plan_live, sampled = [plan[i] for i in live], [sampled[i] for i in live]
         else:
-            self.session.check_status()
+            plan_live = plan
         now = time.perf_counter()
-        for s in wanting:
-            if s.request.first_token_time is None:
+        for s in plan_live:
+            if s.wants_logits and s.request.first_token_time is None:
                 s.request.first_token_time = now
-        for req in self.scheduler.post_process(plan, sampled):
+        for req in self.scheduler.post_process(plan_live, sampled):
             req.finish_time = now
         self.session.after_step()
         self.num_steps += 1
-        return plan
 
     # ------------------------------------------------------------------ the reference's interface
     def warmup(self, prompt: Optional[Prompt] = None, num_tokens: int = 3) -> None:

@@ -51,9 +51,9 @@ class StepGraphs:
     def decode_only(entries: Sequence[Entry]) -> bool:
         return all(len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries)
 
-    def run(self, entries: Sequence[Entry]) -> torch.Tensor:
+    def run(self, entries: Sequence[Entry], ahead: int = 0, token_source: Optional[torch.Tensor] = None) -> torch.Tensor:
         s = self.session
-        longest = max(s.manager.length(e.request) + len(e.tokens) for e in entries)
+        longest = max(s.manager.length(e.request) + len(e.tokens) for e in entries) + ahead
         bucket = -(-longest // self.BUCKET) * self.BUCKET
         stride = -(-bucket // s.manager.page_size)
         lens = [len(e.tokens) for e in entries]
@@ -62,12 +62,16 @@ class StepGraphs:
         slot = self.graphs.get(key)
         if slot is not None:
             ctx, graph, logits = slot
-            ctx.build(entries, s.vocab_size, table_stride=stride, keep_buffer=True)
+            ctx.build(entries, s.vocab_size, table_stride=stride, keep_buffer=True, ahead=ahead)
+            if token_source is not None:
+                ctx.token_ids.copy_(token_source)
             graph.replay()
             self.replays += 1
             s.last_context, s.last_graph = ctx, (graph, logits)
             return logits
-        ctx = BatchContext(s.manager, s.storage, s.rt).build(entries, s.vocab_size, table_stride=stride)
+        ctx = BatchContext(s.manager, s.storage, s.rt).build(entries, s.vocab_size, table_stride=stride, ahead=ahead)
+        if token_source is not None:
+            ctx.token_ids.copy_(token_source)
         ctx.max_kv_len = bucket  # the split count recorded in a graph is the bucket's
         eager = s.model.step(ctx)
         s.last_context, s.last_graph = ctx, None
@@ -168,15 +172,21 @@ class Session:
         self._poison()
         return logits
 
-    def step_reserved(self, entries: Sequence[Entry]) -> torch.Tensor:
+    def step_reserved(self, entries: Sequence[Entry], ahead: int = 0,
+                      token_source: Optional[torch.Tensor] = None) -> torch.Tensor:
         """The step for a caller (the scheduler) that has opened the requests and reserved their
-        pages itself and will record the progress itself: builds the batch and runs it."""
-        return self._run(entries)
+        pages itself and will record the progress itself: builds the batch and runs it.
+        ``ahead``: an earlier step, still running, will have added this many tokens to every request
+        of this one by the time it runs; ``token_source``: int32 on the device, one per row: the token
+        ids of this step (those that the earlier step is about to sample), copied in on the stream."""
+        return self._run(entries, ahead, token_source)
 
-    def _run(self, entries: Sequence[Entry]) -> torch.Tensor:
+    def _run(self, entries: Sequence[Entry], ahead: int = 0, token_source: Optional[torch.Tensor] = None) -> torch.Tensor:
         if self.step_graphs is not None:
-            return self.step_graphs.run(entries)
-        ctx = BatchContext(self.manager, self.storage, self.rt).build(entries, self.vocab_size)
+            return self.step_graphs.run(entries, ahead, token_source)
+        ctx = BatchContext(self.manager, self.storage, self.rt).build(entries, self.vocab_size, ahead=ahead)
+        if token_source is not None:
+            ctx.token_ids.copy_(token_source)
         self.last_context, self.last_graph = ctx, None
         return self.model.step(ctx)
 

@@ -156,6 +156,47 @@ def test_eos_stops_a_request(tiny_folders):
     assert not engine.session.manager.live_requests()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_lookahead_changes_nothing_but_the_timing(tiny_folders, dtype):
+    """Steps launched before the tokens of the step before them have been read: requests that stop at
+    different lengths, one that stops at an end-of-sequence token (it has then been run one token too
+    far, which is dropped), requests that arrive while others decode, sampling with a temperature.
+    The same ids and finish reasons as with every step planned after the last was read."""
+    from qwen3_from_scratch_b200.engine.engine import SyncEngine
+    from qwen3_from_scratch_b200.engine.request import RequestStatus, SamplingParams
+    folder = tiny_folders["b"]
+    prompts = [random_tokens(384, n, 60 + i) for i, n in enumerate([7, 19, 3, 30, 11])]
+    limits = [25, 9, 31, 14, 20]
+    outcomes = []
+    for lookahead in (False, True):
+        engine = SyncEngine(folder, dtype=dtype, block_size=8, num_pages=96, max_num_seqs=4, max_num_tokens=64,
+                            lookahead=lookahead)
+        if lookahead:  # an id that the first request is known to produce: it ends there
+            engine.eos_token_id = outcomes[0][0][0][12]
+        else:
+            engine.eos_token_id = None
+        params = [SamplingParams(max_new_tokens=n, temperature=0.7 if i == 3 else 0.0, top_k=5 if i == 3 else 0, seed=11,
+                                 ignore_eos=i != 0) for i, n in enumerate(limits)]
+        reqs = [engine.add_request(p, params=q) for p, q in zip(prompts[:3], params[:3])]
+        steps = 0
+        while any(r.status != RequestStatus.FINISHED for r in reqs):
+            engine.step()
+            steps += 1
+            if steps == 6:  # two more arrive while the first three decode
+                reqs += [engine.add_request(p, params=q) for p, q in zip(prompts[3:], params[3:])]
+            for i, r in enumerate(reqs):
+                r.key = 1000 + i  # the random stream of a request is keyed by this: the same in both engines
+        engine.drain()
+        outcomes.append(([list(r.output) for r in reqs], [r.finish_reason for r in reqs], engine.num_ahead))
+        engine.session.manager.check()
+        assert not engine.session.manager.live_requests()
+    (ids0, why0, ahead0), (ids1, why1, ahead1) = outcomes
+    assert ahead0 == 0 and ahead1 > 10
+    stop = ids0[0].index(ids0[0][12])  # where the chosen id first appears
+    assert ids1[0] == ids0[0][:stop + 1] and why1[0] == "eos"
+    assert ids1[1:] == ids0[1:] and why1[1:] == why0[1:]
+
+
 def test_preemption_keeps_the_result(tiny_folders):
     """A pool too small for all requests at once: some are preempted and recomputed, and every
     request still produces what it produces alone."""
