@@ -8,6 +8,7 @@ step's tokens are recorded after it; ``end`` gives everything back.
 from __future__ import annotations
 
 import gc
+from collections import OrderedDict
 from typing import Hashable, List, Optional, Sequence
 
 import torch
@@ -33,7 +34,8 @@ class StepGraphs:
 
     Decode-only steps (every request brings one token and wants its logits) are recorded the first
     time their shape appears; other shapes (full-size prompt portions, which a long prompt repeats)
-    when they appear a second time, so that one-off shapes are never recorded.  The first step of a
+    when they appear a second time, so that one-off shapes are never recorded; at most MAX_GRAPHS are
+    kept, the least recently replayed one making room.  The first step of a
     shape always runs kernel by kernel: it is this step's result, and first-use set-up must not
     happen inside a capture.  The graphs share one memory pool: only one of them runs at a time."""
 
@@ -42,7 +44,7 @@ class StepGraphs:
 
     def __init__(self, session: "Session"):
         self.session = session
-        self.graphs = {}
+        self.graphs = OrderedDict()  # least recently replayed first
         self.seen = {}
         self.pool = None
         self.replays = 0
@@ -61,6 +63,7 @@ class StepGraphs:
                sum(len(e.want) for e in entries), bucket)
         slot = self.graphs.get(key)
         if slot is not None:
+            self.graphs.move_to_end(key)
             ctx, graph, logits = slot
             ctx.build(entries, s.vocab_size, table_stride=stride, keep_buffer=True, ahead=ahead)
             if token_source is not None:
@@ -79,9 +82,11 @@ class StepGraphs:
         if len(self.seen) > 4096:
             self.seen.clear()
         wanted = self.decode_only(entries) or self.seen[key] >= 2
-        if not wanted or len(self.graphs) >= self.MAX_GRAPHS:
+        if not wanted:
             return eager
         torch.cuda.synchronize()
+        while len(self.graphs) >= self.MAX_GRAPHS:  # the shape that has not come for the longest time makes room
+            self.graphs.popitem(last=False)
         graph = torch.cuda.CUDAGraph()
         if self.pool is None:
             self.pool = torch.cuda.graph_pool_handle()

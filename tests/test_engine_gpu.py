@@ -123,6 +123,30 @@ def test_portion_graphs_give_what_plain_launches_give(tiny_folders, dtype):
         assert torch.allclose(outs[0], outs[1], atol=1e-5, rtol=0)  # the same kernels in the same order
 
 
+def test_graphs_beyond_the_limit_make_room(tiny_folders):
+    """More step shapes than graphs are kept: the least recently replayed one is dropped and recorded
+    again when its shape comes back; the logits stay those of plain launches."""
+    from qwen3_from_scratch_b200.engine.session import Session
+    folder = tiny_folders["a"]
+    prompts = {r: random_tokens(256, 6 + i, 70 + i) for i, r in enumerate("pqrs")}
+    outs = []
+    for graphs in (True, False):
+        session = Session(folder, dtype="float32", page_size=4, num_pages=64, max_seqs=4, max_step_tokens=64,
+                          cuda_graphs=graphs)
+        if graphs:
+            session.step_graphs.MAX_GRAPHS = 2
+        got = [session.step([(r, ids, (len(ids) - 1,)) for r, ids in prompts.items()]).cpu()]
+        token = 5
+        for live in (4, 3, 2, 1, 2, 3, 4, 1, 4):  # decode steps of changing width: four shapes, room for two
+            for _ in range(2):
+                token = (token * 7 + 3) % 256
+                got.append(session.step([(r, [token], (0,)) for r in "pqrs"[:live]]).cpu())
+        outs.append(torch.cat(got))
+        if graphs:
+            assert len(session.step_graphs.graphs) == 2 and session.step_graphs.replays >= 9
+    assert torch.equal(outs[0], outs[1])
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_graph_replay_gives_what_plain_launches_give(tiny_folders, dtype):
     """Decode steps replayed from CUDA graphs against the same steps launched kernel by kernel."""
