@@ -123,6 +123,26 @@ def test_portion_graphs_give_what_plain_launches_give(tiny_folders, dtype):
         assert torch.allclose(outs[0], outs[1], atol=1e-5, rtol=0)  # the same kernels in the same order
 
 
+def test_decoding_across_context_buckets_with_lookahead(tiny_folders):
+    """The context bucket of the graphs made small, so that decoding crosses it again and again (a new
+    table pitch and a new graph each time) with steps launched ahead; against plain launches, no lookahead."""
+    from qwen3_from_scratch_b200.engine.engine import SyncEngine
+    folder = tiny_folders["b"]
+    prompts = [random_tokens(384, n, 80 + i) for i, n in enumerate([5, 40, 23])]
+    outs = []
+    for fast in (True, False):
+        engine = SyncEngine(folder, dtype="float32", block_size=8, num_pages=96, max_num_seqs=4, max_num_tokens=64,
+                            cuda_graphs=fast, lookahead=fast)
+        if fast:
+            engine.session.step_graphs.BUCKET = 32
+        results, _ = engine.batch_generate(prompts, max_new_tokens=150, ignore_eos=True)
+        outs.append([r.token_ids for r in results])
+        if fast:
+            assert engine.num_ahead > 100 and len(engine.session.step_graphs.graphs) >= 5
+        engine.session.manager.check()
+    assert outs[0] == outs[1]
+
+
 def test_graphs_beyond_the_limit_make_room(tiny_folders):
     """More step shapes than graphs are kept: the least recently replayed one is dropped and recorded
     again when its shape comes back; the logits stay those of plain launches."""
