@@ -343,7 +343,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleave8: bool = False) 
     _done("swiglu", code, f"width {two_i // 2}")
 
 
-SKINNY_MAX_ROWS = 16
+SKINNY_MAX_ROWS = 16  # rows of the few-rows product (two tiles of eight tokens)
 
 
 def gemm_skinny_takes(rows: int, weight: torch.Tensor) -> bool:
