@@ -47,7 +47,9 @@ def write_folder(folder):
 
 
 def main():
-    ref_src = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/src"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to the reference's src folder>")
+    ref_src = sys.argv[1]
     sys.path.insert(0, ref_src)
     from qwen3_from_scratch.factory.config import load_from_file
     from qwen3_from_scratch.inference.context import ModelContext, set_forward_context
