@@ -2,7 +2,7 @@
 code (1483795887/qwen3_from_scratch, ``Qwen3`` on its ``base`` components, float32, CPU) for
 one tiny random model and one token sequence.
 
-    python tests/golden/make_golden.py [path to the reference's src/ folder]
+    python tests/golden/make_golden.py <path to the reference's src/ folder>
 
 The model folder is written by this repository's random-weights writer with the
 configuration and seed below (stored in float32, so that both sides read identical values);
