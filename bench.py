@@ -49,16 +49,41 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"
 
 
 def load_peaks():
+    """Measured peaks of this pool's GPUs if the file is there (keys hbm_gbs, bf16_tflops,
+    bf16_tflops_sustained, looked for at any depth, as numbers or as {"value": number}), else the fallback."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+
+    def find(node, key):
+        if isinstance(node, dict):
+            if key in node:
+                v = node[key]
+                if isinstance(v, dict):
+                    v = v.get("value")
+                if isinstance(v, (int, float)) and v > 0:
+                    return float(v)
+            for child in node.values():
+                got = find(child, key)
+                if got is not None:
+                    return got
+        elif isinstance(node, list):
+            for child in node:
+                got = find(child, key)
+                if got is not None:
+                    return got
+        return None
+
     if os.path.isfile(path):
         try:
             with open(path) as f:
                 data = json.load(f)
-            out = {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data["bf16_tflops"]), "source": "measured"}
-            if "bf16_tflops_sustained" in data:
-                out["bf16_tflops_sustained"] = float(data["bf16_tflops_sustained"])
-            return out
-        except (OSError, ValueError, KeyError, TypeError):
+            hbm, burst = find(data, "hbm_gbs"), find(data, "bf16_tflops")
+            if hbm is not None and burst is not None:
+                out = {"hbm_gbs": hbm, "bf16_tflops": burst, "source": "measured"}
+                sustained = find(data, "bf16_tflops_sustained")
+                if sustained is not None:
+                    out["bf16_tflops_sustained"] = sustained
+                return out
+        except (OSError, ValueError):
             pass
     return dict(FALLBACK_PEAKS)
 
