@@ -270,7 +270,7 @@ def decode_bench(engine, batch, context, steps, warmup, vocab):
     torch.cuda.synchronize()
     e2e_seconds = time.perf_counter() - t0
     engine.lookahead = True
-    d2h = batch * 4 + 4  # sampled ids and the status word
+    d2h = (1 + batch) * 4 + 4  # the sampled ids behind their buffer's first word, and the status word
     # (b) the same step on the device alone: replay the last batch (same lengths, same pages)
     ctx = engine.session.last_context
     # with the default sizes every request ends at exactly `context`; with many long prompts the dry run can
