@@ -73,8 +73,8 @@ _SIGNATURES = {
                        _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
                        _c_void_p, _c_int, _c_void_p, _c_void_p],
     "q3_gemm_skinny": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
-    "q3_sample": [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ull,
-                  _c_void_p, _c_void_p, _c_void_p],
+    "q3_sample": [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ull, _c_int,
+                  _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p],
 }
 
 
@@ -93,6 +93,8 @@ def library() -> ctypes.CDLL:
                     fn = getattr(lib, name)
                     fn.argtypes = argtypes
                     fn.restype = _c_int
+                lib.q3_sample_scratch_bytes.argtypes = [_c_int]
+                lib.q3_sample_scratch_bytes.restype = _c_ll
                 _lib, _lib_path = _Counting(lib), path
     return _lib
 
@@ -370,7 +372,8 @@ def sample(logits: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
            temperature: Optional[torch.Tensor] = None, top_k: Optional[torch.Tensor] = None,
            request_key: Optional[torch.Tensor] = None, position: Optional[torch.Tensor] = None,
            seed: int = 0) -> None:
-    """One token per row of float32 logits: argmax where temperature <= 0, else a Gumbel-max draw."""
+    """One token per row of float32 logits: argmax where temperature <= 0, else a Gumbel-max draw
+    (among the top_k largest logits where top_k > 0)."""
     _check("sample.logits", logits, torch.float32)
     _check("sample.out", out, torch.int32)
     R, V = logits.shape
@@ -384,10 +387,25 @@ def sample(logits: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
         _check("sample.position", position, torch.int32)
     if top_k is not None:
         _check("sample.top_k", top_k, torch.int32)
+    scratch = _sample_scratch(logits.device, R)
     code = library().q3_sample(logits.data_ptr(), R, V, V, _ptr(temperature), _ptr(top_k), _ptr(request_key),
-                               _ptr(position), int(seed) & 0xFFFFFFFFFFFFFFFF, out.data_ptr(), status.data_ptr(),
-                               _stream())
+                               _ptr(position), int(seed) & 0xFFFFFFFFFFFFFFFF,
+                               1 if (top_k is not None and temperature is not None) else 0, scratch.data_ptr(),
+                               scratch.numel(), out.data_ptr(), status.data_ptr(), _stream())
     _done("sample", code)
+
+
+_SAMPLE_SCRATCH = {}
+
+
+def _sample_scratch(device: torch.device, rows: int) -> torch.Tensor:
+    """Zero-filled working memory of the sampling kernels for up to ``rows`` rows (they leave it zeroed)."""
+    have = _SAMPLE_SCRATCH.get(device)
+    need = int(library()._lib.q3_sample_scratch_bytes(max(rows, 8)))
+    if have is None or have.numel() < need:
+        have = torch.zeros(need, dtype=torch.uint8, device=device)
+        _SAMPLE_SCRATCH[device] = have
+    return have
 
 
 def rope(x: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, positions: torch.Tensor,

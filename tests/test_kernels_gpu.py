@@ -626,6 +626,34 @@ def test_sample_matches_the_plain_generator(vocab):
     assert int(st.item()) == 0
 
 
+def test_sample_top_k_with_many_equal_logits():
+    """Top-k where the k-th largest sits among thousands of logits that share their leading bits (more
+    candidates than the kernel's list holds: its slow exact path), where it sits among a handful, and
+    where k reaches into equal values (all of them stay candidates); twice in a row on the same rows."""
+    g = torch.Generator().manual_seed(23)
+    V = 50000
+    rows = []
+    rows.append(torch.full((V,), 1.5) + 1e-4 * torch.rand(V, generator=g))          # all in one bin
+    spread = torch.randn(V, generator=g)
+    spread[torch.randperm(V, generator=g)[:7]] += 12.0                                # seven far above the rest
+    rows.append(spread)
+    flat = torch.zeros(V)
+    flat[torch.randperm(V, generator=g)[:30]] = 3.0                                   # thirty equal at the top
+    rows.append(flat)
+    logits = torch.stack(rows)
+    temps, top_k, keys, pos, seed = [0.9, 1.1, 0.8], [300, 5, 12], [1, 2, 3], [7, 8, 9], 77
+    want = [plain.sample_token(logits[r], temps[r], top_k[r], seed, keys[r], pos[r]) for r in range(3)]
+    st = status()
+    for _ in range(2):
+        out = torch.full((3,), -1, dtype=torch.int32, device="cuda")
+        ops().sample(dev(logits), out, st, temperature=dev(torch.tensor(temps)),
+                     top_k=dev(torch.tensor(top_k, dtype=torch.int32)),
+                     request_key=dev(torch.tensor(keys, dtype=torch.int64)),
+                     position=dev(torch.tensor(pos, dtype=torch.int32)), seed=seed)
+        assert out.tolist() == want
+    assert int(st.item()) == 0
+
+
 def test_sampling_follows_the_softmax_distribution():
     """Many draws (different positions) from a small distribution: frequencies match softmax(l / T)."""
     logits = torch.tensor([2.0, 1.0, 0.0, -1.0, 0.5])
