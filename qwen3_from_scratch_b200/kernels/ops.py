@@ -430,6 +430,15 @@ def gemm_tc_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
     return x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.shape[1] % 8 == 0
 
 
+def gemm_tc_swiglu_pays(rows: int, weight: torch.Tensor) -> bool:
+    """Whether the gate/up product with SwiGLU in its epilogue is the faster way for a prompt portion.
+    It saves the gate kernel's pass over the [rows, 2 I] product, which weighs the more the shorter the
+    reduction is; against that its single-CTA tiles run below the library's rate when the reduction
+    is long.  Measured at 2,048 rows: width 1024 -> 24 us against 32 (library + gate kernel);
+    2048 -> 100 against 87; 4096 -> 373 against 306."""
+    return rows >= 128 and weight.shape[1] <= 1536
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
             swiglu_blocks: bool = False) -> None:
     """out[M, N] = x[M, K] @ w[N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in TMEM).
