@@ -44,7 +44,11 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
 // (With two token tiles the kernel is asked to fit three blocks per SM: left to itself the compiler used
 // fewer registers than that allows and took the loads one after the other: 10.0 us per product at 16 rows
 // against 6.7 us, the output head 86 us against 72.)
-template <int NT, int WK, int EPI, typename OutT>
+// PRE: batches of GS_UNROLL groups whose weights are fetched before the wait on the kernel before.  A
+// product with few output features (o_proj, down_proj: 64 groups of 16, one block each) gives a warp two or
+// three batches; with all of them under way before the wait, what is left after it is one round trip for
+// the activations instead of one more to memory per batch.
+template <int NT, int WK, int EPI, typename OutT, int PRE = 1>
 __global__ void __launch_bounds__(GS_WARPS * 32, NT == 1 ? 1 : 3)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
                    OutT* __restrict__ out, int T, int N, int K, int ldo) {
@@ -67,7 +71,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
   const int r_lo = min(row0 + gid, N - 1), r_hi = min(row0 + gid + 8, N - 1);  // rows past N are clamped, not stored
   const __nv_bfloat16* w_lo = W + (size_t)r_lo * K + 8 * tid4;
   const __nv_bfloat16* w_hi = W + (size_t)r_hi * K + 8 * tid4;
-  uint4 wl[GS_UNROLL], wh[GS_UNROLL];
+  uint4 wl[PRE][GS_UNROLL], wh[PRE][GS_UNROLL];
   auto load_w = [&](int g0, uint4 (&lo)[GS_UNROLL], uint4 (&hi)[GS_UNROLL]) {
 #pragma unroll
     for (int u = 0; u < GS_UNROLL; ++u) {
@@ -77,9 +81,10 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
       hi[u] = in ? ldg_stream(w_hi + k) : make_uint4(0, 0, 0, 0);
     }
   };
-  // The weights do not depend on the kernel before this one: their first batch is already on its
+  // The weights do not depend on the kernel before this one: their first batches are already on their
   // way while that kernel finishes.  The activations are read only after the wait.
-  load_w(g_lo, wl, wh);
+#pragma unroll
+  for (int p = 0; p < PRE; ++p) load_w(g_lo + p * GS_UNROLL, wl[p], wh[p]);
   pdl_wait();
   pdl_launch_dependents();
   const __nv_bfloat16* x_row[NT];
@@ -90,9 +95,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
     x_ok[i] = tok < T;
     x_row[i] = X + (size_t)(x_ok[i] ? tok : 0) * K + 8 * tid4;
   }
-  for (int g0 = g_lo; g0 < g_hi; g0 += GS_UNROLL) {
+  auto multiply = [&](int g0, const uint4 (&lo)[GS_UNROLL], const uint4 (&hi)[GS_UNROLL]) {
     uint4 xv[GS_UNROLL][NT];
-    if (g0 != g_lo) load_w(g0, wl, wh);
 #pragma unroll
     for (int u = 0; u < GS_UNROLL; ++u) {
       const size_t k = (size_t)(g0 + u) * 32;
@@ -105,9 +109,19 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
     for (int u = 0; u < GS_UNROLL; ++u)
 #pragma unroll
       for (int i = 0; i < NT; ++i) {
-        mma_16816(acc[i], wl[u].x, wh[u].x, wl[u].y, wh[u].y, xv[u][i].x, xv[u][i].y);
-        mma_16816(acc[i], wl[u].z, wh[u].z, wl[u].w, wh[u].w, xv[u][i].z, xv[u][i].w);
+        mma_16816(acc[i], lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv[u][i].x, xv[u][i].y);
+        mma_16816(acc[i], lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv[u][i].z, xv[u][i].w);
       }
+  };
+  int g0 = g_lo;
+#pragma unroll
+  for (int p = 0; p < PRE; ++p) {  // batches past the warp's share hold zeros and are skipped
+    if (g0 < g_hi) multiply(g0, wl[p], wh[p]);
+    g0 += GS_UNROLL;
+  }
+  for (; g0 < g_hi; g0 += GS_UNROLL) {
+    load_w(g0, wl[0], wh[0]);
+    multiply(g0, wl[0], wh[0]);
   }
   // acc[i][0..1]: feature row0 + gid, tokens 8i + 2 tid4, +1;  acc[i][2..3]: feature row0 + gid + 8
 #pragma unroll
@@ -155,13 +169,20 @@ static int gemm_skinny_launch(const void* X, const void* W, void* out, int T, in
   while (wk < GS_WARPS && (groups * wk * 2) / GS_WARPS < 148 * 4 && K / (wk * 2) >= 128) wk *= 2;
   const int per_block = GS_WARPS / wk;
   const unsigned grid = (groups + per_block - 1) / per_block;
-#define Q3_GS_GO(WK)                                                                               \
-  q3::launch(gemm_skinny_kernel<NT, WK, EPI, OutT>, dim3(grid), dim3(GS_WARPS * 32), 0, stream,                        \
+#define Q3_GS_GO(WK, PRE)                                                                          \
+  q3::launch(gemm_skinny_kernel<NT, WK, EPI, OutT, PRE>, dim3(grid), dim3(GS_WARPS * 32), 0, stream,                   \
       (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (OutT*)out, T, N, K, ldo)
-  if (wk == 1) Q3_GS_GO(1);
-  else if (wk == 2) Q3_GS_GO(2);
-  else if (wk == 4) Q3_GS_GO(4);
-  else Q3_GS_GO(8);
+  // batches of a warp's share of K; up to three are fetched ahead where eight tokens leave the registers
+  const int batches = ((K + 31) / 32 + wk * GS_UNROLL - 1) / (wk * GS_UNROLL);
+  const int pre = NT == 1 && wk == GS_WARPS ? (batches < 3 ? batches : 3) : 1;
+  if (wk == 1) Q3_GS_GO(1, 1);
+  else if (wk == 2) Q3_GS_GO(2, 1);
+  else if (wk == 4) Q3_GS_GO(4, 1);
+  else if (pre <= 1) Q3_GS_GO(8, 1);
+  else if constexpr (NT == 1) {
+    if (pre == 2) Q3_GS_GO(8, 2);
+    else Q3_GS_GO(8, 3);
+  }
 #undef Q3_GS_GO
   return launch_status();
 }

@@ -150,7 +150,7 @@ def test_swiglu(dtype):
 
 
 @pytest.mark.parametrize("shape", [(1, 4096, 1024), (8, 1024, 2048), (16, 331, 96), (3, 70, 200), (9, 48, 8),
-                                   (5, 151936, 64), (16, 16, 3072)])
+                                   (5, 151936, 64), (16, 16, 3072), (7, 1024, 3072), (3, 1000, 2056), (2, 64, 5000)])
 @pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
 def test_gemm_skinny(shape, out_dtype):
     T, N, K = shape
