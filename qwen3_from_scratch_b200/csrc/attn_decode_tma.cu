@@ -115,9 +115,6 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   if (warp == DT_CONSUMERS) {
     // ------------------------------------------------------------------ loader
     bool ok = true;
-    // the block counts as having let its dependents go once every thread has: the consumers do after
-    // their wait, so this does not let the next kernel in before the one before this has finished
-    pdl_launch_dependents();
     // tiles [i_lo, i_hi) of this block's range; the wait for the kernel before lies between two such
     // runs, not inside the loop
     auto issue = [&](int i_lo, int i_hi) {
@@ -157,6 +154,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int early_tiles = min(count, max(0, pos / DT_KEYS - t_lo));
     issue(0, early_tiles);
     pdl_wait();
+    pdl_launch_dependents();  // after the wait, as everywhere: the next kernel never starts before the one before this ended
     issue(early_tiles, count);
     if (!ok && lane == 0) {
       *abort_word = 1;

@@ -11,6 +11,8 @@
 #include <stdint.h>
 #include <stdlib.h>
 
+#include <atomic>
+
 // dtype tags of the C ABI
 #define Q3_F32 0
 #define Q3_BF16 1
@@ -80,6 +82,14 @@ static inline int launch_status() { return (int)cudaGetLastError(); }
 // running one holds resources on the SMs.
 // Launched the ordinary way both calls do nothing.  Q3B200_PDL=0 in the environment turns the
 // attribute off.
+//
+// What a kernel may read ahead of its wait.  Kernel N+1 starts once every block of kernel N has let
+// its dependents go, which each does only after its own wait, that is after kernel N-1 has completed.
+// So whatever kernel N-1 or an earlier one wrote is complete and visible to kernel N+1 from its first
+// instruction; only what kernel N itself writes needs the wait.  (A kernel launched the ordinary way,
+// a library's for instance, starts after the one before it has completed and lets the next one start
+// when it has completed itself, so the rule holds across it.)  The residual stream is such data for a
+// norm kernel unless the launch directly before it wrote the stream; last_launch_was_plain() tells.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
@@ -91,6 +101,18 @@ static inline bool pdl_enabled() {
   }
   return enabled == 1;
 }
+
+// The stream of this library's most recent launch if that launch did not write a residual stream,
+// else (or before any launch) all ones.  One word, so that a reader never sees half of an update.
+extern std::atomic<uintptr_t> g_plain_launch_stream;
+constexpr uintptr_t NO_PLAIN_LAUNCH = ~(uintptr_t)0;
+
+// True if the most recent launch of this library went to `stream` and wrote no residual stream.
+static inline bool last_launch_was_plain(cudaStream_t stream) {
+  return g_plain_launch_stream.load(std::memory_order_relaxed) == (uintptr_t)stream;
+}
+// To be called right after launching a kernel that writes a residual stream.
+static inline void note_stream_written() { g_plain_launch_stream.store(NO_PLAIN_LAUNCH, std::memory_order_relaxed); }
 
 template <typename... KArgs, typename... Args>
 static inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -105,6 +127,7 @@ static inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  g_plain_launch_stream.store((uintptr_t)stream, std::memory_order_relaxed);
   return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -12,6 +12,8 @@
 
 namespace q3 {
 
+std::atomic<uintptr_t> g_plain_launch_stream{NO_PLAIN_LAUNCH};
+
 // ---------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
@@ -87,21 +89,34 @@ template <> struct Vec4<__nv_bfloat16> {
   }
 };
 
+// `early` != 0: the stream was not written by the launch directly before this one, so its row may be
+// read ahead of the wait; the norm weight, which no kernel writes, always is.
 template <typename T>
 __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ resid, const T* __restrict__ delta,
                                         const float* __restrict__ w, T* __restrict__ out,
-                                        const int* __restrict__ rows, int H, float eps) {
-  pdl_wait();
-  pdl_launch_dependents();
+                                        const int* __restrict__ rows, int H, float eps, int early) {
   extern __shared__ float row_buf[];
   __shared__ float scratch[32];
   const int src_row = rows ? rows[blockIdx.x] : blockIdx.x;
   float* r = resid + (size_t)src_row * H;
   const T* d = delta ? delta + (size_t)src_row * H : nullptr;
+  const int i0 = threadIdx.x * 4;
+  float w0[4] = {0.f, 0.f, 0.f, 0.f}, v0[4] = {0.f, 0.f, 0.f, 0.f};
+  if (i0 < H) {
+    Vec4<float>::load(w + i0, w0);
+    if (early) Vec4<float>::load(r + i0, v0);
+  }
+  pdl_wait();
+  pdl_launch_dependents();
   float ss = 0.f;
-  for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+  for (int i = i0; i < H; i += blockDim.x * 4) {
     float v[4];
-    Vec4<float>::load(r + i, v);
+    if (early && i == i0) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) v[k] = v0[k];
+    } else {
+      Vec4<float>::load(r + i, v);
+    }
     if (d) {
       float dv[4];
       Vec4<T>::load(d + i, dv);
@@ -115,9 +130,14 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ resid, const T* __re
   ss = block_sum(ss, scratch);
   const float rs = 1.0f / sqrtf(ss / (float)H + eps);
   T* o = out + (size_t)blockIdx.x * H;
-  for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+  for (int i = i0; i < H; i += blockDim.x * 4) {
     float wv[4], v[4];
-    Vec4<float>::load(w + i, wv);
+    if (i == i0) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) wv[k] = w0[k];
+    } else {
+      Vec4<float>::load(w + i, wv);
+    }
 #pragma unroll
     for (int k = 0; k < 4; ++k) v[k] = row_buf[i + k] * rs * wv[k];
     Vec4<T>::store(o + i, v);
@@ -133,19 +153,26 @@ constexpr int NW_WARPS = 8;
 template <typename T, int NCH>
 __global__ void __launch_bounds__(NW_WARPS * 32)
 add_rmsnorm_warp_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ w,
-                        T* __restrict__ out, const int* __restrict__ rows, int n_rows, float eps) {
-  pdl_wait();
-  pdl_launch_dependents();
+                        T* __restrict__ out, const int* __restrict__ rows, int n_rows, float eps, int early) {
   constexpr int H = NCH * 128;
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * NW_WARPS + (threadIdx.x >> 5);
-  if (row >= n_rows) return;
-  const int src_row = rows ? rows[row] : row;
+  const bool live = row < n_rows;
+  const int src_row = !live ? 0 : rows ? rows[row] : row;
   float* r = resid + (size_t)src_row * H;
-  const T* d = delta ? delta + (size_t)src_row * H : nullptr;
   float v[NCH][4];
+  if (early && live) {  // the stream's row, ahead of the wait (see add_rmsnorm_vec4_kernel)
 #pragma unroll
-  for (int i = 0; i < NCH; ++i) Vec4<float>::load(r + (i * 32 + lane) * 4, v[i]);
+    for (int i = 0; i < NCH; ++i) Vec4<float>::load(r + (i * 32 + lane) * 4, v[i]);
+  }
+  pdl_wait();
+  pdl_launch_dependents();
+  if (!live) return;
+  const T* d = delta ? delta + (size_t)src_row * H : nullptr;
+  if (!early) {
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) Vec4<float>::load(r + (i * 32 + lane) * 4, v[i]);
+  }
   if (d) {
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
@@ -179,9 +206,9 @@ add_rmsnorm_warp_kernel(float* __restrict__ resid, const T* __restrict__ delta, 
 
 template <typename T, int NCH>
 static void add_rmsnorm_warp_launch(float* resid, const T* delta, const float* w, T* out, const int* rows, int n_rows,
-                                    float eps, cudaStream_t stream) {
+                                    float eps, int early, cudaStream_t stream) {
   q3::launch(add_rmsnorm_warp_kernel<T, NCH>, dim3((n_rows + NW_WARPS - 1) / NW_WARPS), dim3(NW_WARPS * 32), 0, stream,
-             resid, delta, w, out, rows, n_rows, eps);
+             resid, delta, w, out, rows, n_rows, eps, early);
 }
 
 // ---------------------------------------------------------------- plain RMSNorm on vectors
@@ -212,25 +239,40 @@ static int add_rmsnorm_launch(float* resid, const void* delta, const float* w, v
   if (smem > 200 * 1024) return Q3_ERR_SIZE;  // width beyond 51200 is refused
   const bool vec = (H % 4 == 0) && ((uintptr_t)resid % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
                    ((uintptr_t)out % 16 == 0) && (!delta || (uintptr_t)delta % 16 == 0);
+  // the stream may be read ahead of the wait unless the launch before this one wrote it; this launch
+  // writes it when it has a delta to add and no row list
+  const int early = last_launch_was_plain(stream) ? 1 : 0;
+  const bool writes = !rows && delta;
   if (vec && sizeof(T) == 2 && n_rows >= 64 && H % 128 == 0 && H <= 2048) {
     switch (H / 128) {
-#define Q3_NW(N) case N: add_rmsnorm_warp_launch<T, N>(resid, (const T*)delta, w, (T*)out, rows, n_rows, eps, stream); break;
+#define Q3_NW(N) case N: add_rmsnorm_warp_launch<T, N>(resid, (const T*)delta, w, (T*)out, rows, n_rows, eps, early, stream); break;
       Q3_NW(1) Q3_NW(2) Q3_NW(3) Q3_NW(4) Q3_NW(5) Q3_NW(6) Q3_NW(7) Q3_NW(8)
       Q3_NW(9) Q3_NW(10) Q3_NW(11) Q3_NW(12) Q3_NW(13) Q3_NW(14) Q3_NW(15) Q3_NW(16)
 #undef Q3_NW
     }
+    if (writes) note_stream_written();
     return launch_status();
   }
   int threads = vec ? (H / 4) : H;
   threads = ((threads + 31) / 32) * 32;
   if (threads > 512) threads = 512;
   if (threads < 32) threads = 32;
-  auto kern = vec ? add_rmsnorm_vec4_kernel<T> : add_rmsnorm_kernel<T>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+  if (vec) {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_vec4_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    q3::launch(add_rmsnorm_vec4_kernel<T>, dim3(n_rows), dim3(threads), smem, stream, resid, (const T*)delta, w, (T*)out,
+               rows, H, eps, early);
+  } else {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    q3::launch(add_rmsnorm_kernel<T>, dim3(n_rows), dim3(threads), smem, stream, resid, (const T*)delta, w, (T*)out, rows,
+               H, eps);
   }
-  q3::launch(kern, dim3(n_rows), dim3(threads), smem, stream, resid, (const T*)delta, w, (T*)out, rows, H, eps);
+  if (writes) note_stream_written();
   return launch_status();
 }
 
@@ -248,6 +290,7 @@ extern "C" int q3_embed(const void* table, int dtype, const int* ids, float* res
     q3::launch(q3::embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)table, ids, resid, H, V, status);
   else
     return Q3_ERR_DTYPE;
+  q3::note_stream_written();
   return q3::launch_status();
 }
 

@@ -114,6 +114,34 @@ def test_add_rmsnorm_many_rows(dtype, width):
 
 
 @pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("rows", [24, 6000])
+def test_add_rmsnorm_right_after_a_writer_of_the_stream(dtype, rows):
+    """A norm reads the stream ahead of its wait on the launch before it unless that launch wrote the
+    stream.  Three norms in a row (each writes what the next reads), and norms with one short launch
+    of another kind between them (the writer is two launches back: long, so that it would still be
+    running if the later norm could start before it ended)."""
+    g = torch.Generator().manual_seed(12)
+    width, eps = 1024, 1e-6
+    stream = torch.randn(rows, width, generator=g)
+    deltas = [torch.randn(rows, width, generator=g).to(DT[dtype]) for _ in range(3)]
+    w = 1 + 0.1 * torch.randn(width, generator=g)
+    d_dev, w_dev = [dev(d) for d in deltas], dev(w)
+    out = torch.empty(rows, width, device="cuda", dtype=DT[dtype])
+    small_in = dev(torch.randn(1, 64, generator=g).to(DT[dtype]))
+    small_out = torch.empty(1, 32, device="cuda", dtype=DT[dtype])
+    total = stream.double() + sum(d.double() for d in deltas)
+    for between in (False, True):
+        for _ in range(5):
+            s = dev(stream.clone())
+            for d in d_dev:
+                ops().add_rmsnorm(s, d, w_dev, out, eps)
+                if between:
+                    ops().swiglu(small_in, small_out)
+            close(s, total, "float32")
+            close(out, plain.rms_norm(total, w.double(), eps), dtype)
+
+
+@pytest.mark.parametrize("dtype", list(DT))
 def test_rmsnorm_on_head_vectors(dtype):
     g = torch.Generator().manual_seed(2)
     x = torch.randn(11, 5, 48, generator=g).to(DT[dtype])
