@@ -559,7 +559,7 @@ def test_fast_attention_against_plain(case, portion_kernel):
 
 @pytest.mark.parametrize("loader,d,page_size", [("cp_async", 64, 16), ("tma", 64, 16), ("tma", 128, 32),
                                                 ("cp_async", 48, 8)])
-@pytest.mark.parametrize("splits", [1, 2, 3, 7, 32])
+@pytest.mark.parametrize("splits", [1, 2, 3, 4, 7, 12, 31, 32])
 @pytest.mark.parametrize("window", [None, 150])
 def test_decode_splits_agree(splits, window, loader, d, page_size):
     hq, hkv = 8, 2
