@@ -107,6 +107,8 @@ class _Counting:
         self.calls = 0
 
     def __getattr__(self, name):
+        if name not in _SIGNATURES:  # without declared argument types ctypes would cut pointers to 32 bits
+            raise KernelError(f"{name}: no argument types declared for this entry point")
         fn = getattr(self._lib, name)
 
         def counted(*args):
