@@ -13,6 +13,16 @@
 // blocks of eight between gate and up (rows 16j .. 16j+7 = gate[8j ..], rows 16j+8 .. 16j+15 =
 // up[8j ..]): out[t, 8j + i] = up * gate * sigmoid(gate), so the gate/up product never goes to memory.
 //
+// Two more forms take the norm kernels out of a decode step (the reference's block: norm, mixer, add, norm,
+// feed-forward, add; models/transformer_block.py:38-46).  RMSNorm is x * rs * w with one scalar rs per row,
+// and a scalar commutes with the product: W (h * rs * w) = rs * (W (h * w)).  So
+//   * "normed in" (NORMED): X is the float32 residual stream itself; a lane multiplies its eight values by the
+//     norm weight, rounds once to bfloat16 and feeds the tensor core; the epilogue multiplies by
+//     rs = 1 / sqrt(sum(h^2) / K + eps), the sum coming from partial sums that the kernel before left;
+//   * "into the stream" (EPI 2): the product is added to the float32 stream in place, and each block of 16
+//     features leaves the sum of squares of its 16 new values per row, in a fixed order (no atomics): the
+//     partial sums that the next normed-in product reads.
+//
 // Reference for the role: the projections of the reference are nn.Linear (models/self_attn.py:358-386,
 // models/feedback.py:28-34); its fused variant merges up and gate the same way (models/feedback.py:52-62).
 #include "common.cuh"
@@ -48,12 +58,28 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
 // product with few output features (o_proj, down_proj: 64 groups of 16, one block each) gives a warp two or
 // three batches; with all of them under way before the wait, what is left after it is one round trip for
 // the activations instead of one more to memory per batch.
-template <int NT, int WK, int EPI, typename OutT, int PRE = 1>
-__global__ void __launch_bounds__(GS_WARPS * 32, NT == 1 ? 1 : 3)
+struct SkinnyFuse {
+  const float* stream;  // NORMED: the residual stream [T, K] float32, read in place of X
+  const float* norm_w;  // NORMED: the norm's weight [K]
+  const float* ss_in;   // NORMED: [ss_parts][16] partial sums of squares of the stream's rows
+  int ss_parts;
+  float eps;
+  float* ss_out;        // EPI 2: [ceil(N / 16)][16] partial sums of squares of the rows after the add
+  int early;            // EPI 2: the stream may be read ahead of the wait (the launch before did not write it)
+};
+
+constexpr int GS_SS_ROWS = 16;  // row pitch of the partial sums
+constexpr int GS_XS_PAD = 32;   // NORMED: elements between rows of the staged operand (a quarter-warp's 16-byte reads then miss each other's banks)
+constexpr int GS_XS_MAX_BYTES = 160 * 1024;
+
+// EPI 2: out is the float32 stream [T, N] and is added to.  NORMED: see the head of the file.
+template <int NT, int WK, int EPI, typename OutT, int PRE = 1, bool NORMED = false>
+__global__ void __launch_bounds__(GS_WARPS * 32, (NT == 1 && !(NORMED && PRE == 1)) ? 1 : 3)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
-                   OutT* __restrict__ out, int T, int N, int K, int ldo) {
+                   OutT* __restrict__ out, int T, int N, int K, int ldo, const SkinnyFuse fuse) {
   constexpr int GROUPS = GS_WARPS / WK;  // feature groups per block
   __shared__ float red[GS_WARPS][16][8 * NT + 1];
+  __shared__ float rs_s[8 * NT];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tid4 = lane & 3;
   const int group_in_block = warp / WK, ksplit = warp % WK;
@@ -85,33 +111,98 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
   // way while that kernel finishes.  The activations are read only after the wait.
 #pragma unroll
   for (int p = 0; p < PRE; ++p) load_w(g_lo + p * GS_UNROLL, wl[p], wh[p]);
+  float4 w_first = make_float4(0.f, 0.f, 0.f, 0.f);  // NORMED: this thread's four norm weights of the first pass
+  if (NORMED && (int)threadIdx.x < K / 4) w_first = __ldg(reinterpret_cast<const float4*>(fuse.norm_w) + threadIdx.x);
+  // EPI 2: the stream's values that this warp will add to (element e = lane + 32 j of its 16 x 8 NT results)
+  float before[EPI == 2 ? 4 * NT : 1];
+  if (EPI == 2 && fuse.early && ksplit == 0 && active) {
+#pragma unroll
+    for (int j = 0; j < 4 * NT; ++j) {
+      const int e = lane + 32 * j, f = e & 15, tok = e >> 4;
+      before[j] = (tok < T && row0 + f < N) ? reinterpret_cast<const float*>(out)[(size_t)tok * ldo + row0 + f] : 0.f;
+    }
+  }
   pdl_wait();
   pdl_launch_dependents();
+  // NORMED: warp w sums the partial sums of squares of rows w and w + 8; the first two per lane are asked
+  // for here and added after the main loop, so that their latency runs beside the loop's
+  float ss_a[NT], ss_b[NT];
+  if (NORMED) {
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+      const int tok = i * 8 + warp;
+      ss_a[i] = (tok < T && lane < fuse.ss_parts) ? fuse.ss_in[(size_t)lane * GS_SS_ROWS + tok] : 0.f;
+      ss_b[i] = (tok < T && lane + 32 < fuse.ss_parts) ? fuse.ss_in[(size_t)(lane + 32) * GS_SS_ROWS + tok] : 0.f;
+    }
+  }
+  // NORMED: the block first turns the stream's rows into the bfloat16 operand, all together: a thread takes
+  // four neighbouring values of k (its slice of the norm weight was fetched ahead of the wait) of every row,
+  // so that all loads of the stream are in flight at once; the main loop then reads fragments from shared memory.
+  extern __shared__ __align__(16) unsigned char xs_raw[];
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(xs_raw);  // [8 NT][K + GS_XS_PAD]
+  const int xs_pitch = K + GS_XS_PAD;
+  if (NORMED) {
+    for (int c0 = 0; c0 < K / 4; c0 += GS_WARPS * 32) {
+      const int c = c0 + threadIdx.x;
+      const bool in = c < K / 4;
+      const float4 wv = (c0 == 0) ? w_first : (in ? __ldg(reinterpret_cast<const float4*>(fuse.norm_w) + c) : make_float4(0.f, 0.f, 0.f, 0.f));
+#pragma unroll 1
+      for (int half = 0; half < NT; ++half) {  // eight rows at a time: their loads are in flight together
+        float4 xv4[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+          xv4[t] = (in && half * 8 + t < T) ? *(reinterpret_cast<const float4*>(fuse.stream + (size_t)(half * 8 + t) * K) + c)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (in) {
+#pragma unroll
+          for (int t = 0; t < 8; ++t) {
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(xv4[t].x * wv.x, xv4[t].y * wv.y);
+            __nv_bfloat162 p1 = __floats2bfloat162_rn(xv4[t].z * wv.z, xv4[t].w * wv.w);
+            uint2 packed;
+            packed.x = *reinterpret_cast<uint32_t*>(&p0);
+            packed.y = *reinterpret_cast<uint32_t*>(&p1);
+            *reinterpret_cast<uint2*>(xs + (size_t)(half * 8 + t) * xs_pitch + 4 * c) = packed;
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
   const __nv_bfloat16* x_row[NT];
   bool x_ok[NT];
 #pragma unroll
   for (int i = 0; i < NT; ++i) {
     const int tok = i * 8 + gid;
-    x_ok[i] = tok < T;
-    x_row[i] = X + (size_t)(x_ok[i] ? tok : 0) * K + 8 * tid4;
+    x_ok[i] = NORMED || tok < T;  // the staged operand holds zeros for rows past T
+    x_row[i] = NORMED ? xs + (size_t)tok * xs_pitch + 8 * tid4 : X + (size_t)(x_ok[i] ? tok : 0) * K + 8 * tid4;
   }
   auto multiply = [&](int g0, const uint4 (&lo)[GS_UNROLL], const uint4 (&hi)[GS_UNROLL]) {
-    uint4 xv[GS_UNROLL][NT];
+    constexpr int XU = GS_UNROLL;  // groups whose activations are fetched together
 #pragma unroll
-    for (int u = 0; u < GS_UNROLL; ++u) {
-      const size_t k = (size_t)(g0 + u) * 32;
-      const bool in = g0 + u < g_hi && k + 8 * tid4 < (size_t)K;
+    for (int u0 = 0; u0 < GS_UNROLL; u0 += XU) {
+      uint4 xv[XU][NT];
 #pragma unroll
-      for (int i = 0; i < NT; ++i)
-        xv[u][i] = (in && x_ok[i]) ? __ldg(reinterpret_cast<const uint4*>(x_row[i] + k)) : make_uint4(0, 0, 0, 0);
-    }
+      for (int u = 0; u < XU; ++u) {
+        const size_t k = (size_t)(g0 + u0 + u) * 32;
+        const bool in = g0 + u0 + u < g_hi && k + 8 * tid4 < (size_t)K;
+        if (NORMED) {
 #pragma unroll
-    for (int u = 0; u < GS_UNROLL; ++u)
+          for (int i = 0; i < NT; ++i)
+            xv[u][i] = in ? *reinterpret_cast<const uint4*>(x_row[i] + k) : make_uint4(0, 0, 0, 0);
+        } else {
 #pragma unroll
-      for (int i = 0; i < NT; ++i) {
-        mma_16816(acc[i], lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv[u][i].x, xv[u][i].y);
-        mma_16816(acc[i], lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv[u][i].z, xv[u][i].w);
+          for (int i = 0; i < NT; ++i)
+            xv[u][i] = (in && x_ok[i]) ? __ldg(reinterpret_cast<const uint4*>(x_row[i] + k)) : make_uint4(0, 0, 0, 0);
+        }
       }
+#pragma unroll
+      for (int u = 0; u < XU; ++u)
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+          mma_16816(acc[i], lo[u0 + u].x, hi[u0 + u].x, lo[u0 + u].y, hi[u0 + u].y, xv[u][i].x, xv[u][i].y);
+          mma_16816(acc[i], lo[u0 + u].z, hi[u0 + u].z, lo[u0 + u].w, hi[u0 + u].w, xv[u][i].z, xv[u][i].w);
+        }
+    }
   };
   int g0 = g_lo;
 #pragma unroll
@@ -122,6 +213,17 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
   for (; g0 < g_hi; g0 += GS_UNROLL) {
     load_w(g0, wl[0], wh[0]);
     multiply(g0, wl[0], wh[0]);
+  }
+  if (NORMED) {
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+      const int tok = i * 8 + warp;
+      float ss = ss_a[i] + ss_b[i];
+      if (tok < T)
+        for (int p = lane + 64; p < fuse.ss_parts; p += 32) ss += fuse.ss_in[(size_t)p * GS_SS_ROWS + tok];
+      ss = warp_sum(ss);
+      if (lane == 0) rs_s[tok] = 1.0f / sqrtf(ss / (float)K + fuse.eps);
+    }
   }
   // acc[i][0..1]: feature row0 + gid, tokens 8i + 2 tid4, +1;  acc[i][2..3]: feature row0 + gid + 8
 #pragma unroll
@@ -141,7 +243,29 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
       float v = 0.f;
 #pragma unroll
       for (int s = 0; s < WK; ++s) v += red[warp + s][f][tok];
+      if (NORMED) v *= rs_s[tok];
       out[(size_t)tok * ldo + row0 + f] = from_float<OutT>(v);
+    }
+  } else if (EPI == 2) {
+    // added into the stream; the 16 lanes that share a row leave the sum of squares of their new values
+    float* stream = reinterpret_cast<float*>(out);
+#pragma unroll
+    for (int j = 0; j < 4 * NT; ++j) {
+      const int e = lane + 32 * j, f = e & 15, tok = e >> 4;
+      const bool live = tok < T && row0 + f < N;
+      float h = 0.f;
+      if (live) {
+        float v = 0.f;
+#pragma unroll
+        for (int s = 0; s < WK; ++s) v += red[warp + s][f][tok];
+        float* at = stream + (size_t)tok * ldo + row0 + f;
+        h = (fuse.early ? before[j] : *at) + v;
+        *at = h;
+      }
+      float sq = h * h;
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      if (f == 0 && tok < T) fuse.ss_out[(size_t)(row0 >> 4) * GS_SS_ROWS + tok] = sq;
     }
   } else {
     // features 0..7 of the group are gate values, 8..15 the matching up values
@@ -154,14 +278,21 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
         gate += red[warp + s][f][tok];
         up += red[warp + s][f + 8][tok];
       }
+      if (NORMED) {
+        gate *= rs_s[tok];
+        up *= rs_s[tok];
+      }
       out[(size_t)tok * ldo + (row0 >> 1) + f] = from_float<OutT>(up * (gate / (1.0f + expf(-gate))));
     }
   }
 }
 
-template <int NT, int EPI, typename OutT>
+template <int NT, int EPI, typename OutT, bool NORMED = false>
 static int gemm_skinny_launch(const void* X, const void* W, void* out, int T, int N, int K, int ldo,
-                              cudaStream_t stream) {
+                              cudaStream_t stream, SkinnyFuse fuse = SkinnyFuse{}) {
+  if (EPI == 2) fuse.early = last_launch_was_plain(stream) ? 1 : 0;
+  const size_t xs_bytes = NORMED ? (size_t)8 * NT * (K + GS_XS_PAD) * sizeof(__nv_bfloat16) : 0;
+  if (xs_bytes > (size_t)GS_XS_MAX_BYTES) return Q3_ERR_SIZE;
   const int groups = (N + 15) / 16;
   // split K over more warps while that still leaves every warp at least 128 values of k and the
   // grid is short of about four blocks per SM
@@ -170,8 +301,15 @@ static int gemm_skinny_launch(const void* X, const void* W, void* out, int T, in
   const int per_block = GS_WARPS / wk;
   const unsigned grid = (groups + per_block - 1) / per_block;
 #define Q3_GS_GO(WK, PRE)                                                                          \
-  q3::launch(gemm_skinny_kernel<NT, WK, EPI, OutT, PRE>, dim3(grid), dim3(GS_WARPS * 32), 0, stream,                   \
-      (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (OutT*)out, T, N, K, ldo)
+  do {                                                                                                               \
+    auto kern = gemm_skinny_kernel<NT, WK, EPI, OutT, PRE, NORMED>;                                                   \
+    if (xs_bytes > 48 * 1024) {                                                                                       \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)xs_bytes);       \
+      if (e != cudaSuccess) return (int)e;                                                                            \
+    }                                                                                                                 \
+    q3::launch(kern, dim3(grid), dim3(GS_WARPS * 32), xs_bytes, stream, (const __nv_bfloat16*)X,                     \
+               (const __nv_bfloat16*)W, (OutT*)out, T, N, K, ldo, fuse);                                              \
+  } while (0)
   // batches of a warp's share of K; up to three are fetched ahead where eight tokens leave the registers
   const int batches = ((K + 31) / 32 + wk * GS_UNROLL - 1) / (wk * GS_UNROLL);
   const int pre = NT == 1 && wk == GS_WARPS ? (batches < 3 ? batches : 3) : 1;
@@ -184,6 +322,7 @@ static int gemm_skinny_launch(const void* X, const void* W, void* out, int T, in
     else Q3_GS_GO(8, 3);
   }
 #undef Q3_GS_GO
+  if (EPI == 2) note_stream_written();
   return launch_status();
 }
 
@@ -208,4 +347,40 @@ extern "C" int q3_gemm_skinny(const void* X, const void* W, void* out, int T, in
   }
   if (T <= 8) return q3::gemm_skinny_launch<1, 0, bf16>(X, W, out, T, N, K, ldo, stream);
   return q3::gemm_skinny_launch<2, 0, bf16>(X, W, out, T, N, K, ldo, stream);
+}
+
+// The two forms that take the norm kernels out of a decode step (see the head of the file), T <= 16.
+// mode 0: out[T, N] bfloat16 = rs * (W (stream * norm_w)); mode 1: the same with W's rows alternating gate/up in
+// blocks of eight and out [T, N / 2] = up * silu(gate).  x is the float32 stream [T, K]; ss_in holds ss_parts
+// partial sums of squares per row ([ss_parts][16] floats) that add up to sum(stream[t]^2); rs = 1 / sqrt(sum / K + eps).
+// Modes 0 and 1 stage the rows in shared memory (16 (K + 32) bytes for up to 8 rows, twice that for 9 to 16)
+// and refuse a K for which that exceeds 160 KB.
+// mode 2: x is bfloat16 [T, K]; out is the float32 stream [T, N] and becomes out + x W^T; ss_out
+// ([ceil(N / 16)][16] floats) receives the partial sums of squares of the new rows.
+extern "C" int q3_gemm_skinny_fused(const void* x, const void* W, void* out, int T, int N, int K, int ldo, int mode,
+                                    const float* norm_w, const float* ss_in, int ss_parts, float eps, float* ss_out,
+                                    cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return 0;
+  if (T > 16 || K <= 0 || K % 8 || mode < 0 || mode > 2 || (mode == 1 && N % 16)) return Q3_ERR_SIZE;
+  if ((uintptr_t)x % 16 || (uintptr_t)W % 16 || (uintptr_t)out % 16) return Q3_ERR_ALIGN;
+  using bf16 = __nv_bfloat16;
+  q3::SkinnyFuse fuse{};
+  if (mode == 2) {
+    if (!ss_out) return Q3_ERR_SIZE;
+    fuse.ss_out = ss_out;
+    if (T <= 8) return q3::gemm_skinny_launch<1, 2, float>(x, W, out, T, N, K, ldo, stream, fuse);
+    return q3::gemm_skinny_launch<2, 2, float>(x, W, out, T, N, K, ldo, stream, fuse);
+  }
+  if (!norm_w || !ss_in || ss_parts <= 0 || (uintptr_t)norm_w % 16) return Q3_ERR_SIZE;
+  fuse.stream = (const float*)x;
+  fuse.norm_w = norm_w;
+  fuse.ss_in = ss_in;
+  fuse.ss_parts = ss_parts;
+  fuse.eps = eps;
+  if (mode == 1) {
+    if (T <= 8) return q3::gemm_skinny_launch<1, 1, bf16, true>(nullptr, W, out, T, N, K, ldo, stream, fuse);
+    return q3::gemm_skinny_launch<2, 1, bf16, true>(nullptr, W, out, T, N, K, ldo, stream, fuse);
+  }
+  if (T <= 8) return q3::gemm_skinny_launch<1, 0, bf16, true>(nullptr, W, out, T, N, K, ldo, stream, fuse);
+  return q3::gemm_skinny_launch<2, 0, bf16, true>(nullptr, W, out, T, N, K, ldo, stream, fuse);
 }

@@ -15,7 +15,7 @@ import torch
 from ..cache.manager import CacheLayout, layout_of
 from ..config.model_config import ModelConfig
 from ..kernels import ops
-from ..parts.base import ModelSpec, Runtime, StepContext
+from ..parts.base import STREAM_SUMSQ, ModelSpec, Runtime, StepContext
 from ..registry import build_model_spec, create_part, load_config
 from ..weights.loader import load_weights
 
@@ -93,7 +93,10 @@ class Model:
         stream = self.embedding.forward(ctx.token_ids)
         pending = None
         for call in self.spec.order:
-            pending = self.layers[call.layer].forward(stream, pending, ctx, call.cache, call.write_cache)
+            layer = self.layers[call.layer]
+            pending = layer.forward(stream, pending, ctx, call.cache, call.write_cache)
+            if not layer.keeps_stream_stats:
+                ctx.per_step.pop(STREAM_SUMSQ, None)  # whatever it did to the stream, the sums describe it no longer
         if ctx.logit_rows.numel() == 0:
             return torch.empty(0, self.spec.vocab_size, dtype=torch.float32, device=stream.device)
         wanted = self.final_norm.norm_rows(stream, pending, ctx.logit_rows)

@@ -73,6 +73,8 @@ _SIGNATURES = {
                        _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
                        _c_void_p, _c_int, _c_void_p, _c_void_p],
     "q3_gemm_skinny": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "q3_gemm_skinny_fused": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
+                             _c_int, _c_float, _c_void_p, _c_void_p],
     "q3_sample": [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ull, _c_int,
                   _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p],
 }
@@ -368,6 +370,64 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu_bloc
     code = library().q3_gemm_skinny(x.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, want_cols,
                                     1 if out.dtype == torch.float32 else 0, 1 if swiglu_blocks else 0, _stream())
     _done("gemm_skinny", code, f"T {T} N {N} K {K}")
+
+
+SUMSQ_ROWS = 16  # row pitch of the partial sums of squares that the fused few-rows products exchange
+
+
+def sumsq_parts(features: int) -> int:
+    """Partial sums per row that ``gemm_skinny_into_stream`` leaves for a stream ``features`` wide."""
+    return (features + 15) // 16
+
+
+def gemm_skinny_normed_takes(rows: int, weight: torch.Tensor) -> bool:
+    """The few-rows product that applies a norm itself stages the rows in shared memory: 16 (K + 32) bytes for
+    up to 8 rows, twice that for 9 to 16, at most 160 KB."""
+    return gemm_skinny_takes(rows, weight) and (1 if rows <= 8 else 2) * 16 * (weight.shape[1] + 32) <= 160 * 1024
+
+
+def gemm_skinny_normed(stream: torch.Tensor, norm_weight: torch.Tensor, sumsq: torch.Tensor, parts: int, eps: float,
+                       w: torch.Tensor, out: torch.Tensor, swiglu_blocks: bool = False) -> None:
+    """out = rmsnorm(stream) @ w^T for up to 16 rows without a norm kernel: the float32 stream is
+    multiplied by the norm weight on its way into the tensor core and the row's 1 / rms in the
+    epilogue, from ``parts`` partial sums of squares per row (``sumsq[p, t]``, as
+    ``gemm_skinny_into_stream`` leaves them).  ``swiglu_blocks`` as in ``gemm_skinny``."""
+    _check("gemm_skinny_normed.stream", stream, torch.float32)
+    _check("gemm_skinny_normed.norm_weight", norm_weight, torch.float32)
+    _check("gemm_skinny_normed.sumsq", sumsq, torch.float32)
+    _check("gemm_skinny_normed.w", w, torch.bfloat16)
+    _check("gemm_skinny_normed.out", out, torch.bfloat16)
+    T, K = stream.shape
+    N = w.shape[0]
+    want_cols = N // 2 if swiglu_blocks else N
+    if (w.shape[1] != K or tuple(out.shape) != (T, want_cols) or norm_weight.numel() != K or sumsq.dim() != 2
+            or sumsq.shape[1] != SUMSQ_ROWS or not 0 < parts <= sumsq.shape[0]):
+        raise KernelError(f"gemm_skinny_normed: stream {tuple(stream.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, "
+                          f"norm weight {tuple(norm_weight.shape)}, sums {tuple(sumsq.shape)} of which {parts}")
+    code = library().q3_gemm_skinny_fused(stream.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, want_cols,
+                                          1 if swiglu_blocks else 0, norm_weight.data_ptr(), sumsq.data_ptr(),
+                                          int(parts), float(eps), None, _stream())
+    _done("gemm_skinny_normed", code, f"T {T} N {N} K {K}")
+
+
+def gemm_skinny_into_stream(x: torch.Tensor, w: torch.Tensor, stream: torch.Tensor, sumsq: torch.Tensor) -> int:
+    """stream += x @ w^T for up to 16 rows (x, w bfloat16; stream float32), and ``sumsq[p, t]`` = the sum of
+    squares of the 16 new values ``stream[t, 16 p : 16 p + 16]``; returns the number of such parts."""
+    _check("gemm_skinny_into_stream.x", x, torch.bfloat16)
+    _check("gemm_skinny_into_stream.w", w, torch.bfloat16)
+    _check("gemm_skinny_into_stream.stream", stream, torch.float32)
+    _check("gemm_skinny_into_stream.sumsq", sumsq, torch.float32)
+    T, K = x.shape
+    N = w.shape[0]
+    parts = sumsq_parts(N)
+    if (w.shape[1] != K or tuple(stream.shape) != (T, N) or sumsq.dim() != 2 or sumsq.shape[1] != SUMSQ_ROWS
+            or sumsq.shape[0] < parts):
+        raise KernelError(f"gemm_skinny_into_stream: x {tuple(x.shape)}, w {tuple(w.shape)}, stream "
+                          f"{tuple(stream.shape)}, sums {tuple(sumsq.shape)}")
+    code = library().q3_gemm_skinny_fused(x.data_ptr(), w.data_ptr(), stream.data_ptr(), T, N, K, N, 2, None, None, 0,
+                                          0.0, sumsq.data_ptr(), _stream())
+    _done("gemm_skinny_into_stream", code, f"T {T} N {N} K {K}")
+    return parts
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, status: torch.Tensor,

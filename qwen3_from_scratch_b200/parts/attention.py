@@ -78,7 +78,14 @@ class GQAAttention(Mixer):
             self._partial = rt.shared("attn.partial", ops.decode_partial_numel(rt.max_seqs, self.num_heads,
                                                                                self.head_dim), dtype=torch.float32)
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
+    fuses_stream = True
+
+    def can_fuse_stream(self, rows: int) -> bool:
+        return self.qkv.takes_stream_norm(rows) and self.o_proj.can_add_into_stream(rows)
+
+    def forward(self, x, ctx: StepContext, cache_id: Optional[int], write_cache: bool, into_stream=None):
+        """``x``: the normed activations, or a ``StreamNorm`` that the QKV product applies itself.
+        ``into_stream``: the output projection adds into this stream and (sumsq, parts) is returned."""
         T = x.shape[0]
         hq, hkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         k_pages, v_pages, table = ctx.kv(cache_id)
@@ -108,6 +115,8 @@ class GQAAttention(Mixer):
                          hq, hkv, d, write_cache, self.rt.status)
         out = self._o[:T]
         self.attend(q, k_pages, v_pages, table, ctx, out)
+        if into_stream is not None:
+            return self.o_proj.into_stream(out.view(T, hq * d), into_stream)
         return self.o_proj(out.view(T, hq * d))
 
     def attend(self, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, table: torch.Tensor,

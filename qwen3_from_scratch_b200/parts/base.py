@@ -166,6 +166,34 @@ class StepContext:
         raise NotImplementedError
 
 
+# ---------------------------------------------------------------------- a norm that is not computed
+
+
+STREAM_SUMSQ = "stream.sumsq"  # key in StepContext.per_step: (sumsq, parts) of the stream as it stands
+
+
+@dataclass
+class StreamNorm:
+    """RMSNorm of the residual stream, not computed: a projection that takes it (``Linear``, for a few
+    rows) multiplies the float32 stream by ``weight`` on its way into the product and by each row's
+    1 / rms afterwards, so that no norm kernel runs.  ``sumsq[p, t]`` for ``p < parts`` are partial sums
+    of squares of row ``t`` of the stream, left by the projection that last added into it."""
+
+    stream: torch.Tensor
+    weight: torch.Tensor
+    eps: float
+    sumsq: torch.Tensor
+    parts: int
+
+    @property
+    def shape(self):
+        return self.stream.shape
+
+    @property
+    def dtype(self):
+        return torch.bfloat16
+
+
 # ---------------------------------------------------------------------- parts
 
 
@@ -222,14 +250,25 @@ class Mixer(Part):
     def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
         raise NotImplementedError
 
+    #: a mixer (or feed-forward) that sets this also has ``can_fuse_stream(rows)``; where that is true its
+    #: ``forward`` takes a ``StreamNorm`` for ``x`` and ``into_stream=stream``, adds its output into the
+    #: stream itself and returns ``(sumsq, parts)`` of the stream's new rows instead of the output
+    fuses_stream = False
+
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
+    fuses_stream = False  # see Mixer.fuses_stream
+
 
 class Block(Part):
     mixer: Mixer
+
+    #: a block that sets this leaves ``ctx.per_step[STREAM_SUMSQ]`` describing the stream as it returns it
+    #: (and returns no pending output); after any other block the model drops the entry
+    keeps_stream_stats = False
 
     def forward(self, stream: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
                 cache_id: Optional[int], write_cache: bool) -> Optional[torch.Tensor]:

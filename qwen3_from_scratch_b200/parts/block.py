@@ -12,7 +12,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..registry import create_part, register_part
-from .base import Block, PartSpec, Runtime, StepContext, WeightSpec
+from .base import STREAM_SUMSQ, Block, PartSpec, Runtime, StepContext, WeightSpec
 
 
 @register_part("block", "pre_norm")
@@ -40,8 +40,27 @@ class PreNormBlock(Block):
         for part in (self.norm1, self.mixer, self.norm2, self.feed_forward):
             part.setup(rt, weights)
 
+    keeps_stream_stats = True
+
+    def fuses(self, rows: int) -> bool:
+        """A few rows (decoding) in bfloat16: the mixer's and the feed-forward's last projections add into
+        the stream themselves and their first ones apply the norm, so that no norm kernel runs."""
+        return (self.rt.dtype == torch.bfloat16 and hasattr(self.norm1, "lazy") and hasattr(self.norm2, "lazy")
+                and getattr(self.mixer, "fuses_stream", False) and getattr(self.feed_forward, "fuses_stream", False)
+                and self.mixer.can_fuse_stream(rows) and self.feed_forward.can_fuse_stream(rows))
+
     def forward(self, stream: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
-                cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
+                cache_id: Optional[int], write_cache: bool) -> Optional[torch.Tensor]:
+        shared = ctx.__dict__.setdefault("per_step", {})
+        stats = shared.pop(STREAM_SUMSQ, None)  # of the stream as the block before left it
+        if self.fuses(stream.shape[0]):
+            if stats is None or pending is not None:
+                x = self.norm1.add_norm(stream, pending)
+            else:
+                x = self.norm1.lazy(stream, stats)
+            stats = self.mixer.forward(x, ctx, cache_id, write_cache, into_stream=stream)
+            shared[STREAM_SUMSQ] = self.feed_forward.forward(self.norm2.lazy(stream, stats), into_stream=stream)
+            return None
         x = self.norm1.add_norm(stream, pending)
         a = self.mixer.forward(x, ctx, cache_id, write_cache)
         x = self.norm2.add_norm(stream, a)

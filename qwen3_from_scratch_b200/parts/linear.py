@@ -15,7 +15,7 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
-from .base import Runtime
+from .base import Runtime, StreamNorm
 
 
 class Linear:
@@ -42,6 +42,11 @@ class Linear:
             if self.full_precision:
                 self._out32 = self._out if self.out_dtype == torch.float32 else make("out32", torch.float32)
         self._weight_t = self.weight.t()
+        self._sumsq = None
+        if not self.full_precision and rt.dtype == torch.bfloat16:
+            parts = ops.sumsq_parts(self.out_features)
+            self._sumsq = (rt.shared(f"{tag}.sumsq", parts, ops.SUMSQ_ROWS, dtype=torch.float32) if tag
+                           else rt.empty(parts, ops.SUMSQ_ROWS, dtype=torch.float32))
 
     def _buffer(self, which: str, rows: int, dtype: torch.dtype) -> torch.Tensor:
         buf = getattr(self, which)
@@ -49,8 +54,27 @@ class Linear:
             return torch.empty(rows, self.out_features, dtype=dtype, device=self.weight.device)
         return buf[:rows]
 
-    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+    def takes_stream_norm(self, rows: int) -> bool:
+        """Whether ``self(StreamNorm)`` works for this many rows (a bfloat16 weight, a few rows)."""
+        return (not self.full_precision and self.out_dtype == torch.bfloat16 and self._out is not None
+                and ops.gemm_skinny_normed_takes(rows, self.weight))
+
+    def can_add_into_stream(self, rows: int) -> bool:
+        return self._sumsq is not None and ops.gemm_skinny_takes(rows, self.weight)
+
+    def into_stream(self, x: torch.Tensor, stream: torch.Tensor):
+        """stream += x W^T for a few rows; returns (sumsq, parts) of the stream's new rows (see StreamNorm)."""
+        parts = ops.gemm_skinny_into_stream(x, self.weight, stream, self._sumsq)
+        return self._sumsq, parts
+
+    def __call__(self, x) -> torch.Tensor:
         rows = x.shape[0]
+        if isinstance(x, StreamNorm):
+            if not self.takes_stream_norm(rows):
+                raise ValueError("this projection does not take a norm that is not computed (see takes_stream_norm)")
+            out = self._buffer("_out", rows, self.out_dtype)
+            ops.gemm_skinny_normed(x.stream, x.weight, x.sumsq, x.parts, x.eps, self.weight, out)
+            return out
         if self.max_rows is not None and rows > self.max_rows:
             raise ValueError(f"{rows} rows exceed the {self.max_rows} this projection was sized for")
         if self.full_precision:

@@ -12,7 +12,7 @@ import torch
 
 from ..kernels import ops
 from ..registry import register_part
-from .base import FeedForward, Runtime, WeightSpec
+from .base import FeedForward, Runtime, StreamNorm, WeightSpec
 from .linear import Linear
 
 
@@ -48,10 +48,19 @@ class SwiGLU(FeedForward):
         self.down = Linear(weights.pop(f"{self.name}.down_proj.weight"), rt, tag="ffn.down")
         self._act = rt.shared("ffn.act", rt.max_tokens, self.intermediate_size)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    fuses_stream = True
+
+    def can_fuse_stream(self, rows: int) -> bool:
+        return (self.blocks_of_eight and self.gate_up.takes_stream_norm(rows) and self.down.can_add_into_stream(rows))
+
+    def forward(self, x, into_stream=None):
         act = self._act[: x.shape[0]]
         rows = x.shape[0]
-        if self.blocks_of_eight and ops.gemm_skinny_takes(rows, self.gate_up.weight):
+        if isinstance(x, StreamNorm):
+            # decoding without norm kernels: the norm is applied inside the gate/up product
+            ops.gemm_skinny_normed(x.stream, x.weight, x.sumsq, x.parts, x.eps, self.gate_up.weight, act,
+                                   swiglu_blocks=True)
+        elif self.blocks_of_eight and ops.gemm_skinny_takes(rows, self.gate_up.weight):
             # decoding: stream the weight once, activation applied before the store
             ops.gemm_skinny(x, self.gate_up.weight, act, swiglu_blocks=True)
         elif (self.blocks_of_eight and ops.gemm_tc_swiglu_pays(rows, self.gate_up.weight)
@@ -61,4 +70,6 @@ class SwiGLU(FeedForward):
             ops.gemm_tc(x, self.gate_up.weight, act, self.rt.status, swiglu_blocks=True)
         else:
             ops.swiglu(self.gate_up(x), act, interleave8=self.blocks_of_eight)
+        if into_stream is not None:
+            return self.down.into_stream(act, into_stream)
         return self.down(act)

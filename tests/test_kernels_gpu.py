@@ -213,6 +213,74 @@ def test_gemm_skinny_with_swiglu(shape):
     close(out2, want, "bfloat16", scale=float(want.abs().max()) * 2)
 
 
+@pytest.mark.parametrize("shape", [(1, 4096, 1024), (8, 1024, 2048), (16, 331, 96), (3, 70, 200), (9, 48, 8), (7, 1024, 3072),
+                                   (5, 64, 5000)])
+def test_gemm_skinny_into_stream(shape):
+    """stream += x W^T in place, with partial sums of squares of the new rows that add up to the rows' own."""
+    T, N, K = shape
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
+    stream = torch.randn(T, N, generator=g) * 3
+    s = dev(stream.clone())
+    parts = ops().sumsq_parts(N)
+    sums = torch.full((parts + 1, ops().SUMSQ_ROWS), float("nan"), device="cuda")
+    for _ in range(2):  # the second call runs right after a launch that wrote a stream
+        s.copy_(dev(stream))
+        assert ops().gemm_skinny_into_stream(dev(x), dev(w), s, sums) == parts
+    want = stream.double() + x.double() @ w.double().t()
+    close(s, want, "float32", scale=float(want.abs().max()), tol=f32_accumulation_tol(K))
+    got = sums[:parts, :T].double().sum(0).cpu()
+    assert torch.allclose(got, (s.cpu().double() ** 2).sum(1), rtol=1e-5)
+    assert torch.isnan(sums[parts]).all()
+
+
+@pytest.mark.parametrize("shape", [(1, 4096, 1024), (8, 6144, 1024), (16, 331, 96), (3, 70, 200), (9, 48, 8), (6, 64, 5000),
+                                   (12, 2048, 4096)])
+@pytest.mark.parametrize("with_swiglu", [False, True])
+def test_gemm_skinny_normed(shape, with_swiglu):
+    """rmsnorm(stream) W^T without a norm kernel: the stream times the norm weight goes into the product and
+    1 / rms is applied after it, from partial sums of squares as gemm_skinny_into_stream leaves them."""
+    T, N, K = shape
+    if with_swiglu:
+        N = N // 16 * 16
+    g = torch.Generator().manual_seed(32)
+    eps = 1e-5
+    stream = torch.randn(T, K, generator=g) * 4
+    nw = 1 + 0.2 * torch.randn(K, generator=g)
+    w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
+    # partial sums the way the producer lays them out: one per 16 columns of the stream, row pitch 16
+    parts = ops().sumsq_parts(K)
+    sq = torch.zeros(parts, ops().SUMSQ_ROWS)
+    padded = torch.zeros(T, parts * 16)
+    padded[:, :K] = stream
+    sq[:, :T] = (padded.view(T, parts, 16) ** 2).sum(2).t()
+    out = torch.full((T, N // 2 if with_swiglu else N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops().gemm_skinny_normed(dev(stream), dev(nw), dev(sq), parts, eps, dev(w), out, swiglu_blocks=with_swiglu)
+    # what the kernel is specified to compute: the stream times the norm weight rounded once to bfloat16, the
+    # product, then 1 / rms; against the plain norm followed by the product it differs by where that one rounding falls
+    rounded = (stream * nw).to(torch.bfloat16).double()
+    rs = 1.0 / torch.sqrt((stream.double() ** 2).mean(1, keepdim=True) + eps)
+    want = (rounded @ w.double().t()) * rs
+    loose = plain.rms_norm(stream.double(), nw.double(), eps) @ w.double().t()
+    assert float((want - loose).abs().max()) <= 4e-3 * float(loose.abs().max())
+    if with_swiglu:
+        gate = want.view(T, N // 16, 2, 8)[:, :, 0].reshape(T, N // 2)
+        up = want.view(T, N // 16, 2, 8)[:, :, 1].reshape(T, N // 2)
+        want = up * gate * torch.sigmoid(gate)
+    close(out, want, "bfloat16")
+
+
+def test_gemm_skinny_normed_refuses_rows_too_wide_to_stage():
+    w = torch.zeros(16, 8192, device="cuda", dtype=torch.bfloat16)
+    assert ops().gemm_skinny_normed_takes(8, w) and not ops().gemm_skinny_normed_takes(9, w)
+    stream = torch.zeros(9, 8192, device="cuda")
+    sq = torch.zeros(ops().sumsq_parts(8192), ops().SUMSQ_ROWS, device="cuda")
+    out = torch.empty(9, 16, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(ops().KernelSizeError):
+        ops().gemm_skinny_normed(stream, torch.ones(8192, device="cuda"), sq, sq.shape[0], 1e-6, w, out)
+
+
 @pytest.mark.parametrize("shape", [(128, 128, 64), (2048, 4096, 1024), (100, 200, 72), (257, 331, 96), (1, 64, 8),
                                    (300, 1024, 3072)])
 @pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])

@@ -197,6 +197,63 @@ def test_block_part(dtype):
     close(stream + pending.float(), want, dtype)
 
 
+def test_block_part_few_rows_run_without_norm_kernels(monkeypatch):
+    """Up to 16 rows in bfloat16: the block's output projections add into the stream themselves and its
+    input projections apply the norms, from partial sums of squares passed from one to the next (and from
+    one block to the next through the step's shared data).  Two calls of the block on caches of their own,
+    as two layers with the same weights would be, against the plain layer applied twice; one norm kernel in
+    all (the first call has no sums yet); and the same block made to take the path with norm kernels."""
+    from qwen3_from_scratch_b200.cache import CacheManager, layout_of
+    from qwen3_from_scratch_b200.cache.storage import CacheStorage
+    from qwen3_from_scratch_b200.engine.batch import BatchContext, Entry
+    from qwen3_from_scratch_b200.kernels import ops
+    from qwen3_from_scratch_b200.parts.base import STREAM_SUMSQ, PartSpec
+    from qwen3_from_scratch_b200.registry import create_part
+    dtype = "bfloat16"
+    H, hq, hkv, d, inter, eps, theta = 80, 4, 2, 32, 104, 1e-5, 10000.0
+    norm = PartSpec("rms_norm", {"dim": H, "eps": eps})
+    block = create_part("block", PartSpec("pre_norm", {
+        "norm1": norm, "norm2": norm,
+        "mixer": PartSpec("gqa_attention", {
+            "hidden_size": H, "num_heads": hq, "num_kv_heads": hkv, "head_dim": d, "qk_norm_eps": eps,
+            "position": PartSpec("rotary_neox", {"head_dim": d, "theta": theta, "max_positions": 512})}),
+        "feed_forward": PartSpec("swiglu", {"hidden_size": H, "intermediate_size": inter}),
+        "names": {"norm1": "input_layernorm", "mixer": "self_attn", "norm2": "post_attention_layernorm",
+                  "feed_forward": "mlp"}}), name="model.layers.0")
+    dev, ref = random_weights(block, dtype)
+    rt = runtime(dtype)
+    block.setup(rt, dev)
+    n = 7
+    x = torch.randn(n, H, generator=torch.Generator().manual_seed(16))
+    cfg = {"head_dim": d, "rms_norm_eps": eps, "rope_theta": theta}
+    once = plain.decoder_layer(x.double(), ref, 0, cfg, torch.arange(n), None)
+    want = plain.decoder_layer(once, ref, 0, cfg, torch.arange(n), None)
+    layout = layout_of({0: block.mixer.cache_spec(), 1: block.mixer.cache_spec()})
+    norm_kernels = []
+    real = ops.add_rmsnorm
+    monkeypatch.setattr(ops, "add_rmsnorm", lambda *a, **k: (norm_kernels.append(1), real(*a, **k))[1])
+    results = []
+    for fused in (True, False):
+        if not fused:
+            monkeypatch.setattr(type(block), "fuses", lambda self, rows: False)
+        manager = CacheManager(layout, 4, 64, rt.max_seqs)
+        storage = CacheStorage(layout, 4, rt.max_seqs, rt.device, rt.dtype)
+        manager.open("r")
+        manager.reserve("r", n)
+        ctx = BatchContext(manager, storage, rt).build([Entry("r", [0] * n)], vocab_size=1)
+        ctx.per_step = {}
+        stream = x.cuda().clone()
+        del norm_kernels[:]
+        assert block.fuses(n) == fused
+        pending = block.forward(stream, None, ctx, 0, True)
+        assert (pending is None and STREAM_SUMSQ in ctx.per_step) if fused else pending is not None
+        pending = block.forward(stream, pending, ctx, 1, True)
+        assert len(norm_kernels) == (1 if fused else 4)
+        results.append(stream.clone() if fused else stream + pending.float())
+        close(results[-1], want, dtype)
+    assert int(rt.status.item()) == 0
+
+
 # ---------------------------------------------------------------------- a toy mixer with state
 def register_toy():
     """Registers, from the test, a mixer that keeps a decayed running sum per request in a state
