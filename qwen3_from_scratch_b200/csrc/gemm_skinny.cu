@@ -50,10 +50,11 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
 }
 
 // NT: token tiles of 8 (1 or 2).  WK: warps that share a group of 16 features and split K.
-// EPI: 0 store, 1 SwiGLU on alternating blocks of eight rows.
-// (With two token tiles the kernel is asked to fit three blocks per SM: left to itself the compiler used
-// fewer registers than that allows and took the loads one after the other: 10.0 us per product at 16 rows
-// against 6.7 us, the output head 86 us against 72.)
+// EPI: 0 store, 1 SwiGLU on alternating blocks of eight rows, 2 added into the float32 stream.
+// (The kernel is asked to fit three blocks per SM where K is not split in the block, which is the long
+// stream of the output head (at 88 registers, two blocks per SM, the head ran 58 us against 50), and with two
+// token tiles: there, left to itself, the compiler used fewer registers than three blocks allow and took
+// the loads one after the other: 10.0 us per product at 16 rows against 6.7 us, the head 86 us against 72.)
 // PRE: batches of GS_UNROLL groups whose weights are fetched before the wait on the kernel before.  A
 // product with few output features (o_proj, down_proj: 64 groups of 16, one block each) gives a warp two or
 // three batches; with all of them under way before the wait, what is left after it is one round trip for
@@ -74,7 +75,7 @@ constexpr int GS_XS_MAX_BYTES = 160 * 1024;
 
 // EPI 2: out is the float32 stream [T, N] and is added to.  NORMED: see the head of the file.
 template <int NT, int WK, int EPI, typename OutT, int PRE = 1, bool NORMED = false>
-__global__ void __launch_bounds__(GS_WARPS * 32, (NT == 1 && !(NORMED && PRE == 1)) ? 1 : 3)
+__global__ void __launch_bounds__(GS_WARPS * 32, (NT == 1 && WK > 1 && !(NORMED && PRE == 1)) ? 1 : 3)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
                    OutT* __restrict__ out, int T, int N, int K, int ldo, const SkinnyFuse fuse) {
   constexpr int GROUPS = GS_WARPS / WK;  // feature groups per block
