@@ -39,6 +39,66 @@ __device__ __forceinline__ const unsigned char* sw_chunk(const unsigned char* ti
   return tile + (chunk >> 3) * 2048 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
 }
 
+// Eight values of a head (chunk c of its CPR chunks; the head's chunks are in CPR neighbouring lanes):
+// x / sqrt(mean(x^2) + eps) * w if w is given, then y_i = x_i cos_i - x_(i + D/2) sin_i and
+// y_(i + D/2) = x_(i + D/2) cos_i + x_i sin_i if the token's cosines and sines are given.  float32 throughout,
+// one rounding to bfloat16 at the end, as in qkv_post.
+template <int CPR>
+__device__ __forceinline__ uint4 norm_rotate_chunk(uint4 raw, int c, const float* __restrict__ w,
+                                                   const float* __restrict__ cos_sin, float eps) {
+  constexpr int D = CPR * 8, HALF = CPR / 2;
+  float x[8];
+  const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    x[2 * k] = __uint_as_float(rw[k] << 16);
+    x[2 * k + 1] = __uint_as_float(rw[k] & 0xffff0000u);
+  }
+  if (w != nullptr) {
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ss += x[k] * x[k];
+#pragma unroll
+    for (int o = CPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rs = 1.0f / sqrtf(ss / (float)D + eps);
+    const float4 w0 = *reinterpret_cast<const float4*>(w + c * 8), w1 = *reinterpret_cast<const float4*>(w + c * 8 + 4);
+    const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) x[k] = x[k] * rs * wv[k];
+  }
+  if (cos_sin != nullptr) {
+    const float* row = cos_sin + (c % HALF) * 8;
+    const float4 c0 = *reinterpret_cast<const float4*>(row), c1 = *reinterpret_cast<const float4*>(row + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(row + D / 2), s1 = *reinterpret_cast<const float4*>(row + D / 2 + 4);
+    const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    const float sign = c < HALF ? -1.0f : 1.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float partner = __shfl_xor_sync(0xffffffffu, x[k], HALF);
+      x[k] = fmaf(partner, sign * sv[k], x[k] * cv[k]);
+    }
+  }
+  return make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
+}
+
+// With `qkv` set the kernel does the work of qkv_post for its own token too (a step in which every row
+// decodes): the query rows are normed and rotated from the raw projection as they are loaded, and the block
+// whose range holds the sequence's last position norms and rotates the new key, copies the new value, writes
+// both to their page and puts them into its own tile of shared memory, which the loader fetched without them.
+// (Head norm: models/self_attn.py:388-401 of the reference; rotation of pairs (i, i + D / 2): models/rope.py.)
+struct DecodeQkv {
+  const __nv_bfloat16* qkv;  // [T, (Hq + 2 Hkv) * D] rows ordered q heads, k heads, v heads; null: q and the pages are ready
+  const float* q_weight;     // [D] or null
+  const float* k_weight;     // [D] or null
+  const float* cos_sin;      // [T, D]: cosines then sines of the token's D / 2 angles, or null (no rotation)
+  float eps;
+  __nv_bfloat16* k_pages;    // the pools, for the new row
+  __nv_bfloat16* v_pages;
+  int write_kv;              // 0: another layer wrote this cache; only the query is made
+  int angles_early;          // cos_sin is older than the launch before this one
+};
+
 template <int D>
 __global__ void __launch_bounds__(DT_THREADS, 2)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -46,7 +106,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        float* __restrict__ partial, const int* __restrict__ q_start,
                        const int* __restrict__ kv_len, const int* __restrict__ block_table, int table_stride,
                        int page_size, int num_pages, int Hq, int Hkv, float scale_log2, int window,
-                       int num_splits, int* status) {
+                       int num_splits, int* status, const DecodeQkv fq) {
   using S = DecodeTmaShape<D>;
   constexpr int KT = D / 16, CPR = D / 8, PITCH = S::Q_PITCH;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -96,12 +156,27 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   // one (which writes this step's key, value and query) may still be running.  Only the tile that
   // holds the sequence's last position, and the query, wait for that kernel.
   if (warp != DT_CONSUMERS) {
+    if (fq.qkv != nullptr) {
+      // the norm weights, which no kernel writes, and the token's cosines and sines, if the launch before this
+      // one did not write them, are asked into L1 ahead of the wait (D floats each: D / 32 lines of 128 bytes)
+      constexpr int LINES = D / 32;
+      const int which = threadIdx.x / LINES, line = threadIdx.x % LINES;
+      const float* base = which == 0 ? fq.q_weight : which == 1 ? fq.k_weight
+                          : (which == 2 && fq.angles_early && fq.cos_sin) ? fq.cos_sin + (size_t)tq * D : nullptr;
+      if (base != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(base + line * 32));
+    }
     pdl_wait();
     pdl_launch_dependents();
     for (int e = threadIdx.x; e < 16 * CPR; e += DT_CONSUMERS * 32) {
-      const int row = e / CPR, c = e % CPR;
+      const int row = e / CPR, c = e % CPR;  // a row's CPR chunks of eight values sit in neighbouring lanes
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (row < g) v = *reinterpret_cast<const uint4*>(q + ((size_t)tq * Hq + hk * g + row) * D + c * 8);
+      if (fq.qkv == nullptr) {
+        if (row < g) v = *reinterpret_cast<const uint4*>(q + ((size_t)tq * Hq + hk * g + row) * D + c * 8);
+      } else {
+        // the raw projection's head hk * g + row: head norm, then rotation (every lane takes part in the shuffles)
+        if (row < g) v = *reinterpret_cast<const uint4*>(fq.qkv + ((size_t)tq * (Hq + 2 * Hkv) + hk * g + row) * D + c * 8);
+        v = norm_rotate_chunk<CPR>(v, c, fq.q_weight, fq.cos_sin ? fq.cos_sin + (size_t)tq * D : nullptr, fq.eps);
+      }
       *reinterpret_cast<uint4*>(q_s + row * PITCH + c * 8) = v;
     }
     asm volatile("bar.sync 1, %0;" ::"n"(DT_CONSUMERS * 32) : "memory");
@@ -174,6 +249,66 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       unsigned char* v_t = ring + (size_t)s * S::STAGE_BYTES + S::TILE_BYTES;
       const int base_n = (t_lo + i) * DT_KEYS;
       const bool edge = base_n < lo || base_n + DT_KEYS - 1 > pos;
+      if (fq.qkv != nullptr && fq.write_kv && t_lo + i == pos / DT_KEYS) {
+        // this step's key and value: made here from the raw projection, written to their page for the steps
+        // to come and into this tile, which was fetched without them.  A lane holds D / 32 neighbouring values.
+        constexpr int VPL = D / 32;
+        const int r = pos - base_n, first = VPL * lane;
+        const __nv_bfloat16* k_raw = fq.qkv + ((size_t)tq * (Hq + 2 * Hkv) + Hq + hk) * D + first;
+        const __nv_bfloat16* v_raw = k_raw + (size_t)Hkv * D;
+        __nv_bfloat16 kn[VPL], vn[VPL];
+        float x[VPL];
+#pragma unroll
+        for (int k = 0; k < VPL; ++k) {
+          x[k] = __bfloat162float(k_raw[k]);
+          vn[k] = v_raw[k];
+        }
+        if (fq.k_weight != nullptr) {
+          float ss = 0.f;
+#pragma unroll
+          for (int k = 0; k < VPL; ++k) ss += x[k] * x[k];
+          ss = warp_sum(ss);
+          const float rs = 1.0f / sqrtf(ss / (float)D + fq.eps);
+#pragma unroll
+          for (int k = 0; k < VPL; ++k) x[k] = x[k] * rs * fq.k_weight[first + k];
+        }
+        if (fq.cos_sin != nullptr) {
+          const float* cs = fq.cos_sin + (size_t)tq * D + (first % (D / 2));
+          const float sign = lane < 16 ? -1.0f : 1.0f;
+#pragma unroll
+          for (int k = 0; k < VPL; ++k) {
+            const float partner = __shfl_xor_sync(0xffffffffu, x[k], 16);
+            x[k] = fmaf(partner, sign * cs[D / 2 + k], x[k] * cs[k]);
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < VPL; ++k) kn[k] = __float2bfloat16_rn(x[k]);
+        const int chunk = first >> 3;
+        const size_t in_tile = (size_t)(chunk >> 3) * 2048 + r * 128 + (((chunk & 7) ^ (r & 7)) << 4) + (first & 7) * 2;
+        const int page = table[pos / page_size];
+        const bool page_ok = page >= 0 && page < num_pages;
+        if (!page_ok && lane == 0) atomicOr(status, Q3_STATUS_BAD_PAGE);
+        const size_t in_pool = (((size_t)(page_ok ? page : 0) * Hkv + hk) * page_size + pos % page_size) * D + first;
+        if (VPL == 4) {
+          const uint2 kp = *reinterpret_cast<const uint2*>(kn), vp = *reinterpret_cast<const uint2*>(vn);
+          *reinterpret_cast<uint2*>(const_cast<unsigned char*>(k_t) + in_tile) = kp;
+          *reinterpret_cast<uint2*>(v_t + in_tile) = vp;
+          if (page_ok) {
+            *reinterpret_cast<uint2*>(fq.k_pages + in_pool) = kp;
+            *reinterpret_cast<uint2*>(fq.v_pages + in_pool) = vp;
+          }
+        } else {
+          const uint32_t kp = *reinterpret_cast<const uint32_t*>(kn), vp = *reinterpret_cast<const uint32_t*>(vn);
+          *reinterpret_cast<uint32_t*>(const_cast<unsigned char*>(k_t) + in_tile) = kp;
+          *reinterpret_cast<uint32_t*>(v_t + in_tile) = vp;
+          if (page_ok) {
+            *reinterpret_cast<uint32_t*>(fq.k_pages + in_pool) = kp;
+            *reinterpret_cast<uint32_t*>(fq.v_pages + in_pool) = vp;
+          }
+        }
+        fence_async_proxy();
+        __syncwarp();
+      }
       if (base_n + DT_KEYS - 1 > pos) {
         // the page's slots past the sequence hold whatever was there: zero those value rows
         const int first_bad = pos - base_n + 1;
@@ -314,7 +449,7 @@ template <int D>
 static int attn_decode_tma_launch(const void* q, const void* k_pages, const void* v_pages, void* out, float* partial,
                                   const int* q_start, const int* kv_len, const int* block_table, int table_stride,
                                   int page_size, int num_pages, int B, int Hq, int Hkv, float scale, int window,
-                                  int num_splits, int* status, cudaStream_t stream) {
+                                  int num_splits, int* status, cudaStream_t stream, DecodeQkv fq = DecodeQkv{}) {
   using S = DecodeTmaShape<D>;
   static bool configured = false;
   if (!configured) {
@@ -332,7 +467,7 @@ static int attn_decode_tma_launch(const void* q, const void* k_pages, const void
   dim3 grid(num_splits, Hkv, B);
   q3::launch(attn_decode_tma_kernel<D>, grid, dim3(DT_THREADS), S::SMEM_BYTES, stream, map_k, map_v,
              (const __nv_bfloat16*)q, (__nv_bfloat16*)out, partial, q_start, kv_len, block_table, table_stride,
-             page_size, num_pages, Hq, Hkv, scale * 1.4426950408889634f, window, num_splits, status);
+             page_size, num_pages, Hq, Hkv, scale * 1.4426950408889634f, window, num_splits, status, fq);
   code = launch_status();
   if (code != 0 || num_splits == 1) return code;
   return q3_attn_combine(partial, out, q_start, B, Hq, D, num_splits, stream);
@@ -358,4 +493,39 @@ extern "C" int q3_attn_decode_tma(const void* q, const void* k_pages, const void
   return q3::attn_decode_tma_launch<128>(q, k_pages, v_pages, out, partial, q_start, kv_len, block_table,
                                          table_stride, page_size, num_pages, B, Hq, Hkv, scale, window, num_splits,
                                          status, stream);
+}
+
+// The same with the work of q3_qkv_post for a step in which every row brings one token (see DecodeQkv):
+// qkv [T, (Hq + 2 Hkv) * D] bfloat16 is the raw projection (token of sequence b: row q_start[b]), q_weight and
+// k_weight float32 [D] or null, cos_sin float32 [T, D] from q3_rope_table or null; the new key and value go to
+// k_pages / v_pages unless write_kv is 0.  No q is read.
+extern "C" int q3_attn_decode_tma_qkv(const void* qkv, const float* q_weight, const float* k_weight, float eps,
+                                      const float* cos_sin, int write_kv, void* k_pages, void* v_pages, void* out,
+                                      float* partial, const int* q_start, const int* kv_len, const int* block_table,
+                                      int table_stride, int page_size, int num_pages, int B, int Hq, int Hkv, int D,
+                                      float scale, int window, int num_splits, int* status, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (Hkv <= 0 || Hq % Hkv || Hq / Hkv > 16 || (D != 64 && D != 128) || page_size <= 0 || page_size % 16 ||
+      num_splits < 1 || table_stride <= 0 || B > 65535 || Hkv > 65535 || !qkv)
+    return Q3_ERR_SIZE;
+  if ((uintptr_t)qkv % 16 || (uintptr_t)k_pages % 16 || (uintptr_t)v_pages % 16 || (uintptr_t)q_weight % 16 ||
+      (uintptr_t)k_weight % 16 || (uintptr_t)cos_sin % 16)
+    return Q3_ERR_ALIGN;
+  q3::DecodeQkv fq{};
+  fq.qkv = (const __nv_bfloat16*)qkv;
+  fq.q_weight = q_weight;
+  fq.k_weight = k_weight;
+  fq.cos_sin = cos_sin;
+  fq.eps = eps;
+  fq.k_pages = (__nv_bfloat16*)k_pages;
+  fq.v_pages = (__nv_bfloat16*)v_pages;
+  fq.write_kv = write_kv;
+  fq.angles_early = q3::last_launch_was_plain(stream) ? 1 : 0;
+  if (D == 64)
+    return q3::attn_decode_tma_launch<64>(nullptr, k_pages, v_pages, out, partial, q_start, kv_len, block_table,
+                                          table_stride, page_size, num_pages, B, Hq, Hkv, scale, window, num_splits,
+                                          status, stream, fq);
+  return q3::attn_decode_tma_launch<128>(nullptr, k_pages, v_pages, out, partial, q_start, kv_len, block_table,
+                                         table_stride, page_size, num_pages, B, Hq, Hkv, scale, window, num_splits,
+                                         status, stream, fq);
 }

@@ -102,16 +102,17 @@ static inline bool pdl_enabled() {
   return enabled == 1;
 }
 
-// The stream of this library's most recent launch if that launch did not write a residual stream,
-// else (or before any launch) all ones.  One word, so that a reader never sees half of an update.
+// The stream of this library's most recent launch if that launch wrote nothing that a later kernel
+// reads ahead of its wait (a residual stream, the step's table of angles), else (or before any
+// launch) all ones.  One word, so that a reader never sees half of an update.
 extern std::atomic<uintptr_t> g_plain_launch_stream;
 constexpr uintptr_t NO_PLAIN_LAUNCH = ~(uintptr_t)0;
 
-// True if the most recent launch of this library went to `stream` and wrote no residual stream.
+// True if the most recent launch of this library went to `stream` and wrote no such data.
 static inline bool last_launch_was_plain(cudaStream_t stream) {
   return g_plain_launch_stream.load(std::memory_order_relaxed) == (uintptr_t)stream;
 }
-// To be called right after launching a kernel that writes a residual stream.
+// To be called right after launching a kernel that writes such data.
 static inline void note_stream_written() { g_plain_launch_stream.store(NO_PLAIN_LAUNCH, std::memory_order_relaxed); }
 
 template <typename... KArgs, typename... Args>

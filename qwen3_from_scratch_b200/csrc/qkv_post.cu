@@ -320,5 +320,6 @@ extern "C" int q3_rope_table(const float* inv_freq, const int* positions, float*
   if (n > 0x7fffffffLL) return Q3_ERR_SIZE;
   q3::launch(q3::rope_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, inv_freq, positions, table,
              T, half);
+  q3::note_stream_written();  // what it writes must not be read ahead of the wait by the launch after it
   return q3::launch_status();
 }

@@ -61,6 +61,9 @@ _SIGNATURES = {
     "q3_attn_decode_tma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
                            _c_void_p, _c_void_p],
+    "q3_attn_decode_tma_qkv": [_c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                               _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                               _c_int, _c_float, _c_int, _c_int, _c_void_p, _c_void_p],
     "q3_attn_prefill": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
                         _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p,
                         _c_void_p],
@@ -595,6 +598,15 @@ def decode_tma_takes(head_dim: int, page_size: int) -> bool:
     return head_dim in (64, 128) and page_size % 16 == 0
 
 
+def decode_takes_raw_qkv(dtype: torch.dtype, num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
+                         num_tokens: int, num_seqs: int, num_decode: int) -> bool:
+    """Whether the decode attention kernel can do the work of ``qkv_post`` itself: every row of the step
+    brings one token and the kernel with the TMA loader takes the shape."""
+    return (num_tokens == num_seqs == num_decode and num_decode > 0
+            and fast_attention_takes(dtype, num_q_heads, num_kv_heads, head_dim)
+            and decode_tma_takes(head_dim, page_size))
+
+
 def decode_splits(num_seqs: int, num_kv_heads: int, max_kv_len: int, window: int, head_dim: int = 128,
                   blocks_per_sm: Optional[int] = None) -> int:
     """How many ranges a sequence's keys are cut into.  Blocks run in waves of (SMs x blocks per
@@ -636,8 +648,11 @@ def _attn_common(name, q, k_pages, v_pages, out, q_start, kv_len, block_table):
 def attn_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                 partial: Optional[torch.Tensor], q_start: torch.Tensor, kv_len: torch.Tensor,
                 block_table: torch.Tensor, num_seqs: int, scale: float, window: int, num_splits: int,
-                status: torch.Tensor, loader: str = "cp_async") -> None:
+                status: torch.Tensor, loader: str = "cp_async", raw_qkv=None) -> None:
     """Split-KV tensor-core attention for the first ``num_seqs`` rows, one query token each.
+    ``raw_qkv = (qkv, q_weight, k_weight, eps, cos_sin, write_kv)`` (TMA loader only): ``q`` only gives the
+    shape; the kernel norms and rotates the query from the raw projection ``qkv[T, (Hq + 2 Hkv) D]`` itself
+    and makes, stores and uses the new key and value (the work of ``qkv_post`` for these tokens).
     ``loader``: ``"cp_async"`` (every warp copies its own tiles) or ``"tma"`` (a loader warp feeds a
     ring of stages through TMA; head size 64 / 128 and pages that are multiples of 16 only)."""
     T, Hq, D, num_pages, Hkv, page_size = _attn_common("attn_decode", q, k_pages, v_pages, out, q_start, kv_len,
@@ -651,6 +666,25 @@ def attn_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, o
         if partial.numel() < num_seqs * Hq * num_splits * (D + 2):
             raise KernelError(f"attn_decode: scratch of {partial.numel()} floats is too small for {num_seqs} "
                               f"sequences x {Hq} heads x {num_splits} splits")
+    if raw_qkv is not None:
+        qkv, q_weight, k_weight, eps, cos_sin, write_kv = raw_qkv
+        if loader != "tma":
+            raise KernelError("attn_decode: only the kernel with the TMA loader takes the raw projection")
+        _check("attn_decode.qkv", qkv, torch.bfloat16)
+        if tuple(qkv.shape) != (T, (Hq + 2 * Hkv) * D) or num_seqs > T:
+            raise KernelError(f"attn_decode: raw projection {tuple(qkv.shape)} for {T} tokens of {Hq}+2x{Hkv} heads of {D}")
+        for nm, t, n in (("q_weight", q_weight, D), ("k_weight", k_weight, D), ("cos_sin", cos_sin, T * D)):
+            if t is not None:
+                _check(f"attn_decode.{nm}", t, torch.float32)
+                if t.numel() != n:
+                    raise KernelError(f"attn_decode: {nm} has {t.numel()} values, {n} expected")
+        code = library().q3_attn_decode_tma_qkv(
+            qkv.data_ptr(), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos_sin), 1 if write_kv else 0,
+            k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), _ptr(partial), q_start.data_ptr(), kv_len.data_ptr(),
+            block_table.data_ptr(), block_table.shape[1], page_size, num_pages, num_seqs, Hq, Hkv, D, float(scale),
+            int(window), int(num_splits), status.data_ptr(), _stream())
+        _done("attn_decode", code, f"heads {Hq}/{Hkv}, head_dim {D}, page {page_size}, raw projection")
+        return
     fn = library().q3_attn_decode_tma if loader == "tma" else library().q3_attn_decode
     code = fn(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(),
               _ptr(partial), q_start.data_ptr(), kv_len.data_ptr(), block_table.data_ptr(),
@@ -698,8 +732,9 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
                     q_start: torch.Tensor, kv_len: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
                     num_seqs: int, num_decode: int, max_q_len: int, max_kv_len: int, scale: float, window: int,
                     status: torch.Tensor, partial: Optional[torch.Tensor] = None,
-                    portion_kernel: str = "auto", decode_kernel: str = "auto") -> None:
-    """Causal attention of a mixed batch over the pages: rows [0, num_decode) bring one token each and
+                    portion_kernel: str = "auto", decode_kernel: str = "auto", raw_qkv=None) -> None:
+    """``raw_qkv``: see ``attn_decode``; only where ``decode_takes_raw_qkv`` says so.
+    Causal attention of a mixed batch over the pages: rows [0, num_decode) bring one token each and
     go to the split-KV decode kernel, the rest to a portion kernel (tcgen05 where it takes the shape,
     else mma.sync; ``portion_kernel="mma"`` forces the latter); shapes no tensor-core kernel takes
     (and float32) go to the plain kernel."""
@@ -714,7 +749,9 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         if partial is None or partial.numel() < num_decode * Hq * splits * (D + 2):
             splits = 1 if partial is None else max(1, partial.numel() // (num_decode * Hq * (D + 2)))
         attn_decode(q, k_pages, v_pages, out, partial, q_start, kv_len, block_table, num_decode, scale, window,
-                    splits, status, loader="tma" if tma else "cp_async")
+                    splits, status, loader="tma" if tma else "cp_async", raw_qkv=raw_qkv)
+    elif raw_qkv is not None:
+        raise KernelError("paged_attention: the raw projection is only taken by a step of single tokens")
     if num_seqs > num_decode:
         rest = (q_start[num_decode:], kv_len[num_decode:], block_table[num_decode:], num_seqs - num_decode, max_q_len)
         if portion_kernel != "mma" and attn_tc_takes(D, k_pages.shape[2], window):

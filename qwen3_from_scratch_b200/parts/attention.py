@@ -92,6 +92,19 @@ class GQAAttention(Mixer):
         q = self._q[:T]
         eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
         fused = self.position.fused_rotary() if self.position is not None else None
+        out = self._o[:T]
+        whole_rotation = fused is None or fused[1] == d
+        if ((self.position is None or fused is not None) and whole_rotation
+                and ops.decode_takes_raw_qkv(self.rt.dtype, hq, hkv, d, k_pages.shape[2], T, ctx.num_seqs, ctx.num_decode)):
+            # every row decodes: the attention kernel norms and rotates its own query and the new key itself
+            # (the step's angles are made before the projection, so that the kernel may fetch them early)
+            cos_sin = self.position.step_table(ctx) if fused is not None else None
+            qkv = self.qkv(x)
+            raw = (qkv, self.q_norm_weight, self.k_norm_weight, eps, cos_sin, write_cache)
+            self.attend(q, k_pages, v_pages, table, ctx, out, raw_qkv=raw)
+            if into_stream is not None:
+                return self.o_proj.into_stream(out.view(T, hq * d), into_stream)
+            return self.o_proj(out.view(T, hq * d))
         qkv = self.qkv(x)
         if self.position is None or fused is not None:
             inv_freq, rotary_dim = fused if fused is not None else (None, 0)
@@ -113,15 +126,14 @@ class GQAAttention(Mixer):
             heads[:, hq:hq + hkv].copy_(self.position.apply(kh, ctx.positions))
             ops.qkv_post(qkv, q, k_pages, v_pages, None, None, 0.0, None, 0, ctx.positions, ctx.tok_seq, table,
                          hq, hkv, d, write_cache, self.rt.status)
-        out = self._o[:T]
         self.attend(q, k_pages, v_pages, table, ctx, out)
         if into_stream is not None:
             return self.o_proj.into_stream(out.view(T, hq * d), into_stream)
         return self.o_proj(out.view(T, hq * d))
 
     def attend(self, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, table: torch.Tensor,
-               ctx: StepContext, out: torch.Tensor) -> None:
+               ctx: StepContext, out: torch.Tensor, raw_qkv=None) -> None:
         """Causal attention of this step's queries over the pages (keys of this step included)."""
         ops.paged_attention(q, k_pages, v_pages, out, ctx.q_start, ctx.kv_len, ctx.tok_seq, table, ctx.num_seqs,
                             ctx.num_decode, ctx.max_q_len, ctx.max_kv_len, self.scale, self.window or 0,
-                            self.rt.status, self._partial)
+                            self.rt.status, self._partial, raw_qkv=raw_qkv)

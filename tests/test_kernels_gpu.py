@@ -516,6 +516,75 @@ def test_attn_ref(dtype, case):
     close(out, want, dtype)
 
 
+@pytest.mark.parametrize("d,page_size,hq,hkv", [(128, 16, 16, 8), (64, 32, 6, 2), (128, 64, 4, 4)])
+@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("window", [None, 70])
+@pytest.mark.parametrize("with_norm", [True, False])
+def test_decode_attention_from_the_raw_projection(d, page_size, hq, hkv, splits, window, with_norm):
+    """A step of single tokens: the decode kernel norms and rotates its query and the new key itself and stores
+    the new key and value, against qkv_post followed by the same kernel.  Lengths that put the new token at
+    the start, in the middle and at the end of a tile and of a page."""
+    o = ops()
+    kv_lens = [200, 17, 161, 1, 16, 64, 65]
+    B, n_heads, eps = len(kv_lens), hq + 2 * hkv, 1e-5
+    g = torch.Generator().manual_seed(41)
+    q, k_list, v_list, tables, num_pages = attention_case("bfloat16", hq, hkv, d, page_size, kv_lens, [1] * B, window, seed=23)
+    qkv = (torch.randn(B, n_heads * d, generator=g) * 2).to(torch.bfloat16)
+    qw = (1 + 0.2 * torch.randn(d, generator=g)) if with_norm else None
+    kw = (1 + 0.2 * torch.randn(d, generator=g)) if with_norm else None
+    inv_freq = 1.0 / (10000.0 ** (torch.arange(0, d, 2).float() / d))
+    positions = torch.tensor([n - 1 for n in kv_lens], dtype=torch.int32)
+    table_dev = dev(table_tensor(tables))
+    cos_sin = torch.empty(B, d, device="cuda")
+    o.rope_table(dev(inv_freq), dev(positions), cos_sin)
+    q_start = dev(torch.arange(B + 1, dtype=torch.int32))
+    tok_seq = dev(torch.arange(B, dtype=torch.int32))
+    lens = dev(torch.tensor(kv_lens, dtype=torch.int32))
+    partial = torch.empty(o.decode_partial_numel(B, hq, d), device="cuda")
+    scale = d ** -0.5
+
+    def pools():  # the row of the new token holds NaN until somebody writes it
+        kl = [k.clone() for k in k_list]
+        vl = [v.clone() for v in v_list]
+        for k, v in zip(kl, vl):
+            k[-1] = float("nan")
+            v[-1] = float("nan")
+        return (dev(paged(kl, page_size, tables, num_pages, torch.bfloat16)),
+                dev(paged(vl, page_size, tables, num_pages, torch.bfloat16)))
+
+    # two kernels
+    k1, v1 = pools()
+    q1 = torch.empty(B, hq, d, device="cuda", dtype=torch.bfloat16)
+    st = status()
+    o.qkv_post(dev(qkv), q1, k1, v1, None if qw is None else dev(qw), None if kw is None else dev(kw), eps, dev(inv_freq), d,
+               dev(positions), tok_seq, table_dev, hq, hkv, d, True, st, cos_sin=cos_sin)
+    out1 = torch.full((B, hq, d), float("nan"), device="cuda", dtype=torch.bfloat16)
+    o.attn_decode(q1, k1, v1, out1, partial, q_start, lens, table_dev, B, scale, window or 0, splits, st, loader="tma")
+    # one kernel
+    k2, v2 = pools()
+    out2 = torch.full_like(out1, float("nan"))
+    raw = (dev(qkv), None if qw is None else dev(qw), None if kw is None else dev(kw), eps, cos_sin, True)
+    o.attn_decode(q1, k2, v2, out2, partial, q_start, lens, table_dev, B, scale, window or 0, splits, st, loader="tma",
+                  raw_qkv=raw)
+    assert int(st.item()) == 0
+    # the same formulas in the same precision; the sums of squares are added in another order, which may move
+    # a value by one bfloat16 step (2^-8 relative) before the attention
+    used = ~torch.isnan(k1.float())
+    assert torch.equal(used, ~torch.isnan(k2.float())) and torch.equal(~torch.isnan(v1.float()), ~torch.isnan(v2.float()))
+    assert torch.equal(v1[used], v2[used])
+    kd = (k1[used].float() - k2[used].float()).abs()
+    assert float(kd.max()) <= 2.0 ** -7 * float(k1[used].float().abs().max())
+    close(out2, out1, "bfloat16")
+    # and without writing (a layer that reads a cache another layer wrote): the pools stay as they are
+    k3, v3 = pools()
+    before_k, before_v = k3.clone(), v3.clone()
+    out3 = torch.full_like(out1, float("nan"))
+    o.attn_decode(q1, k3, v3, out3, partial, q_start, lens, table_dev, B, scale, window or 0, splits, st, loader="tma",
+                  raw_qkv=raw[:5] + (False,))
+    assert torch.equal(torch.nan_to_num(k3.float(), 7.0), torch.nan_to_num(before_k.float(), 7.0))
+    assert torch.equal(torch.nan_to_num(v3.float(), 7.0), torch.nan_to_num(before_v.float(), 7.0))
+
+
 @pytest.mark.parametrize("dtype", list(DT))
 @pytest.mark.parametrize("far", [0, 3, 250, 511])
 def test_attn_ref_finds_one_far_key(dtype, far):
