@@ -269,11 +269,13 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 }
 
 // Merges the splits of one (sequence, head): out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
-// The splits are dealt to the warps of the block and each lane owns pairs of output values, so all
-// of a block's loads are in flight at once: the kernel is two round trips to memory long, however
-// many splits there are.  D is even and at most 256.
+// The splits are dealt to the warps of the block, four at a time per warp with all their loads in flight
+// together, and each lane owns pairs of output values.  A warp sums its splits relative to its own running
+// maximum; the warps' sums are brought to the common maximum when they are added, so the kernel is one round
+// trip to memory long for up to 4 x 8 splits.  D is even and at most 256.
 constexpr int AC_WARPS = 8;
 constexpr int AC_MAX_D = 256;
+constexpr int AC_AT_ONCE = 4;
 
 __global__ void __launch_bounds__(AC_WARPS * 32)
 attn_combine_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
@@ -286,57 +288,75 @@ attn_combine_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.x, b = blockIdx.y;
   const float* base = partial + ((size_t)b * Hq + head) * num_splits * (D + 2);
-  float mx = -INFINITY;
-  for (int s = threadIdx.x; s < num_splits; s += AC_WARPS * 32) mx = fmaxf(mx, base[(size_t)s * (D + 2) + D]);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  if (lane == 0) max_s[warp] = mx;
-  __syncthreads();
-  float big = max_s[0];
-#pragma unroll
-  for (int w = 1; w < AC_WARPS; ++w) big = fmaxf(big, max_s[w]);
-
+  constexpr int PAIRS = AC_MAX_D / 64;
   // lane owns the value pairs d = 2 * lane + 64 * j; warp owns the splits warp, warp + AC_WARPS, ...
-  float2 acc[AC_MAX_D / 64];
+  float2 acc[PAIRS];
 #pragma unroll
-  for (int j = 0; j < AC_MAX_D / 64; ++j) acc[j] = make_float2(0.f, 0.f);
-  float den = 0.f;
-  if (big != -INFINITY) {
-#pragma unroll 2
-    for (int s = warp; s < num_splits; s += AC_WARPS) {
+  for (int j = 0; j < PAIRS; ++j) acc[j] = make_float2(0.f, 0.f);
+  float den = 0.f, mine = -INFINITY;  // relative to 2^mine
+  for (int s0 = warp; s0 < num_splits; s0 += AC_WARPS * AC_AT_ONCE) {
+    float2 ml[AC_AT_ONCE], v[AC_AT_ONCE][PAIRS];
+#pragma unroll
+    for (int u = 0; u < AC_AT_ONCE; ++u) {
+      const int s = s0 + u * AC_WARPS;
       const float* row = base + (size_t)s * (D + 2);
-      const float2 ml = *reinterpret_cast<const float2*>(row + D);  // (maximum, denominator) of the split
-      const float wgt = ml.x == -INFINITY ? 0.f : exp2f(ml.x - big);
-      den += ml.y * wgt;
+      ml[u] = s < num_splits ? *reinterpret_cast<const float2*>(row + D) : make_float2(-INFINITY, 0.f);
 #pragma unroll
-      for (int j = 0; j < AC_MAX_D / 64; ++j) {
+      for (int j = 0; j < PAIRS; ++j) {
         const int d = 2 * lane + 64 * j;
-        if (d < D) {
-          const float2 v = *reinterpret_cast<const float2*>(row + d);
-          acc[j].x += v.x * wgt;
-          acc[j].y += v.y * wgt;
-        }
+        v[u][j] = (s < num_splits && d < D) ? *reinterpret_cast<const float2*>(row + d) : make_float2(0.f, 0.f);
+      }
+    }
+    float top = mine;
+#pragma unroll
+    for (int u = 0; u < AC_AT_ONCE; ++u) top = fmaxf(top, ml[u].x);
+    if (top == -INFINITY) continue;  // nothing but empty splits so far
+    const float keep = mine == -INFINITY ? 0.f : exp2f(mine - top);
+    den *= keep;
+#pragma unroll
+    for (int j = 0; j < PAIRS; ++j) {
+      acc[j].x *= keep;
+      acc[j].y *= keep;
+    }
+    mine = top;
+#pragma unroll
+    for (int u = 0; u < AC_AT_ONCE; ++u) {
+      const float wgt = ml[u].x == -INFINITY ? 0.f : exp2f(ml[u].x - top);
+      den += ml[u].y * wgt;
+#pragma unroll
+      for (int j = 0; j < PAIRS; ++j) {
+        acc[j].x += v[u][j].x * wgt;
+        acc[j].y += v[u][j].y * wgt;
       }
     }
   }
 #pragma unroll
-  for (int j = 0; j < AC_MAX_D / 64; ++j) {
+  for (int j = 0; j < PAIRS; ++j) {
     const int d = 2 * lane + 64 * j;
     if (d < D) {
       acc_s[warp][d] = acc[j].x;
       acc_s[warp][d + 1] = acc[j].y;
     }
   }
-  if (lane == 0) den_s[warp] = den;
+  if (lane == 0) {
+    den_s[warp] = den;
+    max_s[warp] = mine;
+  }
   __syncthreads();
+  float big = max_s[0];
+#pragma unroll
+  for (int w = 1; w < AC_WARPS; ++w) big = fmaxf(big, max_s[w]);
+  float scale_w[AC_WARPS], dn = 0.f;
+#pragma unroll
+  for (int w = 0; w < AC_WARPS; ++w) {
+    scale_w[w] = max_s[w] == -INFINITY ? 0.f : exp2f(max_s[w] - big);
+    dn += den_s[w] * scale_w[w];
+  }
   const int tq = q_start[b];
   for (int d = threadIdx.x; d < D; d += AC_WARPS * 32) {
-    float a = 0.f, dn = 0.f;
+    float a = 0.f;
 #pragma unroll
-    for (int w = 0; w < AC_WARPS; ++w) {
-      a += acc_s[w][d];
-      dn += den_s[w];
-    }
+    for (int w = 0; w < AC_WARPS; ++w) a += acc_s[w][d] * scale_w[w];
     out[((size_t)tq * Hq + head) * D + d] = __float2bfloat16_rn(dn > 0.f ? a / dn : 0.f);
   }
 }
