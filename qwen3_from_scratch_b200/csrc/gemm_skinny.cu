@@ -75,7 +75,8 @@ constexpr int GS_XS_MAX_BYTES = 160 * 1024;
 
 // EPI 2: out is the float32 stream [T, N] and is added to.  NORMED: see the head of the file.
 template <int NT, int WK, int EPI, typename OutT, int PRE = 1, bool NORMED = false>
-__global__ void __launch_bounds__(GS_WARPS * 32, (NT == 1 && WK > 1 && !(NORMED && PRE == 1)) ? 1 : 3)
+__global__ void __launch_bounds__(GS_WARPS * 32,
+                                  ((NT == 1 && WK > 1 && !(NORMED && PRE == 1)) || (NT == 2 && PRE > 1)) ? 1 : 3)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
                    OutT* __restrict__ out, int T, int N, int K, int ldo, const SkinnyFuse fuse) {
   constexpr int GROUPS = GS_WARPS / WK;  // feature groups per block
@@ -313,12 +314,15 @@ static int gemm_skinny_launch(const void* X, const void* W, void* out, int T, in
   } while (0)
   // batches of a warp's share of K; up to three are fetched ahead where eight tokens leave the registers
   const int batches = ((K + 31) / 32 + wk * GS_UNROLL - 1) / (wk * GS_UNROLL);
-  const int pre = NT == 1 && wk == GS_WARPS ? (batches < 3 ? batches : 3) : 1;
+  // (with two token tiles only where the grid is small anyway, one block of 16 features per SM or fewer: the
+  // products into the stream, o_proj and down_proj, whose warps have two or three batches each)
+  const bool few_blocks = NT == 1 || (EPI == 2 && groups <= 148);
+  const int pre = few_blocks && wk == GS_WARPS ? (batches < 3 ? batches : 3) : 1;
   if (wk == 1) Q3_GS_GO(1, 1);
   else if (wk == 2) Q3_GS_GO(2, 1);
   else if (wk == 4) Q3_GS_GO(4, 1);
   else if (pre <= 1) Q3_GS_GO(8, 1);
-  else if constexpr (NT == 1) {
+  else if constexpr (NT == 1 || EPI == 2) {
     if (pre == 2) Q3_GS_GO(8, 2);
     else Q3_GS_GO(8, 3);
   }

@@ -214,7 +214,7 @@ def test_gemm_skinny_with_swiglu(shape):
 
 
 @pytest.mark.parametrize("shape", [(1, 4096, 1024), (8, 1024, 2048), (16, 331, 96), (3, 70, 200), (9, 48, 8), (7, 1024, 3072),
-                                   (5, 64, 5000)])
+                                   (5, 64, 5000), (12, 1024, 2048), (16, 1024, 3072), (10, 2368, 2048)])
 def test_gemm_skinny_into_stream(shape):
     """stream += x W^T in place, with partial sums of squares of the new rows that add up to the rows' own."""
     T, N, K = shape
