@@ -179,7 +179,9 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
     x_row[i] = NORMED ? xs + (size_t)tok * xs_pitch + 8 * tid4 : X + (size_t)(x_ok[i] ? tok : 0) * K + 8 * tid4;
   }
   auto multiply = [&](int g0, const uint4 (&lo)[GS_UNROLL], const uint4 (&hi)[GS_UNROLL]) {
-    constexpr int XU = GS_UNROLL;  // groups whose activations are fetched together
+    // groups whose activations are fetched together (from shared memory one at a time is enough, and with two
+    // token tiles it keeps the thread within the registers of three blocks per SM)
+    constexpr int XU = (NORMED && NT == 2) ? 1 : GS_UNROLL;
 #pragma unroll
     for (int u0 = 0; u0 < GS_UNROLL; u0 += XU) {
       uint4 xv[XU][NT];
