@@ -66,6 +66,8 @@ struct SkinnyFuse {
   int ss_parts;
   float eps;
   float* ss_out;        // EPI 2: [ceil(N / 16)][16] partial sums of squares of the rows after the add
+  const float* next_w;  // EPI 2, optional: weight [N] of the norm that comes next, and
+  __nv_bfloat16* scaled_out;  // [T, N]: the new rows times that weight, the operand of a NORMED == 2 product
   int early;            // EPI 2: the stream may be read ahead of the wait (the launch before did not write it)
 };
 
@@ -73,10 +75,12 @@ constexpr int GS_SS_ROWS = 16;  // row pitch of the partial sums
 constexpr int GS_XS_PAD = 32;   // NORMED: elements between rows of the staged operand (a quarter-warp's 16-byte reads then miss each other's banks)
 constexpr int GS_XS_MAX_BYTES = 160 * 1024;
 
-// EPI 2: out is the float32 stream [T, N] and is added to.  NORMED: see the head of the file.
-template <int NT, int WK, int EPI, typename OutT, int PRE = 1, bool NORMED = false>
+// EPI 2: out is the float32 stream [T, N] and is added to.  NORMED (see the head of the file): 1 the operand is
+// made here from the stream, 2 X is the operand already (the product that last added into the stream left
+// it, scaled_out); both multiply the result by the row's 1 / rms.
+template <int NT, int WK, int EPI, typename OutT, int PRE = 1, int NORMED = 0>
 __global__ void __launch_bounds__(GS_WARPS * 32,
-                                  ((NT == 1 && WK > 1 && !(NORMED && PRE == 1)) || (NT == 2 && PRE > 1)) ? 1 : 3)
+                                  ((NT == 1 && WK > 1 && !(NORMED != 0 && PRE == 1)) || (NT == 2 && PRE > 1)) ? 1 : 3)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
                    OutT* __restrict__ out, int T, int N, int K, int ldo, const SkinnyFuse fuse) {
   constexpr int GROUPS = GS_WARPS / WK;  // feature groups per block
@@ -114,7 +118,10 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
 #pragma unroll
   for (int p = 0; p < PRE; ++p) load_w(g_lo + p * GS_UNROLL, wl[p], wh[p]);
   float4 w_first = make_float4(0.f, 0.f, 0.f, 0.f);  // NORMED: this thread's four norm weights of the first pass
-  if (NORMED && (int)threadIdx.x < K / 4) w_first = __ldg(reinterpret_cast<const float4*>(fuse.norm_w) + threadIdx.x);
+  if (NORMED == 1 && (int)threadIdx.x < K / 4) w_first = __ldg(reinterpret_cast<const float4*>(fuse.norm_w) + threadIdx.x);
+  // EPI 2: the next norm's weight for this lane's feature (the same for all its elements)
+  const float next_weight = (EPI == 2 && fuse.scaled_out != nullptr && active && row0 + (lane & 15) < N)
+                                ? fuse.next_w[row0 + (lane & 15)] : 0.f;
   // EPI 2: the stream's values that this warp will add to (element e = lane + 32 j of its 16 x 8 NT results)
   float before[EPI == 2 ? 4 * NT : 1];
   if (EPI == 2 && fuse.early && ksplit == 0 && active) {
@@ -143,7 +150,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
   extern __shared__ __align__(16) unsigned char xs_raw[];
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(xs_raw);  // [8 NT][K + GS_XS_PAD]
   const int xs_pitch = K + GS_XS_PAD;
-  if (NORMED) {
+  if (NORMED == 1) {
     for (int c0 = 0; c0 < K / 4; c0 += GS_WARPS * 32) {
       const int c = c0 + threadIdx.x;
       const bool in = c < K / 4;
@@ -175,13 +182,13 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
 #pragma unroll
   for (int i = 0; i < NT; ++i) {
     const int tok = i * 8 + gid;
-    x_ok[i] = NORMED || tok < T;  // the staged operand holds zeros for rows past T
-    x_row[i] = NORMED ? xs + (size_t)tok * xs_pitch + 8 * tid4 : X + (size_t)(x_ok[i] ? tok : 0) * K + 8 * tid4;
+    x_ok[i] = NORMED == 1 || tok < T;  // the staged operand holds zeros for rows past T
+    x_row[i] = NORMED == 1 ? xs + (size_t)tok * xs_pitch + 8 * tid4 : X + (size_t)(x_ok[i] ? tok : 0) * K + 8 * tid4;
   }
   auto multiply = [&](int g0, const uint4 (&lo)[GS_UNROLL], const uint4 (&hi)[GS_UNROLL]) {
     // groups whose activations are fetched together (from shared memory one at a time is enough, and with two
     // token tiles it keeps the thread within the registers of three blocks per SM)
-    constexpr int XU = (NORMED && NT == 2) ? 1 : GS_UNROLL;
+    constexpr int XU = (NORMED == 1 && NT == 2) ? 1 : GS_UNROLL;
 #pragma unroll
     for (int u0 = 0; u0 < GS_UNROLL; u0 += XU) {
       uint4 xv[XU][NT];
@@ -189,7 +196,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
       for (int u = 0; u < XU; ++u) {
         const size_t k = (size_t)(g0 + u0 + u) * 32;
         const bool in = g0 + u0 + u < g_hi && k + 8 * tid4 < (size_t)K;
-        if (NORMED) {
+        if (NORMED == 1) {
 #pragma unroll
           for (int i = 0; i < NT; ++i)
             xv[u][i] = in ? *reinterpret_cast<const uint4*>(x_row[i] + k) : make_uint4(0, 0, 0, 0);
@@ -265,6 +272,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
         float* at = stream + (size_t)tok * ldo + row0 + f;
         h = (fuse.early ? before[j] : *at) + v;
         *at = h;
+        if (fuse.scaled_out != nullptr)
+          fuse.scaled_out[(size_t)tok * ldo + row0 + f] = __float2bfloat16_rn(h * next_weight);
       }
       float sq = h * h;
 #pragma unroll
@@ -291,11 +300,11 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
   }
 }
 
-template <int NT, int EPI, typename OutT, bool NORMED = false>
+template <int NT, int EPI, typename OutT, int NORMED = 0>
 static int gemm_skinny_launch(const void* X, const void* W, void* out, int T, int N, int K, int ldo,
                               cudaStream_t stream, SkinnyFuse fuse = SkinnyFuse{}) {
   if (EPI == 2) fuse.early = last_launch_was_plain(stream) ? 1 : 0;
-  const size_t xs_bytes = NORMED ? (size_t)8 * NT * (K + GS_XS_PAD) * sizeof(__nv_bfloat16) : 0;
+  const size_t xs_bytes = NORMED == 1 ? (size_t)8 * NT * (K + GS_XS_PAD) * sizeof(__nv_bfloat16) : 0;
   if (xs_bytes > (size_t)GS_XS_MAX_BYTES) return Q3_ERR_SIZE;
   const int groups = (N + 15) / 16;
   // split K over more warps while that still leaves every warp at least 128 values of k and the
@@ -356,38 +365,52 @@ extern "C" int q3_gemm_skinny(const void* X, const void* W, void* out, int T, in
   return q3::gemm_skinny_launch<2, 0, bf16>(X, W, out, T, N, K, ldo, stream);
 }
 
-// The two forms that take the norm kernels out of a decode step (see the head of the file), T <= 16.
+// The forms that take the norm kernels out of a decode step (see the head of the file), T <= 16.
 // mode 0: out[T, N] bfloat16 = rs * (W (stream * norm_w)); mode 1: the same with W's rows alternating gate/up in
 // blocks of eight and out [T, N / 2] = up * silu(gate).  x is the float32 stream [T, K]; ss_in holds ss_parts
 // partial sums of squares per row ([ss_parts][16] floats) that add up to sum(stream[t]^2); rs = 1 / sqrt(sum / K + eps).
 // Modes 0 and 1 stage the rows in shared memory (16 (K + 32) bytes for up to 8 rows, twice that for 9 to 16)
 // and refuse a K for which that exceeds 160 KB.
+// modes 3 and 4: as 0 and 1, but x is the bfloat16 operand stream * norm_w itself [T, K], as mode 2 leaves it
+// (no staging, any K).
 // mode 2: x is bfloat16 [T, K]; out is the float32 stream [T, N] and becomes out + x W^T; ss_out
-// ([ceil(N / 16)][16] floats) receives the partial sums of squares of the new rows.
+// ([ceil(N / 16)][16] floats) receives the partial sums of squares of the new rows; if next_w (float32 [N]) and
+// scaled_out (bfloat16 [T, N]) are given, scaled_out = new rows * next_w, rounded once.
 extern "C" int q3_gemm_skinny_fused(const void* x, const void* W, void* out, int T, int N, int K, int ldo, int mode,
                                     const float* norm_w, const float* ss_in, int ss_parts, float eps, float* ss_out,
-                                    cudaStream_t stream) {
+                                    const float* next_w, void* scaled_out, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
-  if (T > 16 || K <= 0 || K % 8 || mode < 0 || mode > 2 || (mode == 1 && N % 16)) return Q3_ERR_SIZE;
+  if (T > 16 || K <= 0 || K % 8 || mode < 0 || mode > 4 || ((mode == 1 || mode == 4) && N % 16)) return Q3_ERR_SIZE;
   if ((uintptr_t)x % 16 || (uintptr_t)W % 16 || (uintptr_t)out % 16) return Q3_ERR_ALIGN;
   using bf16 = __nv_bfloat16;
   q3::SkinnyFuse fuse{};
   if (mode == 2) {
-    if (!ss_out) return Q3_ERR_SIZE;
+    if (!ss_out || ((next_w == nullptr) != (scaled_out == nullptr))) return Q3_ERR_SIZE;
     fuse.ss_out = ss_out;
+    fuse.next_w = next_w;
+    fuse.scaled_out = (bf16*)scaled_out;
     if (T <= 8) return q3::gemm_skinny_launch<1, 2, float>(x, W, out, T, N, K, ldo, stream, fuse);
     return q3::gemm_skinny_launch<2, 2, float>(x, W, out, T, N, K, ldo, stream, fuse);
   }
-  if (!norm_w || !ss_in || ss_parts <= 0 || (uintptr_t)norm_w % 16) return Q3_ERR_SIZE;
-  fuse.stream = (const float*)x;
-  fuse.norm_w = norm_w;
+  if (!ss_in || ss_parts <= 0) return Q3_ERR_SIZE;
   fuse.ss_in = ss_in;
   fuse.ss_parts = ss_parts;
   fuse.eps = eps;
-  if (mode == 1) {
-    if (T <= 8) return q3::gemm_skinny_launch<1, 1, bf16, true>(nullptr, W, out, T, N, K, ldo, stream, fuse);
-    return q3::gemm_skinny_launch<2, 1, bf16, true>(nullptr, W, out, T, N, K, ldo, stream, fuse);
+  if (mode >= 3) {
+    if (mode == 4) {
+      if (T <= 8) return q3::gemm_skinny_launch<1, 1, bf16, 2>(x, W, out, T, N, K, ldo, stream, fuse);
+      return q3::gemm_skinny_launch<2, 1, bf16, 2>(x, W, out, T, N, K, ldo, stream, fuse);
+    }
+    if (T <= 8) return q3::gemm_skinny_launch<1, 0, bf16, 2>(x, W, out, T, N, K, ldo, stream, fuse);
+    return q3::gemm_skinny_launch<2, 0, bf16, 2>(x, W, out, T, N, K, ldo, stream, fuse);
   }
-  if (T <= 8) return q3::gemm_skinny_launch<1, 0, bf16, true>(nullptr, W, out, T, N, K, ldo, stream, fuse);
-  return q3::gemm_skinny_launch<2, 0, bf16, true>(nullptr, W, out, T, N, K, ldo, stream, fuse);
+  if (!norm_w || (uintptr_t)norm_w % 16) return Q3_ERR_SIZE;
+  fuse.stream = (const float*)x;
+  fuse.norm_w = norm_w;
+  if (mode == 1) {
+    if (T <= 8) return q3::gemm_skinny_launch<1, 1, bf16, 1>(nullptr, W, out, T, N, K, ldo, stream, fuse);
+    return q3::gemm_skinny_launch<2, 1, bf16, 1>(nullptr, W, out, T, N, K, ldo, stream, fuse);
+  }
+  if (T <= 8) return q3::gemm_skinny_launch<1, 0, bf16, 1>(nullptr, W, out, T, N, K, ldo, stream, fuse);
+  return q3::gemm_skinny_launch<2, 0, bf16, 1>(nullptr, W, out, T, N, K, ldo, stream, fuse);
 }

@@ -15,7 +15,7 @@ import torch
 from ..cache.manager import CacheLayout, layout_of
 from ..config.model_config import ModelConfig
 from ..kernels import ops
-from ..parts.base import STREAM_SUMSQ, ModelSpec, Runtime, StepContext
+from ..parts.base import NEXT_NORM_WEIGHT, STREAM_SUMSQ, ModelSpec, Runtime, StepContext
 from ..registry import build_model_spec, create_part, load_config
 from ..weights.loader import load_weights
 
@@ -92,8 +92,12 @@ class Model:
         ctx.per_step = {}  # what parts share within a step is computed anew (and so is recorded by a graph capture)
         stream = self.embedding.forward(ctx.token_ids)
         pending = None
-        for call in self.spec.order:
+        order = self.spec.order
+        for i, call in enumerate(order):
             layer = self.layers[call.layer]
+            # the weight of the norm that reads the stream after this layer, for layers that prepare the stream for it
+            nxt = self.layers[order[i + 1].layer] if i + 1 < len(order) else None
+            ctx.per_step[NEXT_NORM_WEIGHT] = getattr(nxt, "first_norm_weight", None)
             pending = layer.forward(stream, pending, ctx, call.cache, call.write_cache)
             if not layer.keeps_stream_stats:
                 ctx.per_step.pop(STREAM_SUMSQ, None)  # whatever it did to the stream, the sums describe it no longer

@@ -77,7 +77,7 @@ _SIGNATURES = {
                        _c_void_p, _c_int, _c_void_p, _c_void_p],
     "q3_gemm_skinny": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "q3_gemm_skinny_fused": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
-                             _c_int, _c_float, _c_void_p, _c_void_p],
+                             _c_int, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "q3_sample": [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ull, _c_int,
                   _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p],
 }
@@ -390,11 +390,14 @@ def gemm_skinny_normed_takes(rows: int, weight: torch.Tensor) -> bool:
 
 
 def gemm_skinny_normed(stream: torch.Tensor, norm_weight: torch.Tensor, sumsq: torch.Tensor, parts: int, eps: float,
-                       w: torch.Tensor, out: torch.Tensor, swiglu_blocks: bool = False) -> None:
+                       w: torch.Tensor, out: torch.Tensor, swiglu_blocks: bool = False,
+                       scaled: Optional[torch.Tensor] = None) -> None:
     """out = rmsnorm(stream) @ w^T for up to 16 rows without a norm kernel: the float32 stream is
     multiplied by the norm weight on its way into the tensor core and the row's 1 / rms in the
     epilogue, from ``parts`` partial sums of squares per row (``sumsq[p, t]``, as
-    ``gemm_skinny_into_stream`` leaves them).  ``swiglu_blocks`` as in ``gemm_skinny``."""
+    ``gemm_skinny_into_stream`` leaves them).  ``scaled``: the bfloat16 operand ``stream * norm_weight``
+    if the product that last added into the stream left it (then nothing is staged and any width is
+    taken).  ``swiglu_blocks`` as in ``gemm_skinny``."""
     _check("gemm_skinny_normed.stream", stream, torch.float32)
     _check("gemm_skinny_normed.norm_weight", norm_weight, torch.float32)
     _check("gemm_skinny_normed.sumsq", sumsq, torch.float32)
@@ -407,15 +410,24 @@ def gemm_skinny_normed(stream: torch.Tensor, norm_weight: torch.Tensor, sumsq: t
             or sumsq.shape[1] != SUMSQ_ROWS or not 0 < parts <= sumsq.shape[0]):
         raise KernelError(f"gemm_skinny_normed: stream {tuple(stream.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, "
                           f"norm weight {tuple(norm_weight.shape)}, sums {tuple(sumsq.shape)} of which {parts}")
-    code = library().q3_gemm_skinny_fused(stream.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, want_cols,
-                                          1 if swiglu_blocks else 0, norm_weight.data_ptr(), sumsq.data_ptr(),
-                                          int(parts), float(eps), None, _stream())
+    x, mode = stream, 1 if swiglu_blocks else 0
+    if scaled is not None:
+        _check("gemm_skinny_normed.scaled", scaled, torch.bfloat16)
+        if tuple(scaled.shape) != (T, K):
+            raise KernelError(f"gemm_skinny_normed: scaled operand {tuple(scaled.shape)} for a stream {(T, K)}")
+        x, mode = scaled, 4 if swiglu_blocks else 3
+    code = library().q3_gemm_skinny_fused(x.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, want_cols, mode,
+                                          norm_weight.data_ptr(), sumsq.data_ptr(), int(parts), float(eps), None, None,
+                                          None, _stream())
     _done("gemm_skinny_normed", code, f"T {T} N {N} K {K}")
 
 
-def gemm_skinny_into_stream(x: torch.Tensor, w: torch.Tensor, stream: torch.Tensor, sumsq: torch.Tensor) -> int:
+def gemm_skinny_into_stream(x: torch.Tensor, w: torch.Tensor, stream: torch.Tensor, sumsq: torch.Tensor,
+                            next_weight: Optional[torch.Tensor] = None, scaled: Optional[torch.Tensor] = None) -> int:
     """stream += x @ w^T for up to 16 rows (x, w bfloat16; stream float32), and ``sumsq[p, t]`` = the sum of
-    squares of the 16 new values ``stream[t, 16 p : 16 p + 16]``; returns the number of such parts."""
+    squares of the 16 new values ``stream[t, 16 p : 16 p + 16]``; returns the number of such parts.  With
+    ``next_weight`` (the weight of the norm that comes next) and ``scaled`` (bfloat16, like stream):
+    ``scaled = stream * next_weight``, rounded once: the operand of ``gemm_skinny_normed``."""
     _check("gemm_skinny_into_stream.x", x, torch.bfloat16)
     _check("gemm_skinny_into_stream.w", w, torch.bfloat16)
     _check("gemm_skinny_into_stream.stream", stream, torch.float32)
@@ -424,11 +436,17 @@ def gemm_skinny_into_stream(x: torch.Tensor, w: torch.Tensor, stream: torch.Tens
     N = w.shape[0]
     parts = sumsq_parts(N)
     if (w.shape[1] != K or tuple(stream.shape) != (T, N) or sumsq.dim() != 2 or sumsq.shape[1] != SUMSQ_ROWS
-            or sumsq.shape[0] < parts):
+            or sumsq.shape[0] < parts or (next_weight is None) != (scaled is None)):
         raise KernelError(f"gemm_skinny_into_stream: x {tuple(x.shape)}, w {tuple(w.shape)}, stream "
                           f"{tuple(stream.shape)}, sums {tuple(sumsq.shape)}")
+    if scaled is not None:
+        _check("gemm_skinny_into_stream.next_weight", next_weight, torch.float32)
+        _check("gemm_skinny_into_stream.scaled", scaled, torch.bfloat16)
+        if next_weight.numel() != N or tuple(scaled.shape) != (T, N):
+            raise KernelError(f"gemm_skinny_into_stream: next weight {tuple(next_weight.shape)}, scaled "
+                              f"{tuple(scaled.shape)} for a stream {(T, N)}")
     code = library().q3_gemm_skinny_fused(x.data_ptr(), w.data_ptr(), stream.data_ptr(), T, N, K, N, 2, None, None, 0,
-                                          0.0, sumsq.data_ptr(), _stream())
+                                          0.0, sumsq.data_ptr(), _ptr(next_weight), _ptr(scaled), _stream())
     _done("gemm_skinny_into_stream", code, f"T {T} N {N} K {K}")
     return parts
 

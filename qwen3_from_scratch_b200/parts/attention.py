@@ -80,12 +80,14 @@ class GQAAttention(Mixer):
 
     fuses_stream = True
 
-    def can_fuse_stream(self, rows: int) -> bool:
-        return self.qkv.takes_stream_norm(rows) and self.o_proj.can_add_into_stream(rows)
+    def can_fuse_stream(self, rows: int, scaled: bool = True) -> bool:
+        return self.qkv.takes_stream_norm(rows, scaled) and self.o_proj.can_add_into_stream(rows)
 
-    def forward(self, x, ctx: StepContext, cache_id: Optional[int], write_cache: bool, into_stream=None):
+    def forward(self, x, ctx: StepContext, cache_id: Optional[int], write_cache: bool, into_stream=None,
+                next_norm_weight=None):
         """``x``: the normed activations, or a ``StreamNorm`` that the QKV product applies itself.
-        ``into_stream``: the output projection adds into this stream and (sumsq, parts) is returned."""
+        ``into_stream``: the output projection adds into this stream and its ``StreamStats`` are returned
+        (with the rows times ``next_norm_weight`` if that is given)."""
         T = x.shape[0]
         hq, hkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         k_pages, v_pages, table = ctx.kv(cache_id)
@@ -103,7 +105,7 @@ class GQAAttention(Mixer):
             raw = (qkv, self.q_norm_weight, self.k_norm_weight, eps, cos_sin, write_cache)
             self.attend(q, k_pages, v_pages, table, ctx, out, raw_qkv=raw)
             if into_stream is not None:
-                return self.o_proj.into_stream(out.view(T, hq * d), into_stream)
+                return self.o_proj.into_stream(out.view(T, hq * d), into_stream, next_norm_weight)
             return self.o_proj(out.view(T, hq * d))
         qkv = self.qkv(x)
         if self.position is None or fused is not None:
@@ -128,7 +130,7 @@ class GQAAttention(Mixer):
                          hq, hkv, d, write_cache, self.rt.status)
         self.attend(q, k_pages, v_pages, table, ctx, out)
         if into_stream is not None:
-            return self.o_proj.into_stream(out.view(T, hq * d), into_stream)
+            return self.o_proj.into_stream(out.view(T, hq * d), into_stream, next_norm_weight)
         return self.o_proj(out.view(T, hq * d))
 
     def attend(self, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, table: torch.Tensor,

@@ -169,21 +169,35 @@ class StepContext:
 # ---------------------------------------------------------------------- a norm that is not computed
 
 
-STREAM_SUMSQ = "stream.sumsq"  # key in StepContext.per_step: (sumsq, parts) of the stream as it stands
+STREAM_SUMSQ = "stream.sumsq"  # key in StepContext.per_step: StreamStats of the stream as it stands
+NEXT_NORM_WEIGHT = "stream.next_norm_weight"  # key in StepContext.per_step: weight of the next block's first norm
+
+
+@dataclass
+class StreamStats:
+    """What the projection that last added into the residual stream left about the stream's rows:
+    ``sumsq[p, t]`` for ``p < parts`` are partial sums of squares of row ``t``; ``scaled``, if given, is
+    the rows times ``scaled_for`` (a norm's weight), rounded once to bfloat16."""
+
+    sumsq: torch.Tensor
+    parts: int
+    scaled: Optional[torch.Tensor] = None
+    scaled_for: Optional[torch.Tensor] = None
 
 
 @dataclass
 class StreamNorm:
     """RMSNorm of the residual stream, not computed: a projection that takes it (``Linear``, for a few
-    rows) multiplies the float32 stream by ``weight`` on its way into the product and by each row's
-    1 / rms afterwards, so that no norm kernel runs.  ``sumsq[p, t]`` for ``p < parts`` are partial sums
-    of squares of row ``t`` of the stream, left by the projection that last added into it."""
+    rows) multiplies the float32 stream by ``weight`` on its way into the product (or takes ``scaled``,
+    the stream times this weight in bfloat16, if the projection before left it) and by each row's
+    1 / rms afterwards, so that no norm kernel runs."""
 
     stream: torch.Tensor
     weight: torch.Tensor
     eps: float
     sumsq: torch.Tensor
     parts: int
+    scaled: Optional[torch.Tensor] = None
 
     @property
     def shape(self):
@@ -251,8 +265,9 @@ class Mixer(Part):
         raise NotImplementedError
 
     #: a mixer (or feed-forward) that sets this also has ``can_fuse_stream(rows)``; where that is true its
-    #: ``forward`` takes a ``StreamNorm`` for ``x`` and ``into_stream=stream``, adds its output into the
-    #: stream itself and returns ``(sumsq, parts)`` of the stream's new rows instead of the output
+    #: ``forward`` takes a ``StreamNorm`` for ``x`` and ``into_stream=stream`` (with ``next_norm_weight``, the
+    #: weight of the norm that will read the stream next, or None), adds its output into the stream itself and
+    #: returns the ``StreamStats`` of the stream's new rows instead of the output
     fuses_stream = False
 
 

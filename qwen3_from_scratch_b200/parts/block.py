@@ -12,7 +12,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..registry import create_part, register_part
-from .base import STREAM_SUMSQ, Block, PartSpec, Runtime, StepContext, WeightSpec
+from .base import NEXT_NORM_WEIGHT, STREAM_SUMSQ, Block, PartSpec, Runtime, StepContext, WeightSpec
 
 
 @register_part("block", "pre_norm")
@@ -42,6 +42,12 @@ class PreNormBlock(Block):
 
     keeps_stream_stats = True
 
+    @property
+    def first_norm_weight(self) -> Optional[torch.Tensor]:
+        """The weight of the norm this block applies to the stream first, if the block before may prepare
+        the stream for it (see StreamStats.scaled)."""
+        return self.norm1.weight if hasattr(self.norm1, "lazy") else None
+
     def fuses(self, rows: int) -> bool:
         """A few rows (decoding) in bfloat16: the mixer's and the feed-forward's last projections add into
         the stream themselves and their first ones apply the norm, so that no norm kernel runs."""
@@ -54,12 +60,18 @@ class PreNormBlock(Block):
         shared = ctx.__dict__.setdefault("per_step", {})
         stats = shared.pop(STREAM_SUMSQ, None)  # of the stream as the block before left it
         if self.fuses(stream.shape[0]):
-            if stats is None or pending is not None:
-                x = self.norm1.add_norm(stream, pending)
-            else:
+            rows = stream.shape[0]
+            x = None
+            if stats is not None and pending is None:
                 x = self.norm1.lazy(stream, stats)
-            stats = self.mixer.forward(x, ctx, cache_id, write_cache, into_stream=stream)
-            shared[STREAM_SUMSQ] = self.feed_forward.forward(self.norm2.lazy(stream, stats), into_stream=stream)
+                if not self.mixer.can_fuse_stream(rows, x.scaled is not None):
+                    x = None
+            if x is None:
+                x = self.norm1.add_norm(stream, pending)
+            stats = self.mixer.forward(x, ctx, cache_id, write_cache, into_stream=stream,
+                                       next_norm_weight=self.norm2.weight)
+            shared[STREAM_SUMSQ] = self.feed_forward.forward(self.norm2.lazy(stream, stats), into_stream=stream,
+                                                             next_norm_weight=shared.get(NEXT_NORM_WEIGHT))
             return None
         x = self.norm1.add_norm(stream, pending)
         a = self.mixer.forward(x, ctx, cache_id, write_cache)

@@ -15,7 +15,7 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
-from .base import Runtime, StreamNorm
+from .base import Runtime, StreamNorm, StreamStats
 
 
 class Linear:
@@ -42,11 +42,16 @@ class Linear:
             if self.full_precision:
                 self._out32 = self._out if self.out_dtype == torch.float32 else make("out32", torch.float32)
         self._weight_t = self.weight.t()
-        self._sumsq = None
+        self._sumsq = self._scaled = None
         if not self.full_precision and rt.dtype == torch.bfloat16:
             parts = ops.sumsq_parts(self.out_features)
-            self._sumsq = (rt.shared(f"{tag}.sumsq", parts, ops.SUMSQ_ROWS, dtype=torch.float32) if tag
-                           else rt.empty(parts, ops.SUMSQ_ROWS, dtype=torch.float32))
+            rows = ops.SKINNY_MAX_ROWS
+            if tag:
+                self._sumsq = rt.shared(f"{tag}.sumsq", parts, ops.SUMSQ_ROWS, dtype=torch.float32)
+                self._scaled = rt.shared(f"{tag}.scaled", rows, self.out_features, dtype=torch.bfloat16)
+            else:
+                self._sumsq = rt.empty(parts, ops.SUMSQ_ROWS, dtype=torch.float32)
+                self._scaled = rt.empty(rows, self.out_features, dtype=torch.bfloat16)
 
     def _buffer(self, which: str, rows: int, dtype: torch.dtype) -> torch.Tensor:
         buf = getattr(self, which)
@@ -54,26 +59,31 @@ class Linear:
             return torch.empty(rows, self.out_features, dtype=dtype, device=self.weight.device)
         return buf[:rows]
 
-    def takes_stream_norm(self, rows: int) -> bool:
-        """Whether ``self(StreamNorm)`` works for this many rows (a bfloat16 weight, a few rows)."""
-        return (not self.full_precision and self.out_dtype == torch.bfloat16 and self._out is not None
-                and ops.gemm_skinny_normed_takes(rows, self.weight))
+    def takes_stream_norm(self, rows: int, scaled: bool = True) -> bool:
+        """Whether ``self(StreamNorm)`` works for this many rows (a bfloat16 weight, a few rows); without the
+        scaled operand the rows are staged in shared memory, which bounds the width."""
+        if self.full_precision or self.out_dtype != torch.bfloat16 or self._out is None:
+            return False
+        return ops.gemm_skinny_takes(rows, self.weight) if scaled else ops.gemm_skinny_normed_takes(rows, self.weight)
 
     def can_add_into_stream(self, rows: int) -> bool:
         return self._sumsq is not None and ops.gemm_skinny_takes(rows, self.weight)
 
-    def into_stream(self, x: torch.Tensor, stream: torch.Tensor):
-        """stream += x W^T for a few rows; returns (sumsq, parts) of the stream's new rows (see StreamNorm)."""
-        parts = ops.gemm_skinny_into_stream(x, self.weight, stream, self._sumsq)
-        return self._sumsq, parts
+    def into_stream(self, x: torch.Tensor, stream: torch.Tensor,
+                    next_norm_weight: Optional[torch.Tensor] = None) -> StreamStats:
+        """stream += x W^T for a few rows; returns what the next norm needs to know about the new rows, with
+        the rows times ``next_norm_weight`` in bfloat16 if that weight is given (see StreamNorm)."""
+        scaled = self._scaled[: x.shape[0]] if next_norm_weight is not None else None
+        parts = ops.gemm_skinny_into_stream(x, self.weight, stream, self._sumsq, next_norm_weight, scaled)
+        return StreamStats(self._sumsq, parts, scaled, next_norm_weight)
 
     def __call__(self, x) -> torch.Tensor:
         rows = x.shape[0]
         if isinstance(x, StreamNorm):
-            if not self.takes_stream_norm(rows):
+            if not self.takes_stream_norm(rows, x.scaled is not None):
                 raise ValueError("this projection does not take a norm that is not computed (see takes_stream_norm)")
             out = self._buffer("_out", rows, self.out_dtype)
-            ops.gemm_skinny_normed(x.stream, x.weight, x.sumsq, x.parts, x.eps, self.weight, out)
+            ops.gemm_skinny_normed(x.stream, x.weight, x.sumsq, x.parts, x.eps, self.weight, out, scaled=x.scaled)
             return out
         if self.max_rows is not None and rows > self.max_rows:
             raise ValueError(f"{rows} rows exceed the {self.max_rows} this projection was sized for")

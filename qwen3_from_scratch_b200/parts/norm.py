@@ -12,7 +12,7 @@ import torch
 
 from ..kernels import ops
 from ..registry import register_part
-from .base import Norm, Runtime, StreamNorm, WeightSpec
+from .base import Norm, Runtime, StreamNorm, StreamStats, WeightSpec
 
 
 @register_part("norm", "rms_norm")
@@ -41,11 +41,11 @@ class RMSNorm(Norm):
         ops.add_rmsnorm(stream, delta, self.weight, out, self.eps)
         return out
 
-    def lazy(self, stream: torch.Tensor, stats) -> StreamNorm:
-        """This norm of the stream for a projection that applies it itself; ``stats`` = (sumsq, parts) of the
-        stream's rows as the projection that last added into the stream left them."""
-        sumsq, parts = stats
-        return StreamNorm(stream, self.weight, self.eps, sumsq, parts)
+    def lazy(self, stream: torch.Tensor, stats: StreamStats) -> StreamNorm:
+        """This norm of the stream for a projection that applies it itself, from what the projection that
+        last added into the stream left about its rows."""
+        scaled = stats.scaled if stats.scaled_for is self.weight else None
+        return StreamNorm(stream, self.weight, self.eps, stats.sumsq, stats.parts, scaled)
 
     def norm_rows(self, stream: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
         out = torch.empty(rows.numel(), self.dim, dtype=self.rt.dtype, device=stream.device)

@@ -225,9 +225,15 @@ def test_gemm_skinny_into_stream(shape):
     s = dev(stream.clone())
     parts = ops().sumsq_parts(N)
     sums = torch.full((parts + 1, ops().SUMSQ_ROWS), float("nan"), device="cuda")
+    next_w = 1 + 0.3 * torch.randn(N, generator=g)
+    scaled = torch.full((T, N), float("nan"), device="cuda", dtype=torch.bfloat16)
     for _ in range(2):  # the second call runs right after a launch that wrote a stream
         s.copy_(dev(stream))
         assert ops().gemm_skinny_into_stream(dev(x), dev(w), s, sums) == parts
+    s.copy_(dev(stream))
+    assert ops().gemm_skinny_into_stream(dev(x), dev(w), s, sums, dev(next_w), scaled) == parts
+    # the new rows times the next norm's weight, rounded once
+    assert torch.equal(scaled.cpu(), (s.cpu() * next_w).to(torch.bfloat16))
     want = stream.double() + x.double() @ w.double().t()
     close(s, want, "float32", scale=float(want.abs().max()), tol=f32_accumulation_tol(K))
     got = sums[:parts, :T].double().sum(0).cpu()
@@ -238,7 +244,8 @@ def test_gemm_skinny_into_stream(shape):
 @pytest.mark.parametrize("shape", [(1, 4096, 1024), (8, 6144, 1024), (16, 331, 96), (3, 70, 200), (9, 48, 8), (6, 64, 5000),
                                    (12, 2048, 4096)])
 @pytest.mark.parametrize("with_swiglu", [False, True])
-def test_gemm_skinny_normed(shape, with_swiglu):
+@pytest.mark.parametrize("operand", ["staged", "scaled"])
+def test_gemm_skinny_normed(shape, with_swiglu, operand):
     """rmsnorm(stream) W^T without a norm kernel: the stream times the norm weight goes into the product and
     1 / rms is applied after it, from partial sums of squares as gemm_skinny_into_stream leaves them."""
     T, N, K = shape
@@ -256,7 +263,10 @@ def test_gemm_skinny_normed(shape, with_swiglu):
     padded[:, :K] = stream
     sq[:, :T] = (padded.view(T, parts, 16) ** 2).sum(2).t()
     out = torch.full((T, N // 2 if with_swiglu else N), float("nan"), device="cuda", dtype=torch.bfloat16)
-    ops().gemm_skinny_normed(dev(stream), dev(nw), dev(sq), parts, eps, dev(w), out, swiglu_blocks=with_swiglu)
+    # "scaled": the operand comes ready, as gemm_skinny_into_stream leaves it; "staged": the kernel makes it
+    scaled = dev((stream * nw).to(torch.bfloat16)) if operand == "scaled" else None
+    ops().gemm_skinny_normed(dev(stream), dev(nw), dev(sq), parts, eps, dev(w), out, swiglu_blocks=with_swiglu,
+                             scaled=scaled)
     # what the kernel is specified to compute: the stream times the norm weight rounded once to bfloat16, the
     # product, then 1 / rms; against the plain norm followed by the product it differs by where that one rounding falls
     rounded = (stream * nw).to(torch.bfloat16).double()

@@ -232,8 +232,11 @@ def test_block_part_few_rows_run_without_norm_kernels(monkeypatch):
     norm_kernels = []
     real = ops.add_rmsnorm
     monkeypatch.setattr(ops, "add_rmsnorm", lambda *a, **k: (norm_kernels.append(1), real(*a, **k))[1])
-    results = []
-    for fused in (True, False):
+    from qwen3_from_scratch_b200.parts.base import NEXT_NORM_WEIGHT
+    # "scaled": the model has told the block which norm reads the stream next, so its last projection leaves
+    # the stream times that weight for it; "staged": nobody has, the next block makes the operand itself
+    for way in ("scaled", "staged", "norm kernels"):
+        fused = way != "norm kernels"
         if not fused:
             monkeypatch.setattr(type(block), "fuses", lambda self, rows: False)
         manager = CacheManager(layout, 4, 64, rt.max_seqs)
@@ -241,16 +244,19 @@ def test_block_part_few_rows_run_without_norm_kernels(monkeypatch):
         manager.open("r")
         manager.reserve("r", n)
         ctx = BatchContext(manager, storage, rt).build([Entry("r", [0] * n)], vocab_size=1)
-        ctx.per_step = {}
+        ctx.per_step = {NEXT_NORM_WEIGHT: block.first_norm_weight} if way == "scaled" else {}
         stream = x.cuda().clone()
         del norm_kernels[:]
         assert block.fuses(n) == fused
         pending = block.forward(stream, None, ctx, 0, True)
-        assert (pending is None and STREAM_SUMSQ in ctx.per_step) if fused else pending is not None
+        if fused:
+            assert pending is None
+            assert (ctx.per_step[STREAM_SUMSQ].scaled is not None) == (way == "scaled")
+        else:
+            assert pending is not None
         pending = block.forward(stream, pending, ctx, 1, True)
         assert len(norm_kernels) == (1 if fused else 4)
-        results.append(stream.clone() if fused else stream + pending.float())
-        close(results[-1], want, dtype)
+        close(stream.clone() if fused else stream + pending.float(), want, dtype)
     assert int(rt.status.item()) == 0
 
 
