@@ -133,15 +133,19 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
   }
   pdl_wait();
   pdl_launch_dependents();
-  // NORMED: warp w sums the partial sums of squares of rows w and w + 8; the first two per lane are asked
+  // NORMED: warp w sums the partial sums of squares of rows w and w + 8; the first ones per lane are asked
   // for here and added after the main loop, so that their latency runs beside the loop's
-  float ss_a[NT], ss_b[NT];
+  constexpr int SS_EARLY = NT == 1 ? 8 : 2;  // per lane: 32 SS_EARLY partial sums per row (a stream 4,096 wide has 256)
+  float ss_early[NT][SS_EARLY];
   if (NORMED) {
 #pragma unroll
     for (int i = 0; i < NT; ++i) {
       const int tok = i * 8 + warp;
-      ss_a[i] = (tok < T && lane < fuse.ss_parts) ? fuse.ss_in[(size_t)lane * GS_SS_ROWS + tok] : 0.f;
-      ss_b[i] = (tok < T && lane + 32 < fuse.ss_parts) ? fuse.ss_in[(size_t)(lane + 32) * GS_SS_ROWS + tok] : 0.f;
+#pragma unroll
+      for (int j = 0; j < SS_EARLY; ++j) {
+        const int p = lane + 32 * j;
+        ss_early[i][j] = (tok < T && p < fuse.ss_parts) ? fuse.ss_in[(size_t)p * GS_SS_ROWS + tok] : 0.f;
+      }
     }
   }
   // NORMED: the block first turns the stream's rows into the bfloat16 operand, all together: a thread takes
@@ -229,9 +233,11 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
 #pragma unroll
     for (int i = 0; i < NT; ++i) {
       const int tok = i * 8 + warp;
-      float ss = ss_a[i] + ss_b[i];
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < SS_EARLY; ++j) ss += ss_early[i][j];
       if (tok < T)
-        for (int p = lane + 64; p < fuse.ss_parts; p += 32) ss += fuse.ss_in[(size_t)p * GS_SS_ROWS + tok];
+        for (int p = lane + 32 * SS_EARLY; p < fuse.ss_parts; p += 32) ss += fuse.ss_in[(size_t)p * GS_SS_ROWS + tok];
       ss = warp_sum(ss);
       if (lane == 0) rs_s[tok] = 1.0f / sqrtf(ss / (float)K + fuse.eps);
     }
@@ -323,11 +329,12 @@ static int gemm_skinny_launch(const void* X, const void* W, void* out, int T, in
     q3::launch(kern, dim3(grid), dim3(GS_WARPS * 32), xs_bytes, stream, (const __nv_bfloat16*)X,                     \
                (const __nv_bfloat16*)W, (OutT*)out, T, N, K, ldo, fuse);                                              \
   } while (0)
-  // batches of a warp's share of K; up to three are fetched ahead where eight tokens leave the registers
+  // batches of a warp's share of K; up to three are fetched ahead of the wait, but only where the grid is one
+  // block per SM or less (o_proj and down_proj of a narrow model: 64 blocks): the registers of three batches
+  // leave room for one block per SM, and a larger grid would then run in waves whose later blocks fetch
+  // nothing ahead (at 4,096 wide, 384 blocks, that cost 8 % of the step)
   const int batches = ((K + 31) / 32 + wk * GS_UNROLL - 1) / (wk * GS_UNROLL);
-  // (with two token tiles only where the grid is small anyway, one block of 16 features per SM or fewer: the
-  // products into the stream, o_proj and down_proj, whose warps have two or three batches each)
-  const bool few_blocks = NT == 1 || (EPI == 2 && groups <= 148);
+  const bool few_blocks = grid <= 148u && (NT == 1 || EPI == 2);
   const int pre = few_blocks && wk == GS_WARPS ? (batches < 3 ? batches : 3) : 1;
   if (wk == 1) Q3_GS_GO(1, 1);
   else if (wk == 2) Q3_GS_GO(2, 1);
