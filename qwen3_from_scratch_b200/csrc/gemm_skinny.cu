@@ -16,12 +16,11 @@
 // Two more forms take the norm kernels out of a decode step (the reference's block: norm, mixer, add, norm,
 // feed-forward, add; models/transformer_block.py:38-46).  RMSNorm is x * rs * w with one scalar rs per row,
 // and a scalar commutes with the product: W (h * rs * w) = rs * (W (h * w)).  So
-//   * "normed in" (NORMED): X is the float32 residual stream itself; a lane multiplies its eight values by the
-//     norm weight, rounds once to bfloat16 and feeds the tensor core; the epilogue multiplies by
-//     rs = 1 / sqrt(sum(h^2) / K + eps), the sum coming from partial sums that the kernel before left;
-//   * "into the stream" (EPI 2): the product is added to the float32 stream in place, and each block of 16
-//     features leaves the sum of squares of its 16 new values per row, in a fixed order (no atomics): the
-//     partial sums that the next normed-in product reads.
+//   * "into the stream" (EPI 2): the product is added to the float32 stream in place; each block of 16
+//     features leaves the sum of squares of its 16 new values per row, in a fixed order (no atomics), and,
+//     given the weight of the norm that comes next, the new values times that weight, rounded once to bfloat16;
+//   * "normed in" (NORMED): X is that bfloat16 operand h * w; the epilogue multiplies the result by
+//     rs = 1 / sqrt(sum(h^2) / K + eps), the sum coming from the partial sums.
 //
 // Reference for the role: the projections of the reference are nn.Linear (models/self_attn.py:358-386,
 // models/feedback.py:28-34); its fused variant merges up and gate the same way (models/feedback.py:52-62).
@@ -60,27 +59,23 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
 // three batches; with all of them under way before the wait, what is left after it is one round trip for
 // the activations instead of one more to memory per batch.
 struct SkinnyFuse {
-  const float* stream;  // NORMED: the residual stream [T, K] float32, read in place of X
-  const float* norm_w;  // NORMED: the norm's weight [K]
   const float* ss_in;   // NORMED: [ss_parts][16] partial sums of squares of the stream's rows
   int ss_parts;
   float eps;
   float* ss_out;        // EPI 2: [ceil(N / 16)][16] partial sums of squares of the rows after the add
   const float* next_w;  // EPI 2, optional: weight [N] of the norm that comes next, and
-  __nv_bfloat16* scaled_out;  // [T, N]: the new rows times that weight, the operand of a NORMED == 2 product
+  __nv_bfloat16* scaled_out;  // [T, N]: the new rows times that weight, the operand of a NORMED product
   int early;            // EPI 2: the stream may be read ahead of the wait (the launch before did not write it)
 };
 
 constexpr int GS_SS_ROWS = 16;  // row pitch of the partial sums
-constexpr int GS_XS_PAD = 32;   // NORMED: elements between rows of the staged operand (a quarter-warp's 16-byte reads then miss each other's banks)
-constexpr int GS_XS_MAX_BYTES = 160 * 1024;
 
-// EPI 2: out is the float32 stream [T, N] and is added to.  NORMED (see the head of the file): 1 the operand is
-// made here from the stream, 2 X is the operand already (the product that last added into the stream left
-// it, scaled_out); both multiply the result by the row's 1 / rms.
-template <int NT, int WK, int EPI, typename OutT, int PRE = 1, int NORMED = 0>
+// EPI 2: out is the float32 stream [T, N] and is added to.  NORMED (see the head of the file): X is the stream
+// times a norm's weight (scaled_out of the product that last added into the stream), and the result is
+// multiplied by the row's 1 / rms.
+template <int NT, int WK, int EPI, typename OutT, int PRE = 1, bool NORMED = false>
 __global__ void __launch_bounds__(GS_WARPS * 32,
-                                  ((NT == 1 && WK > 1 && !(NORMED != 0 && PRE == 1)) || (NT == 2 && PRE > 1)) ? 1 : 3)
+                                  ((NT == 1 && WK > 1 && !(NORMED && PRE == 1)) || (NT == 2 && PRE > 1)) ? 1 : 3)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
                    OutT* __restrict__ out, int T, int N, int K, int ldo, const SkinnyFuse fuse) {
   constexpr int GROUPS = GS_WARPS / WK;  // feature groups per block
@@ -117,8 +112,6 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
   // way while that kernel finishes.  The activations are read only after the wait.
 #pragma unroll
   for (int p = 0; p < PRE; ++p) load_w(g_lo + p * GS_UNROLL, wl[p], wh[p]);
-  float4 w_first = make_float4(0.f, 0.f, 0.f, 0.f);  // NORMED: this thread's four norm weights of the first pass
-  if (NORMED == 1 && (int)threadIdx.x < K / 4) w_first = __ldg(reinterpret_cast<const float4*>(fuse.norm_w) + threadIdx.x);
   // EPI 2: the next norm's weight for this lane's feature (the same for all its elements)
   const float next_weight = (EPI == 2 && fuse.scaled_out != nullptr && active && row0 + (lane & 15) < N)
                                 ? fuse.next_w[row0 + (lane & 15)] : 0.f;
@@ -148,51 +141,16 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
       }
     }
   }
-  // NORMED: the block first turns the stream's rows into the bfloat16 operand, all together: a thread takes
-  // four neighbouring values of k (its slice of the norm weight was fetched ahead of the wait) of every row,
-  // so that all loads of the stream are in flight at once; the main loop then reads fragments from shared memory.
-  extern __shared__ __align__(16) unsigned char xs_raw[];
-  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(xs_raw);  // [8 NT][K + GS_XS_PAD]
-  const int xs_pitch = K + GS_XS_PAD;
-  if (NORMED == 1) {
-    for (int c0 = 0; c0 < K / 4; c0 += GS_WARPS * 32) {
-      const int c = c0 + threadIdx.x;
-      const bool in = c < K / 4;
-      const float4 wv = (c0 == 0) ? w_first : (in ? __ldg(reinterpret_cast<const float4*>(fuse.norm_w) + c) : make_float4(0.f, 0.f, 0.f, 0.f));
-#pragma unroll 1
-      for (int half = 0; half < NT; ++half) {  // eight rows at a time: their loads are in flight together
-        float4 xv4[8];
-#pragma unroll
-        for (int t = 0; t < 8; ++t)
-          xv4[t] = (in && half * 8 + t < T) ? *(reinterpret_cast<const float4*>(fuse.stream + (size_t)(half * 8 + t) * K) + c)
-                                            : make_float4(0.f, 0.f, 0.f, 0.f);
-        if (in) {
-#pragma unroll
-          for (int t = 0; t < 8; ++t) {
-            __nv_bfloat162 p0 = __floats2bfloat162_rn(xv4[t].x * wv.x, xv4[t].y * wv.y);
-            __nv_bfloat162 p1 = __floats2bfloat162_rn(xv4[t].z * wv.z, xv4[t].w * wv.w);
-            uint2 packed;
-            packed.x = *reinterpret_cast<uint32_t*>(&p0);
-            packed.y = *reinterpret_cast<uint32_t*>(&p1);
-            *reinterpret_cast<uint2*>(xs + (size_t)(half * 8 + t) * xs_pitch + 4 * c) = packed;
-          }
-        }
-      }
-    }
-    __syncthreads();
-  }
   const __nv_bfloat16* x_row[NT];
   bool x_ok[NT];
 #pragma unroll
   for (int i = 0; i < NT; ++i) {
     const int tok = i * 8 + gid;
-    x_ok[i] = NORMED == 1 || tok < T;  // the staged operand holds zeros for rows past T
-    x_row[i] = NORMED == 1 ? xs + (size_t)tok * xs_pitch + 8 * tid4 : X + (size_t)(x_ok[i] ? tok : 0) * K + 8 * tid4;
+    x_ok[i] = tok < T;
+    x_row[i] = X + (size_t)(x_ok[i] ? tok : 0) * K + 8 * tid4;
   }
   auto multiply = [&](int g0, const uint4 (&lo)[GS_UNROLL], const uint4 (&hi)[GS_UNROLL]) {
-    // groups whose activations are fetched together (from shared memory one at a time is enough, and with two
-    // token tiles it keeps the thread within the registers of three blocks per SM)
-    constexpr int XU = (NORMED == 1 && NT == 2) ? 1 : GS_UNROLL;
+    constexpr int XU = GS_UNROLL;  // groups whose activations are fetched together
 #pragma unroll
     for (int u0 = 0; u0 < GS_UNROLL; u0 += XU) {
       uint4 xv[XU][NT];
@@ -200,15 +158,9 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
       for (int u = 0; u < XU; ++u) {
         const size_t k = (size_t)(g0 + u0 + u) * 32;
         const bool in = g0 + u0 + u < g_hi && k + 8 * tid4 < (size_t)K;
-        if (NORMED == 1) {
-#pragma unroll
-          for (int i = 0; i < NT; ++i)
-            xv[u][i] = in ? *reinterpret_cast<const uint4*>(x_row[i] + k) : make_uint4(0, 0, 0, 0);
-        } else {
 #pragma unroll
           for (int i = 0; i < NT; ++i)
             xv[u][i] = (in && x_ok[i]) ? __ldg(reinterpret_cast<const uint4*>(x_row[i] + k)) : make_uint4(0, 0, 0, 0);
-        }
       }
 #pragma unroll
       for (int u = 0; u < XU; ++u)
@@ -306,12 +258,10 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
   }
 }
 
-template <int NT, int EPI, typename OutT, int NORMED = 0>
+template <int NT, int EPI, typename OutT, bool NORMED = false>
 static int gemm_skinny_launch(const void* X, const void* W, void* out, int T, int N, int K, int ldo,
                               cudaStream_t stream, SkinnyFuse fuse = SkinnyFuse{}) {
   if (EPI == 2) fuse.early = last_launch_was_plain(stream) ? 1 : 0;
-  const size_t xs_bytes = NORMED == 1 ? (size_t)8 * NT * (K + GS_XS_PAD) * sizeof(__nv_bfloat16) : 0;
-  if (xs_bytes > (size_t)GS_XS_MAX_BYTES) return Q3_ERR_SIZE;
   const int groups = (N + 15) / 16;
   // split K over more warps while that still leaves every warp at least 128 values of k and the
   // grid is short of about four blocks per SM
@@ -320,15 +270,8 @@ static int gemm_skinny_launch(const void* X, const void* W, void* out, int T, in
   const int per_block = GS_WARPS / wk;
   const unsigned grid = (groups + per_block - 1) / per_block;
 #define Q3_GS_GO(WK, PRE)                                                                          \
-  do {                                                                                                               \
-    auto kern = gemm_skinny_kernel<NT, WK, EPI, OutT, PRE, NORMED>;                                                   \
-    if (xs_bytes > 48 * 1024) {                                                                                       \
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)xs_bytes);       \
-      if (e != cudaSuccess) return (int)e;                                                                            \
-    }                                                                                                                 \
-    q3::launch(kern, dim3(grid), dim3(GS_WARPS * 32), xs_bytes, stream, (const __nv_bfloat16*)X,                     \
-               (const __nv_bfloat16*)W, (OutT*)out, T, N, K, ldo, fuse);                                              \
-  } while (0)
+  q3::launch(gemm_skinny_kernel<NT, WK, EPI, OutT, PRE, NORMED>, dim3(grid), dim3(GS_WARPS * 32), 0, stream,           \
+             (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (OutT*)out, T, N, K, ldo, fuse)
   // batches of a warp's share of K; up to three are fetched ahead of the wait, but only where the grid is one
   // block per SM or less (o_proj and down_proj of a narrow model: 64 blocks): the registers of three batches
   // leave room for one block per SM, and a larger grid would then run in waves whose later blocks fetch
@@ -373,21 +316,18 @@ extern "C" int q3_gemm_skinny(const void* X, const void* W, void* out, int T, in
 }
 
 // The forms that take the norm kernels out of a decode step (see the head of the file), T <= 16.
-// mode 0: out[T, N] bfloat16 = rs * (W (stream * norm_w)); mode 1: the same with W's rows alternating gate/up in
-// blocks of eight and out [T, N / 2] = up * silu(gate).  x is the float32 stream [T, K]; ss_in holds ss_parts
-// partial sums of squares per row ([ss_parts][16] floats) that add up to sum(stream[t]^2); rs = 1 / sqrt(sum / K + eps).
-// Modes 0 and 1 stage the rows in shared memory (16 (K + 32) bytes for up to 8 rows, twice that for 9 to 16)
-// and refuse a K for which that exceeds 160 KB.
-// modes 3 and 4: as 0 and 1, but x is the bfloat16 operand stream * norm_w itself [T, K], as mode 2 leaves it
-// (no staging, any K).
 // mode 2: x is bfloat16 [T, K]; out is the float32 stream [T, N] and becomes out + x W^T; ss_out
 // ([ceil(N / 16)][16] floats) receives the partial sums of squares of the new rows; if next_w (float32 [N]) and
 // scaled_out (bfloat16 [T, N]) are given, scaled_out = new rows * next_w, rounded once.
+// mode 3: x is such a scaled operand [T, K] of a stream whose rows' sums of squares add up from ss_in
+// ([ss_parts][16] floats): out[T, N] bfloat16 = rs * (x W^T) with rs = 1 / sqrt(sum / K + eps), which is
+// rmsnorm(stream) W^T.  mode 4: the same with W's rows alternating gate/up in blocks of eight and
+// out [T, N / 2] = up * silu(gate).
 extern "C" int q3_gemm_skinny_fused(const void* x, const void* W, void* out, int T, int N, int K, int ldo, int mode,
-                                    const float* norm_w, const float* ss_in, int ss_parts, float eps, float* ss_out,
-                                    const float* next_w, void* scaled_out, cudaStream_t stream) {
+                                    const float* ss_in, int ss_parts, float eps, float* ss_out, const float* next_w,
+                                    void* scaled_out, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
-  if (T > 16 || K <= 0 || K % 8 || mode < 0 || mode > 4 || ((mode == 1 || mode == 4) && N % 16)) return Q3_ERR_SIZE;
+  if (T > 16 || K <= 0 || K % 8 || mode < 2 || mode > 4 || (mode == 4 && N % 16)) return Q3_ERR_SIZE;
   if ((uintptr_t)x % 16 || (uintptr_t)W % 16 || (uintptr_t)out % 16) return Q3_ERR_ALIGN;
   using bf16 = __nv_bfloat16;
   q3::SkinnyFuse fuse{};
@@ -403,21 +343,10 @@ extern "C" int q3_gemm_skinny_fused(const void* x, const void* W, void* out, int
   fuse.ss_in = ss_in;
   fuse.ss_parts = ss_parts;
   fuse.eps = eps;
-  if (mode >= 3) {
-    if (mode == 4) {
-      if (T <= 8) return q3::gemm_skinny_launch<1, 1, bf16, 2>(x, W, out, T, N, K, ldo, stream, fuse);
-      return q3::gemm_skinny_launch<2, 1, bf16, 2>(x, W, out, T, N, K, ldo, stream, fuse);
-    }
-    if (T <= 8) return q3::gemm_skinny_launch<1, 0, bf16, 2>(x, W, out, T, N, K, ldo, stream, fuse);
-    return q3::gemm_skinny_launch<2, 0, bf16, 2>(x, W, out, T, N, K, ldo, stream, fuse);
+  if (mode == 4) {
+    if (T <= 8) return q3::gemm_skinny_launch<1, 1, bf16, true>(x, W, out, T, N, K, ldo, stream, fuse);
+    return q3::gemm_skinny_launch<2, 1, bf16, true>(x, W, out, T, N, K, ldo, stream, fuse);
   }
-  if (!norm_w || (uintptr_t)norm_w % 16) return Q3_ERR_SIZE;
-  fuse.stream = (const float*)x;
-  fuse.norm_w = norm_w;
-  if (mode == 1) {
-    if (T <= 8) return q3::gemm_skinny_launch<1, 1, bf16, 1>(nullptr, W, out, T, N, K, ldo, stream, fuse);
-    return q3::gemm_skinny_launch<2, 1, bf16, 1>(nullptr, W, out, T, N, K, ldo, stream, fuse);
-  }
-  if (T <= 8) return q3::gemm_skinny_launch<1, 0, bf16, 1>(nullptr, W, out, T, N, K, ldo, stream, fuse);
-  return q3::gemm_skinny_launch<2, 0, bf16, 1>(nullptr, W, out, T, N, K, ldo, stream, fuse);
+  if (T <= 8) return q3::gemm_skinny_launch<1, 0, bf16, true>(x, W, out, T, N, K, ldo, stream, fuse);
+  return q3::gemm_skinny_launch<2, 0, bf16, true>(x, W, out, T, N, K, ldo, stream, fuse);
 }

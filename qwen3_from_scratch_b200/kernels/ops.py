@@ -76,7 +76,7 @@ _SIGNATURES = {
                        _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
                        _c_void_p, _c_int, _c_void_p, _c_void_p],
     "q3_gemm_skinny": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
-    "q3_gemm_skinny_fused": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
+    "q3_gemm_skinny_fused": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                              _c_int, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "q3_sample": [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ull, _c_int,
                   _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p],
@@ -383,41 +383,25 @@ def sumsq_parts(features: int) -> int:
     return (features + 15) // 16
 
 
-def gemm_skinny_normed_takes(rows: int, weight: torch.Tensor) -> bool:
-    """The few-rows product that applies a norm itself stages the rows in shared memory: 16 (K + 32) bytes for
-    up to 8 rows, twice that for 9 to 16, at most 160 KB."""
-    return gemm_skinny_takes(rows, weight) and (1 if rows <= 8 else 2) * 16 * (weight.shape[1] + 32) <= 160 * 1024
-
-
-def gemm_skinny_normed(stream: torch.Tensor, norm_weight: torch.Tensor, sumsq: torch.Tensor, parts: int, eps: float,
-                       w: torch.Tensor, out: torch.Tensor, swiglu_blocks: bool = False,
-                       scaled: Optional[torch.Tensor] = None) -> None:
-    """out = rmsnorm(stream) @ w^T for up to 16 rows without a norm kernel: the float32 stream is
-    multiplied by the norm weight on its way into the tensor core and the row's 1 / rms in the
-    epilogue, from ``parts`` partial sums of squares per row (``sumsq[p, t]``, as
-    ``gemm_skinny_into_stream`` leaves them).  ``scaled``: the bfloat16 operand ``stream * norm_weight``
-    if the product that last added into the stream left it (then nothing is staged and any width is
-    taken).  ``swiglu_blocks`` as in ``gemm_skinny``."""
-    _check("gemm_skinny_normed.stream", stream, torch.float32)
-    _check("gemm_skinny_normed.norm_weight", norm_weight, torch.float32)
+def gemm_skinny_normed(scaled: torch.Tensor, sumsq: torch.Tensor, parts: int, eps: float, w: torch.Tensor,
+                       out: torch.Tensor, swiglu_blocks: bool = False) -> None:
+    """out = rmsnorm(stream) @ w^T for up to 16 rows without a norm kernel.  ``scaled`` is the stream times
+    the norm's weight in bfloat16 and ``sumsq[p, t]`` for ``p < parts`` are partial sums of squares of the
+    stream's row ``t``, both as ``gemm_skinny_into_stream`` leaves them; the product of ``scaled`` is multiplied
+    by the row's 1 / rms = 1 / sqrt(sum / K + eps) before it is stored.  ``swiglu_blocks`` as in ``gemm_skinny``."""
+    _check("gemm_skinny_normed.scaled", scaled, torch.bfloat16)
     _check("gemm_skinny_normed.sumsq", sumsq, torch.float32)
     _check("gemm_skinny_normed.w", w, torch.bfloat16)
     _check("gemm_skinny_normed.out", out, torch.bfloat16)
-    T, K = stream.shape
+    T, K = scaled.shape
     N = w.shape[0]
     want_cols = N // 2 if swiglu_blocks else N
-    if (w.shape[1] != K or tuple(out.shape) != (T, want_cols) or norm_weight.numel() != K or sumsq.dim() != 2
+    if (w.shape[1] != K or tuple(out.shape) != (T, want_cols) or sumsq.dim() != 2
             or sumsq.shape[1] != SUMSQ_ROWS or not 0 < parts <= sumsq.shape[0]):
-        raise KernelError(f"gemm_skinny_normed: stream {tuple(stream.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, "
-                          f"norm weight {tuple(norm_weight.shape)}, sums {tuple(sumsq.shape)} of which {parts}")
-    x, mode = stream, 1 if swiglu_blocks else 0
-    if scaled is not None:
-        _check("gemm_skinny_normed.scaled", scaled, torch.bfloat16)
-        if tuple(scaled.shape) != (T, K):
-            raise KernelError(f"gemm_skinny_normed: scaled operand {tuple(scaled.shape)} for a stream {(T, K)}")
-        x, mode = scaled, 4 if swiglu_blocks else 3
-    code = library().q3_gemm_skinny_fused(x.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, want_cols, mode,
-                                          norm_weight.data_ptr(), sumsq.data_ptr(), int(parts), float(eps), None, None,
+        raise KernelError(f"gemm_skinny_normed: operand {tuple(scaled.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, "
+                          f"sums {tuple(sumsq.shape)} of which {parts}")
+    code = library().q3_gemm_skinny_fused(scaled.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, want_cols,
+                                          4 if swiglu_blocks else 3, sumsq.data_ptr(), int(parts), float(eps), None, None,
                                           None, _stream())
     _done("gemm_skinny_normed", code, f"T {T} N {N} K {K}")
 
@@ -445,7 +429,7 @@ def gemm_skinny_into_stream(x: torch.Tensor, w: torch.Tensor, stream: torch.Tens
         if next_weight.numel() != N or tuple(scaled.shape) != (T, N):
             raise KernelError(f"gemm_skinny_into_stream: next weight {tuple(next_weight.shape)}, scaled "
                               f"{tuple(scaled.shape)} for a stream {(T, N)}")
-    code = library().q3_gemm_skinny_fused(x.data_ptr(), w.data_ptr(), stream.data_ptr(), T, N, K, N, 2, None, None, 0,
+    code = library().q3_gemm_skinny_fused(x.data_ptr(), w.data_ptr(), stream.data_ptr(), T, N, K, N, 2, None, 0,
                                           0.0, sumsq.data_ptr(), _ptr(next_weight), _ptr(scaled), _stream())
     _done("gemm_skinny_into_stream", code, f"T {T} N {N} K {K}")
     return parts

@@ -80,8 +80,8 @@ class GQAAttention(Mixer):
 
     fuses_stream = True
 
-    def can_fuse_stream(self, rows: int, scaled: bool = True) -> bool:
-        return self.qkv.takes_stream_norm(rows, scaled) and self.o_proj.can_add_into_stream(rows)
+    def can_fuse_stream(self, rows: int) -> bool:
+        return self.qkv.takes_stream_norm(rows) and self.o_proj.can_add_into_stream(rows)
 
     def forward(self, x, ctx: StepContext, cache_id: Optional[int], write_cache: bool, into_stream=None,
                 next_norm_weight=None):

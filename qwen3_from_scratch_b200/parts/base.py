@@ -188,16 +188,15 @@ class StreamStats:
 @dataclass
 class StreamNorm:
     """RMSNorm of the residual stream, not computed: a projection that takes it (``Linear``, for a few
-    rows) multiplies the float32 stream by ``weight`` on its way into the product (or takes ``scaled``,
-    the stream times this weight in bfloat16, if the projection before left it) and by each row's
-    1 / rms afterwards, so that no norm kernel runs."""
+    rows) runs on ``scaled``, the stream times the norm's ``weight`` in bfloat16 as the projection before
+    left it, and multiplies its result by each row's 1 / rms (from ``sumsq``), so that no norm kernel runs."""
 
     stream: torch.Tensor
     weight: torch.Tensor
     eps: float
     sumsq: torch.Tensor
     parts: int
-    scaled: Optional[torch.Tensor] = None
+    scaled: torch.Tensor
 
     @property
     def shape(self):

@@ -60,13 +60,8 @@ class PreNormBlock(Block):
         shared = ctx.__dict__.setdefault("per_step", {})
         stats = shared.pop(STREAM_SUMSQ, None)  # of the stream as the block before left it
         if self.fuses(stream.shape[0]):
-            rows = stream.shape[0]
-            x = None
-            if stats is not None and pending is None:
-                x = self.norm1.lazy(stream, stats)
-                if not self.mixer.can_fuse_stream(rows, x.scaled is not None):
-                    x = None
-            if x is None:
+            x = self.norm1.lazy(stream, stats) if pending is None else None
+            if x is None:  # the first block of a step, or one that nobody prepared the stream for
                 x = self.norm1.add_norm(stream, pending)
             stats = self.mixer.forward(x, ctx, cache_id, write_cache, into_stream=stream,
                                        next_norm_weight=self.norm2.weight)

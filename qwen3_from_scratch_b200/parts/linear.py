@@ -59,12 +59,10 @@ class Linear:
             return torch.empty(rows, self.out_features, dtype=dtype, device=self.weight.device)
         return buf[:rows]
 
-    def takes_stream_norm(self, rows: int, scaled: bool = True) -> bool:
-        """Whether ``self(StreamNorm)`` works for this many rows (a bfloat16 weight, a few rows); without the
-        scaled operand the rows are staged in shared memory, which bounds the width."""
-        if self.full_precision or self.out_dtype != torch.bfloat16 or self._out is None:
-            return False
-        return ops.gemm_skinny_takes(rows, self.weight) if scaled else ops.gemm_skinny_normed_takes(rows, self.weight)
+    def takes_stream_norm(self, rows: int) -> bool:
+        """Whether ``self(StreamNorm)`` works for this many rows (a bfloat16 weight, a few rows)."""
+        return (not self.full_precision and self.out_dtype == torch.bfloat16 and self._out is not None
+                and ops.gemm_skinny_takes(rows, self.weight))
 
     def can_add_into_stream(self, rows: int) -> bool:
         return self._sumsq is not None and ops.gemm_skinny_takes(rows, self.weight)
@@ -80,10 +78,10 @@ class Linear:
     def __call__(self, x) -> torch.Tensor:
         rows = x.shape[0]
         if isinstance(x, StreamNorm):
-            if not self.takes_stream_norm(rows, x.scaled is not None):
+            if not self.takes_stream_norm(rows):
                 raise ValueError("this projection does not take a norm that is not computed (see takes_stream_norm)")
             out = self._buffer("_out", rows, self.out_dtype)
-            ops.gemm_skinny_normed(x.stream, x.weight, x.sumsq, x.parts, x.eps, self.weight, out, scaled=x.scaled)
+            ops.gemm_skinny_normed(x.scaled, x.sumsq, x.parts, x.eps, self.weight, out)
             return out
         if self.max_rows is not None and rows > self.max_rows:
             raise ValueError(f"{rows} rows exceed the {self.max_rows} this projection was sized for")

@@ -50,17 +50,15 @@ class SwiGLU(FeedForward):
 
     fuses_stream = True
 
-    def can_fuse_stream(self, rows: int, scaled: bool = True) -> bool:
-        return (self.blocks_of_eight and self.gate_up.takes_stream_norm(rows, scaled)
-                and self.down.can_add_into_stream(rows))
+    def can_fuse_stream(self, rows: int) -> bool:
+        return self.blocks_of_eight and self.gate_up.takes_stream_norm(rows) and self.down.can_add_into_stream(rows)
 
     def forward(self, x, into_stream=None, next_norm_weight=None):
         act = self._act[: x.shape[0]]
         rows = x.shape[0]
         if isinstance(x, StreamNorm):
             # decoding without norm kernels: the norm is applied inside the gate/up product
-            ops.gemm_skinny_normed(x.stream, x.weight, x.sumsq, x.parts, x.eps, self.gate_up.weight, act,
-                                   swiglu_blocks=True, scaled=x.scaled)
+            ops.gemm_skinny_normed(x.scaled, x.sumsq, x.parts, x.eps, self.gate_up.weight, act, swiglu_blocks=True)
         elif self.blocks_of_eight and ops.gemm_skinny_takes(rows, self.gate_up.weight):
             # decoding: stream the weight once, activation applied before the store
             ops.gemm_skinny(x, self.gate_up.weight, act, swiglu_blocks=True)

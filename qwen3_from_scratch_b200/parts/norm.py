@@ -41,11 +41,12 @@ class RMSNorm(Norm):
         ops.add_rmsnorm(stream, delta, self.weight, out, self.eps)
         return out
 
-    def lazy(self, stream: torch.Tensor, stats: StreamStats) -> StreamNorm:
-        """This norm of the stream for a projection that applies it itself, from what the projection that
-        last added into the stream left about its rows."""
-        scaled = stats.scaled if stats.scaled_for is self.weight else None
-        return StreamNorm(stream, self.weight, self.eps, stats.sumsq, stats.parts, scaled)
+    def lazy(self, stream: torch.Tensor, stats: StreamStats) -> Optional[StreamNorm]:
+        """This norm of the stream for a projection that applies it itself, if the projection that last
+        added into the stream prepared the stream for this norm's weight; else None."""
+        if stats is None or stats.scaled is None or stats.scaled_for is not self.weight:
+            return None
+        return StreamNorm(stream, self.weight, self.eps, stats.sumsq, stats.parts, stats.scaled)
 
     def norm_rows(self, stream: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
         out = torch.empty(rows.numel(), self.dim, dtype=self.rt.dtype, device=stream.device)

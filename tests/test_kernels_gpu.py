@@ -242,12 +242,12 @@ def test_gemm_skinny_into_stream(shape):
 
 
 @pytest.mark.parametrize("shape", [(1, 4096, 1024), (8, 6144, 1024), (16, 331, 96), (3, 70, 200), (9, 48, 8), (6, 64, 5000),
-                                   (12, 2048, 4096)])
+                                   (12, 2048, 4096), (8, 1024, 5120)])
 @pytest.mark.parametrize("with_swiglu", [False, True])
-@pytest.mark.parametrize("operand", ["staged", "scaled"])
-def test_gemm_skinny_normed(shape, with_swiglu, operand):
-    """rmsnorm(stream) W^T without a norm kernel: the stream times the norm weight goes into the product and
-    1 / rms is applied after it, from partial sums of squares as gemm_skinny_into_stream leaves them."""
+def test_gemm_skinny_normed(shape, with_swiglu):
+    """rmsnorm(stream) W^T without a norm kernel: the operand is the stream times the norm weight in bfloat16,
+    and 1 / rms is applied after the product, from partial sums of squares, both laid out as
+    gemm_skinny_into_stream leaves them."""
     T, N, K = shape
     if with_swiglu:
         N = N // 16 * 16
@@ -256,22 +256,18 @@ def test_gemm_skinny_normed(shape, with_swiglu, operand):
     stream = torch.randn(T, K, generator=g) * 4
     nw = 1 + 0.2 * torch.randn(K, generator=g)
     w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
-    # partial sums the way the producer lays them out: one per 16 columns of the stream, row pitch 16
-    parts = ops().sumsq_parts(K)
+    parts = ops().sumsq_parts(K)  # one partial sum per 16 columns of the stream, row pitch 16
     sq = torch.zeros(parts, ops().SUMSQ_ROWS)
     padded = torch.zeros(T, parts * 16)
     padded[:, :K] = stream
     sq[:, :T] = (padded.view(T, parts, 16) ** 2).sum(2).t()
+    scaled = (stream * nw).to(torch.bfloat16)
     out = torch.full((T, N // 2 if with_swiglu else N), float("nan"), device="cuda", dtype=torch.bfloat16)
-    # "scaled": the operand comes ready, as gemm_skinny_into_stream leaves it; "staged": the kernel makes it
-    scaled = dev((stream * nw).to(torch.bfloat16)) if operand == "scaled" else None
-    ops().gemm_skinny_normed(dev(stream), dev(nw), dev(sq), parts, eps, dev(w), out, swiglu_blocks=with_swiglu,
-                             scaled=scaled)
-    # what the kernel is specified to compute: the stream times the norm weight rounded once to bfloat16, the
-    # product, then 1 / rms; against the plain norm followed by the product it differs by where that one rounding falls
-    rounded = (stream * nw).to(torch.bfloat16).double()
+    ops().gemm_skinny_normed(dev(scaled), dev(sq), parts, eps, dev(w), out, swiglu_blocks=with_swiglu)
+    # what the kernel is specified to compute: the product of the rounded operand, then 1 / rms; against the
+    # plain norm followed by the product it differs by where the one rounding of the activations falls
     rs = 1.0 / torch.sqrt((stream.double() ** 2).mean(1, keepdim=True) + eps)
-    want = (rounded @ w.double().t()) * rs
+    want = (scaled.double() @ w.double().t()) * rs
     loose = plain.rms_norm(stream.double(), nw.double(), eps) @ w.double().t()
     assert float((want - loose).abs().max()) <= 4e-3 * float(loose.abs().max())
     if with_swiglu:
@@ -279,16 +275,6 @@ def test_gemm_skinny_normed(shape, with_swiglu, operand):
         up = want.view(T, N // 16, 2, 8)[:, :, 1].reshape(T, N // 2)
         want = up * gate * torch.sigmoid(gate)
     close(out, want, "bfloat16")
-
-
-def test_gemm_skinny_normed_refuses_rows_too_wide_to_stage():
-    w = torch.zeros(16, 8192, device="cuda", dtype=torch.bfloat16)
-    assert ops().gemm_skinny_normed_takes(8, w) and not ops().gemm_skinny_normed_takes(9, w)
-    stream = torch.zeros(9, 8192, device="cuda")
-    sq = torch.zeros(ops().sumsq_parts(8192), ops().SUMSQ_ROWS, device="cuda")
-    out = torch.empty(9, 16, device="cuda", dtype=torch.bfloat16)
-    with pytest.raises(ops().KernelSizeError):
-        ops().gemm_skinny_normed(stream, torch.ones(8192, device="cuda"), sq, sq.shape[0], 1e-6, w, out)
 
 
 @pytest.mark.parametrize("shape", [(128, 128, 64), (2048, 4096, 1024), (100, 200, 72), (257, 331, 96), (1, 64, 8),

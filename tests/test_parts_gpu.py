@@ -198,11 +198,11 @@ def test_block_part(dtype):
 
 
 def test_block_part_few_rows_run_without_norm_kernels(monkeypatch):
-    """Up to 16 rows in bfloat16: the block's output projections add into the stream themselves and its
-    input projections apply the norms, from partial sums of squares passed from one to the next (and from
-    one block to the next through the step's shared data).  Two calls of the block on caches of their own,
-    as two layers with the same weights would be, against the plain layer applied twice; one norm kernel in
-    all (the first call has no sums yet); and the same block made to take the path with norm kernels."""
+    """Up to 16 rows in bfloat16: the block's output projections add into the stream themselves and leave its
+    rows' sums of squares and the rows times the next norm's weight; the input projections run on that operand
+    and apply 1 / rms (passed from one block to the next through the step's shared data).  Two calls of the
+    block on caches of their own, as two layers with the same weights would be, against the plain layer
+    applied twice; how many norm kernels run; and the same block made to take the path with norm kernels."""
     from qwen3_from_scratch_b200.cache import CacheManager, layout_of
     from qwen3_from_scratch_b200.cache.storage import CacheStorage
     from qwen3_from_scratch_b200.engine.batch import BatchContext, Entry
@@ -233,9 +233,9 @@ def test_block_part_few_rows_run_without_norm_kernels(monkeypatch):
     real = ops.add_rmsnorm
     monkeypatch.setattr(ops, "add_rmsnorm", lambda *a, **k: (norm_kernels.append(1), real(*a, **k))[1])
     from qwen3_from_scratch_b200.parts.base import NEXT_NORM_WEIGHT
-    # "scaled": the model has told the block which norm reads the stream next, so its last projection leaves
-    # the stream times that weight for it; "staged": nobody has, the next block makes the operand itself
-    for way in ("scaled", "staged", "norm kernels"):
+    # "told": the model has told the block which norm reads the stream next, so its last projection leaves the
+    # stream times that weight and the next call needs no norm kernel; "not told": the next call runs its first norm
+    for way in ("told", "not told", "norm kernels"):
         fused = way != "norm kernels"
         if not fused:
             monkeypatch.setattr(type(block), "fuses", lambda self, rows: False)
@@ -244,18 +244,18 @@ def test_block_part_few_rows_run_without_norm_kernels(monkeypatch):
         manager.open("r")
         manager.reserve("r", n)
         ctx = BatchContext(manager, storage, rt).build([Entry("r", [0] * n)], vocab_size=1)
-        ctx.per_step = {NEXT_NORM_WEIGHT: block.first_norm_weight} if way == "scaled" else {}
+        ctx.per_step = {NEXT_NORM_WEIGHT: block.first_norm_weight} if way == "told" else {}
         stream = x.cuda().clone()
         del norm_kernels[:]
         assert block.fuses(n) == fused
         pending = block.forward(stream, None, ctx, 0, True)
         if fused:
             assert pending is None
-            assert (ctx.per_step[STREAM_SUMSQ].scaled is not None) == (way == "scaled")
+            assert (ctx.per_step[STREAM_SUMSQ].scaled is not None) == (way == "told")
         else:
             assert pending is not None
         pending = block.forward(stream, pending, ctx, 1, True)
-        assert len(norm_kernels) == (1 if fused else 4)
+        assert len(norm_kernels) == {"told": 1, "not told": 2, "norm kernels": 4}[way]
         close(stream.clone() if fused else stream + pending.float(), want, dtype)
     assert int(rt.status.item()) == 0
 
