@@ -45,7 +45,16 @@ TINY_C = dict(
     head_dim=48, intermediate_size=136, rms_norm_eps=1e-6, rope_theta=50000.0, tie_word_embeddings=False,
     layer_types=["sliding_attention", "full_attention"], sliding_window=40)
 
-TINY = {"a": (TINY_A, 0), "b": (TINY_B, 2), "c": (TINY_C, 5)}
+# and one with the head size the serving kernels are made for (128, pages of 16: the TMA decode kernel, the
+# tcgen05 portion kernel and product, the decode step without norm and qkv_post kernels), heads * head_dim
+# != width, a windowed layer beside a full one
+TINY_D = dict(
+    architectures=["Qwen3ForCausalLM"], vocab_size=500, hidden_size=256, hidden_act="silu",
+    num_hidden_layers=2, max_position_embeddings=1024, num_key_value_heads=2, num_attention_heads=4,
+    head_dim=128, intermediate_size=384, rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=True,
+    layer_types=["full_attention", "sliding_attention"], sliding_window=100)
+
+TINY = {"a": (TINY_A, 0), "b": (TINY_B, 2), "c": (TINY_C, 5), "d": (TINY_D, 9)}
 
 
 def make_folder(tmp_path_factory, key, dtype="bfloat16", float32_tensors=None):

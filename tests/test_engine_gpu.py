@@ -56,12 +56,16 @@ def test_greedy_generation_equals_the_plain_implementation(tiny_folders, key, pa
     assert engine.session.manager.free_slots() == 4
 
 
-def test_bfloat16_generation_follows_plain_within_near_ties(tiny_folders):
+@pytest.mark.parametrize("key,page,length", [("a", 4, 17), ("d", 16, 150)])
+def test_bfloat16_generation_follows_plain_within_near_ties(tiny_folders, key, page, length):
+    """Through the engine as it serves (graphs, lookahead); "d" has the head size of the serving kernels, so
+    its prompt runs on the tcgen05 kernels and its decode steps without norm and qkv_post kernels."""
     from qwen3_from_scratch_b200.engine.engine import SyncEngine
-    folder = tiny_folders["a"]
+    folder = tiny_folders[key]
     cfg, w = plain.read_model_folder(folder)
-    prompt = random_tokens(256, 17, 2)
-    engine = SyncEngine(folder, dtype="bfloat16", block_size=4, num_pages=64, max_num_seqs=2, max_num_tokens=32)
+    prompt = random_tokens(TINY[key][0]["vocab_size"], length, 2)
+    engine = SyncEngine(folder, dtype="bfloat16", block_size=page, num_pages=64, max_num_seqs=2,
+                        max_num_tokens=max(32, length))
     got = engine.generate(prompt, max_new_tokens=12, ignore_eos=True)
     ids = list(prompt)
     for token in got:
