@@ -36,7 +36,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: Qwen3-0.6B layer sizes
+# the configuration the headline figure is quoted on: Qwen3-0.6B layer sizes
 CONFIG = dict(
     architectures=["Qwen3ForCausalLM"], vocab_size=151936, hidden_size=1024, hidden_act="silu",
     num_hidden_layers=28, max_position_embeddings=40960, num_key_value_heads=8, num_attention_heads=16,

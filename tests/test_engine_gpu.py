@@ -29,7 +29,7 @@ def greedy_by_plain(folder, prompt, n):
 
 @pytest.mark.parametrize("key,page", [("a", 4), ("b", 8)])
 def test_greedy_generation_equals_the_plain_implementation(tiny_folders, key, page):
-    """float32 end to end: the BASELINE tiny workloads (prompts of 5/17/31 and 1/9/33/64/100 tokens,
+    """float32 end to end: two tiny workloads (prompts of 5/17/31 and 1/9/33/64/100 tokens,
     16 greedy tokens each) through batch_generate with chunked prompts and continuous batching."""
     from qwen3_from_scratch_b200.engine.engine import SyncEngine
     folder = tiny_folders[key]
