@@ -75,7 +75,8 @@ constexpr int GS_SS_ROWS = 16;  // row pitch of the partial sums
 // multiplied by the row's 1 / rms.
 template <int NT, int WK, int EPI, typename OutT, int PRE = 1, bool NORMED = false>
 __global__ void __launch_bounds__(GS_WARPS * 32,
-                                  ((NT == 1 && WK > 1 && !(NORMED && PRE == 1)) || (NT == 2 && PRE > 1)) ? 1 : 3)
+                                  ((NT == 1 && WK > 1 && !(NORMED && PRE == 1)) || (NT == 2 && PRE > 1)) ? 1
+                                  : (NT == 2 && EPI == 2) ? 2 : 3)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
                    OutT* __restrict__ out, int T, int N, int K, int ldo, const SkinnyFuse fuse) {
   constexpr int GROUPS = GS_WARPS / WK;  // feature groups per block
@@ -218,6 +219,13 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
   } else if (EPI == 2) {
     // added into the stream; the 16 lanes that share a row leave the sum of squares of their new values
     float* stream = reinterpret_cast<float*>(out);
+    if (!fuse.early) {  // all of them asked for before the first store, which the compiler could not prove apart from them
+#pragma unroll
+      for (int j = 0; j < 4 * NT; ++j) {
+        const int e = lane + 32 * j, f = e & 15, tok = e >> 4;
+        before[j] = (tok < T && row0 + f < N) ? stream[(size_t)tok * ldo + row0 + f] : 0.f;
+      }
+    }
 #pragma unroll
     for (int j = 0; j < 4 * NT; ++j) {
       const int e = lane + 32 * j, f = e & 15, tok = e >> 4;
@@ -227,9 +235,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
         float v = 0.f;
 #pragma unroll
         for (int s = 0; s < WK; ++s) v += red[warp + s][f][tok];
-        float* at = stream + (size_t)tok * ldo + row0 + f;
-        h = (fuse.early ? before[j] : *at) + v;
-        *at = h;
+        h = before[j] + v;
+        stream[(size_t)tok * ldo + row0 + f] = h;
         if (fuse.scaled_out != nullptr)
           fuse.scaled_out[(size_t)tok * ldo + row0 + f] = __float2bfloat16_rn(h * next_weight);
       }

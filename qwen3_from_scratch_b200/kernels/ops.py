@@ -383,6 +383,14 @@ def sumsq_parts(features: int) -> int:
     return (features + 15) // 16
 
 
+def gemm_skinny_normed_pays(rows: int, weight: torch.Tensor) -> bool:
+    """Whether a decode step without norm kernels is the faster one for this many rows and this input width.
+    Measured against the step with norm kernels, decode at context 4,096: up to 8 rows it wins at every width
+    tried (1,024: +4 to +10 %, 2,048: +1 to +4 %, 4,096: +0.4 to +2.5 %); with 9 to 16 rows +5 % at 1,024,
+    +2.6 % at 2,048 and -2.2 % at 4,096, where the product with two token tiles is short of registers."""
+    return rows <= 8 or weight.shape[1] <= 3072
+
+
 def gemm_skinny_normed(scaled: torch.Tensor, sumsq: torch.Tensor, parts: int, eps: float, w: torch.Tensor,
                        out: torch.Tensor, swiglu_blocks: bool = False) -> None:
     """out = rmsnorm(stream) @ w^T for up to 16 rows without a norm kernel.  ``scaled`` is the stream times

@@ -60,9 +60,9 @@ class Linear:
         return buf[:rows]
 
     def takes_stream_norm(self, rows: int) -> bool:
-        """Whether ``self(StreamNorm)`` works for this many rows (a bfloat16 weight, a few rows)."""
+        """Whether ``self(StreamNorm)`` works for this many rows (a bfloat16 weight, a few rows) and pays."""
         return (not self.full_precision and self.out_dtype == torch.bfloat16 and self._out is not None
-                and ops.gemm_skinny_takes(rows, self.weight))
+                and ops.gemm_skinny_takes(rows, self.weight) and ops.gemm_skinny_normed_pays(rows, self.weight))
 
     def can_add_into_stream(self, rows: int) -> bool:
         return self._sumsq is not None and ops.gemm_skinny_takes(rows, self.weight)
