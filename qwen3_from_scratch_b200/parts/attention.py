@@ -6,6 +6,8 @@ rotation, keys/values written to pages, causal attention over the cache, output 
 models/attn.py:388-499 (scale = head_dim^-0.5, q head h reads kv head h // (Hq / Hkv)).
 The window (a query at position p reads keys p - window < n <= p) is what config.json's
 ``sliding_window`` asks of a layer; the reference itself never reads that key.
+In a step where every row brings one token the decode attention kernel does the head norm, the
+rotation and the page write itself, from the raw QKV projection.
 """
 
 from __future__ import annotations

@@ -2,7 +2,9 @@
 
 Reference: models/transformer_block.py:38-46.  The residual stream is float32 and the sums are
 fused into the norms: a block receives the previous sub-layer's output as ``pending`` and hands
-its own feed-forward output on in the same way.
+its own feed-forward output on in the same way.  With a few rows in bfloat16 (decoding) the sums
+and the norms move into the projections instead (``PreNormBlock.fuses``): the last projection of a
+sub-layer adds into the stream, the first one of the next applies the norm, and no norm kernel runs.
 """
 
 from __future__ import annotations

@@ -3,8 +3,9 @@
 bfloat16: with more than 16 rows the product is a library call (cuBLAS through ``torch.mm``),
 as in the reference's engine, whose projections are ``nn.Linear`` (models/self_attn.py:358-386,
 models/feedback.py:28-34); with up to 16 rows (decoding) it is the engine's own weight-streaming
-tensor-core kernel.  float32: the engine's own FFMA kernel, never a
-reduced-precision mode.  A weight that was stored in float32 keeps its float32
+tensor-core kernel, which can also add its result into the residual stream (``into_stream``) and
+apply an RMSNorm of the stream that was never computed (``StreamNorm``).  float32: the engine's own
+FFMA kernel, never a reduced-precision mode.  A weight that was stored in float32 keeps its float32
 product even in a bfloat16 run.
 """
 
