@@ -238,7 +238,7 @@ def decode_bench(engine, batch, context, steps, warmup, vocab):
     on the device alone.  Returns (device seconds, e2e seconds, launches per step, h2d, d2h bytes)."""
     import torch
 
-    from qwen3_from_scratch_b200.engine.request import RequestStatus, SamplingParams
+    from qwen3_from_scratch_b200.engine.request import SamplingParams
     from qwen3_from_scratch_b200.kernels import ops
 
     g = torch.Generator().manual_seed(1234 + batch)

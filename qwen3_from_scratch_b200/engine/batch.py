@@ -10,7 +10,7 @@ tensor per array, each with a copy of its own: inference/model_worker.py:177-210
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Hashable, List, Optional, Sequence, Tuple
+from typing import Hashable, List, Optional, Sequence
 
 import torch
 

@@ -8,7 +8,7 @@ still in their prompt: inference/model_worker.py:212-227).
 
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from typing import Dict, Optional
 
 import torch
 

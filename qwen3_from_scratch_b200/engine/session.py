@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import gc
 from collections import OrderedDict
-from typing import Hashable, List, Optional, Sequence
+from typing import Hashable, Optional, Sequence
 
 import torch
 

@@ -8,7 +8,7 @@ the same tokens alone, in a batch, or after being preempted and recomputed.
 
 from __future__ import annotations
 
-from typing import List, Sequence
+from typing import Sequence
 
 import torch
 

@@ -21,7 +21,7 @@ from typing import Dict, Iterable, List, Sequence
 import torch
 
 from ..parts.base import WeightSpec
-from .safetensors_io import DTYPES, SafetensorsError, SafetensorsFile, model_files
+from .safetensors_io import SafetensorsError, SafetensorsFile, model_files
 
 _FLOAT = ("F32", "BF16", "F16", "F64")
 _INT = ("I64", "I32", "I16", "I8", "U8")
