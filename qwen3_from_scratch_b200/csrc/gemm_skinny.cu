@@ -76,7 +76,7 @@ constexpr int GS_SS_ROWS = 16;  // row pitch of the partial sums
 template <int NT, int WK, int EPI, typename OutT, int PRE = 1, bool NORMED = false>
 __global__ void __launch_bounds__(GS_WARPS * 32,
                                   ((NT == 1 && WK > 1 && !(NORMED && PRE == 1)) || (NT == 2 && PRE > 1)) ? 1
-                                  : (NT == 2 && EPI == 2) ? 2 : 3)
+                                  : (NT == 2 && (EPI == 2 || (NORMED && EPI == 0))) ? 2 : 3)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
                    OutT* __restrict__ out, int T, int N, int K, int ldo, const SkinnyFuse fuse) {
   constexpr int GROUPS = GS_WARPS / WK;  // feature groups per block
