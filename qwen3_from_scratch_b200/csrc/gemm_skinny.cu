@@ -53,7 +53,10 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
 // (The kernel is asked to fit three blocks per SM where K is not split in the block, which is the long
 // stream of the output head (at 88 registers, two blocks per SM, the head ran 58 us against 50), and with two
 // token tiles: there, left to itself, the compiler used fewer registers than three blocks allow and took
-// the loads one after the other: 10.0 us per product at 16 rows against 6.7 us, the head 86 us against 72.)
+// the loads one after the other: 10.0 us per product at 16 rows against 6.7 us, the head 86 us against 72.
+// Two token tiles are short of registers at three blocks per SM, though: the products into the stream and the
+// normed QKV product, whose grids fit two blocks per SM, are asked for two (4,096 x 12,288 at 16 rows: 22.5 us
+// against 33.9).  A warp that fetches two or three batches ahead gets all the registers it wants.)
 // PRE: batches of GS_UNROLL groups whose weights are fetched before the wait on the kernel before.  A
 // product with few output features (o_proj, down_proj: 64 groups of 16, one block each) gives a warp two or
 // three batches; with all of them under way before the wait, what is left after it is one round trip for
