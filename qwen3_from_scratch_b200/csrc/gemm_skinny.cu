@@ -54,9 +54,9 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
 // stream of the output head (at 88 registers, two blocks per SM, the head ran 58 us against 50), and with two
 // token tiles: there, left to itself, the compiler used fewer registers than three blocks allow and took
 // the loads one after the other: 10.0 us per product at 16 rows against 6.7 us, the head 86 us against 72.
-// Two token tiles are short of registers at three blocks per SM, though: the products into the stream and the
-// normed QKV product, whose grids fit two blocks per SM, are asked for two (4,096 x 12,288 at 16 rows: 22.5 us
-// against 33.9).  A warp that fetches two or three batches ahead gets all the registers it wants.)
+// Two token tiles are short of registers at three blocks per SM, though: where the grid fits two blocks per SM
+// (ROOMY) the kernel is asked for two (4,096 x 12,288 at 16 rows into the stream: 22.5 us against 33.9).  A warp
+// that fetches two or three batches ahead gets all the registers it wants.)
 // PRE: batches of GS_UNROLL groups whose weights are fetched before the wait on the kernel before.  A
 // product with few output features (o_proj, down_proj: 64 groups of 16, one block each) gives a warp two or
 // three batches; with all of them under way before the wait, what is left after it is one round trip for
@@ -76,10 +76,11 @@ constexpr int GS_SS_ROWS = 16;  // row pitch of the partial sums
 // EPI 2: out is the float32 stream [T, N] and is added to.  NORMED (see the head of the file): X is the stream
 // times a norm's weight (scaled_out of the product that last added into the stream), and the result is
 // multiplied by the row's 1 / rms.
-template <int NT, int WK, int EPI, typename OutT, int PRE = 1, bool NORMED = false>
+// ROOMY (two token tiles, one batch ahead): the grid fits two blocks per SM, so the thread may have their registers.
+template <int NT, int WK, int EPI, typename OutT, int PRE = 1, bool NORMED = false, bool ROOMY = false>
 __global__ void __launch_bounds__(GS_WARPS * 32,
                                   ((NT == 1 && WK > 1 && !(NORMED && PRE == 1)) || (NT == 2 && PRE > 1)) ? 1
-                                  : (NT == 2 && (EPI == 2 || (NORMED && EPI == 0))) ? 2 : 3)
+                                  : (NT == 2 && ROOMY) ? 2 : 3)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
                    OutT* __restrict__ out, int T, int N, int K, int ldo, const SkinnyFuse fuse) {
   constexpr int GROUPS = GS_WARPS / WK;  // feature groups per block
@@ -279,9 +280,16 @@ static int gemm_skinny_launch(const void* X, const void* W, void* out, int T, in
   while (wk < GS_WARPS && (groups * wk * 2) / GS_WARPS < 148 * 4 && K / (wk * 2) >= 128) wk *= 2;
   const int per_block = GS_WARPS / wk;
   const unsigned grid = (groups + per_block - 1) / per_block;
-#define Q3_GS_GO(WK, PRE)                                                                          \
-  q3::launch(gemm_skinny_kernel<NT, WK, EPI, OutT, PRE, NORMED>, dim3(grid), dim3(GS_WARPS * 32), 0, stream,           \
-             (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (OutT*)out, T, N, K, ldo, fuse)
+#define Q3_GS_GO(WK, PRE)                                                                                         \
+  do {                                                                                                            \
+    if (NT == 2 && PRE == 1 && grid <= 2 * 148u)                                                                  \
+      q3::launch(gemm_skinny_kernel<NT, WK, EPI, OutT, PRE, NORMED, NT == 2 && PRE == 1>, dim3(grid),             \
+                 dim3(GS_WARPS * 32), 0, stream, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (OutT*)out, T, N, K, \
+                 ldo, fuse);                                                                                      \
+    else                                                                                                          \
+      q3::launch(gemm_skinny_kernel<NT, WK, EPI, OutT, PRE, NORMED, false>, dim3(grid), dim3(GS_WARPS * 32), 0,   \
+                 stream, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (OutT*)out, T, N, K, ldo, fuse);       \
+  } while (0)
   // batches of a warp's share of K; up to three are fetched ahead of the wait, but only where the grid is one
   // block per SM or less (o_proj and down_proj of a narrow model: 64 blocks): the registers of three batches
   // leave room for one block per SM, and a larger grid would then run in waves whose later blocks fetch
