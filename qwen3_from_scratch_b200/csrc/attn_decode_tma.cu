@@ -99,8 +99,11 @@ struct DecodeQkv {
   int angles_early;          // cos_sin is older than the launch before this one
 };
 
-template <int D>
-__global__ void __launch_bounds__(DT_THREADS, 2)
+// BLOCKS: blocks per SM the kernel is compiled for.  Three (128 registers) give a large grid half as many
+// slots again as two (batch 8 at context 4,096: six splits, 384 blocks, in one wave: +7.6 % of the step; batch
+// 64: +5 %); two (168 registers) are the faster code where the grid fits their slots anyway (batch 1: +2.6 %).
+template <int D, int BLOCKS>
+__global__ void __launch_bounds__(DT_THREADS, BLOCKS)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                        float* __restrict__ partial, const int* __restrict__ q_start,
@@ -453,8 +456,11 @@ static int attn_decode_tma_launch(const void* q, const void* k_pages, const void
   using S = DecodeTmaShape<D>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<D, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)S::SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_decode_tma_kernel<D, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)S::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -465,7 +471,9 @@ static int attn_decode_tma_launch(const void* q, const void* k_pages, const void
   code = cached_map(&map_v, v_pages, rows, D, DT_KEYS);
   if (code) return code;
   dim3 grid(num_splits, Hkv, B);
-  q3::launch(attn_decode_tma_kernel<D>, grid, dim3(DT_THREADS), S::SMEM_BYTES, stream, map_k, map_v,
+  const bool many = (long long)num_splits * Hkv * B > 2 * 148;  // more blocks than two per SM hold at once
+  auto kernel = many ? attn_decode_tma_kernel<D, 3> : attn_decode_tma_kernel<D, 2>;
+  q3::launch(kernel, grid, dim3(DT_THREADS), S::SMEM_BYTES, stream, map_k, map_v,
              (const __nv_bfloat16*)q, (__nv_bfloat16*)out, partial, q_start, kv_len, block_table, table_stride,
              page_size, num_pages, Hq, Hkv, scale * 1.4426950408889634f, window, num_splits, status, fq);
   code = launch_status();

@@ -755,7 +755,7 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         return
     if num_decode > 0:
         tma = decode_kernel != "cp_async" and decode_tma_takes(D, k_pages.shape[2])
-        splits = decode_splits(num_decode, Hkv, max_kv_len, window, D, blocks_per_sm=2 if tma else None)
+        splits = decode_splits(num_decode, Hkv, max_kv_len, window, D, blocks_per_sm=3 if tma else None)
         if partial is None or partial.numel() < num_decode * Hq * splits * (D + 2):
             splits = 1 if partial is None else max(1, partial.numel() // (num_decode * Hq * (D + 2)))
         attn_decode(q, k_pages, v_pages, out, partial, q_start, kv_len, block_table, num_decode, scale, window,
