@@ -742,7 +742,8 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
                     q_start: torch.Tensor, kv_len: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
                     num_seqs: int, num_decode: int, max_q_len: int, max_kv_len: int, scale: float, window: int,
                     status: torch.Tensor, partial: Optional[torch.Tensor] = None,
-                    portion_kernel: str = "auto", decode_kernel: str = "auto", raw_qkv=None) -> None:
+                    portion_kernel: str = "auto", decode_kernel: str = "auto", raw_qkv=None,
+                    decode_wide_grid: bool = False) -> None:
     """``raw_qkv``: see ``attn_decode``; only where ``decode_takes_raw_qkv`` says so.
     Causal attention of a mixed batch over the pages: rows [0, num_decode) bring one token each and
     go to the split-KV decode kernel, the rest to a portion kernel (tcgen05 where it takes the shape,
@@ -755,7 +756,17 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         return
     if num_decode > 0:
         tma = decode_kernel != "cp_async" and decode_tma_takes(D, k_pages.shape[2])
-        splits = decode_splits(num_decode, Hkv, max_kv_len, window, D, blocks_per_sm=3 if tma else None)
+        if tma:
+            # The kernel is compiled for two and for three blocks per SM and takes the second variant for a
+            # grid of more than 2 x 148 blocks.  A grid of several waves gains from the third block at every
+            # model width tried (batch 64: +3 to +6 %); a grid that fits three blocks per SM but not two (batch
+            # 8 at context 4,096: six splits instead of four) gained 7.6 % of the step at a width of 1,024 and
+            # lost 11 % and 34 % at 2,048 and 4,096, so only a caller that says ``decode_wide_grid`` gets it.
+            splits = decode_splits(num_decode, Hkv, max_kv_len, window, D, blocks_per_sm=2)
+            if decode_wide_grid or num_decode * Hkv * splits > 2 * _SM_COUNT:
+                splits = decode_splits(num_decode, Hkv, max_kv_len, window, D, blocks_per_sm=3)
+        else:
+            splits = decode_splits(num_decode, Hkv, max_kv_len, window, D)
         if partial is None or partial.numel() < num_decode * Hq * splits * (D + 2):
             splits = 1 if partial is None else max(1, partial.numel() // (num_decode * Hq * (D + 2)))
         attn_decode(q, k_pages, v_pages, out, partial, q_start, kv_len, block_table, num_decode, scale, window,
