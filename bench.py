@@ -1,19 +1,30 @@
 """Decode and prefill throughput of the engine on one B200, with roofline fractions.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--model 0.6b|8b|32b]
 
 One "step" is one decode step of the whole batch.  The default run uses the layer sizes of
 Qwen3-0.6B (28 layers, hidden 1024, 16/8 heads of 128, intermediate 3072, vocabulary 151936,
 tied head) with seeded random weights, a batch of 8 and a context of 4096 tokens per sequence,
 pages of 16 tokens.  It prints one JSON line:
 
-  value      decoded tokens per second, timed on the device (CUDA events) over exactly K steps
+  value      decoded tokens per second, timed on the device (CUDA events): K steps, repeated
+             ``--repeats`` times, the median repeat
   e2e        the same through the Python entry point (``SyncEngine.step``): every step copies its
-             token ids and block tables from pinned host memory and reads the sampled ids back
+             token ids and block tables from pinned host memory and reads the sampled ids back; all K
+             steps of a repeat are launched and collected inside its clock.  The repeats decode one after
+             the other, so all but the last run at contexts up to ``repeats * K`` tokens shorter than the
+             device-timed one
   prefill    one step over a 2,048-token prompt: tokens/s and flops / time / bf16 peak
   roofline   bytes a decode step has to read (every weight once + the keys and values of the live
              requests) / its time, against the measured copy bandwidth
-  points     decode tokens/s at batch 1 and 64
+  points     decode tokens/s at the other batch sizes, and (default run) the figures of the Qwen3-8B
+             and Qwen3-32B layer sizes, which ``--model 8b`` / ``--model 32b`` print as lines of their own
+
+``--model 8b`` also runs the load the 8B configuration is quoted on: 64 requests at once, prompts of
+128 to 2,048 random tokens, 256 new tokens each, through ``SyncEngine.batch_generate`` (continuous
+batching, prompts cut into portions beside decoding requests): ``serving`` in its line.  The 8B and 32B
+models take their random weights straight on the device (no file of 16 or 65 GB is written); the 0.6B
+model goes through a folder and the real loader.
 
 Peaks come from MEASURED_PEAKS.json beside this file when it exists, else from the fallback
 figures (6.65 TB/s, 1.59 PFLOP/s).  ``--impl reference`` runs the unmodified reference from
@@ -36,15 +47,28 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# the configuration the headline figure is quoted on: Qwen3-0.6B layer sizes
-CONFIG = dict(
-    architectures=["Qwen3ForCausalLM"], vocab_size=151936, hidden_size=1024, hidden_act="silu",
-    num_hidden_layers=28, max_position_embeddings=40960, num_key_value_heads=8, num_attention_heads=16,
-    head_dim=128, intermediate_size=3072, rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=True)
-FULL_LAYERS = 28
+def _qwen3(hidden, heads, kv_heads, inter, layers, tied):
+    return dict(architectures=["Qwen3ForCausalLM"], vocab_size=151936, hidden_size=hidden, hidden_act="silu",
+                num_hidden_layers=layers, max_position_embeddings=40960, num_key_value_heads=kv_heads,
+                num_attention_heads=heads, head_dim=128, intermediate_size=inter, rms_norm_eps=1e-6,
+                rope_theta=1000000.0, tie_word_embeddings=tied)
+
+
+# The layer sizes the figures are quoted on, the decode batches measured at each (the first is the one of
+# ``value``), and how the random weights get onto the device.
+MODELS = {
+    "0.6b": dict(name="Qwen3-0.6B", config=_qwen3(1024, 16, 8, 3072, 28, True), batches=(8, 1, 64),
+                 weights="folder", serving=False),
+    "8b": dict(name="Qwen3-8B", config=_qwen3(4096, 32, 8, 12288, 36, False), batches=(8, 1, 64),
+               weights="device", serving=True),
+    "32b": dict(name="Qwen3-32B", config=_qwen3(5120, 64, 8, 25600, 64, False), batches=(8, 1, 32),
+                weights="device", serving=False),
+}
+CONFIG = MODELS["0.6b"]["config"]  # the configuration the headline figure is quoted on
 CONTEXT = 4096
 PAGE = 16
 PREFILL_TOKENS = 2048
+SERVING = dict(requests=64, prompt_min=128, prompt_max=2048, new_tokens=256, seed=4242)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -97,7 +121,15 @@ class ClockSampler:
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
     NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
-    def __init__(self):
+    def __init__(self, device_index: int = 0):
+        """``device_index``: the CUDA device that is measured.  NVML and nvidia-smi number GPUs without regard
+        to CUDA_VISIBLE_DEVICES, so the device is looked up by its UUID."""
+        self.uuid = None
+        try:
+            import torch
+            self.uuid = "GPU-" + str(torch.cuda.get_device_properties(device_index).uuid)
+        except Exception:  # an older torch without the field: the first GPU is taken, and said
+            self.uuid = None
         self.samples = []  # (sm MHz, max sm MHz, [active reasons])
         self.proc = None
         self.stopping = threading.Event()
@@ -108,7 +140,8 @@ class ClockSampler:
         try:
             import pynvml
             pynvml.nvmlInit()
-            handle = pynvml.nvmlDeviceGetHandleByIndex(0)
+            handle = (pynvml.nvmlDeviceGetHandleByUUID(self.uuid.encode()) if self.uuid
+                      else pynvml.nvmlDeviceGetHandleByIndex(0))
             bits = {"hw_slowdown": pynvml.nvmlClocksThrottleReasonHwSlowdown,
                     "hw_thermal_slowdown": pynvml.nvmlClocksThrottleReasonHwThermalSlowdown,
                     "sw_thermal_slowdown": pynvml.nvmlClocksThrottleReasonSwThermalSlowdown,
@@ -133,7 +166,7 @@ class ClockSampler:
             self.source = None
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", "-i", self.uuid or "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -169,7 +202,7 @@ class ClockSampler:
         reasons = sorted({r for s in self.samples for r in s[2]})
         return {"sm_mhz": statistics.median(clocks) if clocks else None,
                 "sm_max_mhz": max(s[1] for s in self.samples) if self.samples else None, "reasons": reasons,
-                "samples": len(clocks), "source": self.source}
+                "samples": len(clocks), "source": self.source, "gpu": self.uuid or "index 0"}
 
 
 def model_numbers(cfg, layers):
@@ -189,18 +222,22 @@ def model_numbers(cfg, layers):
     return weight_bytes, kv_bytes_per_token, prefill_flops
 
 
-def time_device_steps(fn, steps, warmup):
+def time_device_steps(fn, steps, warmup, repeats):
+    """Seconds of ``steps`` calls of ``fn`` between CUDA events, once per repeat."""
     import torch
     for _ in range(warmup):
         fn()
-    torch.cuda.synchronize()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(steps):
-        fn()
-    end.record()
-    torch.cuda.synchronize()
-    return start.elapsed_time(end) / 1e3
+    out = []
+    for _ in range(repeats):
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        out.append(start.elapsed_time(end) / 1e3)
+    return out
 
 
 def schedule_lead(engine, batch, prompt_len):
@@ -232,21 +269,21 @@ def schedule_lead(engine, batch, prompt_len):
     return lead
 
 
-def decode_bench(engine, batch, context, steps, warmup, vocab):
-    """Puts ``batch`` requests of ``context - steps - warmup`` tokens in the cache through the entry
-    point, then measures (a) K engine steps end to end and (b) K replays of the last step's batch
-    on the device alone.  Returns (device seconds, e2e seconds, launches per step, h2d, d2h bytes)."""
+def decode_bench(engine, batch, context, steps, warmup, repeats, vocab):
+    """Puts ``batch`` requests in the cache through the entry point, so short that the last timed step
+    brings each to ``context`` tokens, then measures ``repeats`` times (a) K engine steps end to end and
+    (b) K replays of the last step's batch on the device alone.  Returns a dict of the medians."""
     import torch
 
     from qwen3_from_scratch_b200.engine.request import SamplingParams
-    from qwen3_from_scratch_b200.kernels import ops
 
     g = torch.Generator().manual_seed(1234 + batch)
     # Requests whose prompt is done decode while later prompts are still being cut into portions, so
     # request i is `ahead[i]` tokens ahead when the last one starts decoding.  The scheduler is
     # deterministic: a dry run of the same schedule on a cache manager alone tells `ahead`, and the
     # prompts are shortened by it, so that the last timed step brings every request to `context`.
-    total_new = steps + warmup
+    # (The step that the last warm-up call launched ahead is collected before the clock starts: + 1.)
+    total_new = warmup + 1 + repeats * steps
     ahead = schedule_lead(engine, batch, context - total_new)
     reqs = []
     for i in range(batch):
@@ -255,21 +292,26 @@ def decode_bench(engine, batch, context, steps, warmup, vocab):
                                                                       ignore_eos=True)))
     while any(not r.is_decoding for r in reqs):
         engine.step()
-    # (a) end to end through SyncEngine.step: host ids in (pinned copy), sampled ids out, every step
+    # (a) end to end through SyncEngine.step: host ids in (pinned copy), sampled ids out, every step.
+    # Every one of a repeat's K steps is launched and collected between its two clock readings: a step
+    # launched ahead is collected before the first reading, and the K-th call launches nothing beyond itself.
     for _ in range(warmup):
         engine.step()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    h2d = 0
-    for i in range(steps):
-        if i == steps - 1:
-            engine.lookahead = False  # the last call launches nothing beyond the K-th step
-        plan = engine.step()
-        assert len(plan) == batch and all(s.num_tokens == 1 for s in plan)
-        h2d += engine.session.last_context.h2d_bytes
-    torch.cuda.synchronize()
-    e2e_seconds = time.perf_counter() - t0
-    engine.lookahead = True
+    e2e, h2d = [], 0
+    host_ms = []
+    for _ in range(repeats):
+        engine.drain()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(steps):
+            if i == steps - 1:
+                engine.lookahead = False
+            plan = engine.step()
+            assert len(plan) == batch and all(s.num_tokens == 1 for s in plan)
+            h2d += engine.session.last_context.h2d_bytes
+        torch.cuda.synchronize()
+        e2e.append(time.perf_counter() - t0)
+        engine.lookahead = True
     d2h = (1 + batch) * 4 + 4  # the sampled ids behind their buffer's first word, and the status word
     # (b) the same step on the device alone: replay the last batch (same lengths, same pages)
     ctx = engine.session.last_context
@@ -285,16 +327,17 @@ def decode_bench(engine, batch, context, steps, warmup, vocab):
         sampler.sample(logits, zeros, [0] * batch, [0] * batch, [0] * batch, [0] * batch)
 
     launches = session.launches_per_decode_step(ctx) + 1  # + the sampling kernel
-    device_seconds = time_device_steps(one_step, steps, warmup)
+    device = time_device_steps(one_step, steps, warmup, repeats)
     for r in reqs:
         engine.abort(r)
-    return device_seconds, e2e_seconds, launches, h2d // steps, d2h, cached_tokens
+    return dict(device=statistics.median(device), e2e=statistics.median(e2e), device_all=device, e2e_all=e2e,
+                launches=launches, h2d=h2d // (steps * repeats), d2h=d2h, cached=cached_tokens)
 
 
 def prefill_bench(engine, tokens, steps, warmup, vocab):
     import torch
 
-    from qwen3_from_scratch_b200.engine.batch import BatchContext, Entry
+    from qwen3_from_scratch_b200.engine.batch import Entry
     g = torch.Generator().manual_seed(99)
     prompt = torch.randint(0, vocab, (tokens,), generator=g).tolist()
     session = engine.session
@@ -320,69 +363,187 @@ def prefill_bench(engine, tokens, steps, warmup, vocab):
     return times[len(times) // 2] / 1e3
 
 
-def ours(args):
+def serving_bench(engine, vocab):
+    """The load the 8B configuration is quoted on: all requests at once, prompts of random length and random
+    tokens, a fixed number of new tokens each, through ``SyncEngine.batch_generate``.  Run twice: the first
+    run meets every batch shape for the first time (its CUDA graphs are recorded then), the second is the
+    steady state; both are reported."""
     import torch
 
+    w = SERVING
+    g = torch.Generator().manual_seed(w["seed"])
+    lengths = torch.randint(w["prompt_min"], w["prompt_max"] + 1, (w["requests"],), generator=g).tolist()
+    prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
+    runs = []
+    for _ in range(2):
+        steps0, pre0 = engine.num_steps, engine.scheduler.num_preemptions
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        results, batch = engine.batch_generate(prompts, max_new_tokens=w["new_tokens"], ignore_eos=True)
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        assert all(len(r.token_ids) == w["new_tokens"] for r in results)
+        ttft = [r.metrics.ttft for r in results]
+        runs.append({"output_tok_s": batch.total_tokens / wall, "total_tok_s": (batch.total_tokens + sum(lengths)) / wall,
+                     "seconds": wall, "ttft_mean_ms": 1e3 * statistics.mean(ttft), "ttft_max_ms": 1e3 * max(ttft),
+                     "steps": engine.num_steps - steps0, "preemptions": engine.scheduler.num_preemptions - pre0})
+    out = dict(runs[1])
+    out.update(requests=w["requests"], prompt_tokens=sum(lengths), new_tokens_each=w["new_tokens"],
+               first_run_output_tok_s=runs[0]["output_tok_s"])
+    return out
+
+
+def make_engine(spec, layers, batches, context, folder=None):
+    """The engine of one model size: pool for the largest batch at ``context`` plus a prompt's worth."""
     from qwen3_from_scratch_b200.engine.engine import SyncEngine
     from qwen3_from_scratch_b200.registry import config_from_dict
     from qwen3_from_scratch_b200.weights import write_random_model
 
-    peaks = load_peaks()
-    cfg = dict(CONFIG)
-    layers = args.layers or FULL_LAYERS
-    cfg["num_hidden_layers"] = layers
+    cfg = dict(spec["config"], num_hidden_layers=layers)
+    pool_tokens = max(max(batches) * context, SERVING["requests"] * (SERVING["prompt_max"] + SERVING["new_tokens"])
+                      if spec["serving"] else 0) + PREFILL_TOKENS + 64 * PAGE
+    kwargs = dict(dtype="bfloat16", block_size=PAGE, num_pages=pool_tokens // PAGE,
+                  max_num_seqs=max(max(batches), SERVING["requests"] if spec["serving"] else 0), max_num_tokens=4096,
+                  chunked_prefill_size=2048)
+    t0 = time.time()
+    if spec["weights"] == "folder":
+        with tempfile.TemporaryDirectory(prefix="q3b200-bench-") as tmp:
+            write_random_model(tmp, config_from_dict(cfg), seed=0)
+            engine = SyncEngine(tmp, **kwargs)
+    else:
+        with tempfile.TemporaryDirectory(prefix="q3b200-bench-") as tmp:
+            config_from_dict(cfg).save(tmp)
+            engine = SyncEngine(tmp, random_weights=0, **kwargs)
+    print(f"[bench] {spec['name']} sizes, {layers} layers: engine with random weights ready in {time.time() - t0:.1f}s",
+          file=sys.stderr, flush=True)
+    return engine, cfg
+
+
+def measure_model(key, args, peaks, sample_clocks):
+    """All figures of one model size as a dict (see ``line_of``)."""
+    import gc
+
+    import torch
+
+    spec = MODELS[key]
+    full_layers = spec["config"]["num_hidden_layers"]
+    layers = args.layers or full_layers
+    batches = list(spec["batches"])
+    if args.batch and key == args.model:
+        batches = [args.batch] + [b for b in batches if b != args.batch]
+    engine, cfg = make_engine(spec, layers, batches, args.context)
     weight_bytes, kv_per_token, prefill_flops = model_numbers(cfg, layers)
-    batches = sorted({args.batch, 1, 64})
-    with tempfile.TemporaryDirectory(prefix="q3b200-bench-") as folder:
-        t0 = time.time()
-        write_random_model(folder, config_from_dict(cfg), seed=0)
-        print(f"[bench] wrote random {layers}-layer model in {time.time() - t0:.1f}s", file=sys.stderr, flush=True)
-        pool_tokens = max(batches) * args.context + PREFILL_TOKENS + 64 * PAGE
-        engine = SyncEngine(folder, dtype="bfloat16", block_size=PAGE, num_pages=pool_tokens // PAGE,
-                            max_num_seqs=max(batches), max_num_tokens=4096, chunked_prefill_size=2048)
     vocab = cfg["vocab_size"]
-    results = {}
-    clocks = None
-    for b in batches:
-        sampler = ClockSampler() if b == args.batch else None
+    results, clocks = {}, None
+    for b in sorted(batches):
+        sampler = ClockSampler() if (sample_clocks and b == batches[0]) else None
         if sampler:
             sampler.start()
-        dev_s, e2e_s, launches, h2d, d2h, cached = decode_bench(engine, b, args.context, args.steps, args.warmup, vocab)
+        r = decode_bench(engine, b, args.context, args.steps, args.warmup, args.repeats, vocab)
         if sampler:
             clocks = sampler.stop()
-        results[b] = dict(device=dev_s, e2e=e2e_s, launches=launches, h2d=h2d, d2h=d2h, cached=cached)
-        print(f"[bench] batch {b}: {b * args.steps / dev_s:.0f} tok/s on the device, "
-              f"{b * args.steps / e2e_s:.0f} tok/s end to end", file=sys.stderr, flush=True)
+        step_s = r["device"] / args.steps
+        r["tok_s"] = b * args.steps / r["device"]
+        r["e2e_tok_s"] = b * args.steps / r["e2e"]
+        r["gbs"] = (weight_bytes + r["cached"] * kv_per_token) / step_s / 1e9
+        r["frac"] = r["gbs"] / peaks["hbm_gbs"]
+        results[b] = r
+        print(f"[bench] {spec['name']} batch {b}: {r['tok_s']:.0f} tok/s on the device ({step_s * 1e3:.3f} ms/step, "
+              f"{r['frac']:.2f} of the HBM roofline), {r['e2e_tok_s']:.0f} tok/s end to end "
+              f"({r['e2e_tok_s'] / r['tok_s']:.3f} of it; repeats {' '.join(f'{1e3 * t / args.steps:.3f}' for t in r['e2e_all'])} "
+              f"ms/step)", file=sys.stderr, flush=True)
     prefill_s = prefill_bench(engine, PREFILL_TOKENS, max(3, min(args.steps, 10)), args.warmup, vocab)
-    main = results[args.batch]
-    step_s = main["device"] / args.steps
-    step_bytes = weight_bytes + main["cached"] * kv_per_token
-    achieved = step_bytes / step_s / 1e9
     flops = prefill_flops(PREFILL_TOKENS)
+    prefill = {"value": PREFILL_TOKENS / prefill_s, "tokens": PREFILL_TOKENS, "ms": prefill_s * 1e3,
+               "frac": flops / prefill_s / (peaks["bf16_tflops"] * 1e12)}
+    print(f"[bench] {spec['name']} prompt of {PREFILL_TOKENS}: {prefill_s * 1e3:.2f} ms, {prefill['value']:.0f} tok/s, "
+          f"{prefill['frac']:.2f} of the bf16 peak", file=sys.stderr, flush=True)
+    serving = None
+    if spec["serving"] and not args.no_serving:
+        serving = serving_bench(engine, vocab)
+        print(f"[bench] {spec['name']} serving load: {json.dumps(serving)}", file=sys.stderr, flush=True)
+    del engine
+    gc.collect()
+    torch.cuda.empty_cache()
+    return dict(key=key, spec=spec, cfg=cfg, layers=layers, full_layers=full_layers, batches=batches, results=results,
+                prefill=prefill, serving=serving, clocks=clocks)
+
+
+def line_of(m, args, peaks):
+    """The JSON line of one model size."""
+    spec, cfg, results = m["spec"], m["cfg"], m["results"]
+    b0 = m["batches"][0]
+    main = results[b0]
     line = {
-        "metric": "decode tok/s at batch 8 (Qwen3-0.6B sizes, context 4096, bf16, random weights)",
-        "value": args.batch * args.steps / main["device"], "unit": "tokens/s", "n_gpus": 1,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "metric": f"decode tok/s at batch {b0} ({spec['name']} sizes, context {args.context}, bf16, random weights)",
+        "value": main["tok_s"], "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": main["device"] / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic (seeded random weights and token ids)", "impl": "ours",
         "config": {
-            "model": "Qwen3-0.6B sizes, random weights", "global_batch": args.batch, "seq_len": args.context,
-            "parallelism": "single GPU", "layers": layers, "layers_full": FULL_LAYERS,
+            "model": f"{spec['name']} sizes, random weights", "global_batch": b0, "seq_len": args.context,
+            "parallelism": "single GPU", "layers": m["layers"], "layers_full": m["full_layers"],
             "hidden_size": cfg["hidden_size"], "num_attention_heads": cfg["num_attention_heads"],
             "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
-            "intermediate_size": cfg["intermediate_size"], "vocab_size": vocab, "tie_word_embeddings": True,
-            "page_size": PAGE, "prefill_tokens": PREFILL_TOKENS, "l2": "inputs larger than L2 (weights + cache)",
-            "peaks": peaks["source"],
+            "intermediate_size": cfg["intermediate_size"], "vocab_size": cfg["vocab_size"],
+            "tie_word_embeddings": cfg["tie_word_embeddings"], "page_size": PAGE, "prefill_tokens": PREFILL_TOKENS,
+            "repeats": args.repeats, "l2": "inputs larger than L2 (weights + cache)", "peaks": peaks["source"],
         },
-        "e2e": {"value": args.batch * args.steps / main["e2e"], "unit": "tokens/s",
-                "h2d_bytes_per_step": main["h2d"], "d2h_bytes_per_step": main["d2h"]},
+        "e2e": {"value": main["e2e_tok_s"], "unit": "tokens/s", "h2d_bytes_per_step": main["h2d"],
+                "d2h_bytes_per_step": main["d2h"]},
         "gpu_launches": main["launches"] * args.steps,
-        "prefill": {"value": PREFILL_TOKENS / prefill_s, "tokens": PREFILL_TOKENS, "ms": prefill_s * 1e3,
-                    "frac": flops / prefill_s / (peaks["bf16_tflops"] * 1e12)},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / peaks["hbm_gbs"]},
-        "points": {f"decode_b{b}": b * args.steps / results[b]["device"] for b in batches if b != args.batch},
-        "clocks": clocks,
+        "prefill": m["prefill"],
+        "roofline": {"bound": "hbm", "achieved": main["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": main["frac"]},
+        "points": {},
+        "clocks": m["clocks"],
     }
+    for b in m["batches"][1:]:
+        line["points"][f"decode_b{b}"] = results[b]["tok_s"]
+    for b in m["batches"]:
+        line["points"][f"decode_b{b}_e2e"] = results[b]["e2e_tok_s"]
+        line["points"][f"decode_b{b}_hbm_frac"] = results[b]["frac"]
+    if m["serving"]:
+        line["serving"] = m["serving"]
+    return line
+
+
+def ours(args):
+    peaks = load_peaks()
+    m = measure_model(args.model, args, peaks, sample_clocks=True)
+    line = line_of(m, args, peaks)
+    # Every repeat of the end-to-end loop does the device's work of the device-timed loop and more.
+    main = m["results"][m["batches"][0]]
+    if main["e2e_tok_s"] > 1.01 * main["tok_s"]:
+        print(f"[bench] end to end ({main['e2e_tok_s']:.0f}) above the device rate ({main['tok_s']:.0f}): "
+              "the clock of one of them is wrong", file=sys.stderr)
+        return 1
+    if args.model == "0.6b" and not args.headline_only and not args.layers:
+        # the other sizes' figures ride along under `points`; a failure there must not cost the headline
+        started = time.time()
+        for key in ("8b", "32b"):
+            if time.time() - started > 120:
+                print(f"[bench] {key} left out: the run is long already", file=sys.stderr)
+                continue
+            try:
+                other = measure_model(key, args, peaks, sample_clocks=False)
+            except Exception as e:  # noqa: BLE001
+                print(f"[bench] {key} failed: {type(e).__name__}: {e}", file=sys.stderr)
+                line["points"][f"{key}_error"] = f"{type(e).__name__}: {str(e)[:120]}"
+                continue
+            for b in other["batches"]:
+                r = other["results"][b]
+                line["points"][f"{key}_decode_b{b}"] = r["tok_s"]
+                line["points"][f"{key}_decode_b{b}_e2e"] = r["e2e_tok_s"]
+                line["points"][f"{key}_decode_b{b}_hbm_frac"] = r["frac"]
+            line["points"][f"{key}_prefill_tok_s"] = other["prefill"]["value"]
+            line["points"][f"{key}_prefill_frac"] = other["prefill"]["frac"]
+            line["points"][f"{key}_layers"] = other["layers"]
+            if other["serving"]:
+                line["points"][f"{key}_serving_output_tok_s"] = other["serving"]["output_tok_s"]
+                line["points"][f"{key}_serving_ttft_mean_ms"] = other["serving"]["ttft_mean_ms"]
+                line["points"][f"{key}_serving_steps"] = other["serving"]["steps"]
+                line["points"][f"{key}_serving_preemptions"] = other["serving"]["preemptions"]
     print(json.dumps(line))
     return 0
 
@@ -397,16 +558,16 @@ def profile(args):
     from qwen3_from_scratch_b200.engine.engine import SyncEngine
     from qwen3_from_scratch_b200.engine.request import SamplingParams
     from qwen3_from_scratch_b200.registry import config_from_dict
-    from qwen3_from_scratch_b200.weights import write_random_model
 
-    cfg = dict(CONFIG)
-    cfg["num_hidden_layers"] = args.layers or FULL_LAYERS
+    cfg = dict(MODELS[args.model]["config"])
+    cfg["num_hidden_layers"] = args.layers or cfg["num_hidden_layers"]
+    args.batch = args.batch or 8
     with tempfile.TemporaryDirectory(prefix="q3b200-prof-") as folder:
-        write_random_model(folder, config_from_dict(cfg), seed=0)
+        config_from_dict(cfg).save(folder)
         pool_tokens = args.batch * args.context + PREFILL_TOKENS + 64 * PAGE
         engine = SyncEngine(folder, dtype="bfloat16", block_size=PAGE, num_pages=pool_tokens // PAGE,
                             max_num_seqs=max(args.batch, 1), max_num_tokens=4096, chunked_prefill_size=2048,
-                            cuda_graphs=False)
+                            cuda_graphs=False, random_weights=0)
     vocab = cfg["vocab_size"]
     if args.profile == "prefill":
         from qwen3_from_scratch_b200.engine.batch import BatchContext, Entry
@@ -498,8 +659,13 @@ def main() -> int:
     p.add_argument("--steps", type=int, default=64)
     p.add_argument("--warmup", type=int, default=8)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--model", default="0.6b", choices=sorted(MODELS), help="layer sizes (default: the headline's)")
+    p.add_argument("--batch", type=int, default=None, help="decode batch of `value` (default 8)")
     p.add_argument("--context", type=int, default=CONTEXT)
+    p.add_argument("--repeats", type=int, default=5, help="the K-step region is timed this often; the median counts")
+    p.add_argument("--headline-only", action="store_true",
+                   help="default run without the 8B and 32B figures under `points`")
+    p.add_argument("--no-serving", action="store_true", help="--model 8b without the 64-request load")
     p.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in the output)")
     p.add_argument("--leave-out", action="store_true",
                    help="with --profile: time the step as a CUDA graph, whole and with each kind of kernel left out")
@@ -515,7 +681,8 @@ def main() -> int:
         return profile(args)
     if args.impl == "reference":
         from baseline.reference_arm import run_reference
-        return run_reference(args, CONFIG, PAGE)
+        args.batch = args.batch or 8
+        return run_reference(args, MODELS[args.model]["config"], PAGE)
     return ours(args)
 
 

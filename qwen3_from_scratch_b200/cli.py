@@ -41,6 +41,8 @@ def _add_engine_options(p: argparse.ArgumentParser) -> None:
     p.add_argument("--top-k", type=int, default=0)
     p.add_argument("--max-new-tokens", type=int, default=100)
     p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--random-weights", action="store_true",
+                   help="--model needs only config.json: weights are drawn on the device from --seed")
     p.add_argument("--ignore-eos", action="store_true")
     p.add_argument("--eos-token-id", type=int, default=None)
     p.add_argument("--log-interval", type=int, default=0)
@@ -59,7 +61,8 @@ def _engine(args):
                       gpu_utilization=args.gpu_utilization, num_pages=args.num_pages,
                       chunked_prefill_size=args.chunked_prefill_size, temperature=args.temperature,
                       top_k=args.top_k, max_new_tokens=args.max_new_tokens, seed=args.seed,
-                      eos_token_id=args.eos_token_id, log_interval=args.log_interval)
+                      eos_token_id=args.eos_token_id, log_interval=args.log_interval,
+                      random_weights=args.seed if args.random_weights else None)
 
 
 def cmd_generate(args) -> int:

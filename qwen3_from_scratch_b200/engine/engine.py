@@ -84,12 +84,17 @@ class SyncEngine:
                  chunked_prefill_size: int = 512, enable_prefix_cache: bool = False,
                  temperature: float = 0.0, top_k: int = 0, max_new_tokens: int = 100, seed: int = 0,
                  eos_token_id: Optional[int] = None, log_interval: int = 0, cuda_graphs: bool = True,
-                 lookahead: bool = True):
-        """``num_pages`` fixes the size of the cache pool; otherwise ``gpu_utilization`` of the
+                 lookahead: bool = True, random_weights: Optional[int] = None):
+        """``random_weights``: a seed; ``model_path`` then needs only config.json and the weights are drawn on
+        the device.  ``num_pages`` fixes the size of the cache pool; otherwise ``gpu_utilization`` of the
         memory that is free after the weights are loaded is given to it.  ``lookahead``: while a plain
         decode step runs, the step after it is already put on the device (see ``step``)."""
         if enable_prefix_cache:
-            raise NotImplementedError("prefix sharing between requests is not built; pass enable_prefix_cache=False")
+            # The reference's own configurations set this (its default is true: factory/batch_config.py:147).
+            # Sharing pages between requests with a common prefix saves work and changes no output, so the
+            # option is taken and the engine runs without sharing.
+            logger.warning("enable_prefix_cache: prefix sharing between requests is not built; running without it "
+                           "(outputs are the same)")
         self.model_path = model_path
         self.log_interval = log_interval
         self.defaults = SamplingParams(temperature=temperature, top_k=top_k, max_new_tokens=max_new_tokens,
@@ -100,7 +105,7 @@ class SyncEngine:
                                                   max_num_tokens)
         self.session = Session(model_path, dtype=dtype, device=device, page_size=block_size,
                                num_pages=cache_pages, max_seqs=max_num_seqs, max_step_tokens=max_num_tokens,
-                               cuda_graphs=cuda_graphs)
+                               cuda_graphs=cuda_graphs, random_weights=random_weights)
         self.config = self.session.config
         spec = self.session.model.spec
         self.eos_token_id = eos_token_id if eos_token_id is not None else spec.eos_token_id

@@ -18,6 +18,7 @@ from ..kernels import ops
 from ..parts.base import NEXT_NORM_WEIGHT, STREAM_SUMSQ, ModelSpec, Runtime, StepContext
 from ..registry import build_model_spec, create_part, load_config
 from ..weights.loader import load_weights
+from ..weights.random_init import random_weights_on_device
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 
@@ -107,9 +108,10 @@ class Model:
         return self.head.forward(wanted)
 
 
-def load_model(folder: str, dtype, device, max_tokens: int, max_seqs: int):
+def load_model(folder: str, dtype, device, max_tokens: int, max_seqs: int, random_weights: Optional[int] = None):
     """config.json -> configuration -> specification -> parts -> weights on the device.
-    Returns (model, configuration, runtime)."""
+    Returns (model, configuration, runtime).  ``random_weights``: a seed; the folder then needs only its
+    config.json and the weights are drawn on the device instead of read."""
     if not torch.cuda.is_available():
         raise RuntimeError("this engine runs on a CUDA GPU (sm_100a); no GPU is visible")
     ops.library()  # build or load the kernels first: without them nothing below can run
@@ -118,7 +120,10 @@ def load_model(folder: str, dtype, device, max_tokens: int, max_seqs: int):
     compute = resolve_dtype(dtype)
     device = torch.device(device)
     rt = Runtime(device=device, dtype=compute, max_tokens=int(max_tokens), max_seqs=int(max_seqs))
-    weights = load_weights(folder, model.weight_specs(), device=device, compute_dtype=compute,
-                           ignorable=model.spec.ignorable_weights)
+    if random_weights is not None:
+        weights = random_weights_on_device(model.weight_specs(), int(random_weights), device, compute)
+    else:
+        weights = load_weights(folder, model.weight_specs(), device=device, compute_dtype=compute,
+                               ignorable=model.spec.ignorable_weights)
     model.setup(rt, weights)
     return model, config, rt

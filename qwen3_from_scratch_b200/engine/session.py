@@ -109,15 +109,18 @@ class StepGraphs:
 class Session:
     def __init__(self, model_dir: str, dtype="bfloat16", device="cuda:0", page_size: int = 16,
                  num_pages: Optional[int] = None, cache_tokens: Optional[int] = None, max_seqs: int = 32,
-                 max_step_tokens: int = 3000, poison_freed_pages: bool = False, cuda_graphs: bool = True):
+                 max_step_tokens: int = 3000, poison_freed_pages: bool = False, cuda_graphs: bool = True,
+                 random_weights: Optional[int] = None):
         """``num_pages`` pages per group, or ``cache_tokens`` (rounded up to whole pages).
+        ``random_weights``: a seed; the folder then needs only config.json (weights drawn on the device).
         ``cuda_graphs``: replay steps whose shape repeats (decode steps, full-size prompt portions) from
         captured graphs instead of launching kernel by kernel."""
         if num_pages is None:
             if cache_tokens is None:
                 raise ValueError("give num_pages or cache_tokens")
             num_pages = -(-int(cache_tokens) // page_size)
-        self.model, self.config, self.rt = load_model(model_dir, dtype, device, max_step_tokens, max_seqs)
+        self.model, self.config, self.rt = load_model(model_dir, dtype, device, max_step_tokens, max_seqs,
+                                                     random_weights=random_weights)
         layout = self.model.cache_layout()
         self.manager = CacheManager(layout, page_size, num_pages, max_seqs)
         self.storage = CacheStorage(layout, page_size, max_seqs, self.rt.device, self.rt.dtype)

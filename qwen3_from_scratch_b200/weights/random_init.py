@@ -4,13 +4,17 @@ and a seed, so that the real loader is what every test and benchmark goes throug
 Matrices and embeddings are N(0, 0.02), norm weights 1 + N(0, 0.1).  Every tensor has a
 generator of its own, seeded from (seed, tensor name), so a tensor's values do not depend on
 which other tensors the model has or on the order they are written in.
+
+``random_weights_on_device`` fills a model of any size straight on the GPU (same distributions,
+a CUDA generator per tensor): a model of tens of gigabytes then needs no file of that size.  Its
+values are not those of the folder writer's (another generator).
 """
 
 from __future__ import annotations
 
 import hashlib
 import os
-from typing import Dict, Optional
+from typing import Dict, Optional, Sequence
 
 import torch
 
@@ -67,3 +71,30 @@ def write_random_model(folder: str, config: ModelConfig, seed: int, dtype: str =
         for s in specs:
             w.write(s.name, random_tensor(s, seed, stored(s)))
     return folder
+
+
+def random_weights_on_device(specs: Sequence[WeightSpec], seed: int, device, compute_dtype: torch.dtype
+                             ) -> Dict[str, torch.Tensor]:
+    """Every tensor the specs name, drawn on ``device``: what ``load_weights`` would return for a folder
+    stored in bfloat16 (matrices in ``compute_dtype``, vectors float32, integer tables int32)."""
+    device = torch.device(device)
+    out: Dict[str, torch.Tensor] = {}
+    g = torch.Generator(device=device)
+    for spec in specs:
+        digest = hashlib.sha256(f"{seed}:{spec.name}".encode()).digest()
+        g.manual_seed(int.from_bytes(digest[:8], "little") & ((1 << 63) - 1))
+        if spec.kind == "index":
+            out[spec.name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
+            continue
+        dtype = torch.float32 if spec.kind == "vector" else compute_dtype
+        t = torch.empty(spec.shape, dtype=dtype, device=device)
+        if spec.init == "normal":
+            t.normal_(0.0, 0.02, generator=g)
+        elif spec.init == "one_plus_normal":
+            t.normal_(1.0, 0.1, generator=g)
+        elif spec.init == "zeros":
+            t.zero_()
+        else:
+            raise ValueError(f"tensor '{spec.name}': unknown init '{spec.init}'")
+        out[spec.name] = t
+    return out
