@@ -98,7 +98,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   auto page_of = [&](int ordinal) -> int {
     const int n = key_of(ordinal);
     if (ordinal >= my_count || n < lo || n > pos) return -1;
-    const int page = table[page_shift >= 0 ? (n >> page_shift) : (n / page_size)];
+    const int page = table_page(table, page_shift >= 0 ? (n >> page_shift) : (n / page_size), table_stride, status);
     if (page < 0 || page >= num_pages) {
       atomicOr(status, Q3_STATUS_BAD_PAGE);
       return -1;

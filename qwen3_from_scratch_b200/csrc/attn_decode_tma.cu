@@ -201,7 +201,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         int my_y = -1;
         if (chunk0 + lane < i_hi) {
           const int n0 = (t_lo + chunk0 + lane) * DT_KEYS;
-          int page = table[n0 / page_size];
+          int page = table_page(table, n0 / page_size, table_stride, status);
           if (page < 0 || page >= num_pages) {
             atomicOr(status, Q3_STATUS_BAD_PAGE);
             page = 0;
@@ -288,7 +288,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         for (int k = 0; k < VPL; ++k) kn[k] = __float2bfloat16_rn(x[k]);
         const int chunk = first >> 3;
         const size_t in_tile = (size_t)(chunk >> 3) * 2048 + r * 128 + (((chunk & 7) ^ (r & 7)) << 4) + (first & 7) * 2;
-        const int page = table[pos / page_size];
+        const int page = table_page(table, pos / page_size, table_stride, status);
         const bool page_ok = page >= 0 && page < num_pages;
         if (!page_ok && lane == 0) atomicOr(status, Q3_STATUS_BAD_PAGE);
         const size_t in_pool = (((size_t)(page_ok ? page : 0) * Hkv + hk) * page_size + pos % page_size) * D + first;

@@ -53,19 +53,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Address of key/value row `n` of a request in a paged cache [num_pages, Hkv, page_size, D].
-// Returns nullptr (and flags the status word) when the block table has no usable page there.
-template <typename T>
-__device__ __forceinline__ const T* paged_row(const T* pages, const int* table, int n, int page_size,
-                                              int num_pages, int Hkv, int hk, int D, int* status) {
-  const int page = table[n / page_size];
-  if (page < 0 || page >= num_pages) {
-    atomicOr(status, Q3_STATUS_BAD_PAGE);
-    return nullptr;
-  }
-  return pages + (((size_t)page * Hkv + hk) * page_size + (n % page_size)) * D;
-}
-
 // log2 of a page size that is a power of two, else -1 (the kernels then divide).
 static inline int page_shift_of(int page_size) {
   if (page_size <= 0 || (page_size & (page_size - 1))) return -1;

@@ -86,7 +86,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     const __nv_bfloat16 *ks = k_pages, *vs = v_pages;
     int bytes = 0;
     if (n >= lo_key && n <= pos_last) {
-      const int page = table[n / page_size];
+      const int page = table_page(table, n / page_size, table_stride, status);
       if (page >= 0 && page < num_pages) {
         const size_t off = (((size_t)page * Hkv + hk) * page_size + (n % page_size)) * D;
         ks = k_pages + off;

@@ -52,7 +52,7 @@ attn_ref_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T*
   float m = -INFINITY, l = 0.f;
   const int* table = block_table + (size_t)b * table_stride;
   for (int n = lo; n <= pos; ++n) {
-    const int page = table[n / page_size];
+    const int page = table_page(table, n / page_size, table_stride, status);
     if (page < 0 || page >= num_pages) {
       if (lane == 0) atomicOr(status, Q3_STATUS_BAD_PAGE);
       continue;

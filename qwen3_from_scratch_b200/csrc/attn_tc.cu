@@ -95,6 +95,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   const int row0 = qt * AT_BM;
   if (row0 >= total_rows) return;  // before any barrier or allocation: the whole block leaves
   const int past = len - q_len;
+  if (past < 0) {  // more new tokens than the request holds; also before any barrier or allocation
+    if (threadIdx.x == 0) atomicOr(status, Q3_STATUS_BAD_POSITION);
+    return;
+  }
   const int last_row = min(total_rows, row0 + AT_BM) - 1;
   const int pos_first = past + row0 / g, pos_last = past + last_row / g;
   const int n_tiles = pos_last / AT_BN + 1;
@@ -179,7 +183,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     const int pages_per_tile = AT_BN / page_size;
     auto page_id = [&](int j) -> int {  // lane's page of tile j, or -1 if the tile has no such page
       if (lane >= pages_per_tile || j >= n_tiles || j * AT_BN + lane * page_size >= len) return -1;
-      return table[(j * AT_BN) / page_size + lane];
+      return table_page(table, (j * AT_BN) / page_size + lane, table_stride, status);
     };
     int page = page_id(0), page_next = page_id(1);
     bool ok = true;

@@ -28,11 +28,22 @@
 // faulting when table data is bad; the host reads it after the step.
 #define Q3_STATUS_BAD_TOKEN 1   // token id outside the embedding table
 #define Q3_STATUS_BAD_PAGE 2    // page id outside the pool where a live position needs one
-#define Q3_STATUS_BAD_POSITION 4  // negative position or sequence index
+#define Q3_STATUS_BAD_POSITION 4  // negative position or sequence index, or a position beyond the block table's row
 #define Q3_STATUS_BAD_LOGITS 8    // a row of logits with no comparable value (all NaN)
 #define Q3_STATUS_TIMEOUT 16      // a bounded wait on an mbarrier ran out; the block gave up cleanly
 
 namespace q3 {
+
+// Entry `idx` of a request's block-table row of `table_stride` entries.  An index at or beyond the end of
+// the row (a length or position that the table was not made for) is never read: the status word gets
+// BAD_POSITION and the answer is "no page" (-1), which every caller treats like a hole in the table.
+__device__ __forceinline__ int table_page(const int* table, int idx, int table_stride, int* status) {
+  if (idx < 0 || idx >= table_stride) {
+    atomicOr(status, Q3_STATUS_BAD_POSITION);
+    return -1;
+  }
+  return table[idx];
+}
 
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -344,7 +344,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (pos < 0 || seq < 0) {
             atomicOr(status, Q3_STATUS_BAD_POSITION);
           } else {
-            const int page = qkv.block_table[(size_t)seq * qkv.table_stride + pos / qkv.page_size];
+            const int page = table_page(qkv.block_table + (size_t)seq * qkv.table_stride, pos / qkv.page_size,
+                                        qkv.table_stride, status);
             if (page < 0 || page >= qkv.num_pages)
               atomicOr(status, Q3_STATUS_BAD_PAGE);
             else

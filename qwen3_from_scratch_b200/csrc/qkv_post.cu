@@ -68,7 +68,7 @@ qkv_post_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict_
       if (lane == 0) atomicOr(status, Q3_STATUS_BAD_POSITION);
       return;
     }
-    const int page = block_table[(size_t)seq * table_stride + pos / page_size];
+    const int page = table_page(block_table + (size_t)seq * table_stride, pos / page_size, table_stride, status);
     if (page < 0 || page >= num_pages) {
       if (lane == 0) atomicOr(status, Q3_STATUS_BAD_PAGE);
       return;
@@ -159,7 +159,7 @@ qkv_post_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __rest
     if (pos < 0 || seq < 0) {
       if (threadIdx.x == 0) atomicOr(status, Q3_STATUS_BAD_POSITION);
     } else {
-      const int page = block_table[(size_t)seq * table_stride + pos / page_size];
+      const int page = table_page(block_table + (size_t)seq * table_stride, pos / page_size, table_stride, status);
       if (page < 0 || page >= num_pages) {
         if (threadIdx.x == 0) atomicOr(status, Q3_STATUS_BAD_PAGE);
       } else {

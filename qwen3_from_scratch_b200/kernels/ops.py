@@ -20,7 +20,7 @@ F32, BF16 = 0, 1
 STATUS_BITS = {
     1: "a token id outside the embedding table",
     2: "a page id outside the pool where a live position needs one",
-    4: "a negative position or sequence index",
+    4: "a negative position or sequence index, or a position beyond the block table's row",
     8: "a row of logits without a comparable value (all NaN)",
     16: "a bounded wait inside a kernel ran out (the kernel gave up cleanly)",
 }
@@ -751,6 +751,9 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
     (and float32) go to the plain kernel."""
     T, Hq, D = q.shape
     Hkv = k_pages.shape[1]
+    if block_table.dim() != 2 or max_kv_len > block_table.shape[1] * k_pages.shape[2]:
+        raise KernelError(f"paged_attention: the longest request has {max_kv_len} tokens, a block table row of "
+                          f"{block_table.shape[-1]} pages of {k_pages.shape[2]} holds fewer")
     if not fast_attention_takes(q.dtype, Hq, Hkv, D):
         attn_ref(q, k_pages, v_pages, out, q_start, kv_len, tok_seq, block_table, scale, window, status)
         return

@@ -26,18 +26,21 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
-# Two tiny configurations of the architecture that differ in every size and option:
-# layers, width, heads and group size, head size (B: heads * head_dim != width), feed-forward
-# width (B: no multiple of 128), vocabulary, theta, eps, tied/untied head, positions, window.
+# Tiny configurations of the architecture that differ in every size and option: layers, width,
+# heads and group size, head size (B: heads * head_dim != width), feed-forward width (B: no
+# multiple of 128), vocabulary, theta, eps, tied/untied head, positions, window.  A and B have
+# full attention in every layer, like the reference's model, whose own logits for both are kept
+# under tests/golden/; C, D and E have windowed layers.
 TINY_A = dict(
     architectures=["Qwen3ForCausalLM"], vocab_size=256, hidden_size=64, hidden_act="silu",
     num_hidden_layers=2, max_position_embeddings=512, num_key_value_heads=2, num_attention_heads=4,
     head_dim=16, intermediate_size=128, rms_norm_eps=1e-6, rope_theta=10000.0, tie_word_embeddings=True)
 TINY_B = dict(
     architectures=["Qwen3ForCausalLM"], vocab_size=384, hidden_size=80, hidden_act="silu",
-    num_hidden_layers=3, max_position_embeddings=1024, num_key_value_heads=2, num_attention_heads=6,
-    head_dim=32, intermediate_size=200, rms_norm_eps=1e-5, rope_theta=1000000.0, tie_word_embeddings=False,
-    sliding_window=24, use_sliding_window=True, max_window_layers=1)
+    num_hidden_layers=3, max_position_embeddings=256, num_key_value_heads=2, num_attention_heads=6,
+    head_dim=32, intermediate_size=200, rms_norm_eps=1e-5, rope_theta=1000000.0, tie_word_embeddings=False)
+# the same with windowed layers, written the older way (use_sliding_window + max_window_layers)
+TINY_E = dict(TINY_B, max_position_embeddings=1024, sliding_window=24, use_sliding_window=True, max_window_layers=1)
 # a third one with a head size that is no power of two and one kv head
 TINY_C = dict(
     architectures=["Qwen3ForCausalLM"], vocab_size=331, hidden_size=96, hidden_act="silu",
@@ -54,7 +57,7 @@ TINY_D = dict(
     head_dim=128, intermediate_size=384, rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=True,
     layer_types=["full_attention", "sliding_attention"], sliding_window=100)
 
-TINY = {"a": (TINY_A, 0), "b": (TINY_B, 2), "c": (TINY_C, 5), "d": (TINY_D, 9)}
+TINY = {"a": (TINY_A, 0), "b": (TINY_B, 2), "c": (TINY_C, 5), "d": (TINY_D, 9), "e": (TINY_E, 4)}
 
 
 def make_folder(tmp_path_factory, key, dtype="bfloat16", float32_tensors=None):

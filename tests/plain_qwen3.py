@@ -1,6 +1,7 @@
 """Plain, slow implementation of Qwen3 dense, the oracle of the tests.
 
-Whole sequences, no cache, one function for each part, float32 (or float64) on the CPU.
+Whole sequences, no cache, one function for each part, float32 (or float64), on the CPU or,
+for models of real width, on whatever device the weights were moved to (plain torch either way).
 It shares no code with the engine: it reads config.json and model.safetensors itself
 (through the safetensors package) and is written from the formulas of the reference
 (1483795887/qwen3_from_scratch); each function names the file and lines it follows.
@@ -63,7 +64,7 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
 def rope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float, dtype=torch.float32):
     """cos/sin of position * theta^(-2j/D), j < D/2 (models/rotary.py:36-45).  The inverse
     frequencies and the angle are formed in float32 as there, then widened if asked."""
-    inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+    inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=positions.device) / head_dim))
     freqs = torch.einsum("i,j->ij", positions.to(torch.float32), inv_freq)
     return freqs.cos().to(dtype), freqs.sin().to(dtype)
 
@@ -85,8 +86,8 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: 
     hkv = k.shape[1]
     g = hq // hkv
     scale = d ** -0.5
-    m_idx = torch.arange(T)[:, None]
-    n_idx = torch.arange(T)[None, :]
+    m_idx = torch.arange(T, device=q.device)[:, None]
+    n_idx = torch.arange(T, device=q.device)[None, :]
     hidden = n_idx > m_idx
     if window is not None:
         hidden = hidden | (n_idx <= m_idx - window)
@@ -141,8 +142,9 @@ def lm_head(h: torch.Tensor, w: Dict[str, torch.Tensor], config: dict) -> torch.
 
 def forward_logits(config: dict, w: Dict[str, torch.Tensor], ids: Sequence[int]) -> torch.Tensor:
     """Logits at every position of one whole sequence, [T, vocab] (models/qwen3.py:44-50,80-84)."""
-    ids = torch.as_tensor(list(ids), dtype=torch.long)
-    positions = torch.arange(ids.numel())
+    device = w["model.embed_tokens.weight"].device
+    ids = torch.as_tensor(list(ids), dtype=torch.long, device=device)
+    positions = torch.arange(ids.numel(), device=device)
     x = embedding(ids, w["model.embed_tokens.weight"])
     for i, window in enumerate(layer_windows(config)):
         x = decoder_layer(x, w, i, config, positions, window)

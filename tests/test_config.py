@@ -4,7 +4,7 @@ import json
 
 import pytest
 
-from conftest import TINY_A, TINY_B, TINY_C
+from conftest import TINY_A, TINY_B, TINY_C, TINY_E
 from qwen3_from_scratch_b200.config import ConfigError, Qwen3Config
 from qwen3_from_scratch_b200.registry import (build_model_spec, config_from_dict, load_config,
                                               registered_architectures)
@@ -16,7 +16,7 @@ def test_reads_every_size_from_the_file():
     assert (cfg.vocab_size, cfg.hidden_size, cfg.num_hidden_layers) == (384, 80, 3)
     assert (cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim) == (6, 2, 32)
     assert cfg.intermediate_size == 200 and cfg.rms_norm_eps == 1e-5 and cfg.rope_theta == 1e6
-    assert cfg.tie_word_embeddings is False and cfg.max_position_embeddings == 1024
+    assert cfg.tie_word_embeddings is False and cfg.max_position_embeddings == 256
 
 
 def test_head_dim_defaults_to_width_over_heads_only_when_absent():
@@ -57,12 +57,12 @@ def test_unsupported_values_are_refused(patch, word):
 
 
 def test_window_layers_from_either_form_of_the_keys():
-    b = config_from_dict(TINY_B)  # use_sliding_window + max_window_layers
+    b = config_from_dict(TINY_E)  # use_sliding_window + max_window_layers
     assert b.layer_types == ("full_attention", "sliding_attention", "sliding_attention")
     assert b.sliding_window == 24
     c = config_from_dict(TINY_C)  # explicit layer_types
     assert c.layer_types == ("sliding_attention", "full_attention") and c.sliding_window == 40
-    off = dict(TINY_B, use_sliding_window=False)
+    off = dict(TINY_E, use_sliding_window=False)
     assert config_from_dict(off).sliding_window is None
     assert set(config_from_dict(off).layer_types) == {"full_attention"}
 
@@ -75,7 +75,7 @@ def test_unknown_architecture_lists_the_registered_ones():
 
 
 def test_round_trip_through_a_folder(tmp_path):
-    for data in (TINY_A, TINY_B, TINY_C):
+    for data in (TINY_A, TINY_B, TINY_C, TINY_E):
         cfg = config_from_dict(data)
         cfg.save(str(tmp_path))
         assert load_config(str(tmp_path)) == cfg

@@ -753,6 +753,93 @@ def test_fast_attention_refuses_what_it_does_not_take():
         o.attn_decode(q, pages, pages, q.clone(), None, ints, ints, ints.view(1, 2), 1, 1.0, 0, 1, status())
 
 
+@pytest.mark.parametrize("kernel", ["attn_ref_f32", "attn_ref_bf16", "decode_cp_async", "decode_tma", "attn_prefill",
+                                    "attn_tc", "qkv_post_f32", "qkv_post_bf16", "decode_tma_raw"])
+def test_a_length_beyond_the_block_table_is_flagged_and_not_read(kernel):
+    """A request's length (or a token's position) one page beyond what the row pitch of the block table
+    holds.  The first request's row is followed in memory by the second one's, whose entries are valid page
+    ids: a kernel that indexed past the row's end would silently read (or, writing, overwrite) the other
+    request's pages.  Every kernel must set the bad-position bit instead, touch no page it was not given,
+    and leave finite output."""
+    o = ops()
+    bf16 = not kernel.endswith("f32")
+    dtype = torch.bfloat16 if bf16 else torch.float32
+    hq, hkv, d, page_size = 4, 2, 128 if bf16 else 48, 16
+    g = torch.Generator().manual_seed(31)
+    stride = 3                                   # pages a row of the table holds
+    good_len = stride * page_size                # the longest length the table was made for
+    bad_len = good_len + page_size               # one page beyond
+    q_len = 1 if kernel.startswith(("decode", "attn_ref")) else 20
+    num_pages = 2 * stride + 2
+    table = torch.tensor([[0, 1, 2], [3, 4, 5]], dtype=torch.int32)
+    k_pages = dev(torch.randn(num_pages, hkv, page_size, d, generator=g).to(dtype))
+    v_pages = dev(torch.randn(num_pages, hkv, page_size, d, generator=g).to(dtype))
+    q = dev(torch.randn(2 * q_len, hq, d, generator=g).to(dtype))
+    out = torch.zeros_like(q)
+    q_start = dev(torch.tensor([0, q_len, 2 * q_len], dtype=torch.int32))
+    tok_seq = dev(torch.tensor([0] * q_len + [1] * q_len, dtype=torch.int32))
+    partial = torch.empty(o.decode_partial_numel(2, hq, d), device="cuda")
+    scale = d ** -0.5
+
+    def run(lengths):
+        st = status()
+        kv_len = dev(torch.tensor(lengths, dtype=torch.int32))
+        if kernel.startswith("attn_ref"):
+            o.attn_ref(q, k_pages, v_pages, out, q_start, kv_len, tok_seq, dev(table), scale, 0, st)
+        elif kernel in ("decode_cp_async", "decode_tma"):
+            o.attn_decode(q, k_pages, v_pages, out, partial, q_start, kv_len, dev(table), 2, scale, 0, 2, st,
+                          loader=kernel[7:])
+        elif kernel == "attn_prefill":
+            o.attn_prefill(q, k_pages, v_pages, out, q_start, kv_len, dev(table), 2, q_len, scale, 0, st)
+        elif kernel == "attn_tc":
+            o.attn_tc(q, k_pages, v_pages, out, q_start, kv_len, dev(table), 2, q_len, scale, st)
+        elif kernel.startswith("qkv_post") or kernel == "decode_tma_raw":
+            T = 2 * q_len
+            qkv = dev(torch.randn(T, (hq + 2 * hkv) * d, generator=g).to(dtype))
+            positions = dev(torch.tensor([n - q_len + i for n in lengths for i in range(q_len)], dtype=torch.int32))
+            before = (k_pages.clone(), v_pages.clone())
+            if kernel == "decode_tma_raw":
+                o.attn_decode(q, k_pages, v_pages, out, partial, q_start, kv_len, dev(table), 2, scale, 0, 2, st,
+                              loader="tma", raw_qkv=(qkv, None, None, 0.0, None, True))
+            else:
+                o.qkv_post(qkv, out, k_pages, v_pages, None, None, 0.0, None, 0, positions, tok_seq, dev(table),
+                           hq, hkv, d, True, st)
+            # only slots of the tokens whose position the table covers may have changed
+            allowed = torch.zeros(num_pages, page_size, dtype=torch.bool)
+            for b, n in enumerate(lengths):
+                for pos in range(n - q_len, n):
+                    if pos // page_size < stride:
+                        allowed[int(table[b, pos // page_size]), pos % page_size] = True
+            for now, was in zip((k_pages, v_pages), before):
+                changed = (now != was).any(dim=3).any(dim=1).cpu()
+                assert not bool((changed & ~allowed).any()), "a slot outside the request's own pages was written"
+            k_pages.copy_(before[0])
+            v_pages.copy_(before[1])
+        torch.cuda.synchronize()
+        return int(st.item())
+
+    assert run([good_len, good_len - 5]) == 0
+    assert bool(torch.isfinite(out.float()).all())
+    word = run([bad_len, good_len - 5])
+    assert word & 4, f"status {word}: the bad-position bit is not set"
+    assert bool(torch.isfinite(out.float()).all())
+    with pytest.raises(o.KernelError):  # where the host knows the longest length it says so before any launch
+        o.paged_attention(q, k_pages, v_pages, out, q_start, dev(torch.tensor([bad_len, 5], dtype=torch.int32)), tok_seq,
+                          dev(table), 2, 2 if q_len == 1 else 0, q_len, bad_len, scale, 0, status(), partial)
+
+
+def test_attn_tc_flags_more_new_tokens_than_the_request_holds():
+    o = ops()
+    hq, hkv, d, page_size = 4, 2, 128, 16
+    q = torch.zeros(40, hq, d, device="cuda", dtype=torch.bfloat16)
+    pages = torch.zeros(4, hkv, page_size, d, device="cuda", dtype=torch.bfloat16)
+    st = status()
+    o.attn_tc(q, pages, pages, q.clone(), dev(torch.tensor([0, 40], dtype=torch.int32)),
+              dev(torch.tensor([30], dtype=torch.int32)), dev(torch.tensor([[0, 1, 2]], dtype=torch.int32)), 1, 40,
+              d ** -0.5, st)
+    assert int(st.item()) & 4
+
+
 def test_sample_greedy_ties_and_all_nan():
     logits = torch.zeros(3, 1000)
     logits[0, [400, 17, 900]] = 5.0

@@ -11,10 +11,14 @@ from safetensors import safe_open
 
 import plain_qwen3 as plain
 
-GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "tiny_reference_logits.safetensors")
+GOLDEN_DIR = os.path.join(os.path.dirname(__file__), "golden")
 
 
-def test_plain_matches_reference_logits(tmp_path):
+@pytest.mark.parametrize("name", ["tiny_reference_logits.safetensors", "tiny_b_reference_logits.safetensors"])
+def test_plain_matches_reference_logits(tmp_path, name):
+    """Tiny A (tied head, theta 1e4, eps 1e-6, 4:2 heads of 16) and tiny B (untied head, theta 1e6, eps 1e-5,
+    6:2 heads of 32 on a width of 80, feed-forward of 200, three layers, 100 tokens)."""
+    GOLDEN = os.path.join(GOLDEN_DIR, name)
     from qwen3_from_scratch_b200.registry import config_from_dict
     from qwen3_from_scratch_b200.weights import write_random_model
     with safe_open(GOLDEN, framework="pt") as f:

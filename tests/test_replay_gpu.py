@@ -10,8 +10,9 @@ from harness import Replayer, assert_close, plain_logits
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-LENGTHS = {"a": [5, 17, 31, 70, 131], "b": [1, 9, 33, 64, 100], "c": [3, 50, 97, 160], "d": [20, 150, 33, 300]}
-PAGE = {"a": 4, "b": 8, "c": 16, "d": 16}
+LENGTHS = {"a": [5, 17, 31, 70, 131], "b": [1, 9, 33, 64, 100], "c": [3, 50, 97, 160], "d": [20, 150, 33, 300],
+           "e": [2, 25, 49, 120]}
+PAGE = {"a": 4, "b": 8, "c": 16, "d": 16, "e": 8}
 
 
 def sequences(key):
