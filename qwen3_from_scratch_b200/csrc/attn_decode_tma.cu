@@ -215,7 +215,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           const uint32_t use = (uint32_t)i / DT_STAGES;
           const int y = __shfl_sync(0xffffffffu, my_y, u);
           if (use > 0) ok = ok && mbar_wait(empty + s, (use - 1) & 1, abort_word);
-          if (lane == 0 && ok) {
+          if (lane == 0 && ok && i != tc_drop_copy) {  // (the test of the give-up path drops one copy: see tc_common.cuh)
             unsigned char* stage = ring + (size_t)s * S::STAGE_BYTES;
             mbar_expect_tx(full + s, S::STAGE_BYTES);
 #pragma unroll
@@ -247,7 +247,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     bool ok = true;
     for (int i = warp; i < count; i += DT_CONSUMERS) {
       const int s = i % DT_STAGES;
-      ok = ok && mbar_wait(full + s, ((uint32_t)i / DT_STAGES) & 1, abort_word);
+      // (no short cut once a wait has run out: a copy that the loader did issue is still waited for, within
+      // the limit, before its stage is read and handed back)
+      ok = mbar_wait(full + s, ((uint32_t)i / DT_STAGES) & 1, abort_word) && ok;
       const unsigned char* k_t = ring + (size_t)s * S::STAGE_BYTES;
       unsigned char* v_t = ring + (size_t)s * S::STAGE_BYTES + S::TILE_BYTES;
       const int base_n = (t_lo + i) * DT_KEYS;
@@ -482,6 +484,9 @@ static int attn_decode_tma_launch(const void* q, const void* k_pages, const void
 }
 
 }  // namespace q3
+
+// For the tests of the give-up path: see set_wait_test in tc_common.cuh.
+extern "C" int q3_attn_decode_tma_wait_test(unsigned limit, int drop) { return q3::set_wait_test(limit, drop); }
 
 // Same arguments as q3_attn_decode.  Takes D = 64 or 128, page sizes that are multiples of 16 and up to
 // 16 query heads per kv head; refuses the rest.

@@ -200,9 +200,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       const uint32_t have = __popc(__ballot_sync(0xffffffffu, y >= 0));
       const uint32_t bytes = have * page_size * D * 2;
       if (use > 0) ok = ok && mbar_wait(empty + st, (use - 1) & 1, &abort_flag);
-      if (lane == 0 && ok) mbar_expect_tx(full + st, bytes);
+      const bool kept = is_v || j != tc_drop_copy;  // false only in the tests of the give-up path (see tc_common.cuh)
+      if (lane == 0 && ok && kept) mbar_expect_tx(full + st, bytes);
       __syncwarp();
-      if (y >= 0 && ok) {
+      if (y >= 0 && ok && kept) {
 #pragma unroll
         for (int a = 0; a < ATOMS; ++a)
           tma_load_2d(dst_base + st * S::K_BYTES + a * (AT_BN * 128) + lane * page_size * 128, map, full + st, a * 64, y);
@@ -450,6 +451,9 @@ static int attn_tc_launch(const void* q, const void* k_pages, const void* v_page
 }
 
 }  // namespace q3
+
+// For the tests of the give-up path: see set_wait_test in tc_common.cuh.
+extern "C" int q3_attn_tc_wait_test(unsigned limit, int drop) { return q3::set_wait_test(limit, drop); }
 
 // Same arguments as q3_attn_prefill, without a window.  Takes D = 64 or 128 and page sizes 8, 16, 32, 64;
 // refuses the rest (the caller then uses q3_attn_prefill).

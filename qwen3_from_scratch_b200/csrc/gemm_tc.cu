@@ -271,6 +271,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             ok = false;
             break;
           }
+          if ((int)it == tc_drop_copy) continue;  // tests of the give-up path only (see tc_common.cuh)
           unsigned char* a_s = tiles + (size_t)s * S::STAGE_BYTES;
           mbar_expect_tx(&full[s], S::STAGE_BYTES);
           tma_load_2d(a_s, &map_a, &full[s], kt * TC_BK, m0);
@@ -450,6 +451,9 @@ extern "C" int q3_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
   if (out_f32) return q3::gemm_tc_dispatch<0, float>(A, W, C, M, N, K, ldc, status, stream);
   return q3::gemm_tc_dispatch<0, bf16>(A, W, C, M, N, K, ldc, status, stream);
 }
+
+// For the tests of the give-up path: see set_wait_test in tc_common.cuh.
+extern "C" int q3_gemm_tc_wait_test(unsigned limit, int drop) { return q3::set_wait_test(limit, drop); }
 
 // The merged QKV projection of an attention layer with the work of q3_qkv_post in its epilogue:
 // qkv = A[T, K] * W[(Hq + 2 Hkv) D, K]^T is rounded to bfloat16 and, head by head, normed, rotated and

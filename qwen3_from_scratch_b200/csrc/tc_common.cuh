@@ -20,6 +20,14 @@ namespace q3 {
 constexpr int TC_BK = 64;  // one 128-byte swizzle atom of bfloat16
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 24;
 
+// How many polls a wait on an mbarrier makes before it gives up, and a hook for the tests of that path:
+// the loader of a kernel leaves out its copy number `tc_drop_copy` (and the barrier's expectation of it),
+// so that the barrier never completes and every role of the block has to give up, flag the status word,
+// free what it holds and return.  Each file that includes this header has its own copy of the two words
+// and exports a setter for them (q3_*_wait_test); the defaults are what serving uses.
+static __constant__ uint32_t tc_wait_limit = TC_WAIT_LIMIT;
+static __constant__ int tc_drop_copy = -1;
+
 __device__ __forceinline__ uint32_t s_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -41,7 +49,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false if the phase did not complete in time or another role gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
+  const uint32_t limit = tc_wait_limit;
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 1023u) == 1023u && *abort_flag) return false;
   }
@@ -167,6 +176,16 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// ---------------------------------------------------------------- host side: the wait limit of this file's kernels
+// `limit` polls per wait (0: the default) and the ordinal of the loader's copy that is left out (-1: none).
+// The words are set for the current device, before the next launch (a blocking copy).
+static int set_wait_test(unsigned limit, int drop) {
+  const uint32_t polls = limit ? limit : TC_WAIT_LIMIT;
+  cudaError_t e = cudaMemcpyToSymbol(tc_wait_limit, &polls, sizeof(polls));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(tc_drop_copy, &drop, sizeof(drop));
+  return (int)e;
+}
 
 // ---------------------------------------------------------------- host side: tensor maps
 static PFN_cuTensorMapEncodeTiled tensor_map_encoder() {

@@ -83,6 +83,9 @@ _SIGNATURES = {
 }
 
 
+_WAIT_TEST = ("q3_gemm_tc_wait_test", "q3_attn_tc_wait_test", "q3_attn_decode_tma_wait_test")
+
+
 def library() -> ctypes.CDLL:
     """The loaded kernel library; compiles it at the first call if it is not built yet."""
     global _lib, _lib_path
@@ -97,6 +100,10 @@ def library() -> ctypes.CDLL:
                 for name, argtypes in _SIGNATURES.items():
                     fn = getattr(lib, name)
                     fn.argtypes = argtypes
+                    fn.restype = _c_int
+                for name in _WAIT_TEST:
+                    fn = getattr(lib, name)
+                    fn.argtypes = [ctypes.c_uint, _c_int]
                     fn.restype = _c_int
                 lib.q3_sample_scratch_bytes.argtypes = [_c_int]
                 lib.q3_sample_scratch_bytes.restype = _c_ll
@@ -173,6 +180,19 @@ def _done(kernel: str, code: int, detail: str = "") -> None:
     if code == -5:
         raise KernelError(f"{kernel}: the CUDA driver refused a tensor-map request ({detail})")
     raise KernelError(f"{kernel}: CUDA launch failed with error {code} ({detail})")
+
+
+def set_wait_test(limit: int = 0, drop_copy: int = -1) -> None:
+    """For tests of the path on which a kernel gives up a wait: every wait on an mbarrier in the TMA / tcgen05
+    kernels polls ``limit`` times (0: the serving default of 2^24) and the loader of each leaves out its copy
+    number ``drop_copy`` (-1: none), whose barrier then never completes.  Call it with no arguments to put the
+    defaults back.  Synchronises the device."""
+    torch.cuda.synchronize()
+    for name in _WAIT_TEST:
+        code = getattr(library()._lib, name)(int(limit), int(drop_copy))
+        if code:
+            raise KernelError(f"{name}: CUDA error {code}")
+    torch.cuda.synchronize()
 
 
 def describe_status(word: int) -> str:

@@ -270,6 +270,33 @@ def test_request_that_cannot_fit_is_refused(tiny_folders):
         engine.add_request("text without a tokenizer")
 
 
+def test_a_kernel_that_gave_up_a_wait_raises_and_the_engine_carries_on(tiny_folders):
+    """The time-out bit of the status word reaches the caller as ``DeviceStatusError``; after it the same
+    session runs other requests correctly (nothing was left held on the device)."""
+    from harness import Replayer, assert_close, plain_logits
+    from qwen3_from_scratch_b200.engine.session import DeviceStatusError, Session
+    from qwen3_from_scratch_b200.kernels import ops
+    folder = tiny_folders["d"]
+    vocab = TINY["d"][0]["vocab_size"]
+    session = Session(folder, dtype="bfloat16", page_size=16, cache_tokens=1024, max_seqs=4, max_step_tokens=512,
+                      cuda_graphs=False)
+    doomed = random_tokens(vocab, 300, 41)
+    try:
+        ops.set_wait_test(limit=1 << 14, drop_copy=1)
+        session.step([("doomed", doomed, [len(doomed) - 1])])
+        with pytest.raises(DeviceStatusError, match="wait"):
+            session.check_status()
+    finally:
+        ops.set_wait_test()
+    session.end("doomed")
+    seqs = {"after": random_tokens(vocab, 280, 42)}
+    rep = Replayer(session, seqs)
+    rep.step([("after", 200)])
+    while rep.remaining("after"):
+        rep.step([("after", 1)])
+    assert_close(rep.result(), plain_logits(folder, seqs), "bfloat16", "after a time-out")
+
+
 def run_trace(folder, dtype, steps, out, max_tokens, extra=()):
     env = dict(os.environ)
     cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,

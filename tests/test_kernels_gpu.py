@@ -840,6 +840,72 @@ def test_attn_tc_flags_more_new_tokens_than_the_request_holds():
     assert int(st.item()) & 4
 
 
+@pytest.mark.parametrize("kernel", ["gemm_tc", "attn_tc", "attn_decode_tma"])
+def test_a_wait_that_runs_out_is_given_up_cleanly(kernel):
+    """The bounded waits of the TMA / tcgen05 kernels, made to run out: the loader is told to leave out one
+    copy, so the barrier that copy would complete never does.  With the poll limit made small the kernel must
+    return by itself with the time-out bit set, and the next ordinary launch of the same kernel (which needs
+    the tensor memory and the barriers' shared memory that the abandoned blocks held) must give the right
+    result.  No wait anywhere spins without a limit; nothing here faults."""
+    o = ops()
+    g = torch.Generator().manual_seed(77)
+    if kernel == "gemm_tc":
+        x = dev(torch.randn(256, 256, generator=g).to(torch.bfloat16))
+        w = dev(torch.randn(384, 256, generator=g).to(torch.bfloat16))
+        out = torch.zeros(256, 384, device="cuda", dtype=torch.bfloat16)
+
+        def run(st):
+            o.gemm_tc(x, w, out, st)
+
+        def check():
+            close(out, x.double() @ w.double().t(), "bfloat16")
+    else:
+        hq, hkv, d, page_size = 4, 2, 128, 16
+        decode = kernel == "attn_decode_tma"
+        kv_lens, q_lens = ([300, 200], [1, 1]) if decode else ([300], [300])
+        q, k_list, v_list, tables, num_pages = attention_case("bfloat16", hq, hkv, d, page_size, kv_lens, q_lens, None)
+        k_pages = dev(paged(k_list, page_size, tables, num_pages, torch.bfloat16))
+        v_pages = dev(paged(v_list, page_size, tables, num_pages, torch.bfloat16))
+        qd = dev(q)
+        out = torch.zeros_like(qd)
+        q_start = dev(torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32))
+        kv = dev(torch.tensor(kv_lens, dtype=torch.int32))
+        table = dev(table_tensor(tables))
+        partial = torch.empty(o.decode_partial_numel(len(q_lens), hq, d), device="cuda")
+
+        def run(st):
+            if decode:
+                o.attn_decode(qd, k_pages, v_pages, out, partial, q_start, kv, table, len(q_lens), d ** -0.5, 0, 2, st,
+                              loader="tma")
+            else:
+                o.attn_tc(qd, k_pages, v_pages, out, q_start, kv, table, 1, q_lens[0], d ** -0.5, st)
+
+        def check():
+            want = reference_attention(q.double(), [k.double() for k in k_list], [v.double() for v in v_list], q_lens, None)
+            close(out, want, "bfloat16")
+
+    st = status()
+    run(st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    check()
+    try:
+        o.set_wait_test(limit=1 << 14, drop_copy=1)
+        run(st)
+        torch.cuda.synchronize()
+        word = int(st.item())
+    finally:
+        o.set_wait_test()
+    assert word & 16, f"status {word}: the time-out bit is not set"
+    assert "wait" in o.describe_status(word)
+    st.zero_()
+    out.zero_()
+    run(st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    check()
+
+
 def test_sample_greedy_ties_and_all_nan():
     logits = torch.zeros(3, 1000)
     logits[0, [400, 17, 900]] = 5.0
