@@ -1,8 +1,8 @@
 """Cache manager: who holds which page and which state slot.  Host side only, no device code.
 
 Keys and values live in pages of ``page_size`` tokens.  Caches (one per entry of the model's
-run order that keeps keys/values) with the same needs form a *group*: same heads, same head
-size, same window.  A group has a page pool of its own, and every request has one block table
+run order that keeps keys/values) with the same needs form a *group*: the same planes (for attention:
+keys and values of so many heads of such a size) and the same window.  A group has a page pool of its own, and every request has one block table
 per group: logical page i of the request -> page id, shared by all caches of the group (page
 p addresses the same slot in each of them, as in the reference's one tensor for all layers,
 inference/kv_cache/paged_cache.py:21-33).
@@ -23,7 +23,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
-from ..parts.base import KVCacheSpec, StateSpec
+from ..parts.base import PagedCacheSpec, StateSpec
 
 
 class CacheError(RuntimeError):
@@ -40,9 +40,9 @@ class OutOfSlots(CacheError):
 
 @dataclass
 class PageGroup:
-    """Caches that share page ids: same KV shape and window."""
+    """Caches that share page ids: same planes and window."""
 
-    spec: KVCacheSpec
+    spec: PagedCacheSpec
     cache_ids: List[int]
     num_pages: int = 0
 
@@ -62,16 +62,19 @@ class CacheLayout:
 
 
 def layout_of(cache_specs: Dict[int, object]) -> CacheLayout:
-    """``cache_specs``: cache id -> KVCacheSpec | StateSpec | None (what each mixer asked for)."""
+    """``cache_specs``: cache id -> PagedCacheSpec | StateSpec | None (what each mixer asked for)."""
     layout = CacheLayout()
-    by_spec: Dict[KVCacheSpec, PageGroup] = {}
+    by_spec: Dict[PagedCacheSpec, PageGroup] = {}
     for cache_id in sorted(cache_specs):
         spec = cache_specs[cache_id]
         if spec is None:
             continue
         if isinstance(spec, StateSpec):
             layout.states[cache_id] = spec
-        elif isinstance(spec, KVCacheSpec):
+        elif isinstance(spec, PagedCacheSpec):
+            names = [p.name for p in spec.planes]
+            if not names or len(set(names)) != len(names):
+                raise ValueError(f"cache {cache_id}: a paged cache needs planes with distinct names, got {names}")
             if spec not in by_spec:
                 by_spec[spec] = PageGroup(spec, [])
                 layout.groups.append(by_spec[spec])

@@ -1,9 +1,10 @@
 """Device memory behind the cache manager: the pages of every group and the state slots.
 
-One group = one tensor ``[caches, 2, num_pages, kv_heads, page_size, head_dim]`` in the compute
-dtype (index 0 of the second axis holds keys, 1 values).  A page's keys of one head are
-contiguous (page_size x head_dim), which is the unit the attention kernels fetch.
-State caches are ``[max_seqs, *shape]`` tensors, zero when a slot is handed to a new request.
+A group's caches declare named planes (``PagedCacheSpec.planes``; ``k`` and ``v`` for attention).  Every
+plane of a group is one tensor ``[caches, num_pages, heads, page_size, width]`` in the plane's dtype, so
+that one cache's pages of one plane are a contiguous ``[num_pages, heads, page_size, width]`` array and a
+page's vectors of one head are contiguous (page_size x width), which is the unit the attention kernels
+fetch.  State caches are ``[max_seqs, *shape]`` tensors, zero when a slot is handed to a new request.
 """
 
 from __future__ import annotations
@@ -18,13 +19,15 @@ from .manager import CacheLayout
 class CacheStorage:
     def __init__(self, layout: CacheLayout, page_size: int, max_seqs: int, device, dtype: torch.dtype):
         self.layout, self.page_size, self.dtype = layout, page_size, dtype
-        self.group_pages: List[torch.Tensor] = []
+        self.group_planes: List[Dict[str, torch.Tensor]] = []  # per group: plane name -> its tensor
         self._where: Dict[int, Tuple[int, int]] = {}
         for g, group in enumerate(layout.groups):
-            spec = group.spec
-            self.group_pages.append(torch.zeros(
-                len(group.cache_ids), 2, group.num_pages, spec.num_kv_heads, page_size, spec.head_dim,
-                dtype=dtype, device=device))
+            planes = {}
+            for plane in group.spec.planes:
+                pdtype = torch.float32 if plane.dtype == "float32" else dtype
+                planes[plane.name] = torch.zeros(len(group.cache_ids), group.num_pages, plane.heads, page_size,
+                                                 plane.width, dtype=pdtype, device=device)
+            self.group_planes.append(planes)
             for i, cache_id in enumerate(group.cache_ids):
                 self._where[cache_id] = (g, i)
         self.states: Dict[int, torch.Tensor] = {}
@@ -35,9 +38,14 @@ class CacheStorage:
     def group_of(self, cache_id: int) -> int:
         return self._where[cache_id][0]
 
-    def kv_pages(self, cache_id: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    def planes(self, cache_id: int) -> Dict[str, torch.Tensor]:
+        """Plane name -> ``[num_pages, heads, page_size, width]`` of one cache."""
         g, i = self._where[cache_id]
-        return self.group_pages[g][i, 0], self.group_pages[g][i, 1]
+        return {name: t[i] for name, t in self.group_planes[g].items()}
+
+    def kv_pages(self, cache_id: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        planes = self.planes(cache_id)
+        return planes["k"], planes["v"]
 
     def clear_slot(self, slot: int) -> None:
         for state in self.states.values():
@@ -49,9 +57,10 @@ class CacheStorage:
         for g, page in freed:
             by_group.setdefault(g, []).append(page)
         for g, pages in by_group.items():
-            idx = torch.tensor(sorted(set(pages)), device=self.group_pages[g].device)
-            self.group_pages[g][:, :, idx] = float("nan")
+            for t in self.group_planes[g].values():
+                idx = torch.tensor(sorted(set(pages)), device=t.device)
+                t[:, idx] = float("nan")
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.group_pages) + sum(
+        return sum(t.numel() * t.element_size() for planes in self.group_planes for t in planes.values()) + sum(
             t.numel() * t.element_size() for t in self.states.values())

@@ -388,6 +388,33 @@ static int attn_decode_launch(const void* q, const void* k_pages, const void* v_
 
 }  // namespace q3
 
+// Streaming multiprocessors of the current device.
+extern "C" int q3_sm_count() { return q3::sm_count(); }
+
+// Blocks of the decode kernel for head size D that one SM holds at once, as the CUDA runtime reckons it from
+// the compiled kernel's registers and shared memory (0: a head size the kernel does not take, or an error).
+extern "C" int q3_attn_decode_blocks_per_sm(int D) {
+  if (D % 16 || D < 16 || D > 256) return 0;
+  int blocks = 0;
+  cudaError_t e = cudaErrorInvalidValue;
+#define Q3_AD_OCC(KT)                                                                                          \
+  case KT: {                                                                                                   \
+    using S = q3::DecodeShape<KT>;                                                                             \
+    e = cudaFuncSetAttribute(q3::attn_decode_kernel<KT>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
+                             (int)S::SMEM_BYTES);                                                              \
+    if (e == cudaSuccess)                                                                                      \
+      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, q3::attn_decode_kernel<KT>, q3::AD_WARPS * 32, \
+                                                        S::SMEM_BYTES);                                        \
+    break;                                                                                                     \
+  }
+  switch (D / 16) {
+    Q3_AD_OCC(1) Q3_AD_OCC(2) Q3_AD_OCC(3) Q3_AD_OCC(4) Q3_AD_OCC(5) Q3_AD_OCC(6) Q3_AD_OCC(7) Q3_AD_OCC(8)
+    Q3_AD_OCC(9) Q3_AD_OCC(10) Q3_AD_OCC(11) Q3_AD_OCC(12) Q3_AD_OCC(13) Q3_AD_OCC(14) Q3_AD_OCC(15) Q3_AD_OCC(16)
+  }
+#undef Q3_AD_OCC
+  return e == cudaSuccess ? blocks : 0;
+}
+
 // Decode attention for B sequences that each bring one query token.
 // q, out: bf16 [T, Hq, D] (the token of sequence b is row q_start[b]); pages: bf16 [num_pages, Hkv, page_size, D];
 // partial: float32 scratch of at least B * Hq * num_splits * (D + 2) elements (unused when num_splits == 1).

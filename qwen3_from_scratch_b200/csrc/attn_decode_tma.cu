@@ -473,7 +473,7 @@ static int attn_decode_tma_launch(const void* q, const void* k_pages, const void
   code = cached_map(&map_v, v_pages, rows, D, DT_KEYS);
   if (code) return code;
   dim3 grid(num_splits, Hkv, B);
-  const bool many = (long long)num_splits * Hkv * B > 2 * 148;  // more blocks than two per SM hold at once
+  const bool many = (long long)num_splits * Hkv * B > 2LL * sm_count();  // more blocks than two per SM hold at once
   auto kernel = many ? attn_decode_tma_kernel<D, 3> : attn_decode_tma_kernel<D, 2>;
   q3::launch(kernel, grid, dim3(DT_THREADS), S::SMEM_BYTES, stream, map_k, map_v,
              (const __nv_bfloat16*)q, (__nv_bfloat16*)out, partial, q_start, kv_len, block_table, table_stride,

@@ -82,6 +82,20 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
 
+// Streaming multiprocessors of the current device (asked once per device; grids, split counts and the
+// choice between kernel variants are sized by it, never by a constant).
+static inline int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
+  if (cached[dev] <= 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 // ---------------------------------------------------------------- programmatic dependent launch
 // Every kernel of this library starts with pdl_wait() and then pdl_launch_dependents().  Launched
 // with the programmatic-serialization attribute (launch() below), a kernel's blocks may become

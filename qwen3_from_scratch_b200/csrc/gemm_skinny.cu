@@ -274,15 +274,16 @@ static int gemm_skinny_launch(const void* X, const void* W, void* out, int T, in
                               cudaStream_t stream, SkinnyFuse fuse = SkinnyFuse{}) {
   if (EPI == 2) fuse.early = last_launch_was_plain(stream) ? 1 : 0;
   const int groups = (N + 15) / 16;
+  const int sms = sm_count();
   // split K over more warps while that still leaves every warp at least 128 values of k and the
   // grid is short of about four blocks per SM
   int wk = 1;
-  while (wk < GS_WARPS && (groups * wk * 2) / GS_WARPS < 148 * 4 && K / (wk * 2) >= 128) wk *= 2;
+  while (wk < GS_WARPS && (groups * wk * 2) / GS_WARPS < sms * 4 && K / (wk * 2) >= 128) wk *= 2;
   const int per_block = GS_WARPS / wk;
   const unsigned grid = (groups + per_block - 1) / per_block;
 #define Q3_GS_GO(WK, PRE)                                                                                         \
   do {                                                                                                            \
-    if (NT == 2 && PRE == 1 && grid <= 2 * 148u)                                                                  \
+    if (NT == 2 && PRE == 1 && grid <= 2u * (unsigned)sms)                                                                  \
       q3::launch(gemm_skinny_kernel<NT, WK, EPI, OutT, PRE, NORMED, NT == 2 && PRE == 1>, dim3(grid),             \
                  dim3(GS_WARPS * 32), 0, stream, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (OutT*)out, T, N, K, \
                  ldo, fuse);                                                                                      \
@@ -295,7 +296,7 @@ static int gemm_skinny_launch(const void* X, const void* W, void* out, int T, in
   // leave room for one block per SM, and a larger grid would then run in waves whose later blocks fetch
   // nothing ahead (at 4,096 wide, 384 blocks, that cost 8 % of the step)
   const int batches = ((K + 31) / 32 + wk * GS_UNROLL - 1) / (wk * GS_UNROLL);
-  const bool few_blocks = grid <= 148u && (NT == 1 || EPI == 2);
+  const bool few_blocks = grid <= (unsigned)sms && (NT == 1 || EPI == 2);
   const int pre = few_blocks && wk == GS_WARPS ? (batches < 3 ? batches : 3) : 1;
   if (wk == 1) Q3_GS_GO(1, 1);
   else if (wk == 2) Q3_GS_GO(2, 1);

@@ -385,17 +385,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
-static int tc_sm_count() {
-  static int sms = 0;
-  if (!sms) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-      sms = 0;
-    if (sms <= 0) sms = 148;
-  }
-  return sms;
-}
-
 template <int BN, int EPI, typename OutT, int HD = 128>
 static int gemm_tc_launch(const void* A, const void* W, void* C, int M, int N, int K, int ldc, int* status,
                           cudaStream_t stream, const QkvEpilogue& qkv = QkvEpilogue{}) {
@@ -414,7 +403,7 @@ static int gemm_tc_launch(const void* A, const void* W, void* C, int M, int N, i
   if (code) return code;
   const long long tiles = (long long)((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM);
   if (tiles > 0x7fffffffLL) return Q3_ERR_SIZE;
-  const int grid = (int)(tiles < tc_sm_count() ? tiles : tc_sm_count());
+  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
   q3::launch(gemm_tc_kernel<BN, EPI, OutT, HD>, dim3(grid), dim3(TC_THREADS), S::SMEM_BYTES, stream, map_a, map_b,
              (OutT*)C, M, N, K, ldc, qkv, status);
   return launch_status();
@@ -422,7 +411,7 @@ static int gemm_tc_launch(const void* A, const void* W, void* C, int M, int N, i
 
 // The tile width that needs fewer rounds of the SMs: rounds x width is the cost of the slowest block.
 static int tc_pick_bn(int M, int N) {
-  const long long sms = tc_sm_count();
+  const long long sms = sm_count();
   const long long m_tiles = (M + TC_BM - 1) / TC_BM;
   const long long t256 = m_tiles * ((N + 255) / 256), t128 = m_tiles * ((N + 127) / 128);
   const long long c256 = ((t256 + sms - 1) / sms) * 256, c128 = ((t128 + sms - 1) / sms) * 128;

@@ -10,7 +10,7 @@ tensor per array, each with a copy of its own: inference/model_worker.py:177-210
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Hashable, List, Optional, Sequence
+from typing import Dict, Hashable, List, Optional, Sequence
 
 import torch
 
@@ -24,12 +24,17 @@ class Entry:
     request: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()  # indices into ``tokens`` whose logits are asked for
+    # per-token integers that a part of the model defines for itself (positions on several axes, segment
+    # ids, ...): name -> one int, or one row of ints, per token; they reach the parts as ``ctx.extra[name]``
+    extra: Optional[Dict[str, Sequence]] = None
 
 
 class BatchContext(StepContext):
     def __init__(self, manager: CacheManager, storage: CacheStorage, rt: Runtime):
         self.manager, self.storage, self.rt = manager, storage, rt
         self._tables: List[torch.Tensor] = []
+        self._extra_layout: List = []
+        self.extra: Dict[str, torch.Tensor] = {}
         self._head_views = None
         self._cuts = None
         self.requests: List[Hashable] = []
@@ -41,11 +46,12 @@ class BatchContext(StepContext):
         Writes tokens, positions and lengths into the pinned buffer and copies them; False if the step is
         not of that kind (nothing has been touched then)."""
         m, B = self.manager, len(entries)
-        if self._cuts[:7] != [B, B, B, B + 1, B, B, B] or (table_stride is not None and self._fixed_stride != table_stride):
+        if (self._cuts[:7] != [B, B, B, B + 1, B, B, B] or self._extra_layout
+                or (table_stride is not None and self._fixed_stride != table_stride)):
             return False
         tokens, starts, versions = [], [], []
         for e, request in zip(entries, self.requests):
-            if e.request != request or len(e.tokens) != 1 or tuple(e.want) != (0,):
+            if e.request != request or len(e.tokens) != 1 or tuple(e.want) != (0,) or e.extra:
                 return False
             t = int(e.tokens[0])
             if not 0 <= t < vocab_size:
@@ -75,10 +81,35 @@ class BatchContext(StepContext):
         self.h2d_bytes = (7 * B + 1) * 4
         return True
 
-    def kv(self, cache_id: int):
-        g = self.storage.group_of(cache_id)
-        k, v = self.storage.kv_pages(cache_id)
-        return k, v, self._tables[g]
+    @staticmethod
+    def _extra_of(entries: Sequence[Entry], order: Sequence[int]):
+        """The entries' ``extra`` arrays in the batch's row order: (all values flat, [(name, width)])."""
+        names = sorted(entries[0].extra or {})
+        flat: List[int] = []
+        layout = []
+        for e in entries:
+            if sorted(e.extra or {}) != names:
+                raise ValueError(f"request {e.request!r} brings the per-token arrays {sorted(e.extra or {})}, "
+                                 f"others of the step bring {names}")
+        for name in names:
+            width = None
+            for orig in order:
+                e = entries[orig]
+                rows = e.extra[name]
+                if len(rows) != len(e.tokens):
+                    raise ValueError(f"request {e.request!r}: '{name}' has {len(rows)} rows for {len(e.tokens)} tokens")
+                for r in rows:
+                    vals = [int(r)] if isinstance(r, int) else [int(x) for x in r]
+                    if width is None:
+                        width = len(vals)
+                    if len(vals) != width or width == 0:
+                        raise ValueError(f"request {e.request!r}: rows of '{name}' differ in width")
+                    flat.extend(vals)
+            layout.append((name, width))
+        return flat, layout
+
+    def pages(self, cache_id: int):
+        return self.storage.planes(cache_id), self._tables[self.storage.group_of(cache_id)]
 
     def state(self, cache_id: int):
         return self.storage.states[cache_id]
@@ -133,18 +164,20 @@ class BatchContext(StepContext):
                 if not 0 <= int(w) < len(e.tokens):
                     raise ValueError(f"request {e.request!r}: wanted place {w} is outside its {len(e.tokens)} tokens")
                 logit_rows.append(base + int(w))
+        extra_flat, extra_layout = self._extra_of(entries, order)
         T, B, R = len(tokens), len(order), len(logit_rows)
         if T > self.rt.max_tokens:
             raise ValueError(f"a step of {T} tokens exceeds the {self.rt.max_tokens} the engine was sized for")
         if B > self.rt.max_seqs:
             raise ValueError(f"a step of {B} requests exceeds the {self.rt.max_seqs} the engine was sized for")
         n_groups = len(m.layout.groups)
-        head = tokens + positions + tok_seq + q_start + kv_len + slots + logit_rows
+        head = tokens + positions + tok_seq + q_start + kv_len + slots + logit_rows + extra_flat
         versions = [m.table_version(r) for r in self.requests]
         self.num_tokens, self.num_seqs = T, B
         self.max_q_len, self.max_kv_len = max(self.q_lens), max(self.kv_lens)
         self.num_decode = sum(1 for n in self.q_lens if n == 1)
         if (keep_buffer and getattr(self, "_cuts", None) is not None and self._cuts[:7] == [T, T, T, B + 1, B, B, R]
+                and self._extra_layout == extra_layout
                 and self._versions == versions and (table_stride is None or self._fixed_stride == table_stride)):
             # same requests, no block table changed since the last build: only the short arrays travel
             n_head = len(head)
@@ -172,7 +205,7 @@ class BatchContext(StepContext):
                 flat_tables.extend([-1] * (stride - len(r)))
         flat = head + flat_tables
         self._versions, self._fixed_stride = versions, table_stride
-        cuts = [T, T, T, B + 1, B, B, R] + [B * s for s in strides]
+        cuts = [T, T, T, B + 1, B, B, R] + [T * w for _, w in extra_layout] + [B * s for s in strides]
         if keep_buffer and getattr(self, "_cuts", None) == cuts:
             self._copied.synchronize()  # the previous copy out of the pinned buffer has finished
             self._host.copy_(torch.tensor(flat, dtype=torch.int32))
@@ -184,13 +217,15 @@ class BatchContext(StepContext):
             raise ValueError("this batch does not have the layout of the buffer it was asked to reuse")
         host = torch.tensor(flat, dtype=torch.int32).pin_memory()
         dev = host.to(self.rt.device, non_blocking=True)
-        self._host, self._dev, self._cuts = host, dev, cuts
+        self._host, self._dev, self._cuts, self._extra_layout = host, dev, cuts, extra_layout
         self._head_views = None
         self._copied = torch.cuda.Event()
         self._copied.record()
         views = torch.split(dev, cuts)
         (self.token_ids, self.positions, self.tok_seq, self.q_start, self.kv_len, self.slot_ids,
          self.logit_rows) = views[:7]
-        self._tables = [views[7 + g].view(B, strides[g]) for g in range(n_groups)]
+        n_extra = len(extra_layout)
+        self.extra = {name: views[7 + i].view(T, w) for i, (name, w) in enumerate(extra_layout)}
+        self._tables = [views[7 + n_extra + g].view(B, strides[g]) for g in range(n_groups)]
         self.h2d_bytes = host.numel() * 4
         return self

@@ -102,7 +102,7 @@ class SyncEngine:
         cache_pages = num_pages
         if cache_pages is None:
             cache_pages = self._pages_from_memory(model_path, dtype, device, block_size, gpu_utilization,
-                                                  max_num_tokens)
+                                                  max_num_seqs)
         self.session = Session(model_path, dtype=dtype, device=device, page_size=block_size,
                                num_pages=cache_pages, max_seqs=max_num_seqs, max_step_tokens=max_num_tokens,
                                cuda_graphs=cuda_graphs, random_weights=random_weights)
@@ -157,7 +157,7 @@ class SyncEngine:
                    log_interval=log_interval, **kwargs)
 
     @staticmethod
-    def _pages_from_memory(model_path, dtype, device, block_size, gpu_utilization, max_num_tokens) -> int:
+    def _pages_from_memory(model_path, dtype, device, block_size, gpu_utilization, max_num_seqs) -> int:
         """Pages that fit in ``gpu_utilization`` of what will be free once the weights are loaded
         (the reference sizes its pool from free memory the same way: inference/model_worker.py:49-59)."""
         from ..cache.manager import CacheManager  # noqa: F401
@@ -172,10 +172,15 @@ class SyncEngine:
                 n *= d
             weight_bytes += n * (4 if s.kind == "vector" else item)
         layout = model.cache_layout()
-        per_page = sum(len(g.cache_ids) * 2 * g.spec.num_kv_heads * g.spec.head_dim * block_size * item
-                       for g in layout.groups)
+        per_page = sum(len(g.cache_ids) * g.spec.bytes_per_token(item) * block_size for g in layout.groups)
+        state_bytes = 0  # the slots of fixed-size state are there for max_num_seqs requests whatever runs
+        for spec in layout.states.values():
+            n = 4 if spec.dtype == "float32" else item
+            for d in spec.shape:
+                n *= d
+            state_bytes += n * max_num_seqs
         free, _total = torch.cuda.mem_get_info(torch.device(device))
-        budget = int((free - weight_bytes) * gpu_utilization)
+        budget = int((free - weight_bytes - state_bytes) * gpu_utilization)
         pages = budget // max(per_page, 1) if per_page else 1
         if pages < 1:
             raise RuntimeError(f"no memory left for the cache: {free} bytes free, weights need {weight_bytes}")

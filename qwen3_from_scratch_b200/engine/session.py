@@ -60,7 +60,9 @@ class StepGraphs:
         stride = -(-bucket // s.manager.page_size)
         lens = [len(e.tokens) for e in entries]
         key = (sum(lens), len(entries), sum(1 for n in lens if n == 1), max(lens),
-               sum(len(e.want) for e in entries), bucket)
+               sum(len(e.want) for e in entries), bucket,
+               tuple(sorted((name, len(rows[0]) if rows and not isinstance(rows[0], int) else 1)
+                            for name, rows in (entries[0].extra or {}).items())))
         slot = self.graphs.get(key)
         if slot is not None:
             self.graphs.move_to_end(key)

@@ -105,6 +105,10 @@ def library() -> ctypes.CDLL:
                     fn = getattr(lib, name)
                     fn.argtypes = [ctypes.c_uint, _c_int]
                     fn.restype = _c_int
+                lib.q3_sm_count.argtypes = []
+                lib.q3_sm_count.restype = _c_int
+                lib.q3_attn_decode_blocks_per_sm.argtypes = [_c_int]
+                lib.q3_attn_decode_blocks_per_sm.restype = _c_int
                 lib.q3_sample_scratch_bytes.argtypes = [_c_int]
                 lib.q3_sample_scratch_bytes.restype = _c_ll
                 _lib, _lib_path = _Counting(lib), path
@@ -404,10 +408,9 @@ def sumsq_parts(features: int) -> int:
 
 
 def gemm_skinny_normed_pays(rows: int, weight: torch.Tensor) -> bool:
-    """Whether a decode step without norm kernels is the faster one for this many rows and this input width.
-    Measured against the step with norm kernels, decode at context 4,096: up to 8 rows it wins at every width
-    tried (1,024: +4 to +10 %, 2,048: +1 to +4 %, 4,096: +0.4 to +2.5 %); with 9 to 16 rows +5 % at 1,024,
-    +2.6 % at 2,048 and -2.2 % at 4,096, where the product with two token tiles is short of registers."""
+    """Whether a decode step without norm kernels is the faster one for this many rows and this reduction
+    length: always with one token tile (up to 8 rows); with two only while the reduction is short, where the
+    product with two token tiles is not yet short of registers (measured: profiles/decode_step_rules.md)."""
     return rows <= 8 or weight.shape[1] <= 3072
 
 
@@ -529,8 +532,7 @@ def gemm_tc_swiglu_pays(rows: int, weight: torch.Tensor) -> bool:
     """Whether the gate/up product with SwiGLU in its epilogue is the faster way for a prompt portion.
     It saves the gate kernel's pass over the [rows, 2 I] product, which weighs the more the shorter the
     reduction is; against that its single-CTA tiles run below the library's rate when the reduction
-    is long.  Measured at 2,048 rows: width 1024 -> 24 us against 32 (library + gate kernel);
-    2048 -> 100 against 87; 4096 -> 373 against 306."""
+    is long (measured: profiles/gemm_tc_swiglu__prefill_2048.md)."""
     return rows >= 128 and weight.shape[1] <= 1536
 
 
@@ -569,10 +571,9 @@ def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages: 
                 status: torch.Tensor) -> None:
     """x[T, K] @ w[(Hq + 2 Hkv) D, K]^T on the tensor cores with ``qkv_post`` as the epilogue: the
     projection is rounded to bfloat16, normed and rotated head by head and written to ``q_out`` and the
-    cache pages; it is never stored itself.  The attention part does not use it yet: its epilogue (two
-    heads of 128 rows by four warps) hides under the next tile's main loop only when that loop is long,
-    and at an input width of 1024 it took 44 us for 2048 rows where the library product and qkv_post
-    take 17 + 16."""
+    cache pages; it is never stored itself.  The attention part does not use it: its epilogue (two heads
+    of 128 rows by four warps) hides under the next tile's main loop only when that loop is long
+    (measured: profiles/gemm_tc_swiglu__prefill_2048.md)."""
     for name, t in (("x", x), ("w", w), ("q_out", q_out), ("k_pages", k_pages), ("v_pages", v_pages)):
         _check(f"gemm_tc_qkv.{name}", t, torch.bfloat16)
     for name, t in (("positions", positions), ("tok_seq", tok_seq), ("block_table", block_table)):
@@ -608,19 +609,32 @@ def fast_attention_takes(dtype: torch.dtype, num_q_heads: int, num_kv_heads: int
             and num_q_heads % num_kv_heads == 0 and num_q_heads // num_kv_heads <= 16)
 
 
-# registers per thread of attn_decode_kernel<D / 16> as compiled (ptxas -v), for the occupancy estimate
-_DECODE_REGS = {1: 56, 2: 64, 3: 72, 4: 96, 5: 128, 6: 128, 7: 128, 8: 168, 9: 168, 10: 168, 11: 216, 12: 232,
-                13: 244, 14: 252, 15: 255, 16: 255}
-_SM_COUNT = 148
+_DEVICE_FACTS = {}
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device (asked once)."""
+    key = ("sms", torch.cuda.current_device())
+    if key not in _DEVICE_FACTS:
+        _DEVICE_FACTS[key] = max(1, int(library()._lib.q3_sm_count()))
+    return _DEVICE_FACTS[key]
 
 
 def decode_blocks_per_sm(head_dim: int) -> int:
-    """Blocks of the decode kernel that fit one SM (shared memory and registers)."""
-    tile = 16 * (head_dim + 8) * 2
-    smem = tile * (1 + 4 * 2 * 2)
-    by_smem = (227 * 1024) // smem
-    by_regs = 65536 // (_DECODE_REGS.get(head_dim // 16, 255) * 128)
-    return max(1, min(by_smem, by_regs, 16))
+    """Blocks of the cp.async decode kernel that one SM holds at once, as the CUDA runtime reckons it from the
+    compiled kernel (registers, shared memory); asked once per head size."""
+    key = ("decode blocks", torch.cuda.current_device(), head_dim)
+    if key not in _DEVICE_FACTS:
+        _DEVICE_FACTS[key] = max(1, int(library()._lib.q3_attn_decode_blocks_per_sm(int(head_dim))))
+    return _DEVICE_FACTS[key]
+
+
+def decode_third_block_pays(next_product_bytes: int) -> bool:
+    """Whether a decode grid that fits the SMs at three attention blocks each, but not at two, should be cut
+    into that many ranges.  The third block takes the registers and shared memory in which the blocks of the
+    product after the attention would sit and fetch their weights ahead of their wait, so it pays only
+    while that product's weights are few (measured: profiles/decode_step_rules.md)."""
+    return 0 < next_product_bytes <= 6 * 2 ** 20
 
 
 def decode_tma_takes(head_dim: int, page_size: int) -> bool:
@@ -644,7 +658,7 @@ def decode_splits(num_seqs: int, num_kv_heads: int, max_kv_len: int, window: int
     tiles' worth).  The count that minimises waves x cost per block wins."""
     span = min(max_kv_len, window) if window and window > 0 else max_kv_len
     tiles = max(1, -(-span // 16))
-    slots = _SM_COUNT * (blocks_per_sm or decode_blocks_per_sm(head_dim))
+    slots = sm_count() * (blocks_per_sm or decode_blocks_per_sm(head_dim))
     pairs = max(1, num_seqs * num_kv_heads)
     best, best_cost = 1, None
     for s in range(1, MAX_DECODE_SPLITS + 1):
@@ -763,7 +777,7 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
                     num_seqs: int, num_decode: int, max_q_len: int, max_kv_len: int, scale: float, window: int,
                     status: torch.Tensor, partial: Optional[torch.Tensor] = None,
                     portion_kernel: str = "auto", decode_kernel: str = "auto", raw_qkv=None,
-                    decode_wide_grid: bool = False) -> None:
+                    next_product_bytes: int = 0) -> None:
     """``raw_qkv``: see ``attn_decode``; only where ``decode_takes_raw_qkv`` says so.
     Causal attention of a mixed batch over the pages: rows [0, num_decode) bring one token each and
     go to the split-KV decode kernel, the rest to a portion kernel (tcgen05 where it takes the shape,
@@ -781,12 +795,11 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         tma = decode_kernel != "cp_async" and decode_tma_takes(D, k_pages.shape[2])
         if tma:
             # The kernel is compiled for two and for three blocks per SM and takes the second variant for a
-            # grid of more than 2 x 148 blocks.  A grid of several waves gains from the third block at every
-            # model width tried (batch 64: +3 to +6 %); a grid that fits three blocks per SM but not two (batch
-            # 8 at context 4,096: six splits instead of four) gained 7.6 % of the step at a width of 1,024 and
-            # lost 11 % and 34 % at 2,048 and 4,096, so only a caller that says ``decode_wide_grid`` gets it.
+            # grid of more than two blocks per SM.  A grid of several waves gains from the third block always; a
+            # grid that fits three blocks per SM but not two only where ``decode_third_block_pays``
+            # (``next_product_bytes``: the weights of the product that follows the attention).
             splits = decode_splits(num_decode, Hkv, max_kv_len, window, D, blocks_per_sm=2)
-            if decode_wide_grid or num_decode * Hkv * splits > 2 * _SM_COUNT:
+            if decode_third_block_pays(next_product_bytes) or num_decode * Hkv * splits > 2 * sm_count():
                 splits = decode_splits(num_decode, Hkv, max_kv_len, window, D, blocks_per_sm=3)
         else:
             splits = decode_splits(num_decode, Hkv, max_kv_len, window, D)

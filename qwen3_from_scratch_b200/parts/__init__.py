@@ -1,5 +1,5 @@
 """Parts a model is put together from.  ``parts.base`` holds the interfaces; the built-in
 parts live in the sibling modules and are registered when the registry is first used."""
 
-from .base import (Block, FeedForward, KVCacheSpec, LayerCall, Mixer, ModelSpec, Norm, Part, PartSpec,  # noqa: F401
-                   PositionEncoding, Runtime, StateSpec, StepContext, WeightSpec)
+from .base import (Block, CachePlane, FeedForward, KVCacheSpec, LayerCall, Mixer, ModelSpec, Norm,  # noqa: F401
+                   PagedCacheSpec, Part, PartSpec, PositionEncoding, Runtime, StateSpec, StepContext, WeightSpec)

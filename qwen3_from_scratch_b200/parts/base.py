@@ -66,13 +66,35 @@ class WeightSpec:
 
 
 @dataclass(frozen=True)
-class KVCacheSpec:
-    """Pages of keys and values, one slot per token.  ``window`` = how many of the latest
-    keys a query still reads (None: all of them); pages a window has passed are given back."""
+class CachePlane:
+    """One array of a paged cache: for every token ``heads`` vectors of ``width`` values.
+    ``dtype``: ``"compute"`` (the engine's dtype) or ``"float32"``."""
 
-    num_kv_heads: int
-    head_dim: int
+    name: str
+    heads: int
+    width: int
+    dtype: str = "compute"
+
+
+@dataclass(frozen=True)
+class PagedCacheSpec:
+    """Pages with one slot per token, in one or more named planes (keys and values of attention; one
+    latent vector per token; keys and values of different widths; ...).  A plane's pages are one tensor
+    ``[num_pages, heads, page_size, width]``; all planes of a cache share the page ids.
+    ``window`` = how many of the latest tokens a query still reads (None: all of them); pages a window
+    has passed are given back."""
+
+    planes: Tuple[CachePlane, ...]
     window: Optional[int] = None
+
+    def bytes_per_token(self, compute_itemsize: int) -> int:
+        return sum(p.heads * p.width * (4 if p.dtype == "float32" else compute_itemsize) for p in self.planes)
+
+
+def KVCacheSpec(num_kv_heads: int, head_dim: int, window: Optional[int] = None) -> PagedCacheSpec:
+    """The usual attention cache: planes ``k`` and ``v`` of ``num_kv_heads`` vectors of ``head_dim`` per token."""
+    return PagedCacheSpec((CachePlane("k", int(num_kv_heads), int(head_dim)),
+                           CachePlane("v", int(num_kv_heads), int(head_dim))), window)
 
 
 @dataclass(frozen=True)
@@ -84,7 +106,7 @@ class StateSpec:
     dtype: str = "float32"
 
 
-CacheSpec = Union[KVCacheSpec, StateSpec, None]
+CacheSpec = Union[PagedCacheSpec, StateSpec, None]
 
 # ---------------------------------------------------------------------- runtime
 
@@ -131,8 +153,12 @@ class StepContext:
     after this step), ``slot_ids[B]`` (state slot of each request), ``logit_rows[R]``.
     Host mirrors: ``q_lens``, ``kv_lens``, ``max_q_len``, ``max_kv_len``, ``num_decode``
     (rows that bring exactly one token come first in the batch).
-    ``kv(cache_id)`` gives ``(k_pages, v_pages, block_table)`` of a cache of pages and
-    ``state(cache_id)`` the ``[slots, *shape]`` tensor of a cache of fixed-size state.
+    ``pages(cache_id)`` gives ``({plane name: pages}, block_table)`` of a cache of pages,
+    ``kv(cache_id)`` the same as ``(k_pages, v_pages, block_table)`` for a cache with planes ``k`` and
+    ``v``, and ``state(cache_id)`` the ``[slots, *shape]`` tensor of a cache of fixed-size state.
+    ``extra``: per-token integer arrays that the caller sent along with the tokens (``Entry.extra``),
+    by name, int32 ``[T, width]`` on the device: positions on several axes, segment ids, whatever a part
+    of the model defines for itself; ``positions`` (``start + i``) is always there.
     """
 
     num_tokens: int
@@ -159,8 +185,14 @@ class StepContext:
             store[key] = make()
         return store[key]
 
-    def kv(self, cache_id: int):  # pragma: no cover - interface
+    def pages(self, cache_id: int):  # pragma: no cover - interface
         raise NotImplementedError
+
+    def kv(self, cache_id: int):
+        planes, table = self.pages(cache_id)
+        return planes["k"], planes["v"], table
+
+    extra: Dict[str, torch.Tensor] = {}
 
     def state(self, cache_id: int):  # pragma: no cover - interface
         raise NotImplementedError
@@ -258,6 +290,8 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     def cache_spec(self) -> CacheSpec:
+        """What the mixer keeps per request: ``PagedCacheSpec`` (``KVCacheSpec(...)`` for keys and values),
+        ``StateSpec``, or None."""
         return None
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:

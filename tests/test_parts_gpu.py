@@ -559,3 +559,167 @@ def test_toy_routed_feed_forward_and_position_encoding(tmp_path):
         scale = float(want[r].abs().max())
         assert float((whole[r] - want[r]).abs().max()) <= 1e-5 * scale
         assert float((cut[r] - want[r]).abs().max()) <= 1e-5 * scale
+
+
+# ---------------------------------------------------------------------- a toy mixer with a cache of one plane
+def register_toy_latent():
+    """A third toy architecture, again defined here alone.  Its mixer keeps ONE vector per token (a latent
+    of a width of its own, in float32) in a paged cache with a single plane, and reads two numbers per token
+    that the caller sends beside the token ids (``Entry.extra["axes"]``): it answers a token with the mean of
+    the latents of all tokens so far that share the token's second number, times an output matrix."""
+    from qwen3_from_scratch_b200.config import ModelConfig
+    from qwen3_from_scratch_b200.parts.base import (CachePlane, LayerCall, Mixer, ModelSpec, PagedCacheSpec, PartSpec,
+                                                   WeightSpec)
+    from qwen3_from_scratch_b200.parts.linear import Linear
+    from qwen3_from_scratch_b200.registry import register_architecture, register_part, registered_architectures
+    if "ToyLatentLM" in registered_architectures():
+        return
+
+    @register_part("mixer", "toy_latent_mean")
+    class LatentMean(Mixer):
+        def __init__(self, name, hidden_size, latent):
+            super().__init__(name)
+            self.hidden_size, self.latent = hidden_size, latent
+
+        def weight_specs(self):
+            return [WeightSpec(f"{self.name}.down.weight", (self.latent, self.hidden_size)),
+                    WeightSpec(f"{self.name}.up.weight", (self.hidden_size, self.latent))]
+
+        def cache_spec(self):
+            # per token: the latent and, behind it, the token's second number
+            return PagedCacheSpec((CachePlane("latent", 1, self.latent + 1, "float32"),))
+
+        def setup(self, rt, weights):
+            super().setup(rt, weights)
+            self.down = Linear(weights[f"{self.name}.down.weight"], rt, tag="toy.latent.down")
+            self.up = Linear(weights[f"{self.name}.up.weight"], rt, tag="toy.latent.up")
+
+        def forward(self, x, ctx, cache_id, write_cache):
+            planes, table = ctx.pages(cache_id)
+            pages = planes["latent"]  # [num_pages, 1, page_size, latent + 1]
+            page = pages.shape[2]
+            rows = table.tolist()
+            second = ctx.extra["axes"][:, 1].tolist()
+            lat = self.down(x).float()
+            out = torch.empty_like(lat)
+            at = 0
+            for b, n in enumerate(ctx.q_lens):
+                start = ctx.kv_lens[b] - n
+                for i in range(n):
+                    pos, t = start + i, at + i
+                    if write_cache:
+                        slot = pages[rows[b][pos // page], 0, pos % page]
+                        slot[:self.latent] = lat[t]
+                        slot[self.latent] = float(second[t])
+                    seen = torch.stack([pages[rows[b][p // page], 0, p % page] for p in range(pos + 1)])
+                    same = seen[:, self.latent] == float(second[t])
+                    out[t] = seen[same, :self.latent].mean(dim=0)
+                at += n
+            return self.up(out.to(x.dtype))
+
+    @dataclass(frozen=True)
+    class LatentConfig(ModelConfig):
+        vocab_size: int = 0
+        width: int = 0
+        latent: int = 0
+
+        @classmethod
+        def from_dict(cls, data):
+            return cls(data["architectures"][0], data["vocab_size"], data["width"], data["latent"])
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], "vocab_size": self.vocab_size, "width": self.width,
+                    "latent": self.latent}
+
+    @register_architecture("ToyLatentLM", LatentConfig)
+    def latent_spec(cfg):
+        norm = PartSpec("rms_norm", {"dim": cfg.width, "eps": 1e-6})
+        ff = PartSpec("swiglu", {"hidden_size": cfg.width, "intermediate_size": 2 * cfg.width})
+        attn = PartSpec("gqa_attention", {"hidden_size": cfg.width, "num_heads": 2, "num_kv_heads": 2,
+                                          "head_dim": 16, "qk_norm_eps": None, "position": None})
+        latent = PartSpec("toy_latent_mean", {"hidden_size": cfg.width, "latent": cfg.latent})
+        layers = [(f"layers.{i}", PartSpec("pre_norm", {"norm1": norm, "norm2": norm, "feed_forward": ff, "mixer": m}))
+                  for i, m in enumerate([latent, attn, latent])]
+        return ModelSpec(embedding=("embed", PartSpec("token_embedding", {"vocab_size": cfg.vocab_size,
+                                                                          "hidden_size": cfg.width})),
+                         layers=layers, order=[LayerCall(i, i) for i in range(3)], final_norm=("final_norm", norm),
+                         head=("head", PartSpec("lm_head", {"vocab_size": cfg.vocab_size, "hidden_size": cfg.width})),
+                         vocab_size=cfg.vocab_size, max_positions=4096)
+
+
+def latent_plain_logits(folder, ids, second):
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    from safetensors.torch import load_file
+    w = {k: v.double() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    x = w["embed.weight"][torch.tensor(ids)]
+    n = len(ids)
+    second = torch.tensor(second)
+    for i in range(3):
+        p = f"layers.{i}"
+        h = plain.rms_norm(x, w[f"{p}.norm1.weight"], 1e-6)
+        if i != 1:
+            lat = (h @ w[f"{p}.mixer.down.weight"].t()).float().double()  # the cache holds it in float32
+            mean = torch.stack([lat[:t + 1][second[:t + 1] == second[t]].mean(dim=0) for t in range(n)])
+            a = mean @ w[f"{p}.mixer.up.weight"].t()
+        else:
+            q = (h @ w[f"{p}.mixer.q_proj.weight"].t()).view(n, 2, 16)
+            k = (h @ w[f"{p}.mixer.k_proj.weight"].t()).view(n, 2, 16)
+            v = (h @ w[f"{p}.mixer.v_proj.weight"].t()).view(n, 2, 16)
+            a = plain.causal_attention(q, k, v).reshape(n, -1) @ w[f"{p}.mixer.o_proj.weight"].t()
+        x = x + a
+        x = x + plain.swiglu_mlp(plain.rms_norm(x, w[f"{p}.norm2.weight"], 1e-6), w, f"{p}.feed_forward")
+    return plain.rms_norm(x, w["final_norm.weight"], 1e-6) @ w["head.weight"].t()
+
+
+def test_toy_mixer_with_a_one_plane_cache_and_numbers_sent_beside_the_tokens(tmp_path):
+    """The cache storage gives a mixer the planes it declares (here one, wider than the model's heads, in
+    float32, beside the attention layer's keys and values in a group of their own), and the step context
+    carries per-token integers of the caller's to the parts; whole and in portions, two requests interleaved."""
+    register_toy_latent()
+    from qwen3_from_scratch_b200.engine.batch import Entry
+    from qwen3_from_scratch_b200.engine.session import Session
+    from qwen3_from_scratch_b200.registry import config_from_dict
+    from qwen3_from_scratch_b200.weights import write_random_model
+    cfg = config_from_dict({"architectures": ["ToyLatentLM"], "vocab_size": 61, "width": 32, "latent": 12})
+    folder = str(tmp_path / "latent")
+    write_random_model(folder, cfg, seed=6, dtype="float32")
+    g = torch.Generator().manual_seed(12)
+    ids = {"x": torch.randint(0, 61, (29,), generator=g).tolist(), "y": torch.randint(0, 61, (14,), generator=g).tolist()}
+    axes = {r: [[t, int(v)] for t, v in enumerate(torch.randint(0, 3, (len(s),), generator=g).tolist())]
+            for r, s in ids.items()}
+    want = {r: latent_plain_logits(folder, ids[r], [a[1] for a in axes[r]]).float() for r in ids}
+    session = Session(folder, dtype="float32", page_size=4, cache_tokens=128, max_seqs=4, max_step_tokens=64)
+    layout = session.model.cache_layout()
+    assert [g.cache_ids for g in layout.groups] == [[0, 2], [1]]
+    assert [p.name for p in layout.groups[0].spec.planes] == ["latent"]
+    assert set(session.storage.planes(0)) == {"latent"} and session.storage.planes(0)["latent"].shape[-1] == 13
+    assert session.storage.planes(0)["latent"].dtype == torch.float32 and set(session.storage.planes(1)) == {"k", "v"}
+
+    def run(cuts):
+        fed = {r: 0 for r in ids}
+        rows = {r: [] for r in ids}
+        for cut in cuts:
+            entries = []
+            for r, n in cut:
+                a = fed[r]
+                entries.append(Entry(r, ids[r][a:a + n], list(range(n)), {"axes": axes[r][a:a + n]}))
+                fed[r] += n
+            logits = session.step(entries).float().cpu()
+            session.check_status()
+            at = 0
+            for r, n in cut:
+                rows[r].append(logits[at:at + n])
+                at += n
+        for r in ids:
+            session.end(r)
+        return {r: torch.cat(v) for r, v in rows.items()}
+
+    whole = run([[("x", 29), ("y", 14)]])
+    cut = run([[("x", 6), ("y", 1)], [("x", 1), ("y", 5)], [("y", 7), ("x", 13)], [("x", 9), ("y", 1)]])
+    for r in ids:
+        scale = float(want[r].abs().max())
+        assert float((whole[r] - want[r]).abs().max()) <= 1e-5 * scale
+        assert float((cut[r] - want[r]).abs().max()) <= 1e-5 * scale
+    with pytest.raises(ValueError, match="per-token arrays"):
+        session.step([Entry("x", ids["x"][:3], (), {"axes": axes["x"][:3]}), Entry("y", ids["y"][:3], ())])
