@@ -27,14 +27,55 @@ def unavailable(why: str) -> int:
 
 
 def run_reference(args, config: dict, page: int) -> int:
+    """Runs the workload natively first.  On sm_100 with Triton 3.6 the reference's own attention kernel
+    (kernels/triton/paged_attn.py:315, a loop marked ``warp_specialize=True``) does not compile; the one thing
+    that is then tried is a compiler setting from the environment, ``TRITON_OVERRIDE_ARCH=sm80``: the same
+    unmodified source is compiled without the Blackwell-only passes (no source of the reference is touched).
+    The line says which way the number was made."""
+    import gc
+    first = _attempt(args, config, page, knob=os.environ.get("TRITON_OVERRIDE_ARCH"))
+    if first[0] == "ok" or os.environ.get("TRITON_OVERRIDE_ARCH"):
+        return _report(first)
+    native_error = first[1]
+    if "compile" not in native_error.lower() and "PassManager" not in native_error and "triton" not in native_error.lower():
+        return _report(first)
+    os.environ["TRITON_OVERRIDE_ARCH"] = "sm80"
+    try:
+        import triton
+        triton.knobs.runtime.override_arch = "sm80"
+    except Exception:  # noqa: BLE001 - the environment variable alone is what older versions read
+        pass
+    gc.collect()
+    try:
+        import torch
+        torch.cuda.empty_cache()
+    except Exception:  # noqa: BLE001
+        pass
+    print(f"[reference arm] native compile failed ({native_error[:160]}); trying TRITON_OVERRIDE_ARCH=sm80",
+          file=sys.stderr, flush=True)
+    second = _attempt(args, config, page, knob="sm80")
+    if second[0] != "ok":
+        return unavailable(f"natively: {native_error[:200]}; with TRITON_OVERRIDE_ARCH=sm80: {second[1][:200]}")
+    return _report(second)
+
+
+def _report(result) -> int:
+    if result[0] != "ok":
+        return unavailable(result[1])
+    print(json.dumps(result[1]))
+    return 0
+
+
+def _attempt(args, config: dict, page: int, knob):
+    """("ok", the JSON line as a dict) or ("unavailable", why)."""
     if not os.path.isdir(os.path.join(REF, "qwen3_from_scratch")):
-        return unavailable("baseline/_ref is not installed (pip install --no-index --no-deps --target baseline/_ref)")
+        return ("unavailable", "baseline/_ref is not installed (pip install --no-index --no-deps --target baseline/_ref)")
     try:
         import torch
     except ImportError as e:  # pragma: no cover
-        return unavailable(f"torch is not importable: {e}")
+        return ("unavailable", f"torch is not importable: {e}")
     if not torch.cuda.is_available():
-        return unavailable("no CUDA GPU visible")
+        return ("unavailable", "no CUDA GPU visible")
     sys.path.insert(0, REF)
     try:
         from qwen3_from_scratch.factory import load_batch_config
@@ -43,7 +84,7 @@ def run_reference(args, config: dict, page: int) -> int:
         from qwen3_from_scratch.inference.scheduler_driver import SchedulerDriver
         from qwen3_from_scratch.inference.sequence import Sequence
     except Exception as e:  # noqa: BLE001 - whatever stops the import is the reason
-        return unavailable(f"the reference does not import here: {type(e).__name__}: {e}")
+        return ("unavailable", f"the reference does not import here: {type(e).__name__}: {e}")
 
     from qwen3_from_scratch_b200.registry import config_from_dict
     from qwen3_from_scratch_b200.weights import write_random_model
@@ -79,14 +120,14 @@ def run_reference(args, config: dict, page: int) -> int:
             prompt = torch.randint(0, cfg["vocab_size"], (context - total_new,), generator=g).tolist()
             seq = Sequence(prompt, max_new_tokens=total_new + 8, ignore_eos=True)
             if not driver.add_request(seq):
-                return unavailable("the reference's scheduler refused the request (cache pool too small)")
+                return ("unavailable", "the reference's scheduler refused the request (cache pool too small)")
             seqs.append(seq)
         guard = 0
         while any(s.is_prefill or s.last_token_id == -1 for s in seqs):
             driver.step([])
             guard += 1
             if guard > 10000:
-                return unavailable("the reference did not finish its prompts in 10000 steps")
+                return ("unavailable", "the reference did not finish its prompts in 10000 steps")
         for _ in range(warmup):
             driver.step([])
         torch.cuda.synchronize()
@@ -101,17 +142,17 @@ def run_reference(args, config: dict, page: int) -> int:
         wall = time.perf_counter() - t0
         device = start.elapsed_time(end) / 1e3
     except Exception as e:  # noqa: BLE001
-        return unavailable(f"the reference failed on this workload: {type(e).__name__}: {str(e)[:300]}")
+        return ("unavailable", f"the reference failed on this workload: {type(e).__name__}: {str(e)[:300]}")
     value = batch * steps / device
-    print(json.dumps({
+    return ("ok", {
         "metric": "decode tok/s at batch 8 (Qwen3-0.6B sizes, context 4096, bf16, random weights)",
         "impl": "reference", "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": device / steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"model": "Qwen3-0.6B sizes, random weights", "global_batch": batch, "seq_len": context,
                    "parallelism": "single GPU", "layers": layers, "page_size": page,
-                   "path": "load_batch_config -> ModelWorker -> Scheduler/SchedulerDriver.step (paged_attn)"},
+                   "path": "load_batch_config -> ModelWorker -> Scheduler/SchedulerDriver.step (paged_attn)",
+                   "triton_override_arch": knob or "none"},
         "e2e": {"value": batch * steps / wall, "unit": "tokens/s", "h2d_bytes_per_step": None,
                 "d2h_bytes_per_step": batch * 8},
-    }))
-    return 0
+    })

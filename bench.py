@@ -682,6 +682,10 @@ def main() -> int:
     if args.impl == "reference":
         from baseline.reference_arm import run_reference
         args.batch = args.batch or 8
+        if args.model != "0.6b":
+            from baseline.reference_arm import unavailable
+            return unavailable(f"the reference arm runs the headline configuration only: the reference reads its weights "
+                               f"from a folder, and a random folder of {MODELS[args.model]['name']} size is not written")
         return run_reference(args, MODELS[args.model]["config"], PAGE)
     return ours(args)
 
