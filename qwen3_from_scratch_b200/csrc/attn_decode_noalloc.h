@@ -17,7 +17,9 @@
  *     splits or the ordinary entry point.
  *   - The first call on a device asks the CUDA runtime for the array's device address
  *     (cudaGetSymbolAddress, with that device current) and keeps it.  Make that first call on each
- *     device before any stream capture begins, and from one thread.
+ *     device before any stream capture begins, and from one thread.  The address is kept for the life
+ *     of the process: after cudaDeviceReset (or anything else that tears the device's context down) it
+ *     is stale, and this entry point must not be called on that device again.
  *   - All calls share the one array, and it keeps whatever the last call left in it.  Nothing has to
  *     be zero at the start: every split writes its whole record (output, maximum, denominator) before
  *     the merging kernel reads it.  Two calls whose kernels can overlap on the GPU (different
