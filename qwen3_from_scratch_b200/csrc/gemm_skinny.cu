@@ -77,9 +77,13 @@ constexpr int GS_SS_ROWS = 16;  // row pitch of the partial sums
 // times a norm's weight (scaled_out of the product that last added into the stream), and the result is
 // multiplied by the row's 1 / rms.
 // ROOMY (two token tiles, one batch ahead): the grid fits two blocks per SM, so the thread may have their registers.
-template <int NT, int WK, int EPI, typename OutT, int PRE = 1, bool NORMED = false, bool ROOMY = false>
+// TIGHT (one token tile, K split in the block, one batch ahead): the grid needs three blocks per SM to be resident
+// at once (more than two per SM, at most three); left to two, its last blocks would run as a wave of their own
+// that cannot fill the memory pipeline (5,120 x 8,192 and 5,120 x 25,600 into the stream: 320 blocks).
+template <int NT, int WK, int EPI, typename OutT, int PRE = 1, bool NORMED = false, bool ROOMY = false, bool TIGHT = false>
 __global__ void __launch_bounds__(GS_WARPS * 32,
-                                  ((NT == 1 && WK > 1 && !(NORMED && PRE == 1)) || (NT == 2 && PRE > 1)) ? 1
+                                  TIGHT ? 3
+                                  : ((NT == 1 && WK > 1 && !(NORMED && PRE == 1)) || (NT == 2 && PRE > 1)) ? 1
                                   : (NT == 2 && ROOMY) ? 2 : 3)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
                    OutT* __restrict__ out, int T, int N, int K, int ldo, const SkinnyFuse fuse) {
@@ -287,6 +291,10 @@ static int gemm_skinny_launch(const void* X, const void* W, void* out, int T, in
       q3::launch(gemm_skinny_kernel<NT, WK, EPI, OutT, PRE, NORMED, NT == 2 && PRE == 1>, dim3(grid),             \
                  dim3(GS_WARPS * 32), 0, stream, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (OutT*)out, T, N, K, \
                  ldo, fuse);                                                                                      \
+    else if (NT == 1 && WK > 1 && PRE == 1 && grid > 2u * (unsigned)sms && grid <= 3u * (unsigned)sms)            \
+      q3::launch(gemm_skinny_kernel<NT, WK, EPI, OutT, PRE, NORMED, false, (NT == 1 && (WK > 1) && PRE == 1)>,    \
+                 dim3(grid), dim3(GS_WARPS * 32), 0, stream, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W,    \
+                 (OutT*)out, T, N, K, ldo, fuse);                                                                 \
     else                                                                                                          \
       q3::launch(gemm_skinny_kernel<NT, WK, EPI, OutT, PRE, NORMED, false>, dim3(grid), dim3(GS_WARPS * 32), 0,   \
                  stream, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (OutT*)out, T, N, K, ldo, fuse);       \
