@@ -178,7 +178,9 @@ def test_swiglu(dtype):
 
 
 @pytest.mark.parametrize("shape", [(1, 4096, 1024), (8, 1024, 2048), (16, 331, 96), (3, 70, 200), (9, 48, 8),
-                                   (5, 151936, 64), (16, 16, 3072), (7, 1024, 3072), (3, 1000, 2056), (2, 64, 5000)])
+                                   (5, 151936, 64), (16, 16, 3072), (7, 1024, 3072), (3, 1000, 2056), (2, 64, 5000),
+                                   # tens of megabytes of weights, K split over 1, 2, 4 and 8 warps, ragged ends
+                                   (3, 6144, 4096), (8, 9000, 1400), (1, 2328, 5448), (7, 600, 20488), (2, 4736, 2648)])
 @pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
 def test_gemm_skinny(shape, out_dtype):
     T, N, K = shape
@@ -193,7 +195,7 @@ def test_gemm_skinny(shape, out_dtype):
     assert ops().gemm_skinny_takes(T, dev(w)) and not ops().gemm_skinny_takes(17, dev(w))
 
 
-@pytest.mark.parametrize("shape", [(1, 3072, 1024), (8, 136, 96), (13, 200, 80)])
+@pytest.mark.parametrize("shape", [(1, 3072, 1024), (8, 136, 96), (13, 200, 80), (5, 12288, 1024), (8, 3000, 4104)])
 def test_gemm_skinny_with_swiglu(shape):
     T, inter, K = shape
     g = torch.Generator().manual_seed(9)
@@ -214,7 +216,8 @@ def test_gemm_skinny_with_swiglu(shape):
 
 
 @pytest.mark.parametrize("shape", [(1, 4096, 1024), (8, 1024, 2048), (16, 331, 96), (3, 70, 200), (9, 48, 8), (7, 1024, 3072),
-                                   (5, 64, 5000), (12, 1024, 2048), (16, 1024, 3072), (10, 2368, 2048)])
+                                   (5, 64, 5000), (12, 1024, 2048), (16, 1024, 3072), (10, 2368, 2048),
+                                   (4, 4096, 4096), (8, 5120, 8192), (1, 1000, 12296)])
 def test_gemm_skinny_into_stream(shape):
     """stream += x W^T in place, with partial sums of squares of the new rows that add up to the rows' own."""
     T, N, K = shape
@@ -242,7 +245,7 @@ def test_gemm_skinny_into_stream(shape):
 
 
 @pytest.mark.parametrize("shape", [(1, 4096, 1024), (8, 6144, 1024), (16, 331, 96), (3, 70, 200), (9, 48, 8), (6, 64, 5000),
-                                   (12, 2048, 4096), (8, 1024, 5120)])
+                                   (12, 2048, 4096), (8, 1024, 5120), (8, 6144, 4096), (3, 24576, 1024), (2, 2400, 5120)])
 @pytest.mark.parametrize("with_swiglu", [False, True])
 def test_gemm_skinny_normed(shape, with_swiglu):
     """rmsnorm(stream) W^T without a norm kernel: the operand is the stream times the norm weight in bfloat16,
