@@ -429,6 +429,8 @@ def measure_model(key, args, peaks, sample_clocks):
     full_layers = spec["config"]["num_hidden_layers"]
     layers = args.layers or full_layers
     batches = list(spec["batches"])
+    if args.batches and key == args.model:
+        batches = [int(b) for b in args.batches.split(",")]
     if args.batch and key == args.model:
         batches = [args.batch] + [b for b in batches if b != args.batch]
     engine, cfg = make_engine(spec, layers, batches, args.context)
@@ -661,6 +663,8 @@ def main() -> int:
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--model", default="0.6b", choices=sorted(MODELS), help="layer sizes (default: the headline's)")
     p.add_argument("--batch", type=int, default=None, help="decode batch of `value` (default 8)")
+    p.add_argument("--batches", default=None,
+                   help="decode batch sizes to measure, comma separated, the first one is `value` (default: the model's three)")
     p.add_argument("--context", type=int, default=CONTEXT)
     p.add_argument("--repeats", type=int, default=5, help="the K-step region is timed this often; the median counts")
     p.add_argument("--headline-only", action="store_true",

@@ -382,7 +382,9 @@ static int attn_decode_launch(const void* q, const void* k_pages, const void* v_
   int code = launch_status();
   if (code != 0 || num_splits == 1) return code;
   dim3 cgrid(Hq, B);
+  g_launch_early = false;  // as in q3_attn_combine
   q3::launch(attn_combine_kernel, dim3(cgrid), dim3(AC_WARPS * 32), 0, stream, partial, (__nv_bfloat16*)out, q_start, Hq, S::D, num_splits);
+  g_launch_early = true;
   return launch_status();
 }
 
@@ -499,7 +501,13 @@ extern "C" int q3_attn_combine(const float* partial, void* out, const int* q_sta
   if (B <= 0 || num_splits <= 1) return 0;
   if (D <= 0 || D > q3::AC_MAX_D || (D & 1)) return Q3_ERR_SIZE;
   dim3 cgrid(Hq, B);
+  // The merge starts when the attention has completed, not early (the one ordinary launch of a decode step):
+  // its blocks, resident and waiting while the attention still has blocks to place, took the places of those
+  // blocks.  With 256 merge blocks beside a grid of two waves (the 8B sizes, batch 8 at a context of 16,384)
+  // the attention ran twice as long and the step 28 % longer.
+  q3::g_launch_early = false;
   q3::launch(q3::attn_combine_kernel, cgrid, dim3(q3::AC_WARPS * 32), 0, stream, partial, (__nv_bfloat16*)out, q_start, Hq, D,
              num_splits);
+  q3::g_launch_early = true;
   return q3::launch_status();
 }

@@ -140,6 +140,11 @@ static inline bool last_launch_was_plain(cudaStream_t stream) {
 // To be called right after launching a kernel that writes such data.
 static inline void note_stream_written() { g_plain_launch_stream.store(NO_PLAIN_LAUNCH, std::memory_order_relaxed); }
 
+// A launch made while this is false is an ordinary one: the kernel starts when the one before it in the stream
+// has completed (set around a launch by a launcher that wants that: the merge of the decode attention's splits,
+// attn_decode.cu).
+extern thread_local bool g_launch_early;
+
 template <typename... KArgs, typename... Args>
 static inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                          Args... args) {
@@ -152,7 +157,7 @@ static inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = (pdl_enabled() && g_launch_early) ? 1 : 0;
   g_plain_launch_stream.store((uintptr_t)stream, std::memory_order_relaxed);
   return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }

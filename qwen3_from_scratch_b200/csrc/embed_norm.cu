@@ -13,6 +13,7 @@
 namespace q3 {
 
 std::atomic<uintptr_t> g_plain_launch_stream{NO_PLAIN_LAUNCH};
+thread_local bool g_launch_early = true;
 
 // ---------------------------------------------------------------- embedding
 template <typename T>
