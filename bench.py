@@ -365,9 +365,10 @@ def prefill_bench(engine, tokens, steps, warmup, vocab):
 
 def serving_bench(engine, vocab):
     """The load the 8B configuration is quoted on: all requests at once, prompts of random length and random
-    tokens, a fixed number of new tokens each, through ``SyncEngine.batch_generate``.  Run twice: the first
-    run meets every batch shape for the first time (its CUDA graphs are recorded then), the second is the
-    steady state; both are reported."""
+    tokens, a fixed number of new tokens each, through ``SyncEngine.batch_generate``.  Run three times: the
+    first run meets every batch shape for the first time (decode shapes are recorded as CUDA graphs then, the
+    mixed steps run kernel by kernel), the second records the mixed steps' shapes, the third replays every
+    step.  A live load lies between the first and the third; both are reported."""
     import torch
 
     w = SERVING
@@ -375,7 +376,7 @@ def serving_bench(engine, vocab):
     lengths = torch.randint(w["prompt_min"], w["prompt_max"] + 1, (w["requests"],), generator=g).tolist()
     prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
     runs = []
-    for _ in range(2):
+    for _ in range(3):
         steps0, pre0 = engine.num_steps, engine.scheduler.num_preemptions
         torch.cuda.synchronize()
         t0 = time.perf_counter()
@@ -387,9 +388,10 @@ def serving_bench(engine, vocab):
         runs.append({"output_tok_s": batch.total_tokens / wall, "total_tok_s": (batch.total_tokens + sum(lengths)) / wall,
                      "seconds": wall, "ttft_mean_ms": 1e3 * statistics.mean(ttft), "ttft_max_ms": 1e3 * max(ttft),
                      "steps": engine.num_steps - steps0, "preemptions": engine.scheduler.num_preemptions - pre0})
-    out = dict(runs[1])
+    out = dict(runs[2])
     out.update(requests=w["requests"], prompt_tokens=sum(lengths), new_tokens_each=w["new_tokens"],
-               first_run_output_tok_s=runs[0]["output_tok_s"])
+               first_run_output_tok_s=runs[0]["output_tok_s"], first_run_ttft_mean_ms=runs[0]["ttft_mean_ms"],
+               second_run_output_tok_s=runs[1]["output_tok_s"])
     return out
 
 
@@ -516,7 +518,9 @@ def ours(args):
     line = line_of(m, args, peaks)
     # Every repeat of the end-to-end loop does the device's work of the device-timed loop and more.
     main = m["results"][m["batches"][0]]
-    if main["e2e_tok_s"] > 1.01 * main["tok_s"]:
+    # (the end-to-end repeats decode one after the other, so all but the last run at contexts up to
+    # repeats x K tokens shorter than the device-timed step: up to about 1 % fewer bytes)
+    if main["e2e_tok_s"] > 1.03 * main["tok_s"]:
         print(f"[bench] end to end ({main['e2e_tok_s']:.0f}) above the device rate ({main['tok_s']:.0f}): "
               "the clock of one of them is wrong", file=sys.stderr)
         return 1
@@ -543,6 +547,7 @@ def ours(args):
             line["points"][f"{key}_layers"] = other["layers"]
             if other["serving"]:
                 line["points"][f"{key}_serving_output_tok_s"] = other["serving"]["output_tok_s"]
+                line["points"][f"{key}_serving_first_run_output_tok_s"] = other["serving"]["first_run_output_tok_s"]
                 line["points"][f"{key}_serving_ttft_mean_ms"] = other["serving"]["ttft_mean_ms"]
                 line["points"][f"{key}_serving_steps"] = other["serving"]["steps"]
                 line["points"][f"{key}_serving_preemptions"] = other["serving"]["preemptions"]

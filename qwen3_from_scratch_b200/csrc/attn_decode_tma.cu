@@ -100,8 +100,8 @@ struct DecodeQkv {
 };
 
 // BLOCKS: blocks per SM the kernel is compiled for.  Three (128 registers) give a large grid half as many
-// slots again as two (batch 8 at context 4,096: six splits, 384 blocks, in one wave: +7.6 % of the step; batch
-// 64: +5 %); two (168 registers) are the faster code where the grid fits their slots anyway (batch 1: +2.6 %).
+// places again as two; two (168 registers) are the faster code where the grid fits their places anyway
+// (figures: profiles/attn_decode_tma__decode_b8_ctx4096.md).
 template <int D, int BLOCKS>
 __global__ void __launch_bounds__(DT_THREADS, BLOCKS)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,

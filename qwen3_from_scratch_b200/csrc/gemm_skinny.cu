@@ -51,12 +51,11 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
 // NT: token tiles of 8 (1 or 2).  WK: warps that share a group of 16 features and split K.
 // EPI: 0 store, 1 SwiGLU on alternating blocks of eight rows, 2 added into the float32 stream.
 // (The kernel is asked to fit three blocks per SM where K is not split in the block, which is the long
-// stream of the output head (at 88 registers, two blocks per SM, the head ran 58 us against 50), and with two
-// token tiles: there, left to itself, the compiler used fewer registers than three blocks allow and took
-// the loads one after the other: 10.0 us per product at 16 rows against 6.7 us, the head 86 us against 72.
-// Two token tiles are short of registers at three blocks per SM, though: where the grid fits two blocks per SM
-// (ROOMY) the kernel is asked for two (4,096 x 12,288 at 16 rows into the stream: 22.5 us against 33.9).  A warp
-// that fetches two or three batches ahead gets all the registers it wants.)
+// stream of the output head, and with two token tiles: there, left to itself, the compiler used fewer registers
+// than three blocks allow and took the loads one after the other.  Two token tiles are short of registers at
+// three blocks per SM, though: where the grid fits two blocks per SM (ROOMY) the kernel is asked for two.  A warp
+// that fetches two or three batches ahead gets all the registers it wants.  Figures:
+// profiles/gemm_skinny__decode_b8.md.)
 // PRE: batches of GS_UNROLL groups whose weights are fetched before the wait on the kernel before.  A
 // product with few output features (o_proj, down_proj: 64 groups of 16, one block each) gives a warp two or
 // three batches; with all of them under way before the wait, what is left after it is one round trip for
@@ -79,7 +78,7 @@ constexpr int GS_SS_ROWS = 16;  // row pitch of the partial sums
 // ROOMY (two token tiles, one batch ahead): the grid fits two blocks per SM, so the thread may have their registers.
 // TIGHT (one token tile, K split in the block, one batch ahead): the grid needs three blocks per SM to be resident
 // at once (more than two per SM, at most three); left to two, its last blocks would run as a wave of their own
-// that cannot fill the memory pipeline (5,120 x 8,192 and 5,120 x 25,600 into the stream: 320 blocks).
+// that cannot fill the memory pipeline (products of 5,120 features: 320 blocks).
 template <int NT, int WK, int EPI, typename OutT, int PRE = 1, bool NORMED = false, bool ROOMY = false, bool TIGHT = false>
 __global__ void __launch_bounds__(GS_WARPS * 32,
                                   TIGHT ? 3
@@ -302,7 +301,7 @@ static int gemm_skinny_launch(const void* X, const void* W, void* out, int T, in
   // batches of a warp's share of K; up to three are fetched ahead of the wait, but only where the grid is one
   // block per SM or less (o_proj and down_proj of a narrow model: 64 blocks): the registers of three batches
   // leave room for one block per SM, and a larger grid would then run in waves whose later blocks fetch
-  // nothing ahead (at 4,096 wide, 384 blocks, that cost 8 % of the step)
+  // nothing ahead
   const int batches = ((K + 31) / 32 + wk * GS_UNROLL - 1) / (wk * GS_UNROLL);
   const bool few_blocks = grid <= (unsigned)sms && (NT == 1 || EPI == 2);
   const int pre = few_blocks && wk == GS_WARPS ? (batches < 3 ? batches : 3) : 1;

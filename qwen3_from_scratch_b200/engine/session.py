@@ -86,23 +86,32 @@ class StepGraphs:
         wanted = self.decode_only(entries) or self.seen[key] >= 2
         if not wanted:
             return eager
-        torch.cuda.synchronize()
         while len(self.graphs) >= self.MAX_GRAPHS:  # the shape that has not come for the longest time makes room
             self.graphs.popitem(last=False)
         graph = torch.cuda.CUDAGraph()
         if self.pool is None:
             self.pool = torch.cuda.graph_pool_handle()
-        # No garbage collection while recording: the collector may destroy an older engine's graphs,
-        # and destroying a graph is a CUDA call that invalidates a capture in progress.
-        gc.collect()
+            self.capture_stream = torch.cuda.Stream(device=s.rt.device)
+        # Recorded with capture_begin / capture_end on a stream of the engine's own rather than through
+        # torch.cuda.graph(), which synchronises the device, runs the garbage collector and empties the
+        # allocator's cache every time (tens of milliseconds, and the steps after it pay for new allocations).
+        # No garbage collection while recording: the collector may destroy an older engine's graphs, and
+        # destroying a graph is a CUDA call that invalidates a capture in progress.
         collecting = gc.isenabled()
         gc.disable()
+        current = torch.cuda.current_stream(s.rt.device)
+        self.capture_stream.wait_stream(current)
         try:
-            with torch.cuda.graph(graph, pool=self.pool):
-                logits = s.model.step(ctx)
+            with torch.cuda.stream(self.capture_stream):
+                graph.capture_begin(pool=self.pool)
+                try:
+                    logits = s.model.step(ctx)
+                finally:
+                    graph.capture_end()
         finally:
             if collecting:
                 gc.enable()
+        current.wait_stream(self.capture_stream)
         self.graphs[key] = (ctx, graph, logits)
         s.last_graph = (graph, logits)
         return eager

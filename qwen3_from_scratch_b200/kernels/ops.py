@@ -629,14 +629,6 @@ def decode_blocks_per_sm(head_dim: int) -> int:
     return _DEVICE_FACTS[key]
 
 
-def decode_third_block_pays(next_product_bytes: int) -> bool:
-    """Whether a decode grid that fits the SMs at three attention blocks each, but not at two, should be cut
-    into that many ranges.  The third block takes the registers and shared memory in which the blocks of the
-    product after the attention would sit and fetch their weights ahead of their wait, so it pays only
-    while that product's weights are few (measured: profiles/decode_step_rules.md)."""
-    return 0 < next_product_bytes <= 6 * 2 ** 20
-
-
 def decode_tma_takes(head_dim: int, page_size: int) -> bool:
     """Whether the decode kernel with the TMA loader takes this shape (else the cp.async one runs)."""
     return head_dim in (64, 128) and page_size % 16 == 0
@@ -776,8 +768,7 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
                     q_start: torch.Tensor, kv_len: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
                     num_seqs: int, num_decode: int, max_q_len: int, max_kv_len: int, scale: float, window: int,
                     status: torch.Tensor, partial: Optional[torch.Tensor] = None,
-                    portion_kernel: str = "auto", decode_kernel: str = "auto", raw_qkv=None,
-                    next_product_bytes: int = 0) -> None:
+                    portion_kernel: str = "auto", decode_kernel: str = "auto", raw_qkv=None) -> None:
     """``raw_qkv``: see ``attn_decode``; only where ``decode_takes_raw_qkv`` says so.
     Causal attention of a mixed batch over the pages: rows [0, num_decode) bring one token each and
     go to the split-KV decode kernel, the rest to a portion kernel (tcgen05 where it takes the shape,
@@ -795,12 +786,8 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         tma = decode_kernel != "cp_async" and decode_tma_takes(D, k_pages.shape[2])
         if tma:
             # The kernel is compiled for two and for three blocks per SM and takes the second variant for a
-            # grid of more than two blocks per SM.  A grid of several waves gains from the third block always; a
-            # grid that fits three blocks per SM but not two only where ``decode_third_block_pays``
-            # (``next_product_bytes``: the weights of the product that follows the attention).
-            splits = decode_splits(num_decode, Hkv, max_kv_len, window, D, blocks_per_sm=2)
-            if decode_third_block_pays(next_product_bytes) or num_decode * Hkv * splits > 2 * sm_count():
-                splits = decode_splits(num_decode, Hkv, max_kv_len, window, D, blocks_per_sm=3)
+            # grid of more than two blocks per SM; the split count reckons with three places per SM.
+            splits = decode_splits(num_decode, Hkv, max_kv_len, window, D, blocks_per_sm=3)
         else:
             splits = decode_splits(num_decode, Hkv, max_kv_len, window, D)
         if partial is None or partial.numel() < num_decode * Hq * splits * (D + 2):

@@ -140,5 +140,4 @@ class GQAAttention(Mixer):
         """Causal attention of this step's queries over the pages (keys of this step included)."""
         ops.paged_attention(q, k_pages, v_pages, out, ctx.q_start, ctx.kv_len, ctx.tok_seq, table, ctx.num_seqs,
                             ctx.num_decode, ctx.max_q_len, ctx.max_kv_len, self.scale, self.window or 0,
-                            self.rt.status, self._partial, raw_qkv=raw_qkv,
-                            next_product_bytes=self.o_proj.weight.numel() * self.o_proj.weight.element_size())
+                            self.rt.status, self._partial, raw_qkv=raw_qkv)
