@@ -636,7 +636,7 @@ def profile(args):
         whole = replay_us()
         print(f"  whole step {whole:9.1f} us, {whole / layers:7.2f} per layer")
         kinds = ["paged_attention", "gemm_skinny", "gemm_skinny_normed", "gemm_skinny_into_stream", "gemm_tc",
-                 "add_rmsnorm", "qkv_post", "swiglu", "rope_table", "embed"]
+                 "gemm_tc_qkv", "add_rmsnorm", "qkv_post", "swiglu", "rope_table", "embed"]
         nothing = {"gemm_skinny_into_stream": lambda x, w, stream, sumsq, *more: ops.sumsq_parts(w.shape[0])}
         for kind in kinds:
             real = getattr(ops, kind)

@@ -7,7 +7,7 @@
 //   warp 1 (one thread)  issues tcgen05.mma (cta_group::1, kind::f16) straight from shared memory through
 //                        matrix descriptors, four instructions of k = 16 per stage; tcgen05.commit hands
 //                        each stage back to the loader and each finished accumulator to the epilogue;
-//   warps 2..5           read the accumulator with tcgen05.ld (each thread owns one row of the tile) and
+//   warps 2..5 (2..9 for the QKV epilogue)  read the accumulator with tcgen05.ld (each thread owns one row of the tile) and
 //                        store bfloat16 or float32, optionally applying SwiGLU to a weight whose rows
 //                        alternate gate/up in blocks of eight.
 // There are two accumulators in TMEM, so the epilogue of one tile runs under the main loop of the next.
@@ -28,18 +28,28 @@
 namespace q3 {
 
 constexpr int TC_BM = 128;
-constexpr int TC_THREADS = 192;
 
-constexpr int TC_HEAD_STAGE_BYTES = TC_BM * 128 * 2;  // one head (up to 128 wide) of the tile's 128 rows, bfloat16
+// The QKV epilogue has eight warps, two for each quarter of the accumulator's rows; each turns one head
+// (up to 128 wide) of its 32 rows around in shared memory at a time.
+constexpr int TC_QKV_EPI_WARPS = 8;
+constexpr int TC_QKV_ROW_PAD = 16;  // a row's 1 / rms and cache offset; also keeps rows off each other's banks
+constexpr int TC_HEAD_STAGE_BYTES = TC_QKV_EPI_WARPS * 32 * (128 * 2 + TC_QKV_ROW_PAD);
+
+template <int EPI>
+struct TcThreads {
+  static constexpr int EPI_WARPS = EPI == 2 ? TC_QKV_EPI_WARPS : 4;
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+};
 
 template <int BN, int EPI = 0>
 struct TcShape {
   static constexpr int A_BYTES = TC_BM * TC_BK * 2;
   static constexpr int B_BYTES = BN * TC_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;  // 4 stages of 48 KB or 6 of 32 KB
   static constexpr int BAR_BYTES = 256;  // 2 * STAGES + 4 barriers and the TMEM address
-  static constexpr int EPI_BYTES = EPI == 2 ? TC_HEAD_STAGE_BYTES : 0;  // where the QKV epilogue turns a head around
+  static constexpr int EPI_BYTES = EPI == 2 ? TC_HEAD_STAGE_BYTES : 0;  // where the QKV epilogue turns heads around
+  // 4 stages of 48 KB or 6 of 32 KB; beside the QKV epilogue's 68 KB, three of 48 KB
+  static constexpr int STAGES = ((EPI == 2 ? 160 : 192) * 1024) / STAGE_BYTES;
   static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + BAR_BYTES + EPI_BYTES + 1024;  // + room to align to 1024
   static constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulators
 };
@@ -60,82 +70,140 @@ struct QkvEpilogue {
   int write_kv;
 };
 
-// One head of the warp's 32 rows.  The thread that owns a row (thread = row, as tcgen05.ld hands the
-// accumulator out) takes the head's D values into registers, rounds them to bfloat16 as a stored
-// projection would be, and does the head norm and the rotation on its own: no shuffles, and every
-// load it needs (its row of cosines and sines) is independent of the others, so their latencies
-// overlap.  The finished row goes to shared memory (16-byte chunk c of row r at chunk position
-// c ^ (r % CH)) and from there to q_out or the cache pages in whole rows, D / 8 lanes to a row.
+// One head of the warp's 32 rows, in two passes.
+// Pass 1, a thread per row (as tcgen05.ld hands the accumulator out): the head's D values are rounded to
+// bfloat16, as a stored projection would be, and put into the row's place in shared memory; the thread sums
+// the squares of its rounded row on the way and leaves 1 / rms and the row's cache offset behind the row.
+// Pass 2, D / 8 neighbouring lanes per row.  A lane owns four values of the head's first half and the four
+// values of the second half that they are rotated with, so that norm and rotation need no other lane; it
+// reads them, the row's 1 / rms and its own cosines and sines (the lanes of a row read 2 D contiguous bytes
+// of each) and stores two 8-byte pieces to q_out or the cache page.  No shuffles and three shared-memory
+// reads per row: under the main loop the tensor core and TMA take the shared-memory pipe nearly whole, and
+// an epilogue that went through it twenty times per row (shuffles count) set the kernel's pace.
+// Cosines and sines are asked for four rows at a time and one such batch ahead, the first before pass 1.
+// Rows are TC_QKV_ROW_PAD bytes apart beyond their 2 D, which keeps pass 1's 16-byte writes (a thread per
+// row, the same column) off each other's banks.
 // `kv_off`: element offset of this lane's row in a page array (without the head), or -1.
+// `release`: the barrier that hands the accumulator back, arrived on once pass 1 has read it, or null.
 template <int D>
 __device__ __forceinline__ void qkv_head_rows(uint32_t tmem_head, unsigned char* mine, int row_base, int rows_here,
-                                              int head, const QkvEpilogue& e, int lane, long long kv_off) {
-  constexpr int CH = D / 8, LPH = D / 8, RPW = 32 / LPH;
+                                              int head, const QkvEpilogue& e, int lane, long long kv_off,
+                                              uint64_t* release) {
+  constexpr int LPH = D / 8, RPW = 32 / LPH, STRIDE = D * 2 + TC_QKV_ROW_PAD;
+  constexpr int ITER = 32 / RPW, BATCH = ITER < 4 ? ITER : 4, NB = ITER / BATCH;
   const bool is_q = head < e.Hq, is_k = !is_q && head < e.Hq + e.Hkv;
   const float* w = is_q ? e.q_weight : (is_k ? e.k_weight : nullptr);
-  const bool live = lane < rows_here;
-  const int t = row_base + lane;
-  float x[D];
+  const bool rotate = (is_q || is_k) && e.cos_sin != nullptr;
+  const int sub = lane / LPH, l = lane % LPH;
+  float4 cs[2][BATCH][2];  // [.][.][0]: cosines of the lane's four pairs, [1]: sines
+  auto fetch = [&](int b, float4 (&buf)[BATCH][2]) {
+#pragma unroll
+    for (int i = 0; i < BATCH; ++i) {
+      const int r = (b * BATCH + i) * RPW + sub;
+      buf[i][0] = make_float4(1.f, 1.f, 1.f, 1.f);
+      buf[i][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r < rows_here) {
+        const float* row = e.cos_sin + (size_t)(row_base + r) * D + l * 4;
+        buf[i][0] = *reinterpret_cast<const float4*>(row);
+        buf[i][1] = *reinterpret_cast<const float4*>(row + D / 2);
+      }
+    }
+  };
+  if (rotate) fetch(0, cs[0]);  // uniform over the warp
+
+  float ss = 0.f;
 #pragma unroll
   for (int c0 = 0; c0 < D; c0 += 32) {
     uint32_t v[32];
     tmem_ld_32(tmem_head + (uint32_t)c0, v);
     tmem_wait_ld();
 #pragma unroll
-    for (int i = 0; i < 32; ++i) x[c0 + i] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i])));
-  }
-  if (is_q || is_k) {  // uniform over the warp
-    if (w) {
-      float ss = 0.f;
+    for (int c = 0; c < 4; ++c) {
+      uint32_t pk[4];
 #pragma unroll
-      for (int i = 0; i < D; ++i) ss += x[i] * x[i];
-      const float rs = 1.0f / sqrtf(ss / (float)D + e.eps);
-#pragma unroll
-      for (int i = 0; i < D; i += 4) {
-        const float4 wv = *reinterpret_cast<const float4*>(w + i);
-        x[i] = x[i] * rs * wv.x;
-        x[i + 1] = x[i + 1] * rs * wv.y;
-        x[i + 2] = x[i + 2] * rs * wv.z;
-        x[i + 3] = x[i + 3] * rs * wv.w;
+      for (int i = 0; i < 4; ++i) {
+        pk[i] = pack2(v[8 * c + 2 * i], v[8 * c + 2 * i + 1]);
+        const float lo = __uint_as_float(pk[i] << 16), hi = __uint_as_float(pk[i] & 0xffff0000u);
+        ss = fmaf(lo, lo, ss);
+        ss = fmaf(hi, hi, ss);
       }
-    }
-    if (e.cos_sin != nullptr && live) {
-      const float* row = e.cos_sin + (size_t)t * D;
-#pragma unroll
-      for (int j = 0; j < D / 2; j += 4) {
-        const float4 c = *reinterpret_cast<const float4*>(row + j), sn = *reinterpret_cast<const float4*>(row + D / 2 + j);
-        const float cv[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const float a = x[j + u], b2 = x[j + u + D / 2];
-          x[j + u] = a * cv[u] - b2 * sv[u];
-          x[j + u + D / 2] = b2 * cv[u] + a * sv[u];
-        }
-      }
+      *reinterpret_cast<uint4*>(mine + lane * STRIDE + (c0 / 8 + c) * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     }
   }
-#pragma unroll
-  for (int c = 0; c < CH; ++c) {
-    uint4 pk;
-    pk.x = pack2(__float_as_uint(x[8 * c + 0]), __float_as_uint(x[8 * c + 1]));
-    pk.y = pack2(__float_as_uint(x[8 * c + 2]), __float_as_uint(x[8 * c + 3]));
-    pk.z = pack2(__float_as_uint(x[8 * c + 4]), __float_as_uint(x[8 * c + 5]));
-    pk.w = pack2(__float_as_uint(x[8 * c + 6]), __float_as_uint(x[8 * c + 7]));
-    *reinterpret_cast<uint4*>(mine + lane * (D * 2) + ((c ^ (lane % CH)) << 4)) = pk;
+  {
+    const float rs = w ? 1.0f / sqrtf(ss / (float)D + e.eps) : 1.0f;
+    *reinterpret_cast<uint4*>(mine + lane * STRIDE + D * 2) =
+        make_uint4(__float_as_uint(rs), (uint32_t)(unsigned long long)kv_off, (uint32_t)((unsigned long long)kv_off >> 32), 0u);
+  }
+  if (release) {  // uniform over the warp
+    tcgen05_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(release);
   }
   __syncwarp();
-  const int sub = lane / LPH, l = lane % LPH;
+
   const int hk = is_k ? head - e.Hq : head - e.Hq - e.Hkv;
-#pragma unroll 4
-  for (int r0 = 0; r0 < 32; r0 += RPW) {
-    const int r = r0 + sub;
-    const long long off = __shfl_sync(0xffffffffu, kv_off, r);
-    if (r >= rows_here) continue;
-    const uint4 chunk = *reinterpret_cast<const uint4*>(mine + r * (D * 2) + ((l ^ (r % CH)) << 4));
-    if (is_q)
-      *reinterpret_cast<uint4*>(e.q_out + ((size_t)(row_base + r) * e.Hq + head) * D + l * 8) = chunk;
-    else if (off >= 0)
-      *reinterpret_cast<uint4*>((is_k ? e.k_pages : e.v_pages) + off + (size_t)hk * e.page_size * D + l * 8) = chunk;
+  float4 w_lo = make_float4(1.f, 1.f, 1.f, 1.f), w_hi = w_lo;
+  if (w) {
+    w_lo = *reinterpret_cast<const float4*>(w + l * 4);
+    w_hi = *reinterpret_cast<const float4*>(w + D / 2 + l * 4);
+  }
+  const float wl[4] = {w_lo.x, w_lo.y, w_lo.z, w_lo.w}, wh[4] = {w_hi.x, w_hi.y, w_hi.z, w_hi.w};
+  auto work = [&](int b, const float4 (&buf)[BATCH][2]) {
+#pragma unroll
+    for (int i = 0; i < BATCH; ++i) {
+      const float4(&c)[2] = buf[i];
+      const int r = (b * BATCH + i) * RPW + sub;
+      const unsigned char* srow = mine + r * STRIDE;
+      const uint4 meta = *reinterpret_cast<const uint4*>(srow + D * 2);
+      uint2 lo2 = *reinterpret_cast<const uint2*>(srow + l * 8), hi2 = *reinterpret_cast<const uint2*>(srow + D + l * 8);
+      if (is_q || is_k) {  // uniform over the warp
+        float lo[4] = {__uint_as_float(lo2.x << 16), __uint_as_float(lo2.x & 0xffff0000u),
+                       __uint_as_float(lo2.y << 16), __uint_as_float(lo2.y & 0xffff0000u)};
+        float hi[4] = {__uint_as_float(hi2.x << 16), __uint_as_float(hi2.x & 0xffff0000u),
+                       __uint_as_float(hi2.y << 16), __uint_as_float(hi2.y & 0xffff0000u)};
+        if (w) {
+          const float rs_r = __uint_as_float(meta.x);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            lo[k] = lo[k] * rs_r * wl[k];
+            hi[k] = hi[k] * rs_r * wh[k];
+          }
+        }
+        if (rotate) {
+          const float cv[4] = {c[0].x, c[0].y, c[0].z, c[0].w}, sv[4] = {c[1].x, c[1].y, c[1].z, c[1].w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float a = lo[k], b2 = hi[k];
+            lo[k] = fmaf(-b2, sv[k], a * cv[k]);
+            hi[k] = fmaf(a, sv[k], b2 * cv[k]);
+          }
+        }
+        lo2.x = pack2(__float_as_uint(lo[0]), __float_as_uint(lo[1]));
+        lo2.y = pack2(__float_as_uint(lo[2]), __float_as_uint(lo[3]));
+        hi2.x = pack2(__float_as_uint(hi[0]), __float_as_uint(hi[1]));
+        hi2.y = pack2(__float_as_uint(hi[2]), __float_as_uint(hi[3]));
+      }
+      if (r >= rows_here) continue;
+      __nv_bfloat16* dst;
+      if (is_q) {
+        dst = e.q_out + ((size_t)(row_base + r) * e.Hq + head) * D;
+      } else {
+        const long long off = (long long)(((unsigned long long)meta.z << 32) | meta.y);
+        if (off < 0) continue;
+        dst = (is_k ? e.k_pages : e.v_pages) + off + (size_t)hk * e.page_size * D;
+      }
+      *reinterpret_cast<uint2*>(dst + l * 4) = lo2;
+      *reinterpret_cast<uint2*>(dst + D / 2 + l * 4) = hi2;
+    }
+  };
+  static_assert(NB % 2 == 0, "batches are worked on in pairs");
+#pragma unroll 1
+  for (int b = 0; b < NB; b += 2) {
+    if (rotate) fetch(b + 1, cs[1]);
+    work(b, cs[0]);
+    if (rotate && b + 2 < NB) fetch(b + 2, cs[0]);
+    work(b + 1, cs[1]);
   }
   __syncwarp();
 }
@@ -204,7 +272,7 @@ __device__ __forceinline__ void tc_store_chunk(const uint32_t (&v)[32], OutT* __
 
 // EPI 0: store.  EPI 1: SwiGLU.  EPI 2: the QKV epilogue with heads of HD values (C is not written).
 template <int BN, int EPI, typename OutT, int HD = 128>
-__global__ void __launch_bounds__(TC_THREADS)
+__global__ void __launch_bounds__(TcThreads<EPI>::THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                OutT* __restrict__ C, int M, int N, int K, int ldc, const __grid_constant__ QkvEpilogue qkv, int* status) {
   using S = TcShape<BN, EPI>;
@@ -236,7 +304,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);  // one arrival from each epilogue warp
+      mbar_init(&acc_empty[b], TcThreads<EPI>::EPI_WARPS);  // one arrival from each epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -336,8 +404,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int row = m0 + quarter * 32 + lane;
       const uint32_t tmem_acc = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
       if (EPI == 2) {
-        // head by head; the cache position of the thread's own row is looked up once per tile
-        unsigned char* mine = head_stage + quarter * 32 * (HD * 2);
+        // Two warps per quarter; each takes every second head of the tile.  The cache position of the
+        // thread's own row is looked up once per tile.  The accumulator goes back to the issuing thread as
+        // soon as the warp's last head has been read out of it, before that head's second pass.
+        constexpr int SLOTS = TcThreads<EPI>::EPI_WARPS / 4;
+        const int ew = warp - 2, slot = ew >> 2;
+        unsigned char* mine = head_stage + ew * 32 * (HD * 2 + TC_QKV_ROW_PAD);
         const int rows_here = min(32, M - (m0 + quarter * 32));
         long long kv_off = -1;
         if (qkv.write_kv && lane < rows_here && n0 + BN > qkv.Hq * HD) {
@@ -353,15 +425,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               kv_off = ((long long)page * qkv.Hkv * qkv.page_size + (pos % qkv.page_size)) * HD;
           }
         }
+        bool released = false;
 #pragma unroll 1
-        for (int h0 = 0; h0 < BN; h0 += HD) {
-          if (n0 + h0 >= N) break;  // uniform over the warp
-          qkv_head_rows<HD>(tmem_acc + (uint32_t)h0, mine, m0 + quarter * 32, rows_here, (n0 + h0) / HD, qkv, lane, kv_off);
+        for (int h0 = slot * HD; h0 < BN && n0 + h0 < N; h0 += SLOTS * HD) {  // uniform over the warp
+          const bool last = h0 + SLOTS * HD >= BN || n0 + h0 + SLOTS * HD >= N;
+          qkv_head_rows<HD>(tmem_acc + (uint32_t)h0, mine, m0 + quarter * 32, rows_here, (n0 + h0) / HD, qkv, lane, kv_off,
+                            last ? &acc_empty[buf] : nullptr);
+          released = released || last;
         }
-        // the accumulator has been read: the next tile may use it
-        tcgen05_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        if (!released) {  // a warp without a head in the matrix's last tile
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
       } else {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -404,7 +480,7 @@ static int gemm_tc_launch(const void* A, const void* W, void* C, int M, int N, i
   const long long tiles = (long long)((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM);
   if (tiles > 0x7fffffffLL) return Q3_ERR_SIZE;
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  q3::launch(gemm_tc_kernel<BN, EPI, OutT, HD>, dim3(grid), dim3(TC_THREADS), S::SMEM_BYTES, stream, map_a, map_b,
+  q3::launch(gemm_tc_kernel<BN, EPI, OutT, HD>, dim3(grid), dim3(TcThreads<EPI>::THREADS), S::SMEM_BYTES, stream, map_a, map_b,
              (OutT*)C, M, N, K, ldc, qkv, status);
   return launch_status();
 }

@@ -564,6 +564,13 @@ def gemm_tc_qkv_takes(rows: int, x: torch.Tensor, weight: torch.Tensor, head_dim
     return (rows >= 128 and gemm_tc_takes(x, weight) and head_dim in (64, 128) and rotary_dim in (0, head_dim))
 
 
+def gemm_tc_qkv_pays(rows: int, weight: torch.Tensor) -> bool:
+    """Whether the projection with ``qkv_post`` as its epilogue is the faster way for a prompt portion.  It
+    saves ``qkv_post``'s pass over the projection; against that its single-CTA tiles run below the library's
+    rate when the reduction is long (measured: profiles/gemm_tc_qkv__prefill_2048.md)."""
+    return rows >= 128 and weight.shape[1] <= 1536
+
+
 def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                 q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                 cos_sin: Optional[torch.Tensor], positions: torch.Tensor, tok_seq: torch.Tensor,
@@ -571,9 +578,7 @@ def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages: 
                 status: torch.Tensor) -> None:
     """x[T, K] @ w[(Hq + 2 Hkv) D, K]^T on the tensor cores with ``qkv_post`` as the epilogue: the
     projection is rounded to bfloat16, normed and rotated head by head and written to ``q_out`` and the
-    cache pages; it is never stored itself.  The attention part does not use it: its epilogue (two heads
-    of 128 rows by four warps) hides under the next tile's main loop only when that loop is long
-    (measured: profiles/gemm_tc_swiglu__prefill_2048.md)."""
+    cache pages; it is never stored itself (``gemm_tc_qkv_pays`` says where the attention part takes it)."""
     for name, t in (("x", x), ("w", w), ("q_out", q_out), ("k_pages", k_pages), ("v_pages", v_pages)):
         _check(f"gemm_tc_qkv.{name}", t, torch.bfloat16)
     for name, t in (("positions", positions), ("tok_seq", tok_seq), ("block_table", block_table)):

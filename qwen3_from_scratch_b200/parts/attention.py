@@ -109,6 +109,17 @@ class GQAAttention(Mixer):
             if into_stream is not None:
                 return self.o_proj.into_stream(out.view(T, hq * d), into_stream, next_norm_weight)
             return self.o_proj(out.view(T, hq * d))
+        if ((self.position is None or fused is not None) and torch.is_tensor(x)
+                and ops.gemm_tc_qkv_takes(T, x, self.qkv.weight, d, fused[1] if fused is not None else 0)
+                and ops.gemm_tc_qkv_pays(T, self.qkv.weight)):
+            # a prompt portion: the projection's own epilogue norms, rotates and writes the pages
+            cos_sin = self.position.step_table(ctx) if fused is not None else None
+            ops.gemm_tc_qkv(x, self.qkv.weight, q, k_pages, v_pages, self.q_norm_weight, self.k_norm_weight, eps,
+                            cos_sin, ctx.positions, ctx.tok_seq, table, hq, hkv, d, write_cache, self.rt.status)
+            self.attend(q, k_pages, v_pages, table, ctx, out)
+            if into_stream is not None:
+                return self.o_proj.into_stream(out.view(T, hq * d), into_stream, next_norm_weight)
+            return self.o_proj(out.view(T, hq * d))
         qkv = self.qkv(x)
         if self.position is None or fused is not None:
             inv_freq, rotary_dim = fused if fused is not None else (None, 0)
