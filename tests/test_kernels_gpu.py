@@ -457,6 +457,40 @@ def test_gemm_tc_qkv(hq, hkv, d, K, T, rotate):
     assert float(kp.abs().sum(dim=(1, 3))[~written].sum()) == 0.0
 
 
+def test_gemm_tc_qkv_without_head_norm_and_without_a_cache_write():
+    """The same epilogue for a layer without head norms that reads a cache another layer wrote: only q is
+    produced (rotated), the pages stay as they are; and a page id outside the pool is reported, not written."""
+    g = torch.Generator().manual_seed(14)
+    hq, hkv, d, K, T, page_size = 6, 2, 128, 192, 150, 16
+    tables, num_pages = make_tables([T], page_size, 5)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn((hq + 2 * hkv) * d, K, generator=g) / K ** 0.5).to(torch.bfloat16)
+    positions = torch.arange(T, dtype=torch.int32)
+    tok_seq = torch.zeros(T, dtype=torch.int32)
+    inv_freq = 1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    k_pages = torch.full((num_pages, hkv, page_size, d), 3.0, device="cuda", dtype=torch.bfloat16)
+    v_pages = torch.full_like(k_pages, 5.0)
+    q_out = torch.full((T, hq, d), float("nan"), device="cuda", dtype=torch.bfloat16)
+    cos_sin = torch.empty(T, d, device="cuda", dtype=torch.float32)
+    ops().rope_table(dev(inv_freq), dev(positions), cos_sin)
+    st = status()
+    ops().gemm_tc_qkv(dev(x), dev(w), q_out, k_pages, v_pages, None, None, 0.0, cos_sin, dev(positions), dev(tok_seq),
+                      dev(table_tensor(tables)), hq, hkv, d, False, st)
+    assert int(st.item()) == 0
+    q = (x.double() @ w.double().t()).to(torch.bfloat16).double().view(T, hq + 2 * hkv, d)[:, :hq]
+    ang = positions.double()[:, None] * inv_freq.double()[None, :]
+    close(q_out, plain.apply_rope(q, ang.cos(), ang.sin()), "bfloat16", tol=1.5 * 2.0 ** -8)
+    assert bool((k_pages == 3.0).all()) and bool((v_pages == 5.0).all())
+    bad = table_tensor(tables)
+    bad[0, 2] = num_pages
+    ops().gemm_tc_qkv(dev(x), dev(w), q_out, k_pages, v_pages, None, None, 0.0, cos_sin, dev(positions), dev(tok_seq),
+                      dev(bad), hq, hkv, d, True, st)
+    assert int(st.item()) & 2
+    hit = [p for p in range(num_pages) if p != tables[0][2] and p in tables[0]]
+    assert bool((k_pages[tables[0][2]] == 3.0).all()), "the rows of the bad page went somewhere"
+    assert not bool((k_pages[hit] == 3.0).all())
+
+
 def reference_attention(q, k_list, v_list, q_lens, window):
     """Per request: the plain whole-sequence attention, of which the last q_len rows are the step's."""
     outs = []
