@@ -648,22 +648,34 @@ def decode_takes_raw_qkv(dtype: torch.dtype, num_q_heads: int, num_kv_heads: int
             and decode_tma_takes(head_dim, page_size))
 
 
+DECODE_LATER_WAVE = 30     # what every wave of blocks after the first costs beside its tiles, in tiles
+DECODE_SATURATING = 2.3    # blocks per SM that together take tiles as fast as the memory gives them
+
+
 def decode_splits(num_seqs: int, num_kv_heads: int, max_kv_len: int, window: int, head_dim: int = 128,
                   blocks_per_sm: Optional[int] = None) -> int:
-    """How many ranges a sequence's keys are cut into.  Blocks run in waves of (SMs x blocks per
-    SM); a block costs its share of the 16-key tiles plus a fixed set-up and merge (about six
-    tiles' worth).  The count that minimises waves x cost per block wins."""
+    """How many ranges a sequence's keys are cut into.  Blocks run in waves of (SMs x blocks per SM).  A
+    block alone walks its 16-key tiles at its own pace; ``DECODE_SATURATING`` blocks per SM together take
+    tiles as fast as the memory gives them, and more blocks then only share that rate; every wave after the
+    first costs a start.  So a wave of n blocks of L tiles costs max(L, n L / saturating), and the count with
+    the least sum over its waves wins, the smaller count on a tie.  The two constants are fitted to sweeps
+    of the decode step over batch and context (profiles/attn_decode_tma__decode_b8_ctx4096.md)."""
     span = min(max_kv_len, window) if window and window > 0 else max_kv_len
     tiles = max(1, -(-span // 16))
-    slots = sm_count() * (blocks_per_sm or decode_blocks_per_sm(head_dim))
+    sms = sm_count()
+    slots = sms * (blocks_per_sm or decode_blocks_per_sm(head_dim))
+    saturating = DECODE_SATURATING * sms
     pairs = max(1, num_seqs * num_kv_heads)
     best, best_cost = 1, None
     for s in range(1, MAX_DECODE_SPLITS + 1):
         if s > 1 and tiles // s < 4:
             break
-        waves = -(-pairs * s // slots)
-        cost = waves * (-(-tiles // s) + 6)
-        if best_cost is None or cost < best_cost:
+        per_block = -(-tiles // s)
+        full, rest = divmod(pairs * s, slots)
+        cost = full * max(per_block, slots * per_block / saturating) + DECODE_LATER_WAVE * (full - 1 if full else 0)
+        if rest:
+            cost += max(per_block, rest * per_block / saturating) + (DECODE_LATER_WAVE if full else 0)
+        if best_cost is None or cost < best_cost - 1e-6:
             best, best_cost = s, cost
     return best
 
