@@ -462,6 +462,13 @@ def measure_model(key, args, peaks, sample_clocks):
                "frac": flops / prefill_s / (peaks["bf16_tflops"] * 1e12)}
     print(f"[bench] {spec['name']} prompt of {PREFILL_TOKENS}: {prefill_s * 1e3:.2f} ms, {prefill['value']:.0f} tok/s, "
           f"{prefill['frac']:.2f} of the bf16 peak", file=sys.stderr, flush=True)
+    # the prompt step at two further lengths (the contract's figure stays the 2,048-token one)
+    more = {}
+    for tokens in (512, 4096):
+        t = prefill_bench(engine, tokens, max(3, min(args.steps, 10)), args.warmup, vocab)
+        more[tokens] = {"tok_s": tokens / t, "frac": prefill_flops(tokens) / t / (peaks["bf16_tflops"] * 1e12)}
+        print(f"[bench] {spec['name']} prompt of {tokens}: {t * 1e3:.2f} ms, {tokens / t:.0f} tok/s, "
+              f"{more[tokens]['frac']:.2f} of the bf16 peak", file=sys.stderr, flush=True)
     serving = None
     if spec["serving"] and not args.no_serving:
         serving = serving_bench(engine, vocab)
@@ -470,7 +477,7 @@ def measure_model(key, args, peaks, sample_clocks):
     gc.collect()
     torch.cuda.empty_cache()
     return dict(key=key, spec=spec, cfg=cfg, layers=layers, full_layers=full_layers, batches=batches, results=results,
-                prefill=prefill, serving=serving, clocks=clocks)
+                prefill=prefill, prefill_more=more, serving=serving, clocks=clocks)
 
 
 def line_of(m, args, peaks):
@@ -507,6 +514,9 @@ def line_of(m, args, peaks):
     for b in m["batches"]:
         line["points"][f"decode_b{b}_e2e"] = results[b]["e2e_tok_s"]
         line["points"][f"decode_b{b}_hbm_frac"] = results[b]["frac"]
+    for tokens, r in m["prefill_more"].items():
+        line["points"][f"prefill_{tokens}_tok_s"] = r["tok_s"]
+        line["points"][f"prefill_{tokens}_frac"] = r["frac"]
     if m["serving"]:
         line["serving"] = m["serving"]
     return line
@@ -544,6 +554,9 @@ def ours(args):
                 line["points"][f"{key}_decode_b{b}_hbm_frac"] = r["frac"]
             line["points"][f"{key}_prefill_tok_s"] = other["prefill"]["value"]
             line["points"][f"{key}_prefill_frac"] = other["prefill"]["frac"]
+            for tokens, r in other["prefill_more"].items():
+                line["points"][f"{key}_prefill_{tokens}_tok_s"] = r["tok_s"]
+                line["points"][f"{key}_prefill_{tokens}_frac"] = r["frac"]
             line["points"][f"{key}_layers"] = other["layers"]
             if other["serving"]:
                 line["points"][f"{key}_serving_output_tok_s"] = other["serving"]["output_tok_s"]
@@ -580,11 +593,12 @@ def profile(args):
         from qwen3_from_scratch_b200.engine.batch import BatchContext, Entry
         session = engine.session
         g = torch.Generator().manual_seed(99)
-        prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=g).tolist()
+        tokens = args.prefill_tokens
+        prompt = torch.randint(0, vocab, (tokens,), generator=g).tolist()
         session.open("p")
-        session.manager.reserve("p", PREFILL_TOKENS)
+        session.manager.reserve("p", tokens)
         ctx = BatchContext(session.manager, session.storage, session.rt).build(
-            [Entry("p", prompt, (PREFILL_TOKENS - 1,))], session.vocab_size)
+            [Entry("p", prompt, (tokens - 1,))], session.vocab_size)
         run = lambda: session.model.step(ctx)  # noqa: E731
     else:
         g = torch.Generator().manual_seed(1234)
@@ -676,6 +690,8 @@ def main() -> int:
                    help="default run without the 8B and 32B figures under `points`")
     p.add_argument("--no-serving", action="store_true", help="--model 8b without the 64-request load")
     p.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in the output)")
+    p.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                   help="with --profile prefill: length of the prompt (at most 4,096)")
     p.add_argument("--leave-out", action="store_true",
                    help="with --profile: time the step as a CUDA graph, whole and with each kind of kernel left out")
     p.add_argument("--profile", choices=["decode", "prefill"], default=None,

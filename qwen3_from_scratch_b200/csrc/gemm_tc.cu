@@ -3,7 +3,8 @@
 //
 // A persistent kernel, one block per SM, that walks over 128 x BN output tiles.  Three roles:
 //   warp 0 (one thread)  brings operand tiles of 64 values of k into shared memory by TMA
-//                        (cp.async.bulk.tensor, 128-byte swizzle, no multicast) under a ring of mbarriers;
+//                        (cp.async.bulk.tensor, 128-byte swizzle, no multicast) under a ring of mbarriers; the
+//                        W tiles of the ring's first round go out before the wait on the kernel before;
 //   warp 1 (one thread)  issues tcgen05.mma (cta_group::1, kind::f16) straight from shared memory through
 //                        matrix descriptors, four instructions of k = 16 per stage; tcgen05.commit hands
 //                        each stage back to the loader and each finished accumulator to the epilogue;
@@ -48,8 +49,8 @@ struct TcShape {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_BYTES = 256;  // 2 * STAGES + 4 barriers and the TMEM address
   static constexpr int EPI_BYTES = EPI == 2 ? TC_HEAD_STAGE_BYTES : 0;  // where the QKV epilogue turns heads around
-  // 4 stages of 48 KB or 6 of 32 KB; beside the QKV epilogue's 68 KB, three of 48 KB
-  static constexpr int STAGES = ((EPI == 2 ? 160 : 192) * 1024) / STAGE_BYTES;
+  // 4 stages of 48 KB or 6 of 32 KB; beside the QKV epilogue's 68 KB, three of 48 KB or four of 32 KB
+  static constexpr int STAGES = ((EPI == 2 ? 156 : 192) * 1024) / STAGE_BYTES;
   static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + BAR_BYTES + EPI_BYTES + 1024;  // + room to align to 1024
   static constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulators
 };
@@ -296,6 +297,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tma_prefetch_map(&map_a);
     tma_prefetch_map(&map_b);
   }
+  int ahead = 0;  // thread 0 (the loader): how many of its first (tile, k tile) pairs have their W tile under way
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < S::STAGES; ++s) {
@@ -307,6 +309,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       mbar_init(&acc_empty[b], TcThreads<EPI>::EPI_WARPS);  // one arrival from each epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // The weights do not depend on the kernel before this one: the W tiles of the ring's first round are
+    // asked for now, the activations' tiles after the wait (the loader below leaves these W tiles out).
+    for (int tile = blockIdx.x; tile < num_tiles && ahead < S::STAGES; tile += gridDim.x) {
+      const int n0 = (tile / m_tiles) * BN;
+      for (int kt = 0; kt < k_tiles && ahead < S::STAGES; ++kt, ++ahead) {
+        mbar_expect_tx(&full[ahead], S::STAGE_BYTES);
+        tma_load_2d(tiles + (size_t)ahead * S::STAGE_BYTES + S::A_BYTES, &map_b, &full[ahead], kt * TC_BK, n0);
+      }
+    }
   }
   pdl_wait();  // the activations come from the kernel before this one
   pdl_launch_dependents();
@@ -333,17 +344,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int kt = 0; kt < k_tiles; ++kt, ++it) {
           const int s = it % S::STAGES;
           const uint32_t use = it / S::STAGES;
-          if (use > 0 && !mbar_wait(&empty[s], (use & 1) ^ 1, &abort_flag)) {
-            abort_flag = 1;
-            atomicOr(status, Q3_STATUS_TIMEOUT);
-            ok = false;
-            break;
+          unsigned char* a_s = tiles + (size_t)s * S::STAGE_BYTES;
+          if ((int)it >= ahead) {
+            if (use > 0 && !mbar_wait(&empty[s], (use & 1) ^ 1, &abort_flag)) {
+              abort_flag = 1;
+              atomicOr(status, Q3_STATUS_TIMEOUT);
+              ok = false;
+              break;
+            }
+            mbar_expect_tx(&full[s], S::STAGE_BYTES);
+            tma_load_2d(a_s + S::A_BYTES, &map_b, &full[s], kt * TC_BK, n0);
           }
           if ((int)it == tc_drop_copy) continue;  // tests of the give-up path only (see tc_common.cuh)
-          unsigned char* a_s = tiles + (size_t)s * S::STAGE_BYTES;
-          mbar_expect_tx(&full[s], S::STAGE_BYTES);
           tma_load_2d(a_s, &map_a, &full[s], kt * TC_BK, m0);
-          tma_load_2d(a_s + S::A_BYTES, &map_b, &full[s], kt * TC_BK, n0);
         }
       }
     }
@@ -555,6 +568,11 @@ extern "C" int q3_gemm_tc_qkv(const void* A, const void* W, int T, int K, int Hq
   e.write_kv = write_kv;
   const int N = (Hq + 2 * Hkv) * D;
   using bf16 = __nv_bfloat16;
-  if (D == 128) return q3::gemm_tc_launch<256, 2, bf16, 128>(A, W, nullptr, T, N, K, 0, status, stream, e);
-  return q3::gemm_tc_launch<256, 2, bf16, 64>(A, W, nullptr, T, N, K, 0, status, stream, e);
+  // tiles of 256 columns (two heads of 128) or of 128 (one): whichever needs fewer rounds of the SMs
+  if (D == 128) {
+    if (q3::tc_pick_bn(T, N) == 256) return q3::gemm_tc_launch<256, 2, bf16, 128>(A, W, nullptr, T, N, K, 0, status, stream, e);
+    return q3::gemm_tc_launch<128, 2, bf16, 128>(A, W, nullptr, T, N, K, 0, status, stream, e);
+  }
+  if (q3::tc_pick_bn(T, N) == 256) return q3::gemm_tc_launch<256, 2, bf16, 64>(A, W, nullptr, T, N, K, 0, status, stream, e);
+  return q3::gemm_tc_launch<128, 2, bf16, 64>(A, W, nullptr, T, N, K, 0, status, stream, e);
 }

@@ -532,8 +532,8 @@ def gemm_tc_swiglu_pays(rows: int, weight: torch.Tensor) -> bool:
     """Whether the gate/up product with SwiGLU in its epilogue is the faster way for a prompt portion.
     It saves the gate kernel's pass over the [rows, 2 I] product, which weighs the more the shorter the
     reduction is; against that its single-CTA tiles run below the library's rate when the reduction
-    is long (measured: profiles/gemm_tc_swiglu__prefill_2048.md)."""
-    return rows >= 128 and weight.shape[1] <= 1536
+    is long or the rows are many (measured: profiles/gemm_tc_swiglu__prefill_2048.md)."""
+    return 128 <= rows < 3072 and weight.shape[1] <= 1536
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
@@ -566,9 +566,10 @@ def gemm_tc_qkv_takes(rows: int, x: torch.Tensor, weight: torch.Tensor, head_dim
 
 def gemm_tc_qkv_pays(rows: int, weight: torch.Tensor) -> bool:
     """Whether the projection with ``qkv_post`` as its epilogue is the faster way for a prompt portion.  It
-    saves ``qkv_post``'s pass over the projection; against that its single-CTA tiles run below the library's
-    rate when the reduction is long (measured: profiles/gemm_tc_qkv__prefill_2048.md)."""
-    return rows >= 128 and weight.shape[1] <= 1536
+    saves ``qkv_post``'s pass over the projection and a launch; against that a launch of it costs about 13 us
+    whatever its size, and its single-CTA tiles run below the library's rate when the reduction is long or the
+    rows are many (measured inside the step: profiles/gemm_tc_qkv__prefill_2048.md)."""
+    return 768 <= rows < 3072 and weight.shape[1] <= 1536
 
 
 def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,

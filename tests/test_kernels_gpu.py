@@ -407,7 +407,7 @@ def test_qkv_post(dtype, hq, hkv, d, rot, with_table):
 
 @pytest.mark.parametrize("rotate", [True, False])
 @pytest.mark.parametrize("hq,hkv,d,K,T", [(8, 2, 128, 256, 200), (5, 2, 128, 96, 130), (3, 1, 64, 136, 333),
-                                          (16, 8, 128, 1024, 256)])
+                                          (16, 8, 128, 1024, 256), (16, 8, 128, 512, 1100), (6, 1, 64, 72, 2500)])
 def test_gemm_tc_qkv(hq, hkv, d, K, T, rotate):
     """The QKV projection with head norm, rotation and cache write in its epilogue against the plain
     formulas applied to the projection rounded to bfloat16; rows and heads that do not fill a tile."""

@@ -31,7 +31,7 @@ SIZES = {
     "32b": dict(hidden_size=5120, num_attention_heads=64, num_key_value_heads=8, intermediate_size=25600,
                 vocab_size=4999, tie_word_embeddings=False),
 }
-LONG = 330
+LONG = 330  # (and one of 900, run whole only)
 SHORT = [24 + 2 * i for i in range(16)]  # sixteen short requests, 24 to 54 tokens
 
 
@@ -81,6 +81,7 @@ def sequences(size):
     for i, n in enumerate(SHORT):
         seqs[f"s{i}"] = random_tokens(vocab, n, 600 + i)
     seqs["late"] = random_tokens(vocab, 70, 700)
+    seqs["longer"] = random_tokens(vocab, 900, 800)  # enough rows for the QKV product that norms, rotates and writes the pages
     return seqs
 
 
