@@ -741,6 +741,22 @@ def test_decode_splits_agree(splits, window, loader, d, page_size):
     close(out, want, "bfloat16")
 
 
+@pytest.mark.parametrize("splits", [None, 2, 5])
+@pytest.mark.parametrize("hq,hkv,d,page_size", [(8, 4, 128, 16), (6, 2, 64, 32)])
+def test_decode_of_many_sequences(splits, hq, hkv, d, page_size):
+    """More (sequence, kv head, range) blocks than the SMs hold at once, so that the grid runs in several waves;
+    ragged lengths, some of them shorter than a range."""
+    g = torch.Generator().manual_seed(31)
+    n = 130 if hkv == 4 else 260
+    kv_lens = [int(x) for x in torch.randint(1, 420, (n,), generator=g)]
+    kv_lens[3], kv_lens[17] = 1, 16
+    q_lens = [1] * n
+    q, k_list, v_list, tables, num_pages = attention_case("bfloat16", hq, hkv, d, page_size, kv_lens, q_lens, None, seed=33)
+    out = run_fast(q, k_list, v_list, tables, num_pages, page_size, kv_lens, q_lens, None, splits=splits, loader="tma")
+    want = reference_attention(q.double(), [k.double() for k in k_list], [v.double() for v in v_list], q_lens, None)
+    close(out, want, "bfloat16")
+
+
 @pytest.mark.parametrize("far", [0, 3, 250, 511])
 @pytest.mark.parametrize("q_len", [1, 6])
 def test_fast_attention_finds_one_far_key(far, q_len):
