@@ -1,8 +1,9 @@
 // Paged decode attention with a TMA producer: the same split-KV scheme and tensor-core arithmetic
 // as attn_decode.cu, but the key/value tiles are brought in by a dedicated loader warp through
-// TMA (cp.async.bulk.tensor, 128-byte swizzle) into a ring of eight stages shared by four consumer
-// warps.  How many bytes are in flight no longer depends on how fast a consumer gets through its
-// tile: the loader runs up to eight 16-key tiles (64 KB per block at D = 128) ahead, which is what
+// TMA (cp.async.bulk.tensor, 128-byte swizzle) into a ring of stages shared by the consumer warps
+// (eight stages and four warps; six and three in the form for four blocks per SM).
+// How many bytes are in flight no longer depends on how fast a consumer gets through its
+// tile: the loader runs up to a ring of 16-key tiles (64 KB per block at D = 128) ahead, which is what
 // a bandwidth-bound kernel wants, and the consumers issue no copy instructions at all.
 //
 // Takes D = 64 or 128 and page sizes that are multiples of 16 (a 16-key tile then lies in one
@@ -15,21 +16,29 @@ extern "C" int q3_attn_combine(const float* partial, void* out, const int* q_sta
 
 namespace q3 {
 
-constexpr int DT_CONSUMERS = 4;
-constexpr int DT_THREADS = (DT_CONSUMERS + 1) * 32;
 constexpr int DT_KEYS = 16;
-constexpr int DT_STAGES = 8;
 
-template <int D>
+// BLOCKS: blocks per SM the kernel is compiled for.  Two or three: four consumer warps and a ring of eight
+// stages.  Four: three consumer warps and six stages, so that four blocks' registers (128 x 128 threads) and
+// shared memory (53 KB) fit an SM.
+template <int BLOCKS>
+struct DecodeTmaBlock {
+  static constexpr int CONSUMERS = BLOCKS >= 4 ? 3 : 4;
+  static constexpr int THREADS = (CONSUMERS + 1) * 32;
+  static constexpr int STAGES = BLOCKS >= 4 ? 6 : 8;
+};
+
+template <int D, int BLOCKS = 2>
 struct DecodeTmaShape {
+  using B = DecodeTmaBlock<BLOCKS>;
   static constexpr int ATOMS = D / 64;
   static constexpr int TILE_BYTES = DT_KEYS * D * 2;        // K (or V) of one tile: ATOMS atoms of 2048 bytes
   static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-  static constexpr int RING_BYTES = DT_STAGES * STAGE_BYTES;
+  static constexpr int RING_BYTES = B::STAGES * STAGE_BYTES;
   static constexpr int Q_PITCH = D + 8;
   static constexpr int Q_BYTES = 16 * Q_PITCH * 2;
-  static constexpr int MERGE_BYTES = DT_CONSUMERS * 16 * (D + 2) * 4;
-  static constexpr int BAR_BYTES = 2 * DT_STAGES * 8 + 16;
+  static constexpr int MERGE_BYTES = B::CONSUMERS * 16 * (D + 2) * 4;
+  static constexpr int BAR_BYTES = 2 * B::STAGES * 8 + 16;
   static constexpr size_t SMEM_BYTES =
       (size_t)(RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES) + Q_BYTES + BAR_BYTES;
 };
@@ -100,18 +109,22 @@ struct DecodeQkv {
 };
 
 // BLOCKS: blocks per SM the kernel is compiled for.  Three (128 registers) give a large grid half as many
-// places again as two; two (168 registers) are the faster code where the grid fits their places anyway
+// places again as two; two (168 registers) are the faster code where the grid fits their places anyway; four
+// (smaller blocks, see DecodeTmaBlock) are for a grid of several waves, where more blocks per SM in different
+// stages of their lives keep the SM's stream over the cache going
 // (figures: profiles/attn_decode_tma__decode_b8_ctx4096.md).
 template <int D, int BLOCKS>
-__global__ void __launch_bounds__(DT_THREADS, BLOCKS)
+__global__ void __launch_bounds__(DecodeTmaBlock<BLOCKS>::THREADS, BLOCKS)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                        float* __restrict__ partial, const int* __restrict__ q_start,
                        const int* __restrict__ kv_len, const int* __restrict__ block_table, int table_stride,
                        int page_size, int num_pages, int Hq, int Hkv, float scale_log2, int window,
                        int num_splits, int* status, const DecodeQkv fq) {
-  using S = DecodeTmaShape<D>;
+  using S = DecodeTmaShape<D, BLOCKS>;
   constexpr int KT = D / 16, CPR = D / 8, PITCH = S::Q_PITCH;
+  constexpr int DT_CONSUMERS = DecodeTmaBlock<BLOCKS>::CONSUMERS, DT_STAGES = DecodeTmaBlock<BLOCKS>::STAGES;
+  constexpr int DT_THREADS = DecodeTmaBlock<BLOCKS>::THREADS;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* ring = smem_raw;
   constexpr int RING_OR_MERGE = S::RING_BYTES > S::MERGE_BYTES ? S::RING_BYTES : S::MERGE_BYTES;
@@ -455,14 +468,16 @@ static int attn_decode_tma_launch(const void* q, const void* k_pages, const void
                                   const int* q_start, const int* kv_len, const int* block_table, int table_stride,
                                   int page_size, int num_pages, int B, int Hq, int Hkv, float scale, int window,
                                   int num_splits, int* status, cudaStream_t stream, DecodeQkv fq = DecodeQkv{}) {
-  using S = DecodeTmaShape<D>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<D, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)S::SMEM_BYTES);
+                                         (int)DecodeTmaShape<D, 2>::SMEM_BYTES);
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(attn_decode_tma_kernel<D, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               (int)S::SMEM_BYTES);
+                               (int)DecodeTmaShape<D, 3>::SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_decode_tma_kernel<D, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)DecodeTmaShape<D, 4>::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -473,11 +488,17 @@ static int attn_decode_tma_launch(const void* q, const void* k_pages, const void
   code = cached_map(&map_v, v_pages, rows, D, DT_KEYS);
   if (code) return code;
   dim3 grid(num_splits, Hkv, B);
-  const bool many = (long long)num_splits * Hkv * B > 2LL * sm_count();  // more blocks than two per SM hold at once
-  auto kernel = many ? attn_decode_tma_kernel<D, 3> : attn_decode_tma_kernel<D, 2>;
-  q3::launch(kernel, grid, dim3(DT_THREADS), S::SMEM_BYTES, stream, map_k, map_v,
-             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, partial, q_start, kv_len, block_table, table_stride,
-             page_size, num_pages, Hq, Hkv, scale * 1.4426950408889634f, window, num_splits, status, fq);
+  const long long blocks = (long long)num_splits * Hkv * B;
+  // two blocks per SM where the grid fits them, three where it fits those, four for a grid of several waves
+  const int per_sm = blocks <= 2LL * sm_count() ? 2 : blocks <= 3LL * sm_count() ? 3 : 4;
+#define Q3_DT_LAUNCH(BL)                                                                                              \
+  q3::launch(attn_decode_tma_kernel<D, BL>, grid, dim3(DecodeTmaBlock<BL>::THREADS), DecodeTmaShape<D, BL>::SMEM_BYTES,  \
+             stream, map_k, map_v, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, partial, q_start, kv_len, block_table, \
+             table_stride, page_size, num_pages, Hq, Hkv, scale * 1.4426950408889634f, window, num_splits, status, fq)
+  if (per_sm == 2) Q3_DT_LAUNCH(2);
+  else if (per_sm == 3) Q3_DT_LAUNCH(3);
+  else Q3_DT_LAUNCH(4);
+#undef Q3_DT_LAUNCH
   code = launch_status();
   if (code != 0 || num_splits == 1) return code;
   return q3_attn_combine(partial, out, q_start, B, Hq, D, num_splits, stream);

@@ -649,22 +649,26 @@ def decode_takes_raw_qkv(dtype: torch.dtype, num_q_heads: int, num_kv_heads: int
             and decode_tma_takes(head_dim, page_size))
 
 
-DECODE_LATER_WAVE = 30     # what every wave of blocks after the first costs beside its tiles, in tiles
 DECODE_SATURATING = 2.3    # blocks per SM that together take tiles as fast as the memory gives them
+DECODE_LATER_WAVE = 5      # what every wave of blocks after the first costs beside its tiles, in tiles
+DECODE_WIDE_GRID = 20      # what the form of the kernel for more blocks per SM costs beside its tiles
+DECODE_LONG_BLOCK = (0.15, 128)  # a single wave of that form: per tile of a block beyond so many
 
 
 def decode_splits(num_seqs: int, num_kv_heads: int, max_kv_len: int, window: int, head_dim: int = 128,
-                  blocks_per_sm: Optional[int] = None) -> int:
+                  blocks_per_sm: Optional[int] = None, wide_blocks_per_sm: Optional[int] = None) -> int:
     """How many ranges a sequence's keys are cut into.  Blocks run in waves of (SMs x blocks per SM).  A
     block alone walks its 16-key tiles at its own pace; ``DECODE_SATURATING`` blocks per SM together take
     tiles as fast as the memory gives them, and more blocks then only share that rate; every wave after the
     first costs a start.  So a wave of n blocks of L tiles costs max(L, n L / saturating), and the count with
-    the least sum over its waves wins, the smaller count on a tie.  The two constants are fitted to sweeps
-    of the decode step over batch and context (profiles/attn_decode_tma__decode_b8_ctx4096.md)."""
+    the least sum over its waves wins, the smaller count on a tie.  ``wide_blocks_per_sm``: the kernel has a
+    form with that many (smaller) blocks per SM, which the launcher takes for a grid that ``blocks_per_sm``
+    do not hold at once.  The constants are fitted to sweeps of the decode step over batch and context
+    (profiles/attn_decode_tma__decode_b8_ctx4096.md)."""
     span = min(max_kv_len, window) if window and window > 0 else max_kv_len
     tiles = max(1, -(-span // 16))
     sms = sm_count()
-    slots = sms * (blocks_per_sm or decode_blocks_per_sm(head_dim))
+    narrow = sms * (blocks_per_sm or decode_blocks_per_sm(head_dim))
     saturating = DECODE_SATURATING * sms
     pairs = max(1, num_seqs * num_kv_heads)
     best, best_cost = 1, None
@@ -672,10 +676,18 @@ def decode_splits(num_seqs: int, num_kv_heads: int, max_kv_len: int, window: int
         if s > 1 and tiles // s < 4:
             break
         per_block = -(-tiles // s)
-        full, rest = divmod(pairs * s, slots)
-        cost = full * max(per_block, slots * per_block / saturating) + DECODE_LATER_WAVE * (full - 1 if full else 0)
+        blocks = pairs * s
+        wide = wide_blocks_per_sm is not None and blocks > narrow
+        slots = sms * wide_blocks_per_sm if wide else narrow
+        full, rest = divmod(blocks, slots)
+        waves = full + (1 if rest else 0)
+        cost = full * max(per_block, slots * per_block / saturating) + DECODE_LATER_WAVE * (waves - 1)
         if rest:
-            cost += max(per_block, rest * per_block / saturating) + (DECODE_LATER_WAVE if full else 0)
+            cost += max(per_block, rest * per_block / saturating)
+        if wide:
+            cost += DECODE_WIDE_GRID
+            if waves == 1:
+                cost += DECODE_LONG_BLOCK[0] * max(0, per_block - DECODE_LONG_BLOCK[1])
         if best_cost is None or cost < best_cost - 1e-6:
             best, best_cost = s, cost
     return best
@@ -803,9 +815,9 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
     if num_decode > 0:
         tma = decode_kernel != "cp_async" and decode_tma_takes(D, k_pages.shape[2])
         if tma:
-            # The kernel is compiled for two and for three blocks per SM and takes the second variant for a
-            # grid of more than two blocks per SM; the split count reckons with three places per SM.
-            splits = decode_splits(num_decode, Hkv, max_kv_len, window, D, blocks_per_sm=3)
+            # The kernel is compiled for two, three and four blocks per SM (the last with fewer warps and
+            # stages per block) and takes the smallest form that holds the grid at once, the last for all larger grids.
+            splits = decode_splits(num_decode, Hkv, max_kv_len, window, D, blocks_per_sm=3, wide_blocks_per_sm=4)
         else:
             splits = decode_splits(num_decode, Hkv, max_kv_len, window, D)
         if partial is None or partial.numel() < num_decode * Hq * splits * (D + 2):

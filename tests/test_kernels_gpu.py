@@ -893,7 +893,7 @@ def test_attn_tc_flags_more_new_tokens_than_the_request_holds():
     assert int(st.item()) & 4
 
 
-@pytest.mark.parametrize("kernel", ["gemm_tc", "attn_tc", "attn_decode_tma"])
+@pytest.mark.parametrize("kernel", ["gemm_tc", "attn_tc", "attn_decode_tma", "attn_decode_tma_many"])
 def test_a_wait_that_runs_out_is_given_up_cleanly(kernel):
     """The bounded waits of the TMA / tcgen05 kernels, made to run out: the loader is told to leave out one
     copy, so the barrier that copy would complete never does.  With the poll limit made small the kernel must
@@ -914,8 +914,11 @@ def test_a_wait_that_runs_out_is_given_up_cleanly(kernel):
             close(out, x.double() @ w.double().t(), "bfloat16")
     else:
         hq, hkv, d, page_size = 4, 2, 128, 16
-        decode = kernel == "attn_decode_tma"
-        kv_lens, q_lens = ([300, 200], [1, 1]) if decode else ([300], [300])
+        decode = kernel.startswith("attn_decode_tma")
+        if kernel == "attn_decode_tma_many":  # more blocks than three per SM: the kernel's form for four per SM
+            kv_lens, q_lens = [40 + i % 30 for i in range(130)], [1] * 130
+        else:
+            kv_lens, q_lens = ([300, 200], [1, 1]) if decode else ([300], [300])
         q, k_list, v_list, tables, num_pages = attention_case("bfloat16", hq, hkv, d, page_size, kv_lens, q_lens, None)
         k_pages = dev(paged(k_list, page_size, tables, num_pages, torch.bfloat16))
         v_pages = dev(paged(v_list, page_size, tables, num_pages, torch.bfloat16))
