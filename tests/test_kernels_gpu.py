@@ -553,12 +553,16 @@ def test_attn_ref(dtype, case):
 @pytest.mark.parametrize("splits", [1, 3, 8])
 @pytest.mark.parametrize("window", [None, 70])
 @pytest.mark.parametrize("with_norm", [True, False])
-def test_decode_attention_from_the_raw_projection(d, page_size, hq, hkv, splits, window, with_norm):
+@pytest.mark.parametrize("many", [False, True])
+def test_decode_attention_from_the_raw_projection(d, page_size, hq, hkv, splits, window, with_norm, many):
     """A step of single tokens: the decode kernel norms and rotates its query and the new key itself and stores
     the new key and value, against qkv_post followed by the same kernel.  Lengths that put the new token at
-    the start, in the middle and at the end of a tile and of a page."""
+    the start, in the middle and at the end of a tile and of a page.  ``many``: seventy more sequences, so that
+    the grid has more blocks than three per SM hold and the kernel's form for four per SM runs."""
+    if many and ((d, hkv) != (128, 8) or not with_norm):
+        pytest.skip("the large grid is run at one shape")
     o = ops()
-    kv_lens = [200, 17, 161, 1, 16, 64, 65]
+    kv_lens = [200, 17, 161, 1, 16, 64, 65] + ([18 + (37 * i) % 190 for i in range(70)] if many else [])
     B, n_heads, eps = len(kv_lens), hq + 2 * hkv, 1e-5
     g = torch.Generator().manual_seed(41)
     q, k_list, v_list, tables, num_pages = attention_case("bfloat16", hq, hkv, d, page_size, kv_lens, [1] * B, window, seed=23)
