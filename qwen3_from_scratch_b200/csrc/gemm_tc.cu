@@ -85,11 +85,12 @@ struct QkvEpilogue {
 // Rows are TC_QKV_ROW_PAD bytes apart beyond their 2 D, which keeps pass 1's 16-byte writes (a thread per
 // row, the same column) off each other's banks.
 // `kv_off`: element offset of this lane's row in a page array (without the head), or -1.
-// `release`: the barrier that hands the accumulator back, arrived on once pass 1 has read it, or null.
+// `release`: the barrier that hands the accumulator back, arrived on once pass 1 has read it, as its address
+// in the cluster's shared window (the block's own address where there is no cluster), or 0.
 template <int D>
 __device__ __forceinline__ void qkv_head_rows(uint32_t tmem_head, unsigned char* mine, int row_base, int rows_here,
                                               int head, const QkvEpilogue& e, int lane, long long kv_off,
-                                              uint64_t* release) {
+                                              uint32_t release) {
   constexpr int LPH = D / 8, RPW = 32 / LPH, STRIDE = D * 2 + TC_QKV_ROW_PAD;
   constexpr int ITER = 32 / RPW, BATCH = ITER < 4 ? ITER : 4, NB = ITER / BATCH;
   const bool is_q = head < e.Hq, is_k = !is_q && head < e.Hq + e.Hkv;
@@ -139,7 +140,7 @@ __device__ __forceinline__ void qkv_head_rows(uint32_t tmem_head, unsigned char*
   if (release) {  // uniform over the warp
     tcgen05_fence_before();
     __syncwarp();
-    if (lane == 0) mbar_arrive(release);
+    if (lane == 0) mbar_arrive_cluster(release);
   }
   __syncwarp();
 
@@ -207,6 +208,50 @@ __device__ __forceinline__ void qkv_head_rows(uint32_t tmem_head, unsigned char*
     work(b + 1, cs[1]);
   }
   __syncwarp();
+}
+
+// The QKV epilogue of one accumulator of 128 rows x BN columns (whole heads of HD), by the block's EPI_WARPS
+// epilogue warps: two warps per quarter of the rows, each taking every second head of the tile.  The cache
+// position of the thread's own row is looked up once per tile.  The accumulator goes back to the issuing thread
+// (one arrival per warp on `release`, an address in the cluster's shared window) as soon as the warp's last head
+// has been read out of it, before that head's second pass.  `tmem_acc` is the accumulator at the warp's lanes,
+// `m0` the first row of these 128.
+template <int HD, int BN, int EPI_WARPS>
+__device__ __forceinline__ void qkv_tile_epilogue(uint32_t tmem_acc, unsigned char* head_stage, int warp, int lane,
+                                                  int m0, int n0, int M, int N, const QkvEpilogue& qkv,
+                                                  uint32_t release, int* status) {
+  constexpr int SLOTS = EPI_WARPS / 4;
+  const int quarter = warp & 3, row = m0 + quarter * 32 + lane;
+  const int ew = warp - 2, slot = ew >> 2;
+  unsigned char* mine = head_stage + ew * 32 * (HD * 2 + TC_QKV_ROW_PAD);
+  const int rows_here = max(0, min(32, M - (m0 + quarter * 32)));
+  long long kv_off = -1;
+  if (qkv.write_kv && lane < rows_here && n0 + BN > qkv.Hq * HD) {
+    const int pos = qkv.positions[row], seq = qkv.tok_seq[row];
+    if (pos < 0 || seq < 0) {
+      atomicOr(status, Q3_STATUS_BAD_POSITION);
+    } else {
+      const int page = table_page(qkv.block_table + (size_t)seq * qkv.table_stride, pos / qkv.page_size,
+                                  qkv.table_stride, status);
+      if (page < 0 || page >= qkv.num_pages)
+        atomicOr(status, Q3_STATUS_BAD_PAGE);
+      else
+        kv_off = ((long long)page * qkv.Hkv * qkv.page_size + (pos % qkv.page_size)) * HD;
+    }
+  }
+  bool released = false;
+#pragma unroll 1
+  for (int h0 = slot * HD; h0 < BN && n0 + h0 < N; h0 += SLOTS * HD) {  // uniform over the warp
+    const bool last = h0 + SLOTS * HD >= BN || n0 + h0 + SLOTS * HD >= N;
+    qkv_head_rows<HD>(tmem_acc + (uint32_t)h0, mine, m0 + quarter * 32, rows_here, (n0 + h0) / HD, qkv, lane, kv_off,
+                      last ? release : 0u);
+    released = released || last;
+  }
+  if (!released) {  // a warp without a head in the matrix's last tile
+    tcgen05_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive_cluster(release);
+  }
 }
 
 // Stores 32 consecutive columns of one row.  EPI 0: as they are.  EPI 1: SwiGLU on column blocks
@@ -417,40 +462,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int row = m0 + quarter * 32 + lane;
       const uint32_t tmem_acc = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
       if (EPI == 2) {
-        // Two warps per quarter; each takes every second head of the tile.  The cache position of the
-        // thread's own row is looked up once per tile.  The accumulator goes back to the issuing thread as
-        // soon as the warp's last head has been read out of it, before that head's second pass.
-        constexpr int SLOTS = TcThreads<EPI>::EPI_WARPS / 4;
-        const int ew = warp - 2, slot = ew >> 2;
-        unsigned char* mine = head_stage + ew * 32 * (HD * 2 + TC_QKV_ROW_PAD);
-        const int rows_here = min(32, M - (m0 + quarter * 32));
-        long long kv_off = -1;
-        if (qkv.write_kv && lane < rows_here && n0 + BN > qkv.Hq * HD) {
-          const int pos = qkv.positions[row], seq = qkv.tok_seq[row];
-          if (pos < 0 || seq < 0) {
-            atomicOr(status, Q3_STATUS_BAD_POSITION);
-          } else {
-            const int page = table_page(qkv.block_table + (size_t)seq * qkv.table_stride, pos / qkv.page_size,
-                                        qkv.table_stride, status);
-            if (page < 0 || page >= qkv.num_pages)
-              atomicOr(status, Q3_STATUS_BAD_PAGE);
-            else
-              kv_off = ((long long)page * qkv.Hkv * qkv.page_size + (pos % qkv.page_size)) * HD;
-          }
-        }
-        bool released = false;
-#pragma unroll 1
-        for (int h0 = slot * HD; h0 < BN && n0 + h0 < N; h0 += SLOTS * HD) {  // uniform over the warp
-          const bool last = h0 + SLOTS * HD >= BN || n0 + h0 + SLOTS * HD >= N;
-          qkv_head_rows<HD>(tmem_acc + (uint32_t)h0, mine, m0 + quarter * 32, rows_here, (n0 + h0) / HD, qkv, lane, kv_off,
-                            last ? &acc_empty[buf] : nullptr);
-          released = released || last;
-        }
-        if (!released) {  // a warp without a head in the matrix's last tile
-          tcgen05_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&acc_empty[buf]);
-        }
+        qkv_tile_epilogue<HD, BN, TcThreads<EPI>::EPI_WARPS>(tmem_acc, head_stage, warp, lane, m0, n0, M, N, qkv,
+                                                             s_addr(&acc_empty[buf]), status);
       } else {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -472,6 +485,261 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(S::TMEM_COLS) : "memory");
   }
+}
+
+// ---------------------------------------------------------------- the same product by pairs of CTAs
+// Two CTAs of a cluster work on one 256 x 256 tile with the paired instruction (cta_group::2, M = 256): the
+// CTA of rank r holds rows 128 r .. 128 r + 127 of the A tile and of the W tile in its own shared memory and
+// rows 128 r .. of the accumulator (all 256 columns) in its own tensor memory.  An instruction of k = 16 then
+// reads 8 KB of operands per SM where the single CTA's 128 x 256 tile reads 12 KB, which with TMA writing as
+// much was more than shared memory gives per clock; a stage is 32 KB per CTA.
+//   warp 0 (one thread, both CTAs)  waits on its own CTA's `empty`, brings its halves in; every copy of
+//                                   the pair is counted by rank 0's `full` barrier (rank 0 expects the bytes of both);
+//   warp 1 (one thread, rank 0)     waits on `full`, issues for the pair, and commits with one arrival on
+//                                   `empty` / `acc_full` in both CTAs;
+//   warps 2..5 (both CTAs)          read their own CTA's accumulator rows, store, and arrive on rank 0's
+//                                   `acc_empty` (eight arrivals hand an accumulator back).
+// Every wait is bounded as above; a role that gives up raises the abort flag of both CTAs.  Both CTAs meet at a
+// cluster barrier before the first copy (a barrier must be initialised before the other CTA's copy counts on
+// it) and before they free tensor memory and return (no arrival or operand read may find a CTA gone).
+template <int EPI = 0>
+struct TcPairShape {
+  static constexpr int BN = 256;
+  static constexpr int A_BYTES = TC_BM * TC_BK * 2;        // this CTA's 128 rows of A
+  static constexpr int B_BYTES = (BN / 2) * TC_BK * 2;     // this CTA's 128 rows of W
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;    // 32 KB
+  static constexpr int EPI_BYTES = EPI == 2 ? TC_HEAD_STAGE_BYTES : 0;
+  static constexpr int STAGES = EPI == 2 ? 4 : 7;          // beside the QKV epilogue's 68 KB, four
+  static constexpr int BAR_BYTES = 256;
+  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + BAR_BYTES + EPI_BYTES + 1024;
+  static constexpr uint32_t TMEM_COLS = 2 * BN;
+  static constexpr int THREADS = TcThreads<EPI>::THREADS;
+};
+
+template <int EPI, typename OutT, int HD = 128>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TcPairShape<EPI>::THREADS)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    OutT* __restrict__ C, int M, int N, int K, int ldc, const __grid_constant__ QkvEpilogue qkv,
+                    int* status) {
+  using S = TcPairShape<EPI>;
+  constexpr int BN = S::BN;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* tiles = base;
+  uint64_t* full = reinterpret_cast<uint64_t*>(base + (size_t)S::STAGES * S::STAGE_BYTES);  // used in rank 0
+  uint64_t* empty = full + S::STAGES;
+  uint64_t* acc_full = empty + S::STAGES;  // [2]
+  uint64_t* acc_empty = acc_full + 2;      // [2], used in rank 0
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  unsigned char* head_stage = base + (size_t)S::STAGES * S::STAGE_BYTES + S::BAR_BYTES;  // EPI 2 only
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int k_tiles = (K + TC_BK - 1) / TC_BK;
+  const int m_tiles = (M + 2 * TC_BM - 1) / (2 * TC_BM), n_tiles = (N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  auto give_up = [&]() {  // one thread
+    abort_flag = 1;
+    st_cluster_u32(cluster_addr(s_addr(&abort_flag), rank ^ 1u), 1u);
+    atomicOr(status, Q3_STATUS_TIMEOUT);
+  };
+
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_map(&map_a);
+    tma_prefetch_map(&map_b);
+  }
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    *tmem_holder = 0;
+    for (int s = 0; s < S::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 2 * TcThreads<EPI>::EPI_WARPS);  // the epilogue warps of both CTAs
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  cluster_sync_all();
+  int ahead = 0;  // thread 0 (the loader): how many of its first (tile, k tile) pairs have their W tile under way
+  if (threadIdx.x == 0) {
+    // as in the kernel above: the W tiles of the ring's first round go out before the wait
+    for (int tile = pair; tile < num_tiles && ahead < S::STAGES; tile += pairs) {
+      const int n0 = (tile / m_tiles) * BN + (int)rank * (BN / 2);
+      for (int kt = 0; kt < k_tiles && ahead < S::STAGES; ++kt, ++ahead) {
+        if (rank == 0) mbar_expect_tx(&full[ahead], 2 * S::STAGE_BYTES);
+        tma_load_2d_pair(tiles + (size_t)ahead * S::STAGE_BYTES + S::A_BYTES, &map_b,
+                         cluster_addr(s_addr(&full[ahead]), 0), kt * TC_BK, n0);
+      }
+    }
+  }
+  pdl_wait();  // the activations come from the kernel before this one
+  pdl_launch_dependents();
+  // Tensor memory is taken only after the wait (see above); the same warp of both CTAs asks, for the pair.
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_holder)),
+                 "r"(S::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- loader
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += pairs) {
+        const int m0 = (tile % m_tiles) * 2 * TC_BM + (int)rank * TC_BM;
+        const int n0 = (tile / m_tiles) * BN + (int)rank * (BN / 2);
+        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+          const int s = it % S::STAGES;
+          const uint32_t use = it / S::STAGES;
+          unsigned char* a_s = tiles + (size_t)s * S::STAGE_BYTES;
+          const uint32_t pair_full = cluster_addr(s_addr(&full[s]), 0);
+          if ((int)it >= ahead) {
+            if (use > 0 && !mbar_wait(&empty[s], (use & 1) ^ 1, &abort_flag)) {
+              give_up();
+              ok = false;
+              break;
+            }
+            if (rank == 0) mbar_expect_tx(&full[s], 2 * S::STAGE_BYTES);
+            tma_load_2d_pair(a_s + S::A_BYTES, &map_b, pair_full, kt * TC_BK, n0);
+          }
+          if ((int)it == tc_drop_copy && rank == 0) continue;  // tests of the give-up path only (see tc_common.cuh)
+          tma_load_2d_pair(a_s, &map_a, pair_full, kt * TC_BK, m0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      // ---- tensor-core issue, for the pair
+      constexpr uint32_t idesc = umma_idesc_pair(BN);
+      uint32_t it = 0, t = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += pairs, ++t) {
+        const uint32_t buf = t & 1;
+        if (t >= 2 && !mbar_wait_cluster(&acc_empty[buf], ((t >> 1) & 1) ^ 1, &abort_flag)) {
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t tmem_acc = tmem_base + buf * BN;
+        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+          const int s = it % S::STAGES;
+          const uint32_t use = it / S::STAGES;
+          if (!mbar_wait_cluster(&full[s], use & 1, &abort_flag)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const unsigned char* a_s = tiles + (size_t)s * S::STAGE_BYTES;
+          const uint64_t a_desc = umma_desc_sw128(a_s), b_desc = umma_desc_sw128(a_s + S::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; ++k)
+            umma_f16_pair(tmem_acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kt | k) != 0);
+          umma_commit_pair(&empty[s]);
+        }
+        if (ok) umma_commit_pair(&acc_full[buf]);
+      }
+      if (!ok) give_up();
+    }
+  } else {
+    // ---- epilogue: this CTA's 128 rows of the tile
+    const int quarter = warp & 3;
+    uint32_t t = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += pairs, ++t) {
+      const int m0 = (tile % m_tiles) * 2 * TC_BM + (int)rank * TC_BM, n0 = (tile / m_tiles) * BN;
+      const uint32_t buf = t & 1;
+      const bool ready = mbar_wait(&acc_full[buf], (t >> 1) & 1, &abort_flag);
+      if (!__all_sync(0xffffffffu, ready)) {
+        if (lane == 0) give_up();
+        ok = false;
+        break;
+      }
+      tcgen05_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t tmem_acc = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+      const uint32_t release = cluster_addr(s_addr(&acc_empty[buf]), 0);
+      if (EPI == 2) {
+        qkv_tile_epilogue<HD, BN, TcThreads<EPI>::EPI_WARPS>(tmem_acc, head_stage, warp, lane, m0, n0, M, N, qkv, release,
+                                                             status);
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (n0 + c0 >= N) break;  // uniform over the warp
+          uint32_t v[32];
+          tmem_ld_32(tmem_acc + (uint32_t)c0, v);
+          tmem_wait_ld();
+          if (row < M) tc_store_chunk<EPI == 2 ? 0 : EPI, OutT>(v, C, row, n0 + c0, N, ldc);
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(release);
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(S::TMEM_COLS) : "memory");
+  }
+}
+
+// How many pairs of CTAs the device runs at a time (a cluster's two CTAs need SMs of one group).
+template <int EPI, typename OutT, int HD>
+static int tc_pair_slots() {
+  static int slots[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (slots[dev] == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * sm_count());
+    cfg.blockDim = dim3(TcPairShape<EPI>::THREADS);
+    cfg.dynamicSmemBytes = TcPairShape<EPI>::SMEM_BYTES;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<EPI, OutT, HD>, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = sm_count() / 2;
+    }
+    slots[dev] = n < sm_count() / 2 ? n : sm_count() / 2;
+  }
+  return slots[dev];
+}
+
+template <int EPI, typename OutT, int HD = 128>
+static int gemm_tc_pair_launch(const void* A, const void* W, void* C, int M, int N, int K, int ldc, int* status,
+                               cudaStream_t stream, const QkvEpilogue& qkv = QkvEpilogue{}) {
+  using S = TcPairShape<EPI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI, OutT, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)S::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  CUtensorMap map_a, map_b;
+  int code = cached_map(&map_a, A, (uint64_t)M, (uint64_t)K, TC_BM);
+  if (code) return code;
+  code = cached_map(&map_b, W, (uint64_t)N, (uint64_t)K, S::BN / 2);
+  if (code) return code;
+  const long long tiles = (long long)((N + S::BN - 1) / S::BN) * ((M + 2 * TC_BM - 1) / (2 * TC_BM));
+  if (tiles > 0x3fffffffLL) return Q3_ERR_SIZE;
+  const int slots = tc_pair_slots<EPI, OutT, HD>();
+  if (slots <= 0) return Q3_ERR_DRIVER;
+  const int pairs = (int)(tiles < slots ? tiles : slots);
+  q3::launch(gemm_tc_pair_kernel<EPI, OutT, HD>, dim3(2 * pairs), dim3(S::THREADS), S::SMEM_BYTES, stream, map_a, map_b,
+             (OutT*)C, M, N, K, ldc, qkv, status);
+  return launch_status();
 }
 
 template <int BN, int EPI, typename OutT, int HD = 128>
@@ -530,6 +798,19 @@ extern "C" int q3_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
   return q3::gemm_tc_dispatch<0, bf16>(A, W, C, M, N, K, ldc, status, stream);
 }
 
+// The same product by pairs of CTAs on 256 x 256 tiles (the paired tensor-core instruction); arguments and
+// limits as q3_gemm_tc.
+extern "C" int q3_gemm_tc_pair(const void* A, const void* W, void* C, int M, int N, int K, int ldc, int out_f32,
+                               int swiglu, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 || (swiglu && (N % 16 || out_f32))) return Q3_ERR_SIZE;
+  if ((uintptr_t)A % 16 || (uintptr_t)W % 16) return Q3_ERR_ALIGN;
+  using bf16 = __nv_bfloat16;
+  if (swiglu) return q3::gemm_tc_pair_launch<1, bf16>(A, W, C, M, N, K, ldc, status, stream);
+  if (out_f32) return q3::gemm_tc_pair_launch<0, float>(A, W, C, M, N, K, ldc, status, stream);
+  return q3::gemm_tc_pair_launch<0, bf16>(A, W, C, M, N, K, ldc, status, stream);
+}
+
 // For the tests of the give-up path: see set_wait_test in tc_common.cuh.
 extern "C" int q3_gemm_tc_wait_test(unsigned limit, int drop) { return q3::set_wait_test(limit, drop); }
 
@@ -537,12 +818,12 @@ extern "C" int q3_gemm_tc_wait_test(unsigned limit, int drop) { return q3::set_w
 // qkv = A[T, K] * W[(Hq + 2 Hkv) D, K]^T is rounded to bfloat16 and, head by head, normed, rotated and
 // written to q_out / the cache pages; it is never stored itself.  Arguments as q3_qkv_post, with A and W
 // as q3_gemm_tc.  Takes bfloat16, D = 64 or 128 and a whole rotation (cos_sin from q3_rope_table) or
-// none; refuses the rest.
+// none; refuses the rest.  pair: by pairs of CTAs (the paired instruction) instead of single CTAs.
 extern "C" int q3_gemm_tc_qkv(const void* A, const void* W, int T, int K, int Hq, int Hkv, int D, const float* q_weight,
                               const float* k_weight, float eps, const float* cos_sin, const int* positions,
                               const int* tok_seq, const int* block_table, int table_stride, int page_size,
-                              void* k_pages, void* v_pages, int num_pages, void* q_out, int write_kv, int* status,
-                              cudaStream_t stream) {
+                              void* k_pages, void* v_pages, int num_pages, void* q_out, int write_kv, int pair,
+                              int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (K <= 0 || K % 8 || (D != 64 && D != 128) || Hq < 0 || Hkv < 0 || page_size <= 0 || table_stride <= 0)
     return Q3_ERR_SIZE;
@@ -568,6 +849,10 @@ extern "C" int q3_gemm_tc_qkv(const void* A, const void* W, int T, int K, int Hq
   e.write_kv = write_kv;
   const int N = (Hq + 2 * Hkv) * D;
   using bf16 = __nv_bfloat16;
+  if (pair) {  // pairs of CTAs on tiles of 256 rows x 256 columns
+    if (D == 128) return q3::gemm_tc_pair_launch<2, bf16, 128>(A, W, nullptr, T, N, K, 0, status, stream, e);
+    return q3::gemm_tc_pair_launch<2, bf16, 64>(A, W, nullptr, T, N, K, 0, status, stream, e);
+  }
   // tiles of 256 columns (two heads of 128) or of 128 (one): whichever needs fewer rounds of the SMs
   if (D == 128) {
     if (q3::tc_pick_bn(T, N) == 256) return q3::gemm_tc_launch<256, 2, bf16, 128>(A, W, nullptr, T, N, K, 0, status, stream, e);

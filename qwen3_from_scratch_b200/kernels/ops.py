@@ -72,9 +72,11 @@ _SIGNATURES = {
     "q3_swiglu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "q3_gemm_tc": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                    _c_void_p],
+    "q3_gemm_tc_pair": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                        _c_void_p],
     "q3_gemm_tc_qkv": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
                        _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
-                       _c_void_p, _c_int, _c_void_p, _c_void_p],
+                       _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
     "q3_gemm_skinny": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "q3_gemm_skinny_fused": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                              _c_int, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
@@ -528,18 +530,25 @@ def gemm_tc_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
     return x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.shape[1] % 8 == 0
 
 
-def gemm_tc_swiglu_pays(rows: int, weight: torch.Tensor) -> bool:
-    """Whether the gate/up product with SwiGLU in its epilogue is the faster way for a prompt portion.
-    It saves the gate kernel's pass over the [rows, 2 I] product, which weighs the more the shorter the
-    reduction is; against that its single-CTA tiles run below the library's rate when the reduction
-    is long or the rows are many (measured: profiles/gemm_tc_swiglu__prefill_2048.md)."""
-    return 128 <= rows < 3072 and weight.shape[1] <= 1536
+def gemm_tc_swiglu_pays(rows: int, weight: torch.Tensor) -> Optional[str]:
+    """Which of the engine's tcgen05 gate/up products with SwiGLU in the epilogue is the faster way for a
+    prompt portion: "pair" (pairs of CTAs on 256 x 256 tiles), "single" (one CTA on 128 x 256) or None (the
+    library's product followed by the gate kernel).  The fused forms save the gate kernel's pass over the
+    [rows, 2 I] product.  The pair form runs at the library's rate and wins from 1,024 rows at every width and
+    from 512 where the reduction is long; the single-CTA form falls behind the library when the reduction is
+    long or the rows are many, and is kept for the short portions of a narrow model
+    (measured: profiles/gemm_tc_swiglu__prefill_2048.md)."""
+    narrow = weight.shape[1] <= 1536
+    if rows >= 1024 or (rows >= 512 and not narrow):
+        return "pair"
+    return "single" if narrow and rows >= 128 else None
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
-            swiglu_blocks: bool = False) -> None:
+            swiglu_blocks: bool = False, pair: bool = False) -> None:
     """out[M, N] = x[M, K] @ w[N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in TMEM).
-    ``swiglu_blocks``: w's rows alternate gate/up in blocks of eight and out is [M, N / 2]."""
+    ``swiglu_blocks``: w's rows alternate gate/up in blocks of eight and out is [M, N / 2].
+    ``pair``: by pairs of CTAs on 256 x 256 tiles (the paired instruction) instead of single CTAs."""
     _check("gemm_tc.x", x, torch.bfloat16)
     _check("gemm_tc.w", w, torch.bfloat16)
     _check("gemm_tc.out", out)
@@ -548,10 +557,10 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.T
     want_cols = N // 2 if swiglu_blocks else N
     if w.shape[1] != K or tuple(out.shape) != (M, want_cols) or out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError(f"gemm_tc: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
-    code = library().q3_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, want_cols,
-                                1 if out.dtype == torch.float32 else 0, 1 if swiglu_blocks else 0,
-                                status.data_ptr(), _stream())
-    _done("gemm_tc", code, f"M {M} N {N} K {K}")
+    entry = library().q3_gemm_tc_pair if pair else library().q3_gemm_tc
+    code = entry(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, want_cols,
+                 1 if out.dtype == torch.float32 else 0, 1 if swiglu_blocks else 0, status.data_ptr(), _stream())
+    _done("gemm_tc", code, f"M {M} N {N} K {K}{' pair' if pair else ''}")
 
 
 # ------------------------------------------------------------------ fast bfloat16 attention
@@ -576,10 +585,11 @@ def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages: 
                 q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                 cos_sin: Optional[torch.Tensor], positions: torch.Tensor, tok_seq: torch.Tensor,
                 block_table: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int, write_kv: bool,
-                status: torch.Tensor) -> None:
+                status: torch.Tensor, pair: bool = False) -> None:
     """x[T, K] @ w[(Hq + 2 Hkv) D, K]^T on the tensor cores with ``qkv_post`` as the epilogue: the
     projection is rounded to bfloat16, normed and rotated head by head and written to ``q_out`` and the
-    cache pages; it is never stored itself (``gemm_tc_qkv_pays`` says where the attention part takes it)."""
+    cache pages; it is never stored itself (``gemm_tc_qkv_pays`` says where the attention part takes it).
+    ``pair``: by pairs of CTAs on tiles of 256 rows (the paired instruction) instead of single CTAs."""
     for name, t in (("x", x), ("w", w), ("q_out", q_out), ("k_pages", k_pages), ("v_pages", v_pages)):
         _check(f"gemm_tc_qkv.{name}", t, torch.bfloat16)
     for name, t in (("positions", positions), ("tok_seq", tok_seq), ("block_table", block_table)):
@@ -605,8 +615,8 @@ def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages: 
         x.data_ptr(), w.data_ptr(), T, K, num_q_heads, num_kv_heads, head_dim, _ptr(q_weight), _ptr(k_weight),
         float(eps), _ptr(cos_sin), positions.data_ptr(), tok_seq.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], page_size, k_pages.data_ptr(), v_pages.data_ptr(), num_pages, q_out.data_ptr(),
-        1 if write_kv else 0, status.data_ptr(), _stream())
-    _done("gemm_tc_qkv", code, f"T {T} K {K} heads {num_q_heads}/{num_kv_heads} x {head_dim}")
+        1 if write_kv else 0, 1 if pair else 0, status.data_ptr(), _stream())
+    _done("gemm_tc_qkv", code, f"T {T} K {K} heads {num_q_heads}/{num_kv_heads} x {head_dim}{' pair' if pair else ''}")
 
 
 def fast_attention_takes(dtype: torch.dtype, num_q_heads: int, num_kv_heads: int, head_dim: int) -> bool:

@@ -64,9 +64,10 @@ class SwiGLU(FeedForward):
             ops.gemm_skinny(x, self.gate_up.weight, act, swiglu_blocks=True)
         elif (self.blocks_of_eight and ops.gemm_tc_swiglu_pays(rows, self.gate_up.weight)
               and ops.gemm_tc_takes(x, self.gate_up.weight)):
-            # prompt portions of a model that is not wide: the engine's tcgen05 product with the activation
-            # in its epilogue, so the [T, 2I] gate/up product never goes to memory
-            ops.gemm_tc(x, self.gate_up.weight, act, self.rt.status, swiglu_blocks=True)
+            # prompt portions: the engine's tcgen05 product with the activation in its epilogue, so the
+            # [T, 2I] gate/up product never goes to memory
+            ops.gemm_tc(x, self.gate_up.weight, act, self.rt.status, swiglu_blocks=True,
+                        pair=ops.gemm_tc_swiglu_pays(rows, self.gate_up.weight) == "pair")
         else:
             ops.swiglu(self.gate_up(x), act, interleave8=self.blocks_of_eight)
         if into_stream is not None:

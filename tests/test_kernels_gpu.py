@@ -283,23 +283,26 @@ def test_gemm_skinny_normed(shape, with_swiglu):
 @pytest.mark.parametrize("shape", [(128, 128, 64), (2048, 4096, 1024), (100, 200, 72), (257, 331, 96), (1, 64, 8),
                                    (300, 1024, 3072)])
 @pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
-def test_gemm_tc(shape, out_dtype):
-    """The tcgen05 / TMA product at sizes that do and do not fill its 128 x 128 x 64 tiles."""
+@pytest.mark.parametrize("pair", [False, True])
+def test_gemm_tc(shape, out_dtype, pair):
+    """The tcgen05 / TMA product at sizes that do and do not fill its tiles, by single CTAs (128 x 128 or 256
+    x 64) and by pairs of CTAs with the paired instruction (256 x 256 x 64)."""
     M, N, K = shape
     g = torch.Generator().manual_seed(10)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16)
     w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
     out = torch.full((M, N), float("nan"), device="cuda", dtype=DT[out_dtype])
     st = status()
-    ops().gemm_tc(dev(x), dev(w), out, st)
+    ops().gemm_tc(dev(x), dev(w), out, st, pair=pair)
     assert int(st.item()) == 0
     want = x.double() @ w.double().t()
     close(out, want, out_dtype, scale=float(want.abs().max()),
           tol=f32_accumulation_tol(K) if out_dtype == "float32" else None)
 
 
-@pytest.mark.parametrize("shape", [(128, 3072, 1024), (300, 136, 96), (2048, 200, 80)])
-def test_gemm_tc_with_swiglu(shape):
+@pytest.mark.parametrize("shape", [(128, 3072, 1024), (300, 136, 96), (2048, 200, 80), (1300, 1000, 2048)])
+@pytest.mark.parametrize("pair", [False, True])
+def test_gemm_tc_with_swiglu(shape, pair):
     T, inter, K = shape
     g = torch.Generator().manual_seed(11)
     x = torch.randn(T, K, generator=g).to(torch.bfloat16)
@@ -308,7 +311,7 @@ def test_gemm_tc_with_swiglu(shape):
     w = torch.cat([gate.view(inter // 8, 8, K), up.view(inter // 8, 8, K)], dim=1).reshape(2 * inter, K).contiguous()
     out = torch.full((T, inter), float("nan"), device="cuda", dtype=torch.bfloat16)
     st = status()
-    ops().gemm_tc(dev(x), dev(w), out, st, swiglu_blocks=True)
+    ops().gemm_tc(dev(x), dev(w), out, st, swiglu_blocks=True, pair=pair)
     assert int(st.item()) == 0
     gv, uv = x.double() @ gate.double().t(), x.double() @ up.double().t()
     close(out, uv * gv * torch.sigmoid(gv), "bfloat16")
@@ -406,9 +409,10 @@ def test_qkv_post(dtype, hq, hkv, d, rot, with_table):
 
 
 @pytest.mark.parametrize("rotate", [True, False])
+@pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("hq,hkv,d,K,T", [(8, 2, 128, 256, 200), (5, 2, 128, 96, 130), (3, 1, 64, 136, 333),
                                           (16, 8, 128, 1024, 256), (16, 8, 128, 512, 1100), (6, 1, 64, 72, 2500)])
-def test_gemm_tc_qkv(hq, hkv, d, K, T, rotate):
+def test_gemm_tc_qkv(hq, hkv, d, K, T, rotate, pair):
     """The QKV projection with head norm, rotation and cache write in its epilogue against the plain
     formulas applied to the projection rounded to bfloat16; rows and heads that do not fill a tile."""
     g = torch.Generator().manual_seed(13)
@@ -432,7 +436,7 @@ def test_gemm_tc_qkv(hq, hkv, d, K, T, rotate):
         ops().rope_table(dev(inv_freq), dev(positions), cos_sin)
     assert ops().gemm_tc_qkv_takes(T, dev(x), dev(w), d, d if rotate else 0)
     ops().gemm_tc_qkv(dev(x), dev(w), q_out, k_pages, v_pages, dev(qw), dev(kw), eps, cos_sin, dev(positions),
-                      dev(tok_seq), dev(table_tensor(tables)), hq, hkv, d, True, st)
+                      dev(tok_seq), dev(table_tensor(tables)), hq, hkv, d, True, st, pair=pair)
     assert int(st.item()) == 0
     qkv = (x.double() @ w.double().t()).to(torch.bfloat16).double().view(T, hq + 2 * hkv, d)
     q, k, v = qkv[:, :hq], qkv[:, hq:hq + hkv], qkv[:, hq + hkv:]
@@ -457,7 +461,8 @@ def test_gemm_tc_qkv(hq, hkv, d, K, T, rotate):
     assert float(kp.abs().sum(dim=(1, 3))[~written].sum()) == 0.0
 
 
-def test_gemm_tc_qkv_without_head_norm_and_without_a_cache_write():
+@pytest.mark.parametrize("pair", [False, True])
+def test_gemm_tc_qkv_without_head_norm_and_without_a_cache_write(pair):
     """The same epilogue for a layer without head norms that reads a cache another layer wrote: only q is
     produced (rotated), the pages stay as they are; and a page id outside the pool is reported, not written."""
     g = torch.Generator().manual_seed(14)
@@ -475,7 +480,7 @@ def test_gemm_tc_qkv_without_head_norm_and_without_a_cache_write():
     ops().rope_table(dev(inv_freq), dev(positions), cos_sin)
     st = status()
     ops().gemm_tc_qkv(dev(x), dev(w), q_out, k_pages, v_pages, None, None, 0.0, cos_sin, dev(positions), dev(tok_seq),
-                      dev(table_tensor(tables)), hq, hkv, d, False, st)
+                      dev(table_tensor(tables)), hq, hkv, d, False, st, pair=pair)
     assert int(st.item()) == 0
     q = (x.double() @ w.double().t()).to(torch.bfloat16).double().view(T, hq + 2 * hkv, d)[:, :hq]
     ang = positions.double()[:, None] * inv_freq.double()[None, :]
@@ -484,7 +489,7 @@ def test_gemm_tc_qkv_without_head_norm_and_without_a_cache_write():
     bad = table_tensor(tables)
     bad[0, 2] = num_pages
     ops().gemm_tc_qkv(dev(x), dev(w), q_out, k_pages, v_pages, None, None, 0.0, cos_sin, dev(positions), dev(tok_seq),
-                      dev(bad), hq, hkv, d, True, st)
+                      dev(bad), hq, hkv, d, True, st, pair=pair)
     assert int(st.item()) & 2
     hit = [p for p in range(num_pages) if p != tables[0][2] and p in tables[0]]
     assert bool((k_pages[tables[0][2]] == 3.0).all()), "the rows of the bad page went somewhere"
@@ -897,7 +902,7 @@ def test_attn_tc_flags_more_new_tokens_than_the_request_holds():
     assert int(st.item()) & 4
 
 
-@pytest.mark.parametrize("kernel", ["gemm_tc", "attn_tc", "attn_decode_tma", "attn_decode_tma_many"])
+@pytest.mark.parametrize("kernel", ["gemm_tc", "gemm_tc_pair", "attn_tc", "attn_decode_tma", "attn_decode_tma_many"])
 def test_a_wait_that_runs_out_is_given_up_cleanly(kernel):
     """The bounded waits of the TMA / tcgen05 kernels, made to run out: the loader is told to leave out one
     copy, so the barrier that copy would complete never does.  With the poll limit made small the kernel must
@@ -906,13 +911,13 @@ def test_a_wait_that_runs_out_is_given_up_cleanly(kernel):
     result.  No wait anywhere spins without a limit; nothing here faults."""
     o = ops()
     g = torch.Generator().manual_seed(77)
-    if kernel == "gemm_tc":
+    if kernel.startswith("gemm_tc"):  # "gemm_tc_pair": both CTAs of a pair must give up, meet and free the pair's TMEM
         x = dev(torch.randn(256, 256, generator=g).to(torch.bfloat16))
         w = dev(torch.randn(384, 256, generator=g).to(torch.bfloat16))
         out = torch.zeros(256, 384, device="cuda", dtype=torch.bfloat16)
 
         def run(st):
-            o.gemm_tc(x, w, out, st)
+            o.gemm_tc(x, w, out, st, pair=kernel == "gemm_tc_pair")
 
         def check():
             close(out, x.double() @ w.double().t(), "bfloat16")
