@@ -573,12 +573,16 @@ def gemm_tc_qkv_takes(rows: int, x: torch.Tensor, weight: torch.Tensor, head_dim
     return (rows >= 128 and gemm_tc_takes(x, weight) and head_dim in (64, 128) and rotary_dim in (0, head_dim))
 
 
-def gemm_tc_qkv_pays(rows: int, weight: torch.Tensor) -> bool:
-    """Whether the projection with ``qkv_post`` as its epilogue is the faster way for a prompt portion.  It
-    saves ``qkv_post``'s pass over the projection and a launch; against that a launch of it costs about 13 us
-    whatever its size, and its single-CTA tiles run below the library's rate when the reduction is long or the
-    rows are many (measured inside the step: profiles/gemm_tc_qkv__prefill_2048.md)."""
-    return 768 <= rows < 3072 and weight.shape[1] <= 1536
+def gemm_tc_qkv_pays(rows: int, weight: torch.Tensor) -> Optional[str]:
+    """Which projection with ``qkv_post`` as its epilogue is the faster way for a prompt portion: "pair"
+    (pairs of CTAs on tiles of 256 rows), "single" (one CTA per tile) or None (the library's product, then
+    ``qkv_post``).  The fused forms save ``qkv_post``'s pass over the projection and a launch; against that a
+    launch costs about 13 us whatever its size, so short portions stay with the library, and where the
+    reduction is long the whole step showed no gain over the library's product (measured inside the step:
+    profiles/gemm_tc_qkv__prefill_2048.md)."""
+    if weight.shape[1] > 1536 or rows < 768:
+        return None
+    return "pair" if rows >= 1024 else "single"
 
 
 def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,

@@ -115,7 +115,8 @@ class GQAAttention(Mixer):
             # a prompt portion: the projection's own epilogue norms, rotates and writes the pages
             cos_sin = self.position.step_table(ctx) if fused is not None else None
             ops.gemm_tc_qkv(x, self.qkv.weight, q, k_pages, v_pages, self.q_norm_weight, self.k_norm_weight, eps,
-                            cos_sin, ctx.positions, ctx.tok_seq, table, hq, hkv, d, write_cache, self.rt.status)
+                            cos_sin, ctx.positions, ctx.tok_seq, table, hq, hkv, d, write_cache, self.rt.status,
+                            pair=ops.gemm_tc_qkv_pays(T, self.qkv.weight) == "pair")
             self.attend(q, k_pages, v_pages, table, ctx, out)
             if into_stream is not None:
                 return self.o_proj.into_stream(out.view(T, hq * d), into_stream, next_norm_weight)

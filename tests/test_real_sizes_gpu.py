@@ -31,7 +31,7 @@ SIZES = {
     "32b": dict(hidden_size=5120, num_attention_heads=64, num_key_value_heads=8, intermediate_size=25600,
                 vocab_size=4999, tie_word_embeddings=False),
 }
-LONG = 330  # (and one of 900, run whole only)
+LONG = 330  # (and two of 800 and 1,024, run whole only)
 SHORT = [24 + 2 * i for i in range(16)]  # sixteen short requests, 24 to 54 tokens
 
 
@@ -81,7 +81,10 @@ def sequences(size):
     for i, n in enumerate(SHORT):
         seqs[f"s{i}"] = random_tokens(vocab, n, 600 + i)
     seqs["late"] = random_tokens(vocab, 70, 700)
-    seqs["longer"] = random_tokens(vocab, 900, 800)  # enough rows for the QKV product that norms, rotates and writes the pages
+    # enough rows for the products that have the work of the kernel after them in their epilogue (QKV with head norm,
+    # rotation and page write; gate/up with SwiGLU): by single CTAs at 800 rows, by pairs of CTAs at 1,024
+    seqs["longer"] = random_tokens(vocab, 800, 800)
+    seqs["longest"] = random_tokens(vocab, 1024, 801)
     return seqs
 
 
