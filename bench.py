@@ -674,6 +674,75 @@ def profile(args):
     return 0
 
 
+def profile_products(args):
+    """``--profile products``: the engine's tcgen05 product (single CTAs and pairs of CTAs) against the
+    library's, stand-alone, on the projections of a prompt portion at four reduction lengths: the plain
+    product, and gate/up with SwiGLU in the epilogue against the library's product followed by the gate
+    kernel.  Each way is recorded as a CUDA graph of 10 launches; the ways are replayed in turn three
+    times and the best time of each counts (under the power cap a long run of one way slows the next)."""
+    import torch
+
+    from qwen3_from_scratch_b200.kernels import ops
+    dev = "cuda:0"
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    reps = 10
+
+    def recorded(fn):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        graph, stream = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            fn()
+            graph.capture_begin()
+            for _ in range(reps):
+                fn()
+            graph.capture_end()
+        torch.cuda.synchronize()
+        return graph
+
+    def best_us(fns):
+        graphs = [recorded(fn) for fn in fns]
+        best = [float("inf")] * len(fns)
+        for _ in range(3):
+            for i, graph in enumerate(graphs):
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record()
+                graph.replay()
+                t1.record()
+                torch.cuda.synchronize()
+                best[i] = min(best[i], t0.elapsed_time(t1) * 1e3 / reps)
+        return best
+
+    # (reduction K, 2 x intermediate, QKV width, name): the sizes of Qwen3-0.6B, 1.7B, 8B and 32B
+    sizes = [(1024, 6144, 4096, "0.6B"), (2048, 12288, 4096, "1.7B"), (4096, 24576, 6144, "8B"),
+             (5120, 51200, 10240, "32B")]
+    if args.only_size:  # a short run for a profiler: one size, one number of rows
+        sizes = [s for s in sizes if s[3].lower() == args.only_size.lower()]
+    print("us: single CTAs / pairs of CTAs / library   (TFLOP/s of the pair form)")
+    for K, two_i, qkv_n, name in sizes:
+        for rows in ((args.only_rows,) if args.only_rows else (512, 2048, 4096)):
+            x = torch.randn(rows, K, device=dev).to(torch.bfloat16)
+            for what, N, swiglu in (("qkv", qkv_n, False), ("gate/up + SwiGLU", two_i, True)):
+                w = (torch.randn(N, K, device=dev) * 0.1).to(torch.bfloat16)
+                out = torch.empty(rows, N // 2 if swiglu else N, device=dev, dtype=torch.bfloat16)
+                full = torch.empty(rows, N, device=dev, dtype=torch.bfloat16)
+
+                def library():
+                    torch.mm(x, w.t(), out=full)
+                    if swiglu:
+                        ops.swiglu(full, out, interleave8=True)
+
+                single, pair, lib = best_us([
+                    lambda: ops.gemm_tc(x, w, out, status, swiglu_blocks=swiglu),
+                    lambda: ops.gemm_tc(x, w, out, status, swiglu_blocks=swiglu, pair=True), library])
+                print(f"  {name:5s} K {K:5d} rows {rows:5d} {what:17s} N {N:6d}: {single:8.1f} / {pair:8.1f} / {lib:8.1f}"
+                      f"   ({2.0 * rows * N * K / pair / 1e6:6.0f})", flush=True)
+                del w, out, full
+    print(f"status word {int(status.item())}")
+    return 0
+
+
 def main() -> int:
     p = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     p.add_argument("--gpus", type=int, default=1)
@@ -692,9 +761,11 @@ def main() -> int:
     p.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in the output)")
     p.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                    help="with --profile prefill: length of the prompt (at most 4,096)")
+    p.add_argument("--only-size", default=None, help="with --profile products: one of 0.6B, 1.7B, 8B, 32B")
+    p.add_argument("--only-rows", type=int, default=None, help="with --profile products: one number of rows")
     p.add_argument("--leave-out", action="store_true",
                    help="with --profile: time the step as a CUDA graph, whole and with each kind of kernel left out")
-    p.add_argument("--profile", choices=["decode", "prefill"], default=None,
+    p.add_argument("--profile", choices=["decode", "prefill", "products"], default=None,
                    help="short run for a profiler instead of the benchmark (see profile())")
     args = p.parse_args()
     if args.gpus != 1:
@@ -702,6 +773,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.profile == "products":
+        return profile_products(args)
     if args.profile:
         return profile(args)
     if args.impl == "reference":

@@ -23,6 +23,10 @@
 // word and a block-wide abort flag, every role leaves its loop, TMEM is released and the block
 // returns; nothing spins forever.
 //
+// A second kernel further down does the same product by pairs of CTAs (clusters of two, 256 x 256 tiles,
+// tcgen05.mma.cta_group::2) with the same three epilogues; it runs at the library's rate where the
+// single-CTA tile is held back by what one SM can fetch and read from shared memory per clock.
+//
 // Role in the reference: nn.Linear / cuBLAS (models/self_attn.py:358-386, models/feedback.py:28-34).
 #include "tc_common.cuh"
 
