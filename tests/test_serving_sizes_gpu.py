@@ -142,3 +142,33 @@ def test_twelve_to_sixteen_requests_decode_together_beside_a_portion(tiny_folder
     assert_follows_plain(cfg, w, prompts, [list(r.output) for r in reqs], "sixteen together")
     engine.session.manager.check()
     assert not engine.session.manager.live_requests()
+
+
+def test_a_step_of_more_than_a_thousand_rows_beside_decoding_requests(tiny_folders):
+    """Four prompts of 300 tokens arrive while two requests decode and are run in one step of 1,202 rows: at
+    this many rows the QKV projection (with head norm, rotation and page write in its epilogue) and the gate/up
+    product (with SwiGLU) are the ones that pairs of CTAs compute with the paired tensor-core instruction."""
+    from qwen3_from_scratch_b200.engine.engine import SyncEngine
+    from qwen3_from_scratch_b200.engine.request import RequestStatus, SamplingParams
+    from qwen3_from_scratch_b200.kernels import ops
+    folder = tiny_folders[KEY]
+    cfg, w = plain.read_model_folder(folder)
+    prompts = [random_tokens(VOCAB, n, 300 + i) for i, n in enumerate([40, 25, 300, 300, 300, 300])]
+    engine = SyncEngine(folder, dtype="bfloat16", block_size=PAGE, num_pages=160, max_num_seqs=8,
+                        max_num_tokens=2048, chunked_prefill_size=2048)
+    weights = engine.session.model.layers[0]
+    assert ops.gemm_tc_qkv_pays(1202, weights.mixer.qkv.weight) == "pair"
+    assert ops.gemm_tc_swiglu_pays(1202, weights.feed_forward.gate_up.weight) == "pair"
+    reqs = [engine.add_request(p, params=SamplingParams(max_new_tokens=24, ignore_eos=True)) for p in prompts[:2]]
+    while not all(r.is_decoding for r in reqs) or min(len(r.output) for r in reqs) < 3:
+        engine.step()
+    reqs += [engine.add_request(p, params=SamplingParams(max_new_tokens=12, ignore_eos=True)) for p in prompts[2:]]
+    largest = 0
+    while any(r.status != RequestStatus.FINISHED for r in reqs):
+        plan = engine.step()
+        largest = max(largest, sum(s.num_tokens for s in plan))
+    engine.drain()
+    assert largest == 1202, f"the largest step had {largest} rows"
+    assert_follows_plain(cfg, w, prompts, [list(r.output) for r in reqs], "a step of 1,202 rows")
+    engine.session.manager.check()
+    assert not engine.session.manager.live_requests()
