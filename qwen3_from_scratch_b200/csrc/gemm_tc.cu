@@ -55,7 +55,7 @@ struct TcShape {
   static constexpr int EPI_BYTES = EPI == 2 ? TC_HEAD_STAGE_BYTES : 0;  // where the QKV epilogue turns heads around
   // 4 stages of 48 KB or 6 of 32 KB; beside the QKV epilogue's 68 KB, three of 48 KB or four of 32 KB
   static constexpr int STAGES = ((EPI == 2 ? 156 : 192) * 1024) / STAGE_BYTES;
-  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + BAR_BYTES + EPI_BYTES + 1024;  // + room to align to 1024
+  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + BAR_BYTES + EPI_BYTES;
   static constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulators
 };
 
@@ -156,20 +156,27 @@ __device__ __forceinline__ void qkv_head_rows(uint32_t tmem_head, unsigned char*
   }
   const float wl[4] = {w_lo.x, w_lo.y, w_lo.z, w_lo.w}, wh[4] = {w_hi.x, w_hi.y, w_hi.z, w_hi.w};
   auto work = [&](int b, const float4 (&buf)[BATCH][2]) {
+    // the batch's rows in three sweeps (all reads, all arithmetic, all stores), so that the rows' chains of
+    // dependent instructions run beside each other instead of one after the other
+    uint4 meta[BATCH];
+    uint2 lo2[BATCH], hi2[BATCH];
 #pragma unroll
     for (int i = 0; i < BATCH; ++i) {
-      const float4(&c)[2] = buf[i];
-      const int r = (b * BATCH + i) * RPW + sub;
-      const unsigned char* srow = mine + r * STRIDE;
-      const uint4 meta = *reinterpret_cast<const uint4*>(srow + D * 2);
-      uint2 lo2 = *reinterpret_cast<const uint2*>(srow + l * 8), hi2 = *reinterpret_cast<const uint2*>(srow + D + l * 8);
-      if (is_q || is_k) {  // uniform over the warp
-        float lo[4] = {__uint_as_float(lo2.x << 16), __uint_as_float(lo2.x & 0xffff0000u),
-                       __uint_as_float(lo2.y << 16), __uint_as_float(lo2.y & 0xffff0000u)};
-        float hi[4] = {__uint_as_float(hi2.x << 16), __uint_as_float(hi2.x & 0xffff0000u),
-                       __uint_as_float(hi2.y << 16), __uint_as_float(hi2.y & 0xffff0000u)};
+      const unsigned char* srow = mine + ((b * BATCH + i) * RPW + sub) * STRIDE;
+      meta[i] = *reinterpret_cast<const uint4*>(srow + D * 2);
+      lo2[i] = *reinterpret_cast<const uint2*>(srow + l * 8);
+      hi2[i] = *reinterpret_cast<const uint2*>(srow + D + l * 8);
+    }
+    if (is_q || is_k) {  // uniform over the warp
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i) {
+        const float4(&c)[2] = buf[i];
+        float lo[4] = {__uint_as_float(lo2[i].x << 16), __uint_as_float(lo2[i].x & 0xffff0000u),
+                       __uint_as_float(lo2[i].y << 16), __uint_as_float(lo2[i].y & 0xffff0000u)};
+        float hi[4] = {__uint_as_float(hi2[i].x << 16), __uint_as_float(hi2[i].x & 0xffff0000u),
+                       __uint_as_float(hi2[i].y << 16), __uint_as_float(hi2[i].y & 0xffff0000u)};
         if (w) {
-          const float rs_r = __uint_as_float(meta.x);
+          const float rs_r = __uint_as_float(meta[i].x);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             lo[k] = lo[k] * rs_r * wl[k];
@@ -185,22 +192,22 @@ __device__ __forceinline__ void qkv_head_rows(uint32_t tmem_head, unsigned char*
             hi[k] = fmaf(a, sv[k], b2 * cv[k]);
           }
         }
-        lo2.x = pack2(__float_as_uint(lo[0]), __float_as_uint(lo[1]));
-        lo2.y = pack2(__float_as_uint(lo[2]), __float_as_uint(lo[3]));
-        hi2.x = pack2(__float_as_uint(hi[0]), __float_as_uint(hi[1]));
-        hi2.y = pack2(__float_as_uint(hi[2]), __float_as_uint(hi[3]));
+        lo2[i].x = pack2(__float_as_uint(lo[0]), __float_as_uint(lo[1]));
+        lo2[i].y = pack2(__float_as_uint(lo[2]), __float_as_uint(lo[3]));
+        hi2[i].x = pack2(__float_as_uint(hi[0]), __float_as_uint(hi[1]));
+        hi2[i].y = pack2(__float_as_uint(hi[2]), __float_as_uint(hi[3]));
       }
-      if (r >= rows_here) continue;
-      __nv_bfloat16* dst;
-      if (is_q) {
-        dst = e.q_out + ((size_t)(row_base + r) * e.Hq + head) * D;
-      } else {
-        const long long off = (long long)(((unsigned long long)meta.z << 32) | meta.y);
-        if (off < 0) continue;
-        dst = (is_k ? e.k_pages : e.v_pages) + off + (size_t)hk * e.page_size * D;
+    }
+#pragma unroll
+    for (int i = 0; i < BATCH; ++i) {
+      const int r = (b * BATCH + i) * RPW + sub;
+      const long long off = (long long)(((unsigned long long)meta[i].z << 32) | meta[i].y);
+      __nv_bfloat16* dst = is_q ? e.q_out + ((size_t)(row_base + r) * e.Hq + head) * D
+                                : (is_k ? e.k_pages : e.v_pages) + off + (size_t)hk * e.page_size * D;
+      if (r < rows_here && (is_q || off >= 0)) {
+        *reinterpret_cast<uint2*>(dst + l * 4) = lo2[i];
+        *reinterpret_cast<uint2*>(dst + D / 2 + l * 4) = hi2[i];
       }
-      *reinterpret_cast<uint2*>(dst + l * 4) = lo2;
-      *reinterpret_cast<uint2*>(dst + D / 2 + l * 4) = hi2;
     }
   };
   static_assert(NB % 2 == 0, "batches are worked on in pairs");
@@ -326,8 +333,10 @@ __global__ void __launch_bounds__(TcThreads<EPI>::THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                OutT* __restrict__ C, int M, int N, int K, int ldc, const __grid_constant__ QkvEpilogue qkv, int* status) {
   using S = TcShape<BN, EPI>;
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  // used as it is declared, so that the compiler knows these are shared-memory addresses (a base rounded up
+  // through an integer made every access of the QKV epilogue's staging rows a generic one)
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* base = smem_raw;
   unsigned char* tiles = base;
   uint64_t* full = reinterpret_cast<uint64_t*>(base + (size_t)S::STAGES * S::STAGE_BYTES);
   uint64_t* empty = full + S::STAGES;
@@ -340,7 +349,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k_tiles = (K + TC_BK - 1) / TC_BK;
   const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
-  const int num_tiles = m_tiles * n_tiles;
+  // the swizzled tiles need a base on a 1024-byte boundary; never seen otherwise, but a wrong answer must not be silent
+  const bool aligned = (s_addr(smem_raw) & 1023u) == 0;
+  const int num_tiles = aligned ? m_tiles * n_tiles : 0;
+  if (!aligned && threadIdx.x == 0) atomicOr(status, Q3_STATUS_TIMEOUT);
 
   if (warp == 0 && lane == 0) {
     tma_prefetch_map(&map_a);
@@ -515,7 +527,7 @@ struct TcPairShape {
   static constexpr int EPI_BYTES = EPI == 2 ? TC_HEAD_STAGE_BYTES : 0;
   static constexpr int STAGES = EPI == 2 ? 4 : 7;          // beside the QKV epilogue's 68 KB, four
   static constexpr int BAR_BYTES = 256;
-  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + BAR_BYTES + EPI_BYTES + 1024;
+  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + BAR_BYTES + EPI_BYTES;
   static constexpr uint32_t TMEM_COLS = 2 * BN;
   static constexpr int THREADS = TcThreads<EPI>::THREADS;
 };
@@ -527,8 +539,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     int* status) {
   using S = TcPairShape<EPI>;
   constexpr int BN = S::BN;
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  // used as it is declared, so that the compiler knows these are shared-memory addresses (a base rounded up
+  // through an integer made every access of the QKV epilogue's staging rows a generic one)
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* base = smem_raw;
   unsigned char* tiles = base;
   uint64_t* full = reinterpret_cast<uint64_t*>(base + (size_t)S::STAGES * S::STAGE_BYTES);  // used in rank 0
   uint64_t* empty = full + S::STAGES;
@@ -543,7 +557,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
   const int k_tiles = (K + TC_BK - 1) / TC_BK;
   const int m_tiles = (M + 2 * TC_BM - 1) / (2 * TC_BM), n_tiles = (N + BN - 1) / BN;
-  const int num_tiles = m_tiles * n_tiles;
+  const bool aligned = (s_addr(smem_raw) & 1023u) == 0;  // as above; the same in both CTAs
+  const int num_tiles = aligned ? m_tiles * n_tiles : 0;
+  if (!aligned && threadIdx.x == 0) atomicOr(status, Q3_STATUS_TIMEOUT);
   auto give_up = [&]() {  // one thread
     abort_flag = 1;
     st_cluster_u32(cluster_addr(s_addr(&abort_flag), rank ^ 1u), 1u);
