@@ -85,59 +85,80 @@ struct QkvEpilogue {
 // of each) and stores two 8-byte pieces to q_out or the cache page.  No shuffles and three shared-memory
 // reads per row: under the main loop the tensor core and TMA take the shared-memory pipe nearly whole, and
 // an epilogue that went through it twenty times per row (shuffles count) set the kernel's pace.
-// Cosines and sines are asked for four rows at a time and one such batch ahead, the first before pass 1.
+// Cosines and sines are asked for four rows at a time and one such batch ahead, the first before pass 1; pass 1
+// asks for the next 32 columns of the row before it works on those it has, and sums the squares in four chains.
+// KIND (0 q, 1 k, 2 v, -1: found from `head`) and FAST (32 rows, and for q and k both norm and rotation) fix at
+// compile time what the general form asks at run time: with two epilogue warps per scheduler the passes are bound
+// by their own instruction count and latencies, and the fixed form has about half the instructions.
 // Rows are TC_QKV_ROW_PAD bytes apart beyond their 2 D, which keeps pass 1's 16-byte writes (a thread per
 // row, the same column) off each other's banks.
 // `kv_off`: element offset of this lane's row in a page array (without the head), or -1.
 // `release`: the barrier that hands the accumulator back, arrived on once pass 1 has read it, as its address
 // in the cluster's shared window (the block's own address where there is no cluster), or 0.
-template <int D>
-__device__ __forceinline__ void qkv_head_rows(uint32_t tmem_head, unsigned char* mine, int row_base, int rows_here,
+template <int D, int KIND, bool FAST>
+__device__ __forceinline__ void qkv_head_rows(uint32_t tmem_head, unsigned char* mine, int row_base, int rows_here_,
                                               int head, const QkvEpilogue& e, int lane, long long kv_off,
                                               uint32_t release) {
   constexpr int LPH = D / 8, RPW = 32 / LPH, STRIDE = D * 2 + TC_QKV_ROW_PAD;
   constexpr int ITER = 32 / RPW, BATCH = ITER < 4 ? ITER : 4, NB = ITER / BATCH;
-  const bool is_q = head < e.Hq, is_k = !is_q && head < e.Hq + e.Hkv;
+  const bool is_q = KIND >= 0 ? KIND == 0 : head < e.Hq, is_k = KIND >= 0 ? KIND == 1 : (!is_q && head < e.Hq + e.Hkv);
   const float* w = is_q ? e.q_weight : (is_k ? e.k_weight : nullptr);
-  const bool rotate = (is_q || is_k) && e.cos_sin != nullptr;
+  const bool has_w = FAST ? KIND < 2 : w != nullptr;
+  const bool rotate = FAST ? KIND < 2 : ((is_q || is_k) && e.cos_sin != nullptr);
+  const int rows_here = FAST ? 32 : rows_here_;
   const int sub = lane / LPH, l = lane % LPH;
   float4 cs[2][BATCH][2];  // [.][.][0]: cosines of the lane's four pairs, [1]: sines
+  const float* cs_row = e.cos_sin + (size_t)(row_base + sub) * D + l * 4;
   auto fetch = [&](int b, float4 (&buf)[BATCH][2]) {
 #pragma unroll
     for (int i = 0; i < BATCH; ++i) {
       const int r = (b * BATCH + i) * RPW + sub;
-      buf[i][0] = make_float4(1.f, 1.f, 1.f, 1.f);
-      buf[i][1] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (r < rows_here) {
-        const float* row = e.cos_sin + (size_t)(row_base + r) * D + l * 4;
+      if (FAST || r < rows_here) {
+        const float* row = cs_row + (size_t)((b * BATCH + i) * RPW) * D;
         buf[i][0] = *reinterpret_cast<const float4*>(row);
         buf[i][1] = *reinterpret_cast<const float4*>(row + D / 2);
       }
     }
   };
+  if (!FAST) {
+#pragma unroll
+    for (int i = 0; i < BATCH; ++i) {
+      cs[0][i][0] = cs[1][i][0] = make_float4(1.f, 1.f, 1.f, 1.f);
+      cs[0][i][1] = cs[1][i][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
   if (rotate) fetch(0, cs[0]);  // uniform over the warp
+  float4 w_lo = make_float4(1.f, 1.f, 1.f, 1.f), w_hi = w_lo;
+  if (has_w) {
+    w_lo = *reinterpret_cast<const float4*>(w + l * 4);
+    w_hi = *reinterpret_cast<const float4*>(w + D / 2 + l * 4);
+  }
 
-  float ss = 0.f;
+  // pass 1: the next piece of the row is asked for before this one is worked on; four sums side by side
+  float ss4[4] = {0.f, 0.f, 0.f, 0.f};
+  uint32_t v[2][32];
+  tmem_ld_32(tmem_head, v[0]);
 #pragma unroll
   for (int c0 = 0; c0 < D; c0 += 32) {
-    uint32_t v[32];
-    tmem_ld_32(tmem_head + (uint32_t)c0, v);
+    uint32_t(&cur)[32] = v[(c0 / 32) & 1];
     tmem_wait_ld();
+    if (c0 + 32 < D) tmem_ld_32(tmem_head + (uint32_t)(c0 + 32), v[((c0 / 32) & 1) ^ 1]);
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       uint32_t pk[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        pk[i] = pack2(v[8 * c + 2 * i], v[8 * c + 2 * i + 1]);
+        pk[i] = pack2(cur[8 * c + 2 * i], cur[8 * c + 2 * i + 1]);
         const float lo = __uint_as_float(pk[i] << 16), hi = __uint_as_float(pk[i] & 0xffff0000u);
-        ss = fmaf(lo, lo, ss);
-        ss = fmaf(hi, hi, ss);
+        ss4[i] = fmaf(lo, lo, ss4[i]);
+        ss4[i] = fmaf(hi, hi, ss4[i]);
       }
       *reinterpret_cast<uint4*>(mine + lane * STRIDE + (c0 / 8 + c) * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     }
   }
   {
-    const float rs = w ? 1.0f / sqrtf(ss / (float)D + e.eps) : 1.0f;
+    const float ss = (ss4[0] + ss4[1]) + (ss4[2] + ss4[3]);
+    const float rs = has_w ? 1.0f / sqrtf(ss / (float)D + e.eps) : 1.0f;
     *reinterpret_cast<uint4*>(mine + lane * STRIDE + D * 2) =
         make_uint4(__float_as_uint(rs), (uint32_t)(unsigned long long)kv_off, (uint32_t)((unsigned long long)kv_off >> 32), 0u);
   }
@@ -149,12 +170,12 @@ __device__ __forceinline__ void qkv_head_rows(uint32_t tmem_head, unsigned char*
   __syncwarp();
 
   const int hk = is_k ? head - e.Hq : head - e.Hq - e.Hkv;
-  float4 w_lo = make_float4(1.f, 1.f, 1.f, 1.f), w_hi = w_lo;
-  if (w) {
-    w_lo = *reinterpret_cast<const float4*>(w + l * 4);
-    w_hi = *reinterpret_cast<const float4*>(w + D / 2 + l * 4);
-  }
   const float wl[4] = {w_lo.x, w_lo.y, w_lo.z, w_lo.w}, wh[4] = {w_hi.x, w_hi.y, w_hi.z, w_hi.w};
+  // where the lane's pieces of row `sub` go: q rows are Hq D apart; k and v rows are found by the row's own offset
+  __nv_bfloat16* const q_dst = e.q_out + ((size_t)(row_base + sub) * e.Hq + head) * D + l * 4;
+  const size_t q_pitch = (size_t)e.Hq * D;
+  __nv_bfloat16* const kv_dst = (is_k ? e.k_pages : e.v_pages) + (size_t)hk * e.page_size * D + l * 4;
+  const unsigned char* const my_rows = mine + sub * STRIDE;
   auto work = [&](int b, const float4 (&buf)[BATCH][2]) {
     // the batch's rows in three sweeps (all reads, all arithmetic, all stores), so that the rows' chains of
     // dependent instructions run beside each other instead of one after the other
@@ -162,7 +183,7 @@ __device__ __forceinline__ void qkv_head_rows(uint32_t tmem_head, unsigned char*
     uint2 lo2[BATCH], hi2[BATCH];
 #pragma unroll
     for (int i = 0; i < BATCH; ++i) {
-      const unsigned char* srow = mine + ((b * BATCH + i) * RPW + sub) * STRIDE;
+      const unsigned char* srow = my_rows + ((b * BATCH + i) * RPW) * STRIDE;
       meta[i] = *reinterpret_cast<const uint4*>(srow + D * 2);
       lo2[i] = *reinterpret_cast<const uint2*>(srow + l * 8);
       hi2[i] = *reinterpret_cast<const uint2*>(srow + D + l * 8);
@@ -175,7 +196,7 @@ __device__ __forceinline__ void qkv_head_rows(uint32_t tmem_head, unsigned char*
                        __uint_as_float(lo2[i].y << 16), __uint_as_float(lo2[i].y & 0xffff0000u)};
         float hi[4] = {__uint_as_float(hi2[i].x << 16), __uint_as_float(hi2[i].x & 0xffff0000u),
                        __uint_as_float(hi2[i].y << 16), __uint_as_float(hi2[i].y & 0xffff0000u)};
-        if (w) {
+        if (has_w) {
           const float rs_r = __uint_as_float(meta[i].x);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
@@ -202,11 +223,10 @@ __device__ __forceinline__ void qkv_head_rows(uint32_t tmem_head, unsigned char*
     for (int i = 0; i < BATCH; ++i) {
       const int r = (b * BATCH + i) * RPW + sub;
       const long long off = (long long)(((unsigned long long)meta[i].z << 32) | meta[i].y);
-      __nv_bfloat16* dst = is_q ? e.q_out + ((size_t)(row_base + r) * e.Hq + head) * D
-                                : (is_k ? e.k_pages : e.v_pages) + off + (size_t)hk * e.page_size * D;
-      if (r < rows_here && (is_q || off >= 0)) {
-        *reinterpret_cast<uint2*>(dst + l * 4) = lo2[i];
-        *reinterpret_cast<uint2*>(dst + D / 2 + l * 4) = hi2[i];
+      __nv_bfloat16* dst = is_q ? q_dst + (size_t)((b * BATCH + i) * RPW) * q_pitch : kv_dst + off;
+      if ((FAST || r < rows_here) && (is_q || off >= 0)) {
+        *reinterpret_cast<uint2*>(dst) = lo2[i];
+        *reinterpret_cast<uint2*>(dst + D / 2) = hi2[i];
       }
     }
   };
@@ -254,8 +274,21 @@ __device__ __forceinline__ void qkv_tile_epilogue(uint32_t tmem_acc, unsigned ch
 #pragma unroll 1
   for (int h0 = slot * HD; h0 < BN && n0 + h0 < N; h0 += SLOTS * HD) {  // uniform over the warp
     const bool last = h0 + SLOTS * HD >= BN || n0 + h0 + SLOTS * HD >= N;
-    qkv_head_rows<HD>(tmem_acc + (uint32_t)h0, mine, m0 + quarter * 32, rows_here, (n0 + h0) / HD, qkv, lane, kv_off,
-                      last ? release : 0u);
+    // Whole groups of 32 rows of a head that is normed and rotated (or a v head) take a form of the code in which
+    // the kind of head, the norm, the rotation and the row count are fixed when it is compiled; the rest (the last
+    // rows of the matrix, a layer without head norms or without rotation) the form that asks as it goes.
+    const int head = (n0 + h0) / HD;
+    const bool head_q = head < qkv.Hq, head_k = !head_q && head < qkv.Hq + qkv.Hkv;
+    const bool fixed = rows_here == 32 && (!(head_q || head_k) || (qkv.cos_sin != nullptr &&
+                                                                  (head_q ? qkv.q_weight : qkv.k_weight) != nullptr));
+#define Q3_QKV_HEAD(KIND, FAST)                                                                                      \
+  qkv_head_rows<HD, KIND, FAST>(tmem_acc + (uint32_t)h0, mine, m0 + quarter * 32, rows_here, head, qkv, lane, kv_off, \
+                                last ? release : 0u)
+    if (!fixed) Q3_QKV_HEAD(-1, false);  // every branch here is uniform over the warp
+    else if (head_q) Q3_QKV_HEAD(0, true);
+    else if (head_k) Q3_QKV_HEAD(1, true);
+    else Q3_QKV_HEAD(2, true);
+#undef Q3_QKV_HEAD
     released = released || last;
   }
   if (!released) {  // a warp without a head in the matrix's last tile
