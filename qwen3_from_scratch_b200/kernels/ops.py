@@ -576,11 +576,11 @@ def gemm_tc_qkv_takes(rows: int, x: torch.Tensor, weight: torch.Tensor, head_dim
 def gemm_tc_qkv_pays(rows: int, weight: torch.Tensor) -> Optional[str]:
     """Which projection with ``qkv_post`` as its epilogue is the faster way for a prompt portion: "pair"
     (pairs of CTAs on tiles of 256 rows), "single" (one CTA per tile) or None (the library's product, then
-    ``qkv_post``).  The fused forms save ``qkv_post``'s pass over the projection and a launch; against that a
-    launch costs about 13 us whatever its size, so short portions stay with the library, and where the
-    reduction is long the whole step showed no gain over the library's product (measured inside the step:
-    profiles/gemm_tc_qkv__prefill_2048.md)."""
-    if weight.shape[1] > 1536 or rows < 768:
+    ``qkv_post``).  The fused forms save ``qkv_post``'s pass over the projection and a launch.  Inside the
+    step they win from 256 rows at a reduction up to 1,536 (3 to 6 % of the step); where the reduction is
+    longer the step showed no gain over the library's product beyond its spread from run to run
+    (profiles/gemm_tc_qkv__prefill_2048.md, profiles/gemm_tc_pair__products.md)."""
+    if weight.shape[1] > 1536 or rows < 256:
         return None
     return "pair" if rows >= 1024 else "single"
 
