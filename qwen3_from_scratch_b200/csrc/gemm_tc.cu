@@ -8,7 +8,7 @@
 //   warp 1 (one thread)  issues tcgen05.mma (cta_group::1, kind::f16) straight from shared memory through
 //                        matrix descriptors, four instructions of k = 16 per stage; tcgen05.commit hands
 //                        each stage back to the loader and each finished accumulator to the epilogue;
-//   warps 2..5 (2..9 for the QKV epilogue)  read the accumulator with tcgen05.ld (each thread owns one row of the tile) and
+//   warps 2..5 (2..9 for the SwiGLU and QKV epilogues)  read the accumulator with tcgen05.ld (each thread owns one row of the tile) and
 //                        store bfloat16 or float32, optionally applying SwiGLU to a weight whose rows
 //                        alternate gate/up in blocks of eight.
 // There are two accumulators in TMEM, so the epilogue of one tile runs under the main loop of the next.
@@ -42,7 +42,9 @@ constexpr int TC_HEAD_STAGE_BYTES = TC_QKV_EPI_WARPS * 32 * (128 * 2 + TC_QKV_RO
 
 template <int EPI>
 struct TcThreads {
-  static constexpr int EPI_WARPS = EPI == 2 ? TC_QKV_EPI_WARPS : 4;
+  // the SwiGLU epilogue too has two warps per quarter of the rows (they take every second piece of 32 columns): with
+  // one warp per scheduler a tile's epilogue is a single chain of latencies, which the last tile of a block shows
+  static constexpr int EPI_WARPS = EPI == 2 ? TC_QKV_EPI_WARPS : (EPI == 1 ? 8 : 4);
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
 };
 
@@ -515,7 +517,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                                              s_addr(&acc_empty[buf]), status);
       } else {
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
+        for (int c0 = ((warp - 2) >> 2) * 32; c0 < BN; c0 += (TcThreads<EPI>::EPI_WARPS / 4) * 32) {
           if (n0 + c0 >= N) break;  // uniform over the warp
           uint32_t v[32];
           tmem_ld_32(tmem_acc + (uint32_t)c0, v);
@@ -546,8 +548,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 //                                   the pair is counted by rank 0's `full` barrier (rank 0 expects the bytes of both);
 //   warp 1 (one thread, rank 0)     waits on `full`, issues for the pair, and commits with one arrival on
 //                                   `empty` / `acc_full` in both CTAs;
-//   warps 2..5 (both CTAs)          read their own CTA's accumulator rows, store, and arrive on rank 0's
-//                                   `acc_empty` (eight arrivals hand an accumulator back).
+//   warps 2..5 or 2..9 (both CTAs)  read their own CTA's accumulator rows, store, and arrive on rank 0's
+//                                   `acc_empty` (the arrivals of both CTAs' epilogue warps hand an accumulator back).
 // Every wait is bounded as above; a role that gives up raises the abort flag of both CTAs.  Both CTAs meet at a
 // cluster barrier before the first copy (a barrier must be initialised before the other CTA's copy counts on
 // it) and before they free tensor memory and return (no arrival or operand read may find a CTA gone).
@@ -727,7 +729,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                                              status);
       } else {
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
+        for (int c0 = ((warp - 2) >> 2) * 32; c0 < BN; c0 += (TcThreads<EPI>::EPI_WARPS / 4) * 32) {
           if (n0 + c0 >= N) break;  // uniform over the warp
           uint32_t v[32];
           tmem_ld_32(tmem_acc + (uint32_t)c0, v);
